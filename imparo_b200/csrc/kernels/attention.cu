@@ -1,0 +1,226 @@
+// Attention over the paged cache: (1) per-head RMS norm + NeoX rotation of q and k and
+// the write of k, v into their pages, one kernel; (2) a general attention kernel for any
+// ragged batch (prompt portions beside single decoded tokens), any head size that is a
+// multiple of 16 up to 256, any number of heads and groups, 32-bit or bfloat16 storage.
+//
+// Formulas (zeraix/imparo): per (token, head) RMS norm then rotation, before the cache
+// write (imparo-model/src/cpu_support.rs:361-376); rotation pairs (i, i+n_rot/2) with
+// angle = position * base^(-2i/n_rot) (imparo-cpu/src/ops.rs:551-569); cache row of a
+// position = table[pos / page] * page + pos % page (imparo-cuda/native/kv_paging.cuh:25-30,
+// there with 64-cell pages); scores s_j = q.k_j * scale for lo <= j <= pos, lo = 0 or
+// pos+1-window, kv head = h / (heads / kv_heads), softmax with the max subtracted
+// (imparo-model/src/cpu_support.rs:402-445; ops.rs:572-583).
+#include "common.cuh"
+
+namespace imparo {
+
+constexpr int MAX_HEAD = 256;
+constexpr int WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
+                          const int* __restrict__ item_of_token,
+                          const float* __restrict__ q_w, const float* __restrict__ k_w,
+                          const float* __restrict__ inv_freq, int n_rot, float eps,
+                          T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                          const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                          int nh, int nkv, int hd, int* status) {
+    __shared__ float rowbuf[WARPS][MAX_HEAD];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hh = blockIdx.y * WARPS + warp;
+    const int total = nh + 2 * nkv;
+    if (hh >= total) return;
+    const int in_width = total * hd;
+    const T* src = qkv + (size_t)t * in_width + (size_t)hh * hd;
+    float* row = rowbuf[warp];
+    const int pos = positions[t];
+    const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) { float v = to_f32(src[d]); row[d] = v; ss += v * v; }
+    if (is_q || is_k) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        const float* w = is_q ? q_w : k_w;
+        __syncwarp();
+        for (int d = lane; d < hd; d += 32) row[d] = row[d] * scale * w[d];
+        __syncwarp();
+        if (inv_freq) {
+            const int half = n_rot >> 1;
+            for (int i = lane; i < half; i += 32) {
+                const float ang = (float)pos * inv_freq[i];
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                const float x0 = row[i], x1 = row[i + half];
+                row[i] = x0 * cs - x1 * sn;
+                row[i + half] = x0 * sn + x1 * cs;
+            }
+        }
+    }
+    __syncwarp();
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * nh * hd + (size_t)hh * hd;
+    } else {
+        const int kvh = is_k ? hh - nh : hh - nh - nkv;
+        const int blk = pos / page_size;
+        int page = -1;
+        if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
+        if (page < 0 || page >= n_pages) {
+            if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);
+            return;
+        }
+        const size_t r = (size_t)page * page_size + (pos % page_size);
+        dst = (is_k ? k_cache : v_cache) + r * ((size_t)nkv * hd) + (size_t)kvh * hd;
+    }
+    for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(row[d]);
+}
+
+// ---- general paged attention ---------------------------------------------------------
+template <typename T> struct Vec;
+template <> struct Vec<float> { using type = float4; static constexpr int N = 4; };
+template <> struct Vec<__nv_bfloat16> { using type = uint4; static constexpr int N = 8; };
+
+__device__ __forceinline__ float dot_vec(const float4& k, const float* q) {
+    return k.x * q[0] + k.y * q[1] + k.z * q[2] + k.w * q[3];
+}
+__device__ __forceinline__ float dot_vec(const uint4& k, const float* q) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&k);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        s += f.x * q[2 * i] + f.y * q[2 * i + 1];
+    }
+    return s;
+}
+
+// One warp per (token, head).  Keys are walked 32 at a time in position order: each lane
+// scores one key, the warp folds the chunk into the running max / sum, then all lanes
+// accumulate the chunk's values, each lane owning head dimensions lane, lane+32, ...
+// The walk depends only on (position, window): never on the batch around the token.
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                       const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                       const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                       int window, float scale, T* __restrict__ out, int nh, int nkv, int hd, int* status) {
+    __shared__ __align__(16) float qbuf[WARPS][MAX_HEAD];
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * WARPS + warp;
+    if (h >= nh) return;
+    const int kvh = h / (nh / nkv);
+    const int pos = positions[t];
+    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
+    const size_t kvw = (size_t)nkv * hd;
+    float* qs = qbuf[warp];
+    const T* qrow = q + ((size_t)t * nh + h) * hd;
+    for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qrow[d]);
+    __syncwarp();
+
+    const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    constexpr int PER = MAX_HEAD / 32;
+    float acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    using V = typename Vec<T>::type;
+    constexpr int VN = Vec<T>::N;
+
+    for (int base = lo; base <= pos; base += 32) {
+        const int j = base + lane;
+        float s = -INFINITY;
+        int rowi = -1;
+        if (j <= pos) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? tab[blk] : -1;
+            if (page < 0 || page >= n_pages) {
+                report(status, IMPARO_ST_PAGE_RANGE, 3, t, page);
+            } else {
+                rowi = page * page_size + (j % page_size);
+                const V* kp = reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
+                float d = 0.f;
+                for (int c = 0; c < hd / VN; ++c) d += dot_vec(kp[c], qs + c * VN);
+                s = d * scale;
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;   // a chunk of unreadable keys only (already reported)
+        const float p = (rowi >= 0) ? expf(s - m_new) : 0.f;
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] *= corr;
+        m = m_new;
+        const int cnt = min(32, pos - base + 1);
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int rj = __shfl_sync(0xffffffffu, rowi, jj);
+            if (rj < 0) continue;
+            const T* vp = v_cache + (size_t)rj * kvw + (size_t)kvh * hd;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] += pj * to_f32(vp[d]);
+            }
+        }
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    T* orow = out + ((size_t)t * nh + h) * hd;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) orow[d] = from_f32<T>(acc[i] * inv);
+    }
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* positions, const int* item_of_token,
+                                         const float* q_w, const float* k_w, const float* inv_freq, int n_rot, float eps,
+                                         void* q_out, void* k_cache, void* v_cache,
+                                         const int* table, int max_blocks, int page_size, int n_pages,
+                                         int n_tok, int nh, int nkv, int hd, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 16 || hd > MAX_HEAD || hd % 16 != 0) return -3;
+    if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
+    dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
+    if (dtype == IMPARO_DT_F32)
+        qk_norm_rope_store_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+            (const float*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (float*)q_out,
+            (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
+    else if (dtype == IMPARO_DT_BF16)
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_paged_attention(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                      const int* positions, const int* item_of_token,
+                                      const int* table, int max_blocks, int page_size, int n_pages,
+                                      int window, float scale, void* out,
+                                      int n_tok, int nh, int nkv, int hd, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 16 || hd > MAX_HEAD || hd % 16 != 0) return -3;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    dim3 grid(n_tok, (nh + WARPS - 1) / WARPS);
+    if (dtype == IMPARO_DT_F32)
+        paged_attention_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+            (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, item_of_token, table,
+            max_blocks, page_size, n_pages, window, scale, (float*)out, nh, nkv, hd, status);
+    else if (dtype == IMPARO_DT_BF16)
+        paged_attention_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions,
+            item_of_token, table, max_blocks, page_size, n_pages, window, scale, (__nv_bfloat16*)out, nh, nkv, hd, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

@@ -1,0 +1,117 @@
+// Gated causal depthwise convolution with per-request rolling state, for a ragged batch.
+//
+// Formula (zeraix/imparo, imparo-cpu/src/ops.rs:109-167; imparo-cuda/native/lfm2_ops.cuh:48-97):
+//   rows of bcx are [b | c | x];  v[t] = b[t]*x[t];  seq = state ++ v  (state = the taps-1
+//   raw v before this portion, oldest first, zeros for a fresh request);
+//   sum[t] = sum_k w[ch,k] * seq[t+k]  (tap 0 meets the oldest value);  y[t] = c[t]*sum[t];
+//   state' = the last taps-1 values of seq (partly the old state when the portion is
+//   shorter than taps-1).  A bias, which the reference does not have, is added to sum
+//   before the gate.
+//
+// One launch does output and state.  A thread owns (token, channel).  Tokens at least
+// taps-1 into their portion need only bcx.  The thread of a portion's FIRST token also
+// computes the outputs of the next taps-2 tokens and then writes the new state; it reads
+// the whole old state into registers first, and no other thread touches that state, so
+// the update in place is race-free.
+#include "common.cuh"
+
+namespace imparo {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename T>
+__global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ w,
+                                  const float* __restrict__ bias, float* __restrict__ state,
+                                  const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
+                                  const int* __restrict__ item_slot, T* __restrict__ y,
+                                  int n_tok, int width, int taps, int n_slots, int* status) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tok * width) return;
+    const int t = (int)(idx / width), ch = (int)(idx % width);
+    const int item = item_of_token[t];
+    const int start = item_row_start[item];
+    const int n = item_row_start[item + 1] - start;
+    const int rel = t - start;
+    const int hist = taps - 1;
+    const size_t stride = (size_t)3 * width;
+    float wk[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)ch * taps + k] : 0.f;
+    const float b0 = bias ? bias[ch] : 0.f;
+
+    if (rel >= hist) {
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) {
+            if (k < taps) {
+                const T* r = bcx + (size_t)(t - hist + k) * stride;
+                acc += wk[k] * (to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]));
+            }
+        }
+        acc += b0;
+        y[(size_t)t * width + ch] = from_f32<T>(to_f32(bcx[(size_t)t * stride + width + ch]) * acc);
+        return;
+    }
+    if (rel != 0) return;
+
+    const int slot = item_slot[item];
+    if (slot < 0 || slot >= n_slots) {
+        if (ch == 0) report(status, IMPARO_ST_SLOT_RANGE, 4, item, slot);
+        return;
+    }
+    float* st = state + (size_t)slot * hist * width + ch;
+    // seq[e], e in [0, hist + m): the old state then the first m values of this portion
+    float seq[2 * MAX_TAPS];
+    const int m = min(n, hist);
+#pragma unroll
+    for (int e = 0; e < MAX_TAPS; ++e) if (e < hist) seq[e] = st[(size_t)e * width];
+#pragma unroll
+    for (int e = 0; e < MAX_TAPS; ++e) {
+        if (e < m) {
+            const T* r = bcx + (size_t)(start + e) * stride;
+            seq[hist + e] = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+        }
+    }
+    for (int e = 0; e < m; ++e) {
+        float acc = 0.f;
+        for (int k = 0; k < taps; ++k) acc += w[(size_t)ch * taps + k] * seq[e + k];
+        acc += b0;
+        y[(size_t)(start + e) * width + ch] = from_f32<T>(to_f32(bcx[(size_t)(start + e) * stride + width + ch]) * acc);
+    }
+    // new state slot s = seq_full[n + s]
+    for (int s = 0; s < hist; ++s) {
+        const int e = n + s;
+        float v;
+        if (e < hist + m) {
+            v = seq[e];
+        } else {
+            const T* r = bcx + (size_t)(start + e - hist) * stride;
+            v = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+        }
+        st[(size_t)s * width] = v;
+    }
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, const float* bias, float* state,
+                                 const int* item_row_start, const int* item_of_token, const int* item_slot,
+                                 void* y, int n_tok, int width, int taps, int n_slots, int* status,
+                                 cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (taps < 2 || taps > MAX_TAPS) return -6;
+    const size_t n = (size_t)n_tok * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == IMPARO_DT_F32)
+        gated_conv_kernel<float><<<blocks, threads, 0, stream>>>((const float*)bcx, w, bias, state, item_row_start,
+                                                                item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
+    else if (dtype == IMPARO_DT_BF16)
+        gated_conv_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)bcx, w, bias, state, item_row_start,
+                                                                         item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

@@ -1,0 +1,121 @@
+// Row-wise kernels: embedding gather, RMS norm, SiLU-gate multiply, bias add.
+//
+// Formulas (zeraix/imparo): embedding rows unscaled (imparo-model/src/cpu_support.rs:327-342);
+// RMS norm mean = sum(x^2)/width, scale = 1/sqrt(mean+eps), y = x*scale*w
+// (imparo-cpu/src/ops.rs:6-22); silu(g)*u with SiLU on the gate (ops.rs:73-78,
+// imparo-model/src/lfm2/workflow_cpu.rs:307-313).
+#include "common.cuh"
+
+namespace imparo {
+
+// ---- embedding -----------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int width, int vocab, int* status) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) report(status, IMPARO_ST_TOKEN_RANGE, 1, t, id);
+        id = 0;
+    }
+    const T* row = table + (size_t)id * width;
+    float* o = out + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// ---- RMS norm ------------------------------------------------------------------------
+// One block per output row.  rows == nullptr: output row r reads input row r; else input
+// row rows[r].  The sum of squares is a fixed tree over blockDim threads, so a row's
+// result never depends on which other rows are in the launch.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ w, float eps, TOut* __restrict__ out,
+                               int width) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TOut* o = out + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
+}
+
+// ---- silu(gate) * up ----------------------------------------------------------------
+// gu: [T, 2F] rows = [gate | up]; out: [T, F]
+template <typename T>
+__global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tok, int F) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_tok * F) return;
+    const size_t t = i / F, f = i % F;
+    const float g = to_f32(gu[t * 2 * F + f]);
+    const float u = to_f32(gu[t * 2 * F + F + f]);
+    out[i] = from_f32<T>(silu(g) * u);
+}
+
+// ---- out[t, :] += bias ----------------------------------------------------------------
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n_tok, int width) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_tok * width) return;
+    out[i] = from_f32<T>(to_f32(out[i]) + bias[i % width]);
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+extern "C" int imparo_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
+                                   int n_tok, int width, int vocab, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == IMPARO_DT_F32)
+        embed_gather_kernel<float><<<n_tok, threads, 0, stream>>>((const float*)table, ids, out, width, vocab, status);
+    else if (table_dtype == IMPARO_DT_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<n_tok, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out,
+                              int out_dtype, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (out_dtype == IMPARO_DT_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, w, eps, (float*)out, width);
+    else if (out_dtype == IMPARO_DT_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, rows, w, eps, (__nv_bfloat16*)out, width);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_swiglu_act(const void* gu, void* out, int dtype, int n_tok, int F, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    const size_t n = (size_t)n_tok * F;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == IMPARO_DT_F32)
+        swiglu_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tok, F);
+    else if (dtype == IMPARO_DT_BF16)
+        swiglu_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_add_bias(void* out, int dtype, const float* bias, int n_tok, int width, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    const size_t n = (size_t)n_tok * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == IMPARO_DT_F32)
+        add_bias_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, bias, n_tok, width);
+    else if (dtype == IMPARO_DT_BF16)
+        add_bias_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, bias, n_tok, width);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

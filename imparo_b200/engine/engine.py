@@ -1,0 +1,182 @@
+"""The Python entry point: load (or draw) a model, own its cache, run steps, generate.
+
+    engine = Engine("model_dir", dtype="bfloat16", ctx=4096, parallel=8)
+    out = engine.generate([[1, 2, 3], [4, 5]], max_tokens=16, temperature=0.0)
+
+Option names follow the reference where it has them: model (-m/--model), ctx (-c/--ctx,
+the context length, default 4096), parallel (-np/--parallel, requests that decode at
+once), the request fields max_tokens and temperature (imparo-server/src/main.rs:178-240,
+1811 ff.).  Page size, page count and the step's token budget are this engine's own.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import CacheFull, CacheManager
+from ..config.registry import load_config
+from ..kernels import lib as _lib
+from ..kernels import ops
+from ..parts.base import Runtime, Workspace
+from ..parts.model import Model
+from ..sampling import Sampler
+from ..weights.loader import load_weights, target_dtype
+from ..weights.random_init import draw_random_tensors
+from .scheduler import Scheduler
+from .step import StepFunction, StepItem
+
+_PRECISIONS = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32", "f32": "float32"}
+
+
+class Engine:
+    def __init__(self, model: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
+                 dtype: str = "bfloat16", device: Union[str, torch.device] = "cuda:0", ctx: int = 4096,
+                 parallel: int = 8, page_size: int = 16, num_pages: Optional[int] = None,
+                 max_step_tokens: int = 2048, random_init: Optional[dict] = None):
+        """model: a folder with config.json and model.safetensors.  Or config (a config.json
+        dictionary) with seed: random weights drawn on the device (random_init may give
+        matrix_std, conv_std, norm_jitter).  ctx: the most positions one request may reach.
+        parallel: the most requests live at once.  num_pages: pages in each pool (default:
+        enough for parallel requests of ctx positions)."""
+        if dtype not in _PRECISIONS:
+            raise ValueError(f"dtype must be one of {sorted(_PRECISIONS)}")
+        self.precision = _PRECISIONS[dtype]
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError("imparo_b200 runs on a CUDA device (sm_100a); there is no CPU path")
+        _lib.kernels()      # build/load now: fail loudly if the extension is missing
+        torch.cuda.set_device(self.device)
+        self.arch, self.config = load_config(model if model is not None else config)
+        self.status = ops.new_status(self.device)
+        self.rt = Runtime(precision=self.precision, device=self.device, status=self.status,
+                          workspace=Workspace(self.device))
+        self.model = Model(self.arch.model_spec(self.config), self.rt)
+        specs = self.model.weight_specs()
+        if model is not None:
+            tensors = load_weights(model, specs, self.precision, self.device)
+        else:
+            if config is None:
+                raise ValueError("give a model folder or a config dictionary")
+            drawn = draw_random_tensors(specs, seed, self.precision, self.device, **(random_init or {}))
+            tensors = {w.name: drawn[w.name].to(target_dtype(w.role, self.precision)) for w in specs if w.name in drawn}
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
+        self.model.bind(tensors)
+        del tensors
+        self.ctx = min(int(ctx), self.model.spec.max_positions)
+        self.parallel = int(parallel)
+        self.page_size = int(page_size)
+        if num_pages is None:
+            num_pages = self.parallel * ((self.ctx + self.page_size - 1) // self.page_size)
+        self.cache = CacheManager(self.model.cache_requirements(), self.page_size, int(num_pages), self.parallel,
+                                  kv_dtype=self.rt.act_dtype, device=self.device)
+        self.max_step_tokens = int(max_step_tokens)
+        self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel)
+        self.sampler = Sampler(self.device, max_rows=max(self.parallel, 8))
+        self.vocab_size = self.model.spec.vocab_size
+        self._stats = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0, "preemptions": 0, "seconds": 0.0}
+
+    # -- the step function, for callers that schedule themselves ---------------------------
+    def add_request(self, request: int) -> None:
+        self.cache.add(request)
+
+    def end_request(self, request: int) -> None:
+        self.cache.release(request)
+
+    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+        """items: StepItem(request, tokens, want).  Returns float32 logits [wanted, vocab]
+        on the device, or None."""
+        self._check_tokens(items)
+        out = self.step_fn(items)
+        return out
+
+    def check_device_status(self) -> None:
+        ops.read_status(self.status)
+
+    def _check_tokens(self, items) -> None:
+        for it in items:
+            toks = it.tokens
+            if len(toks) and (min(toks) < 0 or max(toks) >= self.vocab_size):
+                raise ValueError(f"request {it.request}: token id out of range [0, {self.vocab_size})")
+            if self.cache.has(it.request) and self.cache.cached(it.request) + len(toks) > self.ctx:
+                raise ValueError(f"request {it.request}: {self.cache.cached(it.request)} + {len(toks)} tokens "
+                                 f"exceed the context length {self.ctx}")
+
+    # -- generation --------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Union[int, Sequence[int]] = 16,
+                 temperature: Union[float, Sequence[float]] = 0.0, seed: Union[int, Sequence[int]] = 0,
+                 stop_token_ids: Optional[Sequence[int]] = None, on_step=None) -> List[List[int]]:
+        """Continuous batching over the prompts (lists of token ids).  Returns the generated
+        ids per prompt.  temperature 0 is greedy; seed keys the per-request random stream.
+        A stop token ends its request and is not part of the output.  A request that cannot
+        fit the cache even alone ends with what it has (see failed in stats())."""
+        n = len(prompts)
+        as_list = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n
+        max_new, temps, seeds = as_list(max_tokens), as_list(temperature), as_list(seed)
+        stops = set(self.model.spec.eos_token_ids if stop_token_ids is None else stop_token_ids)
+        sched = Scheduler(self.cache, self.max_step_tokens, self.parallel, self.ctx)
+        tokens: Dict[int, List[int]] = {}
+        index: Dict[int, int] = {}
+        out: List[List[int]] = [[] for _ in range(n)]
+        for i, p in enumerate(prompts):
+            p = list(p)
+            if not p:
+                raise ValueError(f"prompt {i} is empty")
+            if min(p) < 0 or max(p) >= self.vocab_size:
+                raise ValueError(f"prompt {i}: token id out of range [0, {self.vocab_size})")
+            if max_new[i] <= 0:
+                continue            # ends before taking a token (imparo-server/src/sched.rs:427-431)
+            rid = sched.submit(len(p), max_new[i])
+            tokens[rid] = p
+            index[rid] = i
+        failed: List[int] = []
+        t0 = time.perf_counter()
+        idle = 0
+        while sched.has_work():
+            plan = sched.plan()
+            for rid in sched.take_failed():
+                failed.append(index[rid])
+            if not plan:
+                idle += 1
+                if idle > 2:
+                    raise RuntimeError("the scheduler has requests but plans no step")
+                continue
+            idle = 0
+            items = [StepItem(e.request, tokens[e.request][e.start:e.start + e.count],
+                              [e.count - 1] if e.want else []) for e in plan]
+            try:
+                logits = self.step_fn(items, manage_cache=False)
+            except Exception:
+                sched.step_done(False)
+                raise
+            sched.step_done(True)
+            wanting = [e for e in plan if e.want]
+            if wanting:
+                ids = self.sampler.sample(logits, [temps[index[e.request]] for e in wanting],
+                                          [seeds[index[e.request]] for e in wanting],
+                                          [len(out[index[e.request]]) for e in wanting])
+                for e, tok in zip(wanting, ids):
+                    i = index[e.request]
+                    eos = tok in stops
+                    if not eos:
+                        out[i].append(tok)
+                        tokens[e.request].append(tok)
+                    sched.on_token(e.request, eos)
+            self._stats["steps"] += 1
+            self._stats["prompt_tokens"] += sum(e.count for e in plan if e.count > 1 or e.start == 0)
+            self._stats["decode_tokens"] += len(wanting)
+            if on_step is not None:
+                on_step(plan)
+        ops.read_status(self.status)
+        self._stats["seconds"] += time.perf_counter() - t0
+        self._stats["preemptions"] += sched.n_preemptions
+        self._stats["failed"] = failed
+        return out
+
+    def stats(self) -> dict:
+        s = dict(self._stats)
+        s.update(weight_bytes=self.weight_bytes, cache_bytes=self.cache.bytes(), workspace_bytes=self.rt.workspace.bytes(),
+                 free_pages=[self.cache.free_pages(g) for g in range(self.cache.n_groups)],
+                 free_slots=self.cache.free_slots(), precision=self.precision)
+        return s

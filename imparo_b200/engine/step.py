@@ -1,0 +1,194 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step runs only the tokens it is given, from the cache earlier steps left, and returns
+32-bit logits at the wanted places.  A batch may mix portions of prompts with single
+decoded tokens, cut anywhere; a request appears at most once per step.  The reference
+runs either one request's prompt chunk or B one-token rows (imparo-model/src/lib.rs:1131-1156)
+and states the contract kept here: a row reads only its own token, position, cache and
+state (lib.rs:1141-1145); the cache advances only after the step succeeded
+(lib.rs:1784-1791).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheFull, CacheManager
+from ..kernels import ops
+from ..parts.model import Model
+
+
+@dataclass
+class StepItem:
+    """One request's share of a step: its next tokens, and the places among them (0-based)
+    whose logits are wanted."""
+    request: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepBatch:
+    """The step's batch on the device.  All index arrays are int32."""
+    __slots__ = ("n_tokens", "n_items", "token_ids", "positions", "item_of_token", "item_row_start",
+                 "item_slot", "item_start_pos", "tables", "want_rows", "n_want", "max_tokens_per_item",
+                 "max_context", "decode_only", "host")
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class StepFunction:
+    def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_items: int):
+        self.model = model
+        self.cache = cache
+        self.rt = model.rt
+        self.device = self.rt.device
+        self.max_step_tokens = int(max_step_tokens)
+        self.max_items = int(max_items)
+        self._ring = []          # pinned host buffers with the event of their last copy
+        self._turn = 0
+        self._dev = None
+        self._cap = 0
+
+    # -- the batch descriptor -------------------------------------------------------------
+    def _host_buffer(self, n_ints: int) -> torch.Tensor:
+        """A pinned host buffer no copy is still reading: a ring of four, each guarded by
+        the event recorded after its last upload."""
+        if n_ints > self._cap:
+            cap = max(n_ints, 2 * self._cap, 4096)
+            torch.cuda.current_stream().synchronize()
+            self._ring = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), None] for _ in range(4)]
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._cap = cap
+        self._turn = (self._turn + 1) % len(self._ring)
+        slot = self._ring[self._turn]
+        if slot[1] is not None:
+            slot[1].synchronize()
+        return slot[0]
+
+    def build_batch(self, items: Sequence[StepItem]) -> StepBatch:
+        cache = self.cache
+        R = len(items)
+        T = sum(len(it.tokens) for it in items)
+        W = sum(len(it.want) for it in items)
+        ng = cache.n_groups
+        strides = []
+        for g in range(ng):
+            longest = max(cache.table_len(it.request, g) for it in items)
+            strides.append(_round_up(max(longest, 1), 32))
+        sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides]
+        offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
+        host = self._host_buffer(int(offs[-1]))
+        h = host.numpy()
+        tok, pos, iot = (h[offs[i]:offs[i] + T] for i in range(3))
+        row_start = h[offs[3]:offs[3] + R + 1]
+        slot = h[offs[4]:offs[4] + R]
+        start_pos = h[offs[5]:offs[5] + R]
+        want = h[offs[6]:offs[6] + max(W, 1)]
+        t = w = 0
+        for i, it in enumerate(items):
+            n = len(it.tokens)
+            start = cache.cached(it.request)
+            tok[t:t + n] = np.asarray(it.tokens, dtype=np.int64)
+            pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+            iot[t:t + n] = i
+            row_start[i] = t
+            slot[i] = cache.slot(it.request)
+            start_pos[i] = start
+            for j in it.want:
+                if not 0 <= j < n:
+                    raise ValueError(f"request {it.request}: wanted place {j} is not among its {n} tokens")
+                want[w] = t + j
+                w += 1
+            t += n
+        row_start[R] = T
+        for g in range(ng):
+            tab = h[offs[7 + g]:offs[7 + g] + R * strides[g]].reshape(R, strides[g])
+            tab[:] = -1
+            for i, it in enumerate(items):
+                cache.fill_table(it.request, g, tab[i])
+        n_ints = int(offs[-1])
+        self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._ring[self._turn][1] = ev
+        d = self._dev
+        b = StepBatch()
+        b.n_tokens, b.n_items, b.n_want = T, R, W
+        b.token_ids, b.positions, b.item_of_token = (d[offs[i]:offs[i] + T] for i in range(3))
+        b.item_row_start = d[offs[3]:offs[3] + R + 1]
+        b.item_slot = d[offs[4]:offs[4] + R]
+        b.item_start_pos = d[offs[5]:offs[5] + R]
+        b.want_rows = d[offs[6]:offs[6] + max(W, 1)]
+        b.tables = [d[offs[7 + g]:offs[7 + g] + R * strides[g]].view(R, strides[g]) for g in range(ng)]
+        b.max_tokens_per_item = max(len(it.tokens) for it in items)
+        b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
+        b.decode_only = b.max_tokens_per_item == 1
+        b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy()}
+        return b
+
+    # -- one step ---------------------------------------------------------------------------
+    def check_items(self, items: Sequence[StepItem]) -> None:
+        if not items:
+            raise ValueError("a step needs at least one request")
+        if len(items) > self.max_items:
+            raise ValueError(f"a step holds at most {self.max_items} requests, found {len(items)}")
+        seen = set()
+        total = 0
+        for it in items:
+            if it.request in seen:
+                raise ValueError(f"request {it.request} appears twice in one step")
+            seen.add(it.request)
+            if len(it.tokens) < 1:
+                raise ValueError(f"request {it.request} brings no tokens")
+            if not self.cache.has(it.request):
+                raise ValueError(f"request {it.request} is not live in the cache manager")
+            total += len(it.tokens)
+        if total > self.max_step_tokens:
+            raise ValueError(f"a step holds at most {self.max_step_tokens} tokens, found {total}")
+
+    def __call__(self, items: Sequence[StepItem], manage_cache: bool = True) -> Optional[torch.Tensor]:
+        """Runs the step.  Returns logits [wanted, vocab] (float32, on the device) in the
+        order of items and of want, or None when nothing was wanted.
+
+        manage_cache=True: pages for the new tokens are taken here (all items or none;
+        CacheFull leaves everything as it was), and the cache advances once the step has
+        been issued without error.  manage_cache=False: the caller (the scheduler) has
+        reserved the pages and commits or abandons the step itself."""
+        self.check_items(items)
+        cache = self.cache
+        if manage_cache:
+            done = []
+            try:
+                for it in items:
+                    cache.reserve(it.request, len(it.tokens))
+                    done.append(it)
+            except CacheFull:
+                for it in done:
+                    cache.rollback(it.request)
+                raise
+        try:
+            batch = self.build_batch(items)
+            fresh = [int(s) for s, p in zip(batch.host["slots"], batch.host["start_pos"]) if p == 0]
+            if fresh and cache.state:
+                idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)
+                for t in cache.state.values():
+                    t.index_fill_(0, idx, 0.0)
+            x = self.model.forward(batch, self._views)
+            logits = self.model.logits(x, batch.want_rows, batch.n_want) if batch.n_want else None
+        except Exception:
+            if manage_cache:
+                for it in items:
+                    cache.rollback(it.request)
+            raise
+        if manage_cache:
+            for it in items:
+                cache.commit(it.request, len(it.tokens))
+        return logits
+
+    def _views(self, entry: int):
+        return self.cache.views(entry, self.model.schedule[entry].cache_from)

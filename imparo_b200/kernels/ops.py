@@ -1,0 +1,219 @@
+"""Launchers: check what the host can check, then call the CUDA entry points.
+
+Every function works on CUDA tensors only and raises otherwise; there is no CPU or
+library fallback for these operations.  The reference's launchers check layouts on
+the host in the same spirit (imparo-cuda/native/lfm2_ops.cuh:28-42,
+cobatch_rows.cuh:37-61).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import lib as _lib
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 or bfloat16") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*ts) -> None:
+    for t in ts:
+        if t is not None:
+            _need(t.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+            _need(t.is_contiguous(), "kernel arguments must be contiguous")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    reasons = {-1: "unsupported dtype code or missing library handle", -2: "bad accumulate/grid",
+               -3: "head size must be a multiple of 16 between 16 and 256",
+               -4: "rotated dimensions must be even and at most the head size",
+               -5: "kv heads must divide heads", -6: "conv taps must be between 2 and 16",
+               -7: "temperature sampling needs uniform numbers"}
+    if rc < 0:
+        raise KernelError(f"{what}: refused: {reasons.get(rc, rc)}")
+    if rc >= 1000:
+        raise KernelError(f"{what}: cuBLAS status {rc - 1000}")
+    raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.cudart().cudaGetErrorString(rc) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+
+
+# --------------------------------------------------------------------------------------
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_STATUS_TEXT = {1: "token id out of the vocabulary", 2: "cache write to a page out of range",
+                3: "cache read from a page out of range", 4: "state slot out of range",
+                5: "a bounded device wait gave up"}
+
+
+def read_status(status: torch.Tensor) -> None:
+    """Raise if a kernel recorded a bad index since the word was last cleared (synchronizes)."""
+    s = status.tolist()
+    if s[0] != 0:
+        status.zero_()
+        raise KernelError(f"device check failed: {_STATUS_TEXT.get(s[0], s[0])} "
+                          f"(kernel {s[1]}, index {s[2]}, value {s[3]})")
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    _cuda(table, ids, out, status)
+    n, width = out.shape
+    _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
+    _need(out.dtype == torch.float32 and table.shape[1] == width, "embedding output is float32 [tokens, width]")
+    _check(_lib.kernels().imparo_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, width,
+                                              table.shape[0], _ptr(status), _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    _cuda(x, w, out, rows)
+    n, width = out.shape
+    _need(x.dtype == torch.float32 and w.dtype == torch.float32, "rmsnorm reads a float32 stream and float32 weights")
+    _need(x.shape[1] == width and w.numel() == width, "rmsnorm width mismatch")
+    if rows is None:
+        _need(x.shape[0] >= n, "rmsnorm: fewer input rows than output rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n, "rmsnorm: rows must be int32, one per output row")
+    _check(_lib.kernels().imparo_rmsnorm(_ptr(x), _ptr(rows), _ptr(w), float(eps), _ptr(out), _code(out), n, width,
+                                         _stream()), "rmsnorm")
+
+
+def swiglu_act(gu: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(gu, out)
+    n, F = out.shape
+    _need(gu.shape == (n, 2 * F) and gu.dtype == out.dtype, "swiglu_act: gu must be [tokens, 2F] of the output dtype")
+    _check(_lib.kernels().imparo_swiglu_act(_ptr(gu), _ptr(out), _code(out), n, F, _stream()), "swiglu_act")
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    _cuda(out, bias)
+    n, width = out.shape
+    _need(bias.dtype == torch.float32 and bias.numel() == width, "bias must be float32 [width]")
+    _check(_lib.kernels().imparo_add_bias(_ptr(out), _code(out), _ptr(bias), n, width, _stream()), "add_bias")
+
+
+_gemm_ws = {}
+
+
+def _gemm_lib_ready(device) -> None:
+    key = torch.device(device).index or 0
+    if key not in _gemm_ws:
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+        _check(_lib.kernels().imparo_gemm_lib_init(_ptr(ws), ws.numel()), "gemm_lib_init")
+        _gemm_ws[key] = ws
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M,N] (+)= x[M,K] @ w[N,K]^T.  float32 x/w -> the FFMA kernel (true 32-bit);
+    bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16."""
+    _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (M, N), f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _need(x.stride(1) == 1 and out.is_contiguous() and w.is_contiguous(), "linear: rows must be dense")
+    _need(x.dtype == w.dtype, "linear: x and w must share a dtype")
+    if x.dtype == torch.float32:
+        _need(out.dtype == torch.float32, "linear: float32 product writes float32")
+        _check(_lib.kernels().imparo_sgemm_nt(_ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), N, int(accumulate),
+                                              _stream()), "sgemm_nt")
+    elif x.dtype == torch.bfloat16:
+        _need(not accumulate or out.dtype == torch.float32, "linear: accumulate needs a float32 output")
+        _gemm_lib_ready(x.device)
+        _check(_lib.kernels().imparo_gemm_bf16_nt(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), N,
+                                                  int(accumulate), _stream()), "gemm_bf16_nt")
+    else:
+        raise KernelError(f"linear: unsupported dtype {x.dtype}")
+
+
+def qk_norm_rope_store(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, q_out,
+                       k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, status) -> None:
+    """qkv [T, (nh+2*nkv)*hd] -> q_out [T, nh*hd] normed and rotated; k (normed, rotated)
+    and v written into their pages.  nkv == 0: q only (a layer that reads another's cache)."""
+    _cuda(qkv, positions, item_of_token, q_w, k_w, inv_freq, q_out, k_cache, v_cache, table, status)
+    T = q_out.shape[0]
+    _need(qkv.shape == (T, (nh + 2 * nkv) * hd) and q_out.shape[1] == nh * hd, "qk_norm_rope_store: widths")
+    _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
+          and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
+    _need(q_w.dtype == torch.float32 and q_w.numel() == hd, "q norm weight must be float32 [head]")
+    if nkv:
+        _need(k_w.dtype == torch.float32 and k_w.numel() == hd, "k norm weight must be float32 [head]")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype must match activations")
+        _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * hd,
+              "cache arena smaller than n_pages")
+        _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= n_rot // 2, "inv_freq must be float32 [n_rot/2]")
+    max_blocks = table.shape[1] if table is not None else 0
+    _check(_lib.kernels().imparo_qk_norm_rope_store(
+        _ptr(qkv), _code(qkv), _ptr(positions), _ptr(item_of_token), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), n_rot,
+        float(eps), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(table), max_blocks, page_size, n_pages,
+        T, nh, nkv, hd, _ptr(status), _stream()), "qk_norm_rope_store")
+
+
+def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
+                    out, nh, nkv, hd, status) -> None:
+    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, status)
+    T = q.shape[0]
+    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "paged_attention: q/out shapes")
+    _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _check(_lib.kernels().imparo_paged_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd,
+        _ptr(status), _stream()), "paged_attention")
+
+
+def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, taps, status) -> None:
+    _cuda(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, status)
+    T, width = y.shape
+    _need(bcx.shape == (T, 3 * width) and bcx.dtype == y.dtype, "gated_conv: bcx must be [tokens, 3*width]")
+    _need(w.dtype == torch.float32 and w.shape == (width, taps), "gated_conv: taps must be float32 [width, taps]")
+    _need(state.dtype == torch.float32 and state.dim() == 3 and state.shape[1:] == (taps - 1, width),
+          "gated_conv: state must be float32 [slots, taps-1, width]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == width, "gated_conv: bias must be float32 [width]")
+    _check(_lib.kernels().imparo_gated_conv(
+        _ptr(bcx), _code(bcx), _ptr(w), _ptr(bias), _ptr(state), _ptr(item_row_start), _ptr(item_of_token),
+        _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], _ptr(status), _stream()), "gated_conv")
+
+
+def sample_rows(logits, temperature, uniform, out) -> None:
+    """out[r] = greedy pick where temperature[r] <= 0 (or temperature is None), else the
+    inverse-CDF pick of softmax(logits[r] / temperature[r]) at uniform[r]."""
+    _cuda(logits, temperature, uniform, out)
+    n, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= n, "sample_rows: dtypes")
+    if temperature is not None:
+        _need(temperature.dtype == torch.float32 and uniform is not None and uniform.dtype == torch.float32
+              and temperature.numel() >= n and uniform.numel() >= n, "sample_rows: temperature/uniform float32 per row")
+    _check(_lib.kernels().imparo_sample_rows(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, vocab,
+                                             logits.stride(0), _stream()), "sample_rows")

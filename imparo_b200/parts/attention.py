@@ -1,0 +1,83 @@
+"""Grouped-query attention over the paged cache, as a part.
+
+q/k/v projections, per-head RMS norm of q and k, position encoding, cache write,
+causal attention scaled by 1/sqrt(head), output projection
+(imparo-model/src/lfm2/workflow_cpu.rs:203-250; imparo-model/src/cpu_support.rs:361-445).
+A window keeps only keys pos+1-window..pos (cpu_support.rs:387-388,423).  The part knows
+heads, groups, head size, eps, window and its position part; nothing of the model.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import Part, make_part
+from .spec import PagedKV, PartSpec, WeightSpec
+
+
+class AttentionMixer(Part):
+    """params: hidden, n_heads, n_kv_heads, head_dim, eps, window (None or int), position
+    (PartSpec), qk_norm (bool, default True), names (optional dict of tensor names)."""
+
+    NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
+             "o": "self_attn.out_proj.weight", "q_norm": "self_attn.q_layernorm.weight",
+             "k_norm": "self_attn.k_layernorm.weight"}
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        p = params
+        self.hidden = int(p["hidden"])
+        self.nh = int(p["n_heads"])
+        self.nkv = int(p["n_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.eps = float(p["eps"])
+        self.window = int(p["window"]) if p.get("window") else None
+        if self.nh % self.nkv:
+            raise ValueError(f"attention: kv heads {self.nkv} must divide heads {self.nh}")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            raise ValueError(f"attention: head size {self.hd} is not supported by the kernels "
+                             "(multiples of 16 from 16 to 256)")
+        self.scale = 1.0 / math.sqrt(self.hd)
+        self.names = {k: prefix + v for k, v in {**self.NAMES, **p.get("names", {})}.items()}
+        self.position = make_part("position", p.get("position", PartSpec("none")), prefix, rt)
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def weight_specs(self):
+        n, H, hd = self.names, self.hidden, self.hd
+        return [WeightSpec(n["q"], ((self.nh * hd, H),)), WeightSpec(n["k"], ((self.nkv * hd, H),)),
+                WeightSpec(n["v"], ((self.nkv * hd, H),)), WeightSpec(n["o"], ((H, self.nh * hd),)),
+                WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
+                WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))] + self.position.weight_specs()
+
+    def bind(self, tensors):
+        n = self.names
+        # one fused projection [q | k | v]: a layout choice, the arithmetic is unchanged
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        self.q_norm = tensors[n["q_norm"]]
+        self.k_norm = tensors[n["k_norm"]]
+        self.position.bind(tensors)
+
+    def cache_specs(self):
+        return (PagedKV(self.nkv, self.hd, self.window),)
+
+    def forward(self, x, batch, caches, residual):
+        kv = caches[0]
+        rt, T = self.rt, x.shape[0]
+        nh, hd = self.nh, self.hd
+        nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only
+        width = (nh + 2 * nkv) * hd
+        qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype)
+        ops.linear(x, self.w_qkv[:width], qkv)
+        q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype)
+        rot = self.position.rotary()
+        table = batch.tables[kv.group]
+        inv_freq, n_rot = rot if rot is not None else (None, 0)
+        ops.qk_norm_rope_store(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq, n_rot,
+                               self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
+        out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype)
+        ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
+                            self.window, self.scale, out, nh, self.nkv, hd, rt.status)
+        ops.linear(out, self.w_o, residual, accumulate=True)

@@ -1,0 +1,124 @@
+"""Interfaces of the parts a model is put together from, and the registry of part kinds.
+
+A part knows its own sizes and constants (given as parameters) and nothing about the
+model it is in.  Kinds:
+
+  "mixer"        forward(x, batch, caches, residual)  adds its output into residual
+  "feed_forward" forward(x, batch, residual)          adds its output into residual
+  "norm"         forward(x, out=None, rows=None)      -> normed activations
+  "position"     tables / apply for queries and keys
+  "block"        forward(x, batch, caches)            arranges norm, mixer, feed-forward
+  "embedding"    forward(token_ids, out)              -> the 32-bit residual stream
+  "head"         forward(h)                           -> 32-bit logits
+
+x is the normed input in the activation dtype (bfloat16, or float32 in the 32-bit
+path); residual is the 32-bit residual stream [tokens, width].  batch is the step's
+StepBatch.  caches is a tuple with one bound view per entry of the part's
+cache_specs().
+
+Every part declares the tensors it reads (weight_specs) and receives them already on
+the device in the right dtype (bind).  Adding a kind is register_part(kind, name, cls);
+nothing else in the framework changes.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .spec import PartSpec, WeightSpec
+
+
+@dataclass
+class Runtime:
+    """Engine-wide facts handed to every part when it is built."""
+    precision: str                      # "bfloat16" | "float32"
+    device: torch.device
+    status: Optional[torch.Tensor] = None       # int32[4] device word kernels report bad indices into
+    workspace: "Workspace" = None
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return torch.bfloat16 if self.precision == "bfloat16" else torch.float32
+
+    @property
+    def matrix_dtype(self) -> torch.dtype:
+        return self.act_dtype
+
+
+class Workspace:
+    """Activation scratch by tag.  A tag's buffer only ever grows (outside graph capture),
+    so addresses are stable from step to step and never depend on which requests a step
+    carries (the reference sizes activation buffers once per batch width,
+    imparo-model/src/gpu_support.rs:557-715)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = f"{tag}:{dtype}"
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{tag}' would grow while a captured graph holds its address")
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+class Part:
+    """Base of every part.  params are the PartSpec's parameters; prefix is the tensor-name
+    prefix of the layer (or "" for model-level parts)."""
+
+    def __init__(self, params: dict, prefix: str, rt: Runtime):
+        self.params = dict(params)
+        self.prefix = prefix
+        self.rt = rt
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """tensors: full tensor name -> device tensor, for the names of weight_specs()
+        (optional ones absent when the file has none)."""
+
+    def cache_specs(self) -> Tuple:
+        return ()
+
+
+_PARTS: Dict[Tuple[str, str], type] = {}
+
+
+def register_part(kind: str, name: str, cls: type, replace: bool = False) -> None:
+    key = (kind, name)
+    if key in _PARTS and not replace:
+        raise ValueError(f"{kind} part '{name}' is already registered")
+    _PARTS[key] = cls
+
+
+def make_part(kind: str, spec: PartSpec, prefix: str, rt: Runtime) -> Part:
+    _ensure_builtin()
+    try:
+        cls = _PARTS[(kind, spec.kind)]
+    except KeyError:
+        known = sorted(n for k, n in _PARTS if k == kind)
+        raise ValueError(f"unknown {kind} part '{spec.kind}'; known: {', '.join(known)}") from None
+    return cls(spec.params, prefix, rt)
+
+
+def known_parts(kind: str) -> Tuple[str, ...]:
+    _ensure_builtin()
+    return tuple(sorted(n for k, n in _PARTS if k == kind))
+
+
+def _ensure_builtin() -> None:
+    from . import builtin  # noqa: F401  (registers the built-in parts on import)

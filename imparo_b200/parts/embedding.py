@@ -1,0 +1,57 @@
+"""Token embedding and output head as parts.
+
+Embedding: rows of the table, unscaled, into the 32-bit residual stream
+(imparo-model/src/cpu_support.rs:327-342; lfm2/plan.rs:147-151).  Head: logits = h * E^T
+in 32-bit, E the embedding table when tied, no softcap and no scale for this
+architecture (cpu_support.rs:451-466; lfm2/plan.rs:163-169)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import Part
+from .spec import WeightSpec
+
+
+class TokenEmbedding(Part):
+    """params: vocab, width, name."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.vocab = int(params["vocab"])
+        self.width = int(params["width"])
+        self.name = prefix + params["name"]
+        self.table = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, ((self.vocab, self.width),))]
+
+    def bind(self, tensors):
+        self.table = tensors[self.name]
+
+    def forward(self, token_ids: torch.Tensor, n_tokens: int) -> torch.Tensor:
+        out = self.rt.workspace.get("residual", (n_tokens, self.width), torch.float32)
+        ops.embed_gather(self.table, token_ids, out, self.rt.status)
+        return out
+
+
+class LinearHead(Part):
+    """params: vocab, width, name (the table's own tensor, or the embedding's when tied)."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.vocab = int(params["vocab"])
+        self.width = int(params["width"])
+        self.name = prefix + params["name"]
+        self.table = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, ((self.vocab, self.width),))]
+
+    def bind(self, tensors):
+        self.table = tensors[self.name]
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32)
+        ops.linear(h, self.table, logits)
+        return logits

@@ -1,0 +1,36 @@
+"""Tiny LFM2 configurations for tests.  They differ in every size and option: layer
+order, heads and groups (2, 3, 1), head size (16, 32, 48), taps (3, 4, 2), conv bias,
+rope theta, eps, tied or own head, ff auto-adjust, vocabulary and width that are no
+power of two, and a sliding window in C."""
+
+TINY_A = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 256, "hidden_size": 64, "num_hidden_layers": 4,
+    "layer_types": ["conv", "conv", "full_attention", "conv"],
+    "num_attention_heads": 4, "num_key_value_heads": 2,
+    "block_ff_dim": 192, "block_auto_adjust_ff_dim": False,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 10000.0, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 4096,
+}
+
+TINY_B = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 512, "hidden_size": 192, "num_hidden_layers": 6,
+    "layer_types": ["full_attention", "conv", "conv", "full_attention", "conv", "full_attention"],
+    "num_attention_heads": 6, "num_key_value_heads": 2,
+    "block_ff_dim": 768, "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0, "block_multiple_of": 64,
+    "conv_L_cache": 4, "conv_bias": True, "rope_theta": 1000000.0, "norm_eps": 1e-6,
+    "tie_embedding": False, "max_position_embeddings": 4096,
+}
+
+TINY_C = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 331, "hidden_size": 144, "num_hidden_layers": 5,
+    "layer_types": ["sliding_attention", "conv", "full_attention", "sliding_attention", "conv"],
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 48,
+    "block_ff_dim": 200, "block_auto_adjust_ff_dim": False,
+    "conv_L_cache": 2, "conv_bias": False, "rope_theta": 50000.0, "norm_eps": 3e-6,
+    "tie_embedding": True, "max_position_embeddings": 4096, "sliding_window": 24,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
