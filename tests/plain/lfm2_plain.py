@@ -300,3 +300,48 @@ def greedy_generate(model, prompt, n_new):
     for _ in range(n_new):
         toks.append(argmax_first(model.logits(toks)[-1]))
     return toks[len(prompt):]
+
+
+_MASK64 = (1 << 64) - 1
+
+
+def uniform_for(seed, step):
+    """The engine's per-(seed, step) uniform number, restated: splitmix64 of
+    seed * 0x9E3779B97F4A7C15 + step, top 24 bits.  (The reference has no temperature
+    sampling: imparo-server/src/main.rs:3383-3390.)"""
+    z = ((seed & _MASK64) * 0x9E3779B97F4A7C15 + (step & _MASK64) + 0x9E3779B97F4A7C15) & _MASK64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK64
+    z ^= z >> 31
+    return (z >> 40) / float(1 << 24)
+
+
+def sample_temperature(logits, temperature, u):
+    """First index whose running sum of softmax(logits / T), in vocabulary order, exceeds u.
+    Returns (index, distance of u to the nearest boundary of that index's interval)."""
+    z = (logits.astype(np.float64) - logits.max()) / temperature
+    p = np.exp(z)
+    cdf = np.cumsum(p) / p.sum()
+    i = int(np.searchsorted(cdf, u, side="right"))
+    i = min(i, len(cdf) - 1)
+    lo = cdf[i - 1] if i > 0 else 0.0
+    return i, min(u - lo, cdf[i] - u)
+
+
+def generate(model, prompt, n_new, temperature=0.0, seed=0):
+    """Token by token from whole-sequence logits.  -> (tokens, margins): margin is how far
+    each pick was from going another way (top-2 logit gap for greedy, distance of u to an
+    interval boundary for temperature)."""
+    toks, out, margins = list(prompt), [], []
+    for step in range(n_new):
+        row = model.logits(toks)[-1]
+        if temperature > 0:
+            t, margin = sample_temperature(row, temperature, uniform_for(seed, step))
+        else:
+            t = argmax_first(row)
+            top2 = np.partition(row, -2)[-2:]
+            margin = float(top2[1] - top2[0])
+        out.append(t)
+        margins.append(margin)
+        toks.append(t)
+    return out, margins

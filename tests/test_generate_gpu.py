@@ -1,0 +1,104 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: greedy and seeded temperature sampling, continuous batching with prompt
+portions beside decode tokens, few pages."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests.gpu_helpers import make_requests, model_dir, plain_model
+from tests.plain import lfm2_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def agree(got, want, margins, min_margin):
+    """Same tokens, except that a pick the plain implementation made by less than
+    min_margin may go the other way; after that the sequences legitimately differ."""
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert margins[i] < min_margin, f"token {i}: {g} != {w} with margin {margins[i]:.3e}"
+            return
+    assert len(got) == len(want)
+
+
+@pytest.mark.parametrize("dtype,min_margin", [("float32", 1e-5), ("bfloat16", 2e-2)])
+def test_tiny_a_greedy_16_plus_8(dtype, min_margin):
+    from imparo_b200.engine import Engine
+    prompt = make_requests("A", [16], seed=0)["r0"]
+    eng = Engine(model_dir("A"), dtype=dtype, ctx=64, parallel=2, page_size=16, num_pages=4)
+    got = eng.generate([prompt], max_tokens=8)[0]
+    want, margins = P.generate(plain_model("A"), prompt, 8)
+    agree(got, want, margins, min_margin)
+    assert eng.cache.n_requests() == 0 and eng.cache.free_pages(0) == 4
+
+
+@pytest.mark.parametrize("dtype,min_margin", [("float32", 1e-5), ("bfloat16", 2e-2)])
+def test_tiny_b_mixed_batch_greedy_and_temperature(dtype, min_margin):
+    """3 requests (5, 23, 40 tokens), portions of 8 beside running decodes, 12 new tokens
+    each, greedy for one and temperature 0.8 (seeded) for two, pages of 4 tokens."""
+    from imparo_b200.engine import Engine
+    reqs = make_requests("B", [5, 23, 40], seed=1)
+    prompts = list(reqs.values())
+    temps, seeds = [0.0, 0.8, 0.8], [0, 11, 12]
+    eng = Engine(model_dir("B"), dtype=dtype, ctx=64, parallel=3, page_size=4, num_pages=40, max_step_tokens=8)
+    seen = []
+    got = eng.generate(prompts, max_tokens=12, temperature=temps, seed=seeds, on_step=lambda plan: seen.append(plan))
+    for i in range(3):
+        want, margins = P.generate(plain_model("B"), prompts[i], 12, temps[i], seeds[i])
+        agree(got[i], want, margins, min_margin if temps[i] == 0 else 1e-4 if dtype == "float32" else 5e-3)
+    # portions ran beside decode tokens, under the budget
+    assert all(sum(e.count for e in plan) <= 8 for plan in seen)
+    assert any(any(e.count == 1 and e.want for e in plan) and any(e.count > 1 for e in plan) for plan in seen)
+    assert eng.cache.n_requests() == 0 and eng.cache.free_pages(0) == 40
+    eng.cache.check()
+
+
+def test_pages_run_out_during_generation_requests_are_recomputed():
+    """So few pages that running requests are preempted; every request still gets the
+    tokens it would get alone."""
+    from imparo_b200.engine import Engine
+    reqs = make_requests("A", [30, 41, 22, 35], seed=4)
+    prompts = list(reqs.values())
+    eng = Engine(model_dir("A"), dtype="float32", ctx=128, parallel=4, page_size=4, num_pages=34, max_step_tokens=32)
+    got = eng.generate(prompts, max_tokens=24)
+    assert eng.stats()["preemptions"] >= 1
+    for i, p in enumerate(prompts):
+        want, margins = P.generate(plain_model("A"), p, 24)
+        agree(got[i], want, margins, 1e-5)
+    assert eng.cache.free_pages(0) == 34 and eng.cache.free_slots() == 4
+    eng.cache.check()
+
+
+def test_a_request_larger_than_the_pool_fails_alone():
+    from imparo_b200.engine import Engine
+    eng = Engine(model_dir("A"), dtype="float32", ctx=512, parallel=2, page_size=4, num_pages=8)
+    reqs = make_requests("A", [60, 10], seed=6)
+    got = eng.generate(list(reqs.values()), max_tokens=4)
+    assert eng.stats()["failed"] == [0] and got[0] == [] and len(got[1]) == 4
+    assert eng.cache.free_pages(0) == 8
+
+
+def test_stop_token_and_zero_max_tokens():
+    from imparo_b200.engine import Engine
+    prompt = make_requests("A", [12], seed=2)["r0"]
+    eng = Engine(model_dir("A"), dtype="float32", ctx=64, parallel=2)
+    free = eng.generate([prompt], max_tokens=10)[0]
+    stopped = eng.generate([prompt], max_tokens=10, stop_token_ids=[free[3]])[0]
+    assert stopped == free[:free.index(free[3])]
+    assert eng.generate([prompt, prompt], max_tokens=[0, 2]) == [[], free[:2]]
+
+
+def test_command_line_generates_the_same_tokens(tmp_path):
+    prompt = make_requests("A", [16], seed=0)["r0"]
+    want, _ = P.generate(plain_model("A"), prompt, 8)
+    tf = tmp_path / "tokens.txt"
+    tf.write_text(" ".join(map(str, prompt)))
+    r = subprocess.run([sys.executable, "-m", "imparo_b200", "-m", model_dir("A"), "--dtype", "float32", "--decode", "8",
+                        "-c", "64", "-t", str(tf), "--json"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["tokens"] == [want]

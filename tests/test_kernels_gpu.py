@@ -1,0 +1,404 @@
+"""Each CUDA kernel alone against a plain float32/float64 reference of the same operation,
+at sizes other than the engine's test models: widths and vocabularies that are no power of
+two, head sizes 16..256, several head/group counts, page sizes 1..64, scrambled page
+tables, windows, ragged batches."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def ops():
+    from imparo_b200.kernels import ops as o
+    return o
+
+
+def bf16_round(x):
+    return x.to(torch.bfloat16).to(torch.float32)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("width,vocab", [(72, 1000), (2048, 65536), (100, 331)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(width, vocab, dtype):
+    o = ops()
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, width, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(37, width, device=DEV)
+    st = o.new_status(DEV)
+    o.embed_gather(table, ids, out, st)
+    assert torch.equal(out, table[ids.long()].float())
+    o.read_status(st)
+    ids[5] = vocab
+    o.embed_gather(table, ids, out, st)
+    with pytest.raises(o.KernelError, match="token id"):
+        o.read_status(st)
+
+
+@pytest.mark.parametrize("width", [100, 144, 2048, 3000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(width, out_dtype):
+    o = ops()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(19, width, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    eps = 3e-6
+    ref = (x.double() * (1.0 / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)) * w.double())
+    out = torch.empty(19, width, dtype=out_dtype, device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), eps, out)
+    tol = 2e-6 if out_dtype == torch.float32 else 8e-3
+    assert (out.float().cpu().double() - ref).abs().max() <= tol * ref.abs().max()
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, width, dtype=out_dtype, device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), eps, out2, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 53, 71), (37, 130, 64), (64, 64, 16), (130, 1, 5), (7, 331, 144)])
+def test_sgemm_is_true_float32(M, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(2)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    # values with mantissa bits below what a reduced-precision product keeps
+    a = a * (1 + 2.0 ** -15)
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    o.linear(a.to(DEV), w.to(DEV), out)
+    assert (out.cpu().double() - ref).abs().max() <= 2e-6 * max(1.0, ref.abs().max())
+    base = torch.randn(M, N, generator=g)
+    out2 = base.to(DEV).clone()
+    o.linear(a.to(DEV), w.to(DEV), out2, accumulate=True)
+    assert (out2.cpu().double() - (ref + base.double())).abs().max() <= 3e-6 * max(1.0, ref.abs().max())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (5, 200, 136), (77, 512, 192), (300, 1000, 264)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_bf16(M, N, K, out_dtype):
+    o = ops()
+    g = torch.Generator().manual_seed(3)
+    a, w = bf16_round(torch.randn(M, K, generator=g)), bf16_round(torch.randn(N, K, generator=g))
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    o.linear(a.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out)
+    tol = 1e-5 if out_dtype == torch.float32 else 8e-3
+    assert (out.float().cpu().double() - ref).abs().max() <= tol * ref.abs().max()
+    if out_dtype == torch.float32:
+        base = torch.randn(M, N, generator=g)
+        out2 = base.to(DEV).clone()
+        o.linear(a.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out2, accumulate=True)
+        assert (out2.cpu().double() - (ref + base.double())).abs().max() <= 1e-5 * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_act(dtype):
+    o = ops()
+    g = torch.Generator().manual_seed(4)
+    gu = (torch.randn(11, 2 * 200, generator=g) * 4).to(dtype)
+    out = torch.empty(11, 200, dtype=dtype, device=DEV)
+    o.swiglu_act(gu.to(DEV), out)
+    gate, up = gu[:, :200].double(), gu[:, 200:].double()
+    ref = gate / (1 + torch.exp(-gate)) * up
+    tol = 1e-6 if dtype == torch.float32 else 8e-3
+    assert (out.float().cpu().double() - ref).abs().max() <= tol * ref.abs().max()
+
+
+# ---------------------------------------------------------------------------------------
+def conv_reference(bcx, w, bias, state):
+    """numpy restatement of imparo-cpu/src/ops.rs:109-167 for one request's portion."""
+    T, H, taps = bcx.shape[0], w.shape[0], w.shape[1]
+    v = bcx[:, :H] * bcx[:, 2 * H:]
+    seq = np.concatenate([state, v])
+    y = np.zeros((T, H))
+    for t in range(T):
+        acc = sum(w[:, k] * seq[t + k] for k in range(taps))
+        if bias is not None:
+            acc = acc + bias
+        y[t] = bcx[t, H:2 * H] * acc
+    return y, seq[-(taps - 1):]
+
+
+@pytest.mark.parametrize("taps", [2, 3, 4, 7])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gated_conv_ragged_batch(taps, dtype, bias):
+    o = ops()
+    H, n_slots = 72, 5
+    lens = [1, 9, 2, 1, 5]          # shorter than taps-1, equal, longer
+    slots = [3, 0, 4, 1, 2]
+    g = torch.Generator().manual_seed(taps)
+    T = sum(lens)
+    bcx = torch.randn(T, 3 * H, generator=g).to(dtype)
+    w = torch.randn(H, taps, generator=g)
+    b = torch.randn(H, generator=g) if bias else None
+    state = torch.randn(n_slots, taps - 1, H, generator=g)
+    row_start = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    item_of_token = np.repeat(np.arange(len(lens)), lens).astype(np.int32)
+    y = torch.empty(T, H, dtype=dtype, device=DEV)
+    st_dev = state.to(DEV).clone()
+    status = o.new_status(DEV)
+    o.gated_conv(bcx.to(DEV), w.to(DEV), None if b is None else b.to(DEV), st_dev,
+                 torch.from_numpy(row_start).to(DEV), torch.from_numpy(item_of_token).to(DEV),
+                 torch.tensor(slots, dtype=torch.int32, device=DEV), y, taps, status)
+    o.read_status(status)
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    for i, n in enumerate(lens):
+        a = row_start[i]
+        ref_y, ref_s = conv_reference(bcx[a:a + n].double().numpy(), w.double().numpy(),
+                                      None if b is None else b.double().numpy(), state[slots[i]].double().numpy())
+        assert np.abs(y[a:a + n].float().cpu().double().numpy() - ref_y).max() <= tol * max(1.0, np.abs(ref_y).max())
+        assert np.abs(st_dev[slots[i]].cpu().double().numpy() - ref_s).max() <= 2e-6 * max(1.0, np.abs(ref_s).max())
+
+
+def test_gated_conv_matches_the_reference_host_code():
+    """Outputs and next state against tests/golden/conv_golden.json, which the reference's
+    own shortconv_reference / shortconv_state_reference produced."""
+    o = ops()
+    with open(os.path.join(HERE, "golden", "conv_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    for c in cases:
+        H, taps, T = c["width"], c["kernel"], c["n_tok"]
+        bcx = torch.tensor(c["bcx"]).reshape(T, 3 * H).to(DEV)
+        w = torch.tensor(c["weights"]).reshape(H, taps).to(DEV)
+        state = torch.tensor(c["state"]).reshape(1, taps - 1, H).to(DEV)
+        y = torch.empty(T, H, device=DEV)
+        status = o.new_status(DEV)
+        o.gated_conv(bcx, w, None, state, torch.tensor([0, T], dtype=torch.int32, device=DEV),
+                     torch.zeros(T, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                     y, taps, status)
+        o.read_status(status)
+        assert np.allclose(y.cpu().numpy().reshape(-1), np.array(c["output"], np.float32), rtol=2e-6, atol=2e-6)
+        assert np.allclose(state.cpu().numpy().reshape(-1), np.array(c["next_state"], np.float32), rtol=1e-6, atol=1e-7)
+
+
+# ---------------------------------------------------------------------------------------
+def make_paged(rng, lens, page, nkv, hd, dtype, extra_pages=3):
+    """Random keys/values for requests of the given lengths, laid out in scrambled pages."""
+    R = len(lens)
+    blocks = [(n + page - 1) // page for n in lens]
+    n_pages = sum(blocks) + extra_pages
+    perm = rng.permutation(n_pages)
+    stride = max(blocks) + 2
+    table = -np.ones((R, stride), dtype=np.int32)
+    k_cache = torch.zeros(n_pages, page, nkv * hd)
+    v_cache = torch.zeros(n_pages, page, nkv * hd)
+    ks, vs = [], []
+    at = 0
+    for r, n in enumerate(lens):
+        table[r, :blocks[r]] = perm[at:at + blocks[r]]
+        at += blocks[r]
+        k = torch.from_numpy(rng.standard_normal((n, nkv * hd)).astype(np.float32)).to(dtype).float()
+        v = torch.from_numpy(rng.standard_normal((n, nkv * hd)).astype(np.float32)).to(dtype).float()
+        for p in range(n):
+            k_cache[table[r, p // page], p % page] = k[p]
+            v_cache[table[r, p // page], p % page] = v[p]
+        ks.append(k)
+        vs.append(v)
+    return table, k_cache.to(dtype), v_cache.to(dtype), ks, vs, n_pages
+
+
+def attention_reference(q, k, v, pos, nh, nkv, hd, scale, window):
+    """imparo-model/src/cpu_support.rs:402-445 for one query row, in float64."""
+    out = np.zeros((nh, hd))
+    lo = max(0, pos + 1 - window) if window else 0
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        kk = k[lo:pos + 1, kvh * hd:(kvh + 1) * hd]
+        vv = v[lo:pos + 1, kvh * hd:(kvh + 1) * hd]
+        s = kk @ q[h * hd:(h + 1) * hd] * scale
+        p = np.exp(s - s.max())
+        out[h] = (p / p.sum()) @ vv
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256)])
+@pytest.mark.parametrize("page,window", [(1, None), (4, None), (16, 13), (64, None), (8, 40)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_paged_attention(nh, nkv, hd, page, window, dtype):
+    o = ops()
+    rng = np.random.default_rng(nh * 1000 + hd + page)
+    lens = [70, 1, 33, 129]
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, lens, page, nkv, hd, dtype)
+    # queries: a portion of request 0 (positions 50..69), the single token of request 1,
+    # the last token of request 2, three scattered positions of request 3
+    rows = [(0, p) for p in range(50, 70)] + [(1, 0), (2, 32)] + [(3, 0), (3, 64), (3, 128)]
+    q = torch.from_numpy(rng.standard_normal((len(rows), nh * hd)).astype(np.float32)).to(dtype)
+    out = torch.empty(len(rows), nh * hd, dtype=dtype, device=DEV)
+    status = o.new_status(DEV)
+    scale = 1 / math.sqrt(hd)
+    o.paged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV),
+                      torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+                      torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV),
+                      torch.from_numpy(table).to(DEV), page, n_pages, window, scale, out, nh, nkv, hd, status)
+    o.read_status(status)
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+    for i, (r, p) in enumerate(rows):
+        ref = attention_reference(q[i].double().numpy(), ks[r].double().numpy(), vs[r].double().numpy(), p, nh, nkv, hd,
+                                  scale, window)
+        err = np.abs(out[i].float().cpu().double().numpy() - ref).max()
+        assert err <= tol * max(1.0, np.abs(ref).max()), (r, p, err)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far,window", [(3, None), (511, None), (512, None), (0, None), (700, 200), (701, 200), (899, 200)])
+def test_one_far_key_stands_out(dtype, far, window):
+    """Among 900 keys one is scaled so that its score dominates: the output must be that
+    key's value (or must NOT be, when a window has passed it).  Random weights would hide
+    a kernel that drops a far key, a page edge or a window edge."""
+    o = ops()
+    nh, nkv, hd, page = 4, 2, 64, 16
+    rng = np.random.default_rng(far)
+    n = 900
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, [n], page, nkv, hd, dtype)
+    q = torch.from_numpy(rng.standard_normal((1, nh * hd)).astype(np.float32))
+    # key `far` of every kv head points along q of the group's first head, strongly
+    for kvh in range(nkv):
+        h = kvh * (nh // nkv)
+        ks[0][far, kvh * hd:(kvh + 1) * hd] = (q[0, h * hd:(h + 1) * hd] * 12).to(dtype).float()
+    kc = kc.clone()
+    kc[table[0, far // page], far % page] = ks[0][far].to(dtype)
+    out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
+    status = o.new_status(DEV)
+    o.paged_attention(q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                      torch.zeros(1, dtype=torch.int32, device=DEV), torch.from_numpy(table).to(DEV), page, n_pages,
+                      window, 1 / math.sqrt(hd), out, nh, nkv, hd, status)
+    o.read_status(status)
+    visible = window is None or far >= n - window
+    for kvh in range(nkv):
+        h = kvh * (nh // nkv)
+        got = out[0, h * hd:(h + 1) * hd].float().cpu()
+        target = vs[0][far, kvh * hd:(kvh + 1) * hd]
+        close = (got - target).abs().max() < 0.05
+        assert close == visible, (far, window, kvh)
+    ref = attention_reference(q[0].to(dtype).double().numpy(), ks[0].double().numpy(), vs[0].double().numpy(), n - 1, nh, nkv,
+                              hd, 1 / math.sqrt(hd), window)
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+    assert np.abs(out[0].float().cpu().double().numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("nh,nkv,hd,n_rot", [(4, 2, 16, 16), (6, 2, 32, 32), (3, 1, 48, 48), (2, 2, 64, 32), (1, 1, 256, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_store(nh, nkv, hd, n_rot, dtype):
+    o = ops()
+    rng = np.random.default_rng(hd)
+    page, n_pages, eps, theta = 4, 40, 1e-6, 50000.0
+    positions = np.array([0, 1, 2, 3, 4, 17, 900, 4095, 100000, 7], dtype=np.int32)
+    items = np.array([0, 0, 0, 0, 0, 1, 2, 3, 4, 5], dtype=np.int32)
+    T = len(positions)
+    table = -np.ones((6, 100000 // page + 2), dtype=np.int32)
+    perm = rng.permutation(n_pages)
+    used = {}
+    for t in range(T):
+        key = (items[t], positions[t] // page)
+        if key not in used:
+            used[key] = perm[len(used)]
+        table[key] = used[key]
+    qkv = torch.from_numpy(rng.standard_normal((T, (nh + 2 * nkv) * hd)).astype(np.float32)).to(dtype)
+    qw = torch.from_numpy(1 + 0.1 * rng.standard_normal(hd).astype(np.float32))
+    kw = torch.from_numpy(1 + 0.1 * rng.standard_normal(hd).astype(np.float32))
+    inv = (theta ** (-2.0 * np.arange(n_rot // 2) / n_rot)).astype(np.float32)
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    kc = torch.zeros(n_pages, page, nkv * hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    status = o.new_status(DEV)
+    o.qk_norm_rope_store(qkv.to(DEV), torch.from_numpy(positions).to(DEV), torch.from_numpy(items).to(DEV), qw.to(DEV),
+                         kw.to(DEV), torch.from_numpy(inv).to(DEV), n_rot, eps, q_out, kc, vc,
+                         torch.from_numpy(table).to(DEV), page, n_pages, nh, nkv, hd, status)
+    o.read_status(status)
+
+    def ref_rows(x, w, pos):            # x [heads, hd] float64
+        x = x * (1.0 / np.sqrt((x * x).mean(-1, keepdims=True) + eps)) * w
+        ang = (np.float64(pos) * inv.astype(np.float64)).astype(np.float32).astype(np.float64)
+        half = n_rot // 2
+        out = x.copy()
+        out[:, :half] = x[:, :half] * np.cos(ang) - x[:, half:n_rot] * np.sin(ang)
+        out[:, half:n_rot] = x[:, :half] * np.sin(ang) + x[:, half:n_rot] * np.cos(ang)
+        return out
+    # float32 angles: position * inv_freq loses bits at large positions equally in both
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    x = qkv.double().numpy()
+    for t in range(T):
+        qr = ref_rows(x[t, :nh * hd].reshape(nh, hd), qw.double().numpy(), positions[t]).reshape(-1)
+        kr = ref_rows(x[t, nh * hd:(nh + nkv) * hd].reshape(nkv, hd), kw.double().numpy(), positions[t]).reshape(-1)
+        vr = x[t, (nh + nkv) * hd:]
+        pg, off = table[items[t], positions[t] // page], positions[t] % page
+        assert np.abs(q_out[t].float().cpu().numpy() - qr).max() <= tol * np.abs(qr).max(), ("q", t)
+        assert np.abs(kc[pg, off].float().cpu().numpy() - kr).max() <= tol * np.abs(kr).max(), ("k", t)
+        assert np.abs(vc[pg, off].float().cpu().numpy() - vr).max() <= 1e-7, ("v", t)
+    # a write to a page that is not mapped is refused and reported, not done
+    table[0, 0] = -1
+    o.qk_norm_rope_store(qkv.to(DEV), torch.from_numpy(positions).to(DEV), torch.from_numpy(items).to(DEV), qw.to(DEV),
+                         kw.to(DEV), torch.from_numpy(inv).to(DEV), n_rot, eps, q_out, kc, vc,
+                         torch.from_numpy(table).to(DEV), page, n_pages, nh, nkv, hd, status)
+    with pytest.raises(o.KernelError, match="page"):
+        o.read_status(status)
+
+
+def test_kernels_refuse_sizes_they_do_not_take():
+    o = ops()
+    st = o.new_status(DEV)
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    zi = lambda *s: torch.zeros(*s, dtype=torch.int32, device=DEV)
+    with pytest.raises(o.KernelError, match="head size"):
+        o.paged_attention(z(1, 24), z(2, 4, 24), z(2, 4, 24), zi(1), zi(1), zi(1, 4), 4, 2, None, 1.0, z(1, 24), 1, 1, 24, st)
+    with pytest.raises(o.KernelError, match="head size"):
+        o.paged_attention(z(1, 512), z(2, 4, 512), z(2, 4, 512), zi(1), zi(1), zi(1, 4), 4, 2, None, 1.0, z(1, 512), 1, 1, 512, st)
+    with pytest.raises(o.KernelError, match="taps"):
+        o.gated_conv(z(1, 24), z(8, 17), None, z(1, 16, 8), zi(2), zi(1), zi(1), z(1, 8), 17, st)
+    with pytest.raises(o.KernelError):
+        o.rmsnorm(torch.zeros(2, 8), torch.zeros(8), 1e-5, torch.zeros(2, 8))      # CPU tensors: no CPU path
+
+
+# ---------------------------------------------------------------------------------------
+def test_greedy_pick_smallest_index_and_nan():
+    o = ops()
+    V = 70001
+    logits = torch.full((4, V), -1.0)
+    logits[0, 500] = 3.0; logits[0, 69999] = 3.0; logits[0, 123] = 3.0
+    logits[1, :] = float("nan"); logits[1, 77] = -5.0
+    logits[2, :] = float("nan")
+    logits[3, V - 1] = 9.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    o.sample_rows(logits.to(DEV), None, None, out)
+    assert out.tolist() == [123, 77, 0, V - 1]
+
+
+@pytest.mark.parametrize("V", [331, 65536])
+def test_temperature_sampling_is_the_inverse_cdf(V):
+    o = ops()
+    rng = np.random.default_rng(V)
+    n = 64
+    logits = (rng.standard_normal((n, V)) * 3).astype(np.float32)
+    temps = rng.choice([0.0, 0.5, 0.8, 1.3], size=n).astype(np.float32)
+    us = rng.random(n).astype(np.float32)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    o.sample_rows(torch.from_numpy(logits).to(DEV), torch.from_numpy(temps).to(DEV), torch.from_numpy(us).to(DEV), out)
+    got = out.tolist()
+    for r in range(n):
+        if temps[r] == 0:
+            assert got[r] == int(np.argmax(logits[r]))
+            continue
+        p = np.exp((logits[r].astype(np.float64) - logits[r].max()) / temps[r])
+        cdf = np.cumsum(p) / p.sum()
+        want = int(np.searchsorted(cdf, us[r], side="right"))
+        if got[r] != want:
+            # only a target that sits within rounding of a boundary may fall either side
+            edge = min(abs(cdf[min(got[r], want)] - us[r]), abs(cdf[max(got[r], want) - 1] - us[r]))
+            assert abs(got[r] - want) == 1 and edge < 1e-5, (r, got[r], want)
+    # the picks follow the distribution: a row sampled many times
+    row = np.array([0.0, 1.0, 2.0, -1.0] + [-30.0] * (V - 4), dtype=np.float32)
+    m = 4000
+    us = ((np.arange(m) + 0.5) / m).astype(np.float32)
+    out = torch.empty(m, dtype=torch.int32, device=DEV)
+    o.sample_rows(torch.from_numpy(np.tile(row, (m, 1))).to(DEV), torch.full((m,), 1.0, device=DEV),
+                  torch.from_numpy(us).to(DEV), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=4)[:4] / m
+    p = np.exp(row[:4].astype(np.float64)); p /= np.exp(row.astype(np.float64)).sum()
+    assert np.abs(freq - p).max() < 2e-3

@@ -1,0 +1,97 @@
+"""Replay families on the GPU, in 32-bit and in bfloat16, against the plain implementation:
+each request whole; most of it in one step and the last 32 tokens one by one; portions of
+changing size down to two tokens; and mixed, up to four live requests with so few pages
+that they are used again."""
+import numpy as np
+import pytest
+
+from tests import traces
+from tests.gpu_helpers import check_trace, make_requests, model_dir
+from tests.tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+PAGE = {"A": 16, "B": 4, "C": 8}
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51, 80], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58]}
+
+
+def engine_for(name, dtype, steps, parallel=4):
+    from imparo_b200.engine import Engine
+    page = PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, 64)
+    return Engine(model_dir(name), dtype=dtype, ctx=max_tokens, parallel=parallel, page_size=page,
+                  num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_family(name, dtype, family):
+    reqs = make_requests(name, LENGTHS[name])
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[family](reqs)
+    eng = engine_for(name, dtype, steps)
+    check_trace(eng, steps, name, reqs, dtype)
+    if family == "mixed":
+        # the pool is smaller than everything the trace ever held: pages were used again
+        total = sum(traces.round_up(len(t), 64) for t in reqs.values())
+        assert traces.max_live_tokens(steps) < total
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cutting_does_not_change_logits_beyond_rounding(dtype):
+    """The same positions through four ways of cutting: 32-bit results agree to ~1e-6."""
+    from tests.gpu_helpers import run_trace
+    name = "B"
+    reqs = make_requests(name, [61, 47, 75], seed=5)
+    outs = []
+    for build in (traces.whole, traces.tail_one_by_one, traces.portions, lambda r: traces.mixed(r, seed=9)):
+        steps = build(reqs)
+        got = run_trace(engine_for(name, dtype, steps), steps)
+        # gather by (request, position)
+        by_pos, at = {}, {}
+        for s in steps:
+            r = 0
+            for e in s["entries"]:
+                start = at.get(e["id"], 0)
+                for w in e["want"]:
+                    by_pos[(e["id"], start + w)] = got[s["step"]][r]
+                    r += 1
+                at[e["id"]] = start + len(e["tokens"])
+        outs.append(by_pos)
+    keys = set(outs[1]) & set(outs[0])
+    assert len(keys) > 90
+    tol = 5e-6 if dtype == "float32" else 3e-2
+    for k in keys:
+        for o in outs[1:]:
+            if k in o:
+                assert np.abs(o[k] - outs[0][k]).max() <= tol, k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype):
+    name = "A"
+    reqs = make_requests(name, [400], seed=8)
+    steps = traces.tail_one_by_one(reqs, tail=390)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(name, dtype):
+    """Positions 0, 1, 2, ...: one-token prompts, a fresh state slot, the first page."""
+    reqs = make_requests(name, [1, 2, 3, 6], seed=11)
+    for build in (traces.whole, lambda r: traces.tail_one_by_one(r, tail=8)):
+        steps = build(reqs)
+        check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+def test_state_slots_and_pages_start_clean_when_used_again():
+    """A request that takes over a slot and pages another one used sees none of it."""
+    name = "B"
+    a = make_requests(name, [50], seed=20)
+    b = {"other": make_requests(name, [37], seed=21)["r0"]}
+    steps = traces.whole(a) + [dict(s, step=s["step"] + 1) for s in traces.portions(b, sizes=(1, 2, 3))]
+    reqs = dict(a, **b)
+    eng = engine_for(name, "float32", steps, parallel=1)       # one slot: it must be reused
+    check_trace(eng, steps, name, reqs, "float32")

@@ -1,0 +1,171 @@
+"""The scheduler's decisions: admission, portions under a token budget, decode rows first,
+finishing, and what happens when pages run out (the newest running request is preempted
+and recomputed; a request that cannot fit even alone fails)."""
+import pytest
+
+from imparo_b200.cache import CacheManager
+from imparo_b200.engine.scheduler import Scheduler
+from imparo_b200.parts.spec import PagedKV, SlotState
+
+SPECS = [(0, (PagedKV(2, 16),)), (1, (SlotState((2, 8)),))]
+
+
+def make(pages=64, page=4, slots=4, budget=8, ctx=256):
+    cm = CacheManager(SPECS, page, pages, slots, device=None)
+    return cm, Scheduler(cm, budget, slots, ctx)
+
+
+def run_step(s, plan, eos=()):
+    s.step_done(True)
+    finished = []
+    for e in plan:
+        if e.want and s.on_token(e.request, e.request in eos):
+            finished.append(e.request)
+    return finished
+
+
+def test_prompt_is_cut_under_the_budget_and_first_token_comes_from_the_last_portion():
+    cm, s = make(budget=8)
+    a = s.submit(19, 3)
+    plans = []
+    while s.has_work():
+        p = s.plan()
+        plans.append([(e.request, e.start, e.count, e.want) for e in p])
+        run_step(s, p)
+    assert plans == [[(a, 0, 8, False)], [(a, 8, 8, False)], [(a, 16, 3, True)], [(a, 19, 1, True)], [(a, 20, 1, True)]]
+    # 3 new tokens cost 2 decode steps (imparo-server/src/main.rs:1786-1790)
+    assert cm.n_requests() == 0 and cm.free_pages(0) == 64 and cm.free_slots() == 4
+    cm.check()
+
+
+def test_decode_rows_come_first_and_share_the_step_with_portions():
+    cm, s = make(budget=8)
+    a = s.submit(3, 10)
+    run_step(s, s.plan())                       # a: whole prompt, first token
+    b = s.submit(20, 2)
+    p = s.plan()
+    assert [(e.request, e.start, e.count, e.want) for e in p] == [(a, 3, 1, True), (b, 0, 7, False)]
+    run_step(s, p)
+    p = s.plan()
+    assert [(e.request, e.count) for e in p] == [(a, 1), (b, 7)]
+    run_step(s, p)
+    p = s.plan()
+    assert [(e.request, e.start, e.count, e.want) for e in p] == [(a, 5, 1, True), (b, 14, 6, True)]
+    cm.check()
+
+
+def test_several_prompts_in_flight_fifo():
+    cm, s = make(budget=10)
+    a, b, c = s.submit(4, 2), s.submit(4, 2), s.submit(30, 2)
+    p = s.plan()
+    assert [(e.request, e.count, e.want) for e in p] == [(a, 4, True), (b, 4, True), (c, 2, False)]
+
+
+def test_finish_by_eos_and_by_length_frees_everything():
+    cm, s = make()
+    a, b = s.submit(5, 4), s.submit(6, 50)
+    p = s.plan(); run_step(s, p)
+    assert s.n_running == 2
+    p = s.plan(); fin = run_step(s, p, eos={b})
+    assert fin == [b]
+    for _ in range(2):
+        p = s.plan(); fin = run_step(s, p)
+    assert fin == [a] and not s.has_work()
+    assert cm.free_pages(0) == 64 and cm.free_slots() == 4
+    cm.check()
+
+
+def test_admission_waits_for_a_slot_and_for_pages():
+    cm, s = make(pages=6, slots=2, budget=16)
+    a, b, c = s.submit(8, 8), s.submit(8, 8), s.submit(2, 2)
+    p = s.plan()
+    assert [e.request for e in p] == [a, b]       # no third slot
+    run_step(s, p)
+    assert s.n_waiting == 1
+    # a and b now hold 2 pages each; each needs a third page at position 8
+    p = s.plan()
+    assert [e.request for e in p] == [a, b] and cm.free_pages(0) == 0
+    run_step(s, p)
+    cm.check()
+
+
+def test_pages_run_out_newest_is_preempted_and_recomputed():
+    cm, s = make(pages=6, slots=3, budget=16, page=4)
+    a = s.submit(8, 20)
+    run_step(s, s.plan())                         # a holds 2 pages, 9 tokens known
+    b = s.submit(7, 20)
+    p = s.plan()                                  # a decodes (3rd page); b: 2 pages + 1 spare <= 3 free
+    assert [(e.request, e.count) for e in p] == [(a, 1), (b, 7)]
+    run_step(s, p)
+    assert cm.free_pages(0) == 1
+    for _ in range(10):                           # b takes the last page at position 8; a needs one at 12
+        p = s.plan()
+        if s.n_preemptions:
+            break
+        assert [e.request for e in p] == [a, b]
+        run_step(s, p)
+    # a (older) could not get its page: the NEWEST running request, b, gave up what it held
+    assert s.n_preemptions == 1 and s.take_preempted() == [b]
+    assert [e.request for e in p] == [a] and cm.cached(a) == 12
+    assert s.n_running == 1 and s.n_waiting == 1
+    assert s.known_tokens(b) > 7                  # prompt plus what it generated so far
+    run_step(s, p)
+    cm.check()
+    # a runs on alone; b comes back once pages are free and recomputes from position 0
+    seen_b_restart = False
+    for _ in range(200):
+        if not s.has_work():
+            break
+        p = s.plan()
+        for e in p:
+            if e.request == b and e.start == 0:
+                seen_b_restart = True
+        run_step(s, p)
+        cm.check()
+    assert seen_b_restart and not s.has_work()
+    assert cm.free_pages(0) == 6 and cm.free_slots() == 3
+
+
+def test_a_request_that_cannot_fit_alone_fails_and_frees():
+    cm, s = make(pages=3, slots=2, budget=8, page=4)
+    a = s.submit(30, 4)                           # needs 8 pages, the pool has 3
+    failed = []
+    for _ in range(20):
+        if not s.has_work():
+            break
+        p = s.plan()
+        failed += s.take_failed()
+        if p:
+            run_step(s, p)
+    assert failed == [a] and not s.has_work()
+    assert cm.free_pages(0) == 3 and cm.free_slots() == 2
+    cm.check()
+
+
+def test_failed_step_abandons_its_requests():
+    cm, s = make()
+    a, b = s.submit(5, 4), s.submit(6, 4)
+    p = s.plan()
+    s.step_done(False)                            # imparo-server/src/sched.rs:652-660
+    assert sorted(s.take_failed()) == [a, b] and not s.has_work()
+    assert cm.free_pages(0) == 64 and cm.free_slots() == 4
+    cm.check()
+
+
+def test_refused_requests():
+    cm, s = make(ctx=16)
+    with pytest.raises(ValueError):
+        s.submit(0, 4)
+    with pytest.raises(ValueError):
+        s.submit(17, 4)
+    with pytest.raises(ValueError):
+        s.submit(4, 0)
+
+
+def test_context_limit_ends_a_request():
+    cm, s = make(ctx=12, budget=16)
+    a = s.submit(10, 100)
+    n = 0
+    while s.has_work():
+        run_step(s, s.plan()); n += 1
+    assert n == 2 and cm.free_pages(0) == 64      # 10 -> 11 -> 12 known: stop
