@@ -1,0 +1,277 @@
+#!/usr/bin/env python3
+"""Headline measurement: LFM2-1.2B layer sizes, random bfloat16 weights, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests, each with a 2,048-token prompt in
+the cache (context length 4,096, pages of 16 tokens).  `value` is decoded tokens per
+second over exactly K steps, timed on the device with CUDA events after W warm-up steps;
+the step's inputs are larger than L2 (2.3 GB of weights are read every step), so no
+flush is needed between iterations.  `e2e` is the same metric through Engine.generate:
+host token lists in, host token lists out, with the per-step host-to-device copy of the
+batch descriptor and device-to-host copy of the sampled ids inside the timed region.
+One JSON line is printed.  For --gpus N > 1 one line says that this engine is a
+one-GPU engine and the exit code is 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LFM2_1_2B = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
+    "layer_types": ["conv", "conv", "full_attention", "conv", "conv", "full_attention", "conv", "conv",
+                    "full_attention", "conv", "full_attention", "conv", "full_attention", "conv", "full_attention", "conv"],
+    "num_attention_heads": 32, "num_key_value_heads": 8,
+    "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 128000,
+}
+PROMPT = 2048
+CTX = 4096
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+                "bf16_tflops_burst": float(d["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        return dict(FALLBACK_PEAKS, bf16_tflops_burst=FALLBACK_PEAKS["bf16_tflops"], source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(engine):
+    """Bytes a decode step must read for its weights, KV bytes per cached token, and the
+    flops of a prompt of T tokens, from the model's own parts."""
+    cfg = engine.config
+    H, F, V = cfg.hidden_size, cfg.ff_dim, cfg.vocab_size
+    nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    n_attn = sum(1 for e in engine.model.schedule if cfg.layer_types[e.layer] != "conv")
+    n_conv = len(engine.model.schedule) - n_attn
+    per_layer_ffn = 3 * H * F
+    conv = 3 * H * H + H * H
+    attn = (nh + 2 * nkv) * hd * H + H * nh * hd
+    matrix_params = len(engine.model.schedule) * per_layer_ffn + n_conv * conv + n_attn * attn
+    elt = 2 if engine.precision == "bfloat16" else 4
+    weight_bytes = (matrix_params + V * H) * elt          # every matrix once; the tied table is the head
+    kv_per_token = n_attn * 2 * nkv * hd * elt
+
+    def prefill_flops(T):
+        return 2.0 * T * matrix_params + 2.0 * V * H + n_attn * 4.0 * nh * hd * T * (T + 1) / 2
+    return weight_bytes, kv_per_token, prefill_flops, matrix_params + V * H
+
+
+def measure_decode(engine, batch, steps, warmup, rng, sampler=None):
+    """-> (ms per step, launches per step, h2d bytes per step, mean context) with `batch`
+    requests holding PROMPT tokens each."""
+    import torch
+    from imparo_b200.engine import StepItem
+    from imparo_b200.kernels import ops
+    ids = list(range(1000 * batch, 1000 * batch + batch))
+    V = engine.vocab_size
+    for r in ids:
+        engine.add_request(r)
+        engine.step([StepItem(r, rng.integers(0, V, PROMPT).tolist(), [PROMPT - 1])])
+    out_ids = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+    def one():
+        logits = engine.step_fn([StepItem(r, [int(t)], [0]) for r, t in zip(ids, rng.integers(0, V, batch))])
+        ops.sample_rows(logits, None, None, out_ids)
+    for _ in range(max(warmup, 3)):
+        one()
+    torch.cuda.synchronize()
+    before = dict(ops.COUNTS)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.COUNTS["own"] - before["own"]) / steps
+    library = (ops.COUNTS["library"] - before["library"]) / steps
+    ctx = PROMPT + max(warmup, 3) + steps / 2.0
+    engine.check_device_status()
+    for r in ids:
+        engine.end_request(r)
+    return ms, launches, library, ctx
+
+
+def measure_prefill(engine, reps, warmup, rng):
+    import torch
+    from imparo_b200.engine import StepItem
+    V = engine.vocab_size
+    times = []
+    for i in range(warmup + reps):
+        toks = rng.integers(0, V, PROMPT).tolist()
+        engine.add_request(77000 + i)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step_fn([StepItem(77000 + i, toks, [PROMPT - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.end_request(77000 + i)
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def measure_e2e(engine, batch, steps, warmup, rng):
+    """Decode tokens per second through Engine.generate: wall clock from the end of decode
+    step `warmup` to the end of decode step `warmup + steps`, host lists in and out."""
+    V = engine.vocab_size
+    prompts = [rng.integers(0, V, PROMPT).tolist() for _ in range(batch)]
+    stamps, h2d = [], []
+
+    def on_step(plan):
+        if all(e.count == 1 for e in plan) and len(plan) == batch:
+            stamps.append(time.perf_counter())
+    n_new = warmup + steps + 2 + 2 * batch      # requests start decoding up to ~batch steps apart
+    out = engine.generate(prompts, max_tokens=n_new, on_step=on_step, stop_token_ids=[])
+    assert all(len(o) == n_new for o in out) and len(stamps) > warmup + steps, (len(stamps), warmup + steps)
+    dt = stamps[warmup + steps] - stamps[warmup]
+    return batch * steps / dt, engine.step_fn.last_h2d_bytes
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "zeraix/imparo is a Rust workspace (no setup.py or pyproject.toml: "
+                          "pip reports 'not installable') and this image has no cargo/rustc, so it cannot be built or run here"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on ONE GPU; --gpus > 1 is not supported (nothing was measured)")
+        return 2
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    from imparo_b200.kernels import ops
+
+    cfg = dict(LFM2_1_2B)
+    if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
+        cfg["layer_types"] = cfg["layer_types"][:args.layers]
+        cfg["num_hidden_layers"] = args.layers
+    steps, warmup = args.steps, max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    max_batch = args.batch if args.skip_points else max(64, args.batch)
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=max_batch, page_size=PAGE,
+                    max_step_tokens=PROMPT, random_init={"norm_jitter": 0.0})
+    pk = peaks()
+    weight_bytes, kv_per_token, prefill_flops, n_params = model_numbers(engine)
+
+    with ClockSampler() as clocks:
+        ms, launches, library, ctx = measure_decode(engine, args.batch, steps, warmup, rng)
+    value = args.batch * 1000.0 / ms
+    step_bytes = weight_bytes + args.batch * ctx * kv_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    pre_ms = measure_prefill(engine, reps=5, warmup=3, rng=rng)
+    pre_flops = prefill_flops(PROMPT)
+    prefill = {"value": round(PROMPT * 1000.0 / pre_ms, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _, _ = measure_decode(engine, b, max(20, steps // 4), warmup, rng)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+
+    # h2d: the step's descriptor (tokens, positions, request index, row starts, slots, start
+    # positions, wanted rows, one block-table row per request), counted from the copied tensor
+    e2e_value, h2d = measure_e2e(engine, args.batch, steps, warmup, rng)
+
+    line = {
+        "metric": "LFM2-1.2B decode tok/s @ batch 8 (2,048-token prompts, ctx 4,096)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)",
+        "impl": "ours",
+        "config": {"model": "LFM2-1.2B", "global_batch": args.batch, "seq_len": CTX, "prompt_len": PROMPT, "parallelism": "1gpu",
+                   "layers": cfg["num_hidden_layers"], "layers_of_config": LFM2_1_2B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": 32, "kv_heads": 8, "head_dim": 64, "ff_dim": engine.config.ff_dim,
+                   "vocab": cfg["vocab_size"], "conv_L_cache": 3, "page_size": PAGE, "params": n_params,
+                   "l2": "inputs larger than L2 (2.3 GB of weights read per step)", "cuda_graph": True},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(round(launches * steps)), "own_kernels_per_step": round(launches, 1),
+        "library_gemms_per_step": round(library, 1),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"], "bytes_per_step": int(step_bytes)},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -42,7 +42,12 @@ def _round_up(x: int, m: int) -> int:
 
 
 class StepFunction:
-    def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_items: int):
+    def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_items: int,
+                 use_graphs: bool = True):
+        self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", False)
+        self.last_h2d_bytes = 0
+        self._graphs = {}        # key -> [times seen, graph, logits, (own, library) launches, generation]
+        self.graph_replays = 0
         self.model = model
         self.cache = cache
         self.rt = model.rt
@@ -64,6 +69,7 @@ class StepFunction:
             self._ring = [[torch.empty(cap, dtype=torch.int32, pin_memory=True), None] for _ in range(4)]
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._cap = cap
+            self._graphs.clear()     # captured graphs hold the old buffer's address
         self._turn = (self._turn + 1) % len(self._ring)
         slot = self._ring[self._turn]
         if slot[1] is not None:
@@ -112,6 +118,7 @@ class StepFunction:
             for i, it in enumerate(items):
                 cache.fill_table(it.request, g, tab[i])
         n_ints = int(offs[-1])
+        self.last_h2d_bytes = n_ints * 4
         self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -128,8 +135,49 @@ class StepFunction:
         b.max_tokens_per_item = max(len(it.tokens) for it in items)
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
-        b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy()}
+        b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),
+                  "key": (T, R, W, tuple(strides)), "h2d_bytes": n_ints * 4}
         return b
+
+    # -- decode-only steps replay a captured graph ------------------------------------------
+    def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        x = self.model.forward(batch, self._views)
+        return self.model.logits(x, batch.want_rows, batch.n_want) if batch.n_want else None
+
+    def _forward_graphed(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        """A step of single tokens only has the same launches whenever (requests, wanted
+        rows, table widths) repeat: the second time such a step comes it is captured, from
+        then on replayed.  The reference captures its one-token step the same way
+        (imparo-cuda/native/imparo_cuda.cu:7509-7660).  Index data (tokens, positions,
+        tables, wanted rows) is read from the descriptor buffer, whose address is fixed."""
+        ws = self.rt.workspace
+        key = batch.host["key"]
+        entry = self._graphs.get(key)
+        if entry is not None and entry[4] != ws.generation:
+            self._graphs.clear()
+            entry = None
+        if entry is None:
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = [1, None, None, None, ws.generation]
+            return self._forward(batch)
+        if entry[1] is None:
+            before = dict(ops.COUNTS)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                logits = self._forward(batch)
+            entry[1], entry[2] = g, logits
+            entry[3] = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
+            ops.COUNTS.update(before)          # capture launched nothing
+            if entry[4] != ws.generation:      # a buffer moved during the capture run
+                self._graphs.clear()
+                return self._forward(batch)
+        entry[0] += 1
+        entry[1].replay()
+        ops.COUNTS["own"] += entry[3][0]
+        ops.COUNTS["library"] += entry[3][1]
+        self.graph_replays += 1
+        return entry[2]
 
     # -- one step ---------------------------------------------------------------------------
     def check_items(self, items: Sequence[StepItem]) -> None:
@@ -178,8 +226,10 @@ class StepFunction:
                 idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)
                 for t in cache.state.values():
                     t.index_fill_(0, idx, 0.0)
-            x = self.model.forward(batch, self._views)
-            logits = self.model.logits(x, batch.want_rows, batch.n_want) if batch.n_want else None
+            if self.use_graphs and batch.decode_only and not fresh:
+                logits = self._forward_graphed(batch)
+            else:
+                logits = self._forward(batch)
         except Exception:
             if manage_cache:
                 for it in items:

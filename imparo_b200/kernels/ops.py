@@ -48,8 +48,13 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(rc: int, what: str) -> None:
+# Launch counts since import: "own" = this engine's CUDA kernels, "library" = cuBLAS products.
+COUNTS = {"own": 0, "library": 0}
+
+
+def _check(rc: int, what: str, kind: str = "own") -> None:
     if rc == 0:
+        COUNTS[kind] += 1
         return
     reasons = {-1: "unsupported dtype code or missing library handle", -2: "bad accumulate/grid",
                -3: "head size must be a multiple of 16 between 16 and 256",
@@ -148,7 +153,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
         _need(not accumulate or out.dtype == torch.float32, "linear: accumulate needs a float32 output")
         _gemm_lib_ready(x.device)
         _check(_lib.kernels().imparo_gemm_bf16_nt(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), N,
-                                                  int(accumulate), _stream()), "gemm_bf16_nt")
+                                                  int(accumulate), _stream()), "gemm_bf16_nt", "library")
     else:
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
 

@@ -56,7 +56,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
-        self.frozen = False
+        self.generation = 0      # bumped whenever a buffer moves: captured graphs of older generations are stale
 
     def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -65,10 +65,11 @@ class Workspace:
         key = f"{tag}:{dtype}"
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
-            if self.frozen:
-                raise RuntimeError(f"workspace buffer '{tag}' would grow while a captured graph holds its address")
+            if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"workspace buffer '{tag}' would grow during graph capture")
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def bytes(self) -> int:
@@ -78,6 +79,11 @@ class Workspace:
 class Part:
     """Base of every part.  params are the PartSpec's parameters; prefix is the tensor-name
     prefix of the layer (or "" for model-level parts)."""
+
+    # True when forward() takes everything that varies from step to step (tokens, positions,
+    # tables, slots) from the batch's DEVICE arrays, so a step of single tokens can be captured
+    # once and replayed.  A part that reads batch.host in forward() must set this to False.
+    graph_safe = True
 
     def __init__(self, params: dict, prefix: str, rt: Runtime):
         self.params = dict(params)

@@ -17,6 +17,7 @@ class PreNormResidualBlock(Part):
         self.ff_norm = make_part("norm", spec.feed_forward_norm, prefix, rt)
         self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt)
         self.parts = (self.mixer_norm, self.mixer, self.ff_norm, self.ff)
+        self.graph_safe = all(p.graph_safe for p in self.parts)
 
     def weight_specs(self):
         return [w for p in self.parts for w in p.weight_specs()]

@@ -20,6 +20,7 @@ class Model:
         self.final_norm = make_part("norm", spec.final_norm, "", rt)
         self.head = make_part("head", spec.head, "", rt)
         self.schedule = spec.schedule
+        self.graph_safe = all(p.graph_safe for p in self.parts())
         for i, e in enumerate(self.schedule):
             if e.cache_from is not None:
                 mine = self.layers[e.layer].cache_specs()

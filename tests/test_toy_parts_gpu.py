@@ -20,6 +20,7 @@ def register_toy():
     class RunningMeanMixer(Part):
         """out[t] = W * mean(x[0..t]) per request.  Its state: the running sum [H] and the
         count [1], one slot per request."""
+        graph_safe = False      # forward() reads batch.host: not for capture and replay
 
         def __init__(self, params, prefix, rt):
             super().__init__(params, prefix, rt)
