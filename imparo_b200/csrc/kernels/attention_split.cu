@@ -1,0 +1,270 @@
+// Split-key attention for single query tokens (decode rows): the keys of one request are
+// cut into fixed chunks, one CTA per (chunk, kv head, query token) computes an unnormalised
+// partial result for all query heads of the group at once (keys and values are read once
+// per group, not once per head), and a second kernel combines the chunks in order.
+//
+// The reference decodes the same way over its quantised cache: key ranges -> partials ->
+// a deterministic combine (imparo-cuda/native/sm80/attention_decode_vec_d64_q8.cuh:270,475).
+// Scores, softmax and the combine are 32-bit; the split is a function of the chunk size
+// alone, which the launcher derives from the table width, never from arrival order.
+//
+// Scratch: part_acc [tokens, heads, splits, head] and part_ml [tokens, heads, splits, 2]
+// (float32), owned by the caller.
+#include "common.cuh"
+
+namespace imparo {
+
+constexpr int SPLIT_WARPS = 4;
+constexpr int SPLIT_MAX_HEAD = 256;
+
+template <typename T> struct KVec;
+template <> struct KVec<float> { using type = float4; static constexpr int N = 4; };
+template <> struct KVec<__nv_bfloat16> { using type = uint4; static constexpr int N = 8; };
+
+template <int G>
+__device__ __forceinline__ void dot_group(const float4& k, const float* q, int hd, int off, float (&s)[G]) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float4 qv = *reinterpret_cast<const float4*>(q + g * hd + off);
+        s[g] += k.x * qv.x + k.y * qv.y + k.z * qv.z + k.w * qv.w;
+    }
+}
+template <int G>
+__device__ __forceinline__ void dot_group(const uint4& k, const float* q, int hd, int off, float (&s)[G]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&k);
+    const float2 k0 = __bfloat1622float2(p[0]), k1 = __bfloat1622float2(p[1]);
+    const float2 k2 = __bfloat1622float2(p[2]), k3 = __bfloat1622float2(p[3]);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float4 qa = *reinterpret_cast<const float4*>(q + g * hd + off);
+        const float4 qb = *reinterpret_cast<const float4*>(q + g * hd + off + 4);
+        s[g] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
+    }
+}
+
+// dynamic shared memory layout (floats):
+//   qs   [G][hd]                 the group's queries
+//   ps   [WARPS][G][32]          a warp's probabilities for its 32 keys
+//   rows [WARPS][32] (int)       their cache rows
+//   wm, wl [WARPS][G]            per-warp running max / sum
+//   wacc [WARPS][G][hd]          per-warp accumulators
+template <typename T, int G>
+__global__ void __launch_bounds__(SPLIT_WARPS * 32)
+attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                          const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                          const int* __restrict__ table, int max_blocks, int page_size, int n_pages, int window,
+                          float scale, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                          int nh, int nkv, int hd, int chunk, int n_splits, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* qs = smem;
+    float* ps = qs + G * hd;
+    int* rows = reinterpret_cast<int*>(ps + SPLIT_WARPS * G * 32);
+    float* wm = reinterpret_cast<float*>(rows + SPLIT_WARPS * 32);
+    float* wl = wm + SPLIT_WARPS * G;
+    float* wacc = wl + SPLIT_WARPS * G;
+
+    const int pos = positions[t];
+    const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int begin = max(lo, split * chunk), end = min(pos + 1, (split + 1) * chunk);
+    const int h0 = kvh * G;
+    const size_t part_base = ((size_t)t * nh + h0) * n_splits + split;     // + g * n_splits
+    if (begin >= end) {
+        if (threadIdx.x < G) {
+            part_ml[(part_base + (size_t)threadIdx.x * n_splits) * 2] = -INFINITY;
+            part_ml[(part_base + (size_t)threadIdx.x * n_splits) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < G * hd; i += blockDim.x) qs[i] = to_f32(q[((size_t)t * nh + h0) * hd + i]);
+    __syncthreads();
+
+    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
+    const size_t kvw = (size_t)nkv * hd;
+    constexpr int PER = SPLIT_MAX_HEAD / 32;
+    float acc[G][PER];
+    float m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[g][i] = 0.f;
+    }
+    using V = typename KVec<T>::type;
+    constexpr int VN = KVec<T>::N;
+    float* my_ps = ps + warp * G * 32;
+    int* my_rows = rows + warp * 32;
+
+    for (int base = begin + warp * 32; base < end; base += SPLIT_WARPS * 32) {
+        const int j = base + lane;
+        int rowi = -1;
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+        if (j < end) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? tab[blk] : -1;
+            if (page < 0 || page >= n_pages) {
+                report(status, IMPARO_ST_PAGE_RANGE, 5, t, page);
+            } else {
+                rowi = page * page_size + (j % page_size);
+                const V* kp = reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
+                for (int c = 0; c < hd / VN; ++c) dot_group<G>(kp[c], qs, hd, c * VN, s);
+            }
+        }
+        my_rows[lane] = rowi;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float sg = rowi >= 0 ? s[g] * scale : -INFINITY;
+            const float m_new = fmaxf(m[g], warp_max(sg));
+            float p = 0.f, corr = 1.f;
+            if (m_new != -INFINITY) {
+                p = rowi >= 0 ? expf(sg - m_new) : 0.f;
+                corr = m[g] == -INFINITY ? 0.f : expf(m[g] - m_new);
+            }
+            l[g] = l[g] * corr + warp_sum(p);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) acc[g][i] *= corr;
+            m[g] = m_new;
+            my_ps[g * 32 + lane] = p;
+        }
+        __syncwarp();
+        const int cnt = min(32, end - base);
+        for (int jj = 0; jj < cnt; ++jj) {
+            const int rj = my_rows[jj];
+            if (rj < 0) continue;
+            const T* vp = v_cache + (size_t)rj * kvw + (size_t)kvh * hd;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) {
+                    const float v = to_f32(vp[d]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc[g][i] += my_ps[g * 32 + jj] * v;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    // fold the warps, in warp order
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) wacc[((size_t)warp * G + g) * hd + d] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+        const int g = idx / hd, d = idx % hd;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < SPLIT_WARPS; ++w) M = fmaxf(M, wm[w * G + g]);
+        float a = 0.f, L = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < SPLIT_WARPS; ++w) {
+                const float mw = wm[w * G + g];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - M);
+                a += wacc[((size_t)w * G + g) * hd + d] * f;
+                L += wl[w * G + g] * f;
+            }
+        }
+        const size_t pb = part_base + (size_t)g * n_splits;
+        part_acc[pb * hd + d] = a;
+        if (d == 0) { part_ml[pb * 2] = M; part_ml[pb * 2 + 1] = L; }
+    }
+}
+
+// One block per (token, head): fold the splits in order.
+template <typename T>
+__global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                          T* __restrict__ out, int hd, int n_splits) {
+    const size_t th = blockIdx.x;                         // token * nh + head
+    const float* ml = part_ml + th * n_splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float a = 0.f, L = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ls = ml[2 * s + 1];
+            if (ls > 0.f) {
+                const float f = expf(ml[2 * s] - M);
+                a += part_acc[(th * n_splits + s) * hd + d] * f;
+                L += ls * f;
+            }
+        }
+        out[th * hd + d] = from_f32<T>(L > 0.f ? a / L : 0.f);
+    }
+}
+
+template <typename T, int G>
+int launch_partial(const void* q, const void* k_cache, const void* v_cache, const int* positions, const int* item_of_token,
+                   const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
+                   float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                   int* status, cudaStream_t stream) {
+    const size_t smem = sizeof(float) * ((size_t)G * hd + SPLIT_WARPS * G * 32 + SPLIT_WARPS * 32 + 2 * SPLIT_WARPS * G +
+                                         (size_t)SPLIT_WARPS * G * hd);
+    auto kern = attn_split_partial_kernel<T, G>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(n_splits, nkv, n_tok);
+    kern<<<grid, SPLIT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, positions, item_of_token,
+                                                   table, max_blocks, page_size, n_pages, window, scale, part_acc, part_ml,
+                                                   nh, nkv, hd, chunk, n_splits, status);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+template <typename T>
+int dispatch_group(int G, const void* q, const void* k_cache, const void* v_cache, const int* positions, const int* item_of_token,
+                   const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
+                   float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                   int* status, cudaStream_t stream) {
+#define IMPARO_G(g) case g: return launch_partial<T, g>(q, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, \
+        n_pages, window, scale, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, status, stream)
+    switch (G) { IMPARO_G(1); IMPARO_G(2); IMPARO_G(3); IMPARO_G(4); IMPARO_G(5); IMPARO_G(6); IMPARO_G(7); IMPARO_G(8); }
+#undef IMPARO_G
+    return -8;
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+// Returns -8 when the group size (heads / kv heads) is above 8: the caller then uses the
+// general kernel.  n_tok must not exceed 65535 (grid z).
+extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                            const int* positions, const int* item_of_token,
+                                            const int* table, int max_blocks, int page_size, int n_pages,
+                                            int window, float scale, void* out, float* part_acc, float* part_ml,
+                                            int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                                            int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 16 || hd > SPLIT_MAX_HEAD || hd % 16 != 0) return -3;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    if (n_tok > 65535 || nkv > 65535 || chunk < 32 || n_splits < 1) return -2;
+    const int G = nh / nkv;
+    int rc;
+    if (dtype == IMPARO_DT_F32)
+        rc = dispatch_group<float>(G, q, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages,
+                                   window, scale, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, status, stream);
+    else if (dtype == IMPARO_DT_BF16)
+        rc = dispatch_group<__nv_bfloat16>(G, q, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size,
+                                           n_pages, window, scale, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits,
+                                           status, stream);
+    else return -1;
+    if (rc != 0) return rc;
+    const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    if (dtype == IMPARO_DT_F32)
+        attn_split_combine_kernel<float><<<n_tok * nh, threads, 0, stream>>>(part_acc, part_ml, (float*)out, hd, n_splits);
+    else
+        attn_split_combine_kernel<__nv_bfloat16><<<n_tok * nh, threads, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

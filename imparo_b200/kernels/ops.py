@@ -197,6 +197,41 @@ def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_s
         _ptr(status), _stream()), "paged_attention")
 
 
+def split_plan(n_tok: int, nkv: int, upper_context: int):
+    """(chunk, n_splits) for the split-key attention kernel: the largest chunk of 512, 256, 128
+    or 64 keys that still gives about two CTAs per SM; a function of the launch's shape only."""
+    chunk = 64
+    for c in (512, 256, 128):
+        if n_tok * nkv * -(-upper_context // c) >= 296:
+            chunk = c
+            break
+    return chunk, max(1, -(-upper_context // chunk))
+
+
+def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
+                          out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status) -> bool:
+    """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
+    combine).  Returns False, having launched nothing, when the group size is above 8."""
+    if nh // nkv > 8:
+        return False
+    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
+    T = q.shape[0]
+    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "paged_attention_split: q/out shapes")
+    _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _need(part_acc.dtype == torch.float32 and part_acc.numel() >= T * nh * n_splits * hd
+          and part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * n_splits * 2, "split scratch too small")
+    _need(T <= 65535, "paged_attention_split: at most 65535 query tokens per launch")
+    rc = _lib.kernels().imparo_paged_attention_split(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
+        T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
+    _check(rc, "paged_attention_split")
+    COUNTS["own"] += 1          # partial + combine
+    return True
+
+
 def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, taps, status) -> None:
     _cuda(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, status)
     T, width = y.shape

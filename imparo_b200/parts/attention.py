@@ -78,6 +78,16 @@ class AttentionMixer(Part):
         ops.qk_norm_rope_store(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq, n_rot,
                                self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
         out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype)
-        ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
-                            self.window, self.scale, out, nh, self.nkv, hd, rt.status)
+        done = False
+        if nh // self.nkv <= 8 and T <= 65535:
+            # keys cut into chunks; the cut depends on the launch's shape (tokens, table width) only
+            chunk, n_splits = ops.split_plan(T, self.nkv, table.shape[1] * kv.page_size)
+            part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32)
+            part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32)
+            done = ops.paged_attention_split(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size,
+                                             kv.n_pages, self.window, self.scale, out, part_acc, part_ml, chunk,
+                                             n_splits, nh, self.nkv, hd, rt.status)
+        if not done:
+            ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
+                                self.window, self.scale, out, nh, self.nkv, hd, rt.status)
         ops.linear(out, self.w_o, residual, accumulate=True)

@@ -218,10 +218,33 @@ def attention_reference(q, k, v, pos, nh, nkv, hd, scale, window):
     return out.reshape(-1)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256)])
+def run_attention(kind, q, kc, vc, positions, items, table, page, n_pages, window, scale, out, nh, nkv, hd, status,
+                  chunk=None):
+    """kind: "general" (one warp per token and head) or "split" (key chunks + ordered combine)."""
+    o = ops()
+    if kind == "general":
+        o.paged_attention(q, kc, vc, positions, items, table, page, n_pages, window, scale, out, nh, nkv, hd, status)
+        return
+    T = q.shape[0]
+    upper = table.shape[1] * page
+    if chunk is None:
+        chunk, n_splits = o.split_plan(T, nkv, upper)
+    else:
+        n_splits = -(-upper // chunk)
+    part_acc = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
+    assert o.paged_attention_split(q, kc, vc, positions, items, table, page, n_pages, window, scale, out, part_acc, part_ml,
+                                   chunk, n_splits, nh, nkv, hd, status)
+
+
+KINDS = [("general", None), ("split", None), ("split", 64), ("split", 512)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256), (8, 1, 64)])
 @pytest.mark.parametrize("page,window", [(1, None), (4, None), (16, 13), (64, None), (8, 40)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_paged_attention(nh, nkv, hd, page, window, dtype):
+@pytest.mark.parametrize("kind,chunk", KINDS)
+def test_paged_attention(nh, nkv, hd, page, window, dtype, kind, chunk):
     o = ops()
     rng = np.random.default_rng(nh * 1000 + hd + page)
     lens = [70, 1, 33, 129]
@@ -233,10 +256,10 @@ def test_paged_attention(nh, nkv, hd, page, window, dtype):
     out = torch.empty(len(rows), nh * hd, dtype=dtype, device=DEV)
     status = o.new_status(DEV)
     scale = 1 / math.sqrt(hd)
-    o.paged_attention(q.to(DEV), kc.to(DEV), vc.to(DEV),
-                      torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
-                      torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV),
-                      torch.from_numpy(table).to(DEV), page, n_pages, window, scale, out, nh, nkv, hd, status)
+    run_attention(kind, q.to(DEV), kc.to(DEV), vc.to(DEV),
+                  torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV),
+                  torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV),
+                  torch.from_numpy(table).to(DEV), page, n_pages, window, scale, out, nh, nkv, hd, status, chunk)
     o.read_status(status)
     tol = 3e-6 if dtype == torch.float32 else 1e-2
     for i, (r, p) in enumerate(rows):
@@ -247,8 +270,10 @@ def test_paged_attention(nh, nkv, hd, page, window, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("far,window", [(3, None), (511, None), (512, None), (0, None), (700, 200), (701, 200), (899, 200)])
-def test_one_far_key_stands_out(dtype, far, window):
+@pytest.mark.parametrize("far,window", [(3, None), (511, None), (512, None), (0, None), (700, 200), (701, 200), (899, 200),
+                                        (63, None), (64, None), (127, None), (128, None)])
+@pytest.mark.parametrize("kind,chunk", KINDS)
+def test_one_far_key_stands_out(dtype, far, window, kind, chunk):
     """Among 900 keys one is scaled so that its score dominates: the output must be that
     key's value (or must NOT be, when a window has passed it).  Random weights would hide
     a kernel that drops a far key, a page edge or a window edge."""
@@ -266,9 +291,9 @@ def test_one_far_key_stands_out(dtype, far, window):
     kc[table[0, far // page], far % page] = ks[0][far].to(dtype)
     out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
     status = o.new_status(DEV)
-    o.paged_attention(q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV),
-                      torch.zeros(1, dtype=torch.int32, device=DEV), torch.from_numpy(table).to(DEV), page, n_pages,
-                      window, 1 / math.sqrt(hd), out, nh, nkv, hd, status)
+    run_attention(kind, q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                  torch.zeros(1, dtype=torch.int32, device=DEV), torch.from_numpy(table).to(DEV), page, n_pages,
+                  window, 1 / math.sqrt(hd), out, nh, nkv, hd, status, chunk)
     o.read_status(status)
     visible = window is None or far >= n - window
     for kvh in range(nkv):
