@@ -204,6 +204,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "zeraix/imparo is a Rust workspace (no setup.py or pyproject.toml: "
@@ -223,7 +224,7 @@ def main():
         cfg["num_hidden_layers"] = args.layers
     steps, warmup = args.steps, max(args.warmup, 3)
     rng = np.random.default_rng(0)
-    max_batch = args.batch if args.skip_points else max(64, args.batch)
+    max_batch = args.batch if (args.skip_points or args.only_decode) else max(64, args.batch)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=max_batch, page_size=PAGE,
                     max_step_tokens=PROMPT, random_init={"norm_jitter": 0.0})
     pk = peaks()
@@ -235,6 +236,10 @@ def main():
     step_bytes = weight_bytes + args.batch * ctx * kv_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
+    if args.only_decode:
+        print(json.dumps({"metric": "decode only", "batch": args.batch, "ms_per_step": round(ms, 4), "value": round(value, 1),
+                          "achieved_gbs": round(achieved, 1), "own_kernels_per_step": launches, "library_gemms_per_step": library}))
+        return 0
     pre_ms = measure_prefill(engine, reps=5, warmup=3, rng=rng)
     pre_flops = prefill_flops(PROMPT)
     prefill = {"value": round(PROMPT * 1000.0 / pre_ms, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),

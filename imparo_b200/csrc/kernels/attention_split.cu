@@ -42,12 +42,19 @@ __device__ __forceinline__ void dot_group(const uint4& k, const float* q, int hd
     }
 }
 
+__device__ __forceinline__ void unpack(const float4& v, float* o) { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+__device__ __forceinline__ void unpack(const uint4& v, float* o) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(p[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+
 // dynamic shared memory layout (floats):
 //   qs   [G][hd]                 the group's queries
 //   ps   [WARPS][G][32]          a warp's probabilities for its 32 keys
 //   rows [WARPS][32] (int)       their cache rows
 //   wm, wl [WARPS][G]            per-warp running max / sum
-//   wacc [WARPS][G][hd]          per-warp accumulators
+//   wacc [WARPS][KPI][G][hd]     per-warp, per-lane-group accumulators (KPI = keys per load instruction)
 template <typename T, int G>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -82,17 +89,25 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
 
     const int* tab = table + (size_t)item_of_token[t] * max_blocks;
     const size_t kvw = (size_t)nkv * hd;
-    constexpr int PER = SPLIT_MAX_HEAD / 32;
-    float acc[G][PER];
+    using V = typename KVec<T>::type;
+    constexpr int VN = KVec<T>::N;
+    // Values: a row of hd elements is read by LPR lanes with one vector each (VPL vectors when
+    // the row has more than 32 vectors), so one load instruction of the warp covers KPI keys.
+    const int vecs = hd / VN;
+    const int LPR = vecs < 32 ? vecs : 32;            // lanes per row
+    const int VPL = vecs / LPR;                       // vectors per lane (1, or 2 for float32 head 256)
+    const int KPI = 32 / LPR;                         // keys per instruction
+    const int grp = lane / LPR, lig = lane % LPR;     // lane group = which key, lane in group = which vector
+    const bool pv_lane = grp < KPI;
+    constexpr int ACC = 8;                            // VN * VPL <= 8
+    float acc[G][ACC];
     float m[G], l[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) acc[g][i] = 0.f;
+        for (int i = 0; i < ACC; ++i) acc[g][i] = 0.f;
     }
-    using V = typename KVec<T>::type;
-    constexpr int VN = KVec<T>::N;
     float* my_ps = ps + warp * G * 32;
     int* my_rows = rows + warp * 32;
 
@@ -110,7 +125,7 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
             } else {
                 rowi = page * page_size + (j % page_size);
                 const V* kp = reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
-                for (int c = 0; c < hd / VN; ++c) dot_group<G>(kp[c], qs, hd, c * VN, s);
+                for (int c = 0; c < vecs; ++c) dot_group<G>(kp[c], qs, hd, c * VN, s);
             }
         }
         my_rows[lane] = rowi;
@@ -125,36 +140,47 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
             }
             l[g] = l[g] * corr + warp_sum(p);
 #pragma unroll
-            for (int i = 0; i < PER; ++i) acc[g][i] *= corr;
+            for (int i = 0; i < ACC; ++i) acc[g][i] *= corr;
             m[g] = m_new;
             my_ps[g * 32 + lane] = p;
         }
         __syncwarp();
         const int cnt = min(32, end - base);
-        for (int jj = 0; jj < cnt; ++jj) {
-            const int rj = my_rows[jj];
-            if (rj < 0) continue;
-            const T* vp = v_cache + (size_t)rj * kvw + (size_t)kvh * hd;
+        // all loads of a round are independent of the arithmetic: the compiler keeps several
+        // rounds in flight
+#pragma unroll 4
+        for (int r = 0; r * KPI < cnt; ++r) {
+            const int jj = r * KPI + grp;
+            const bool live = pv_lane && jj < cnt;
+            const int rj = live ? my_rows[jj] : -1;
+            // branch-free: a dead lane reads row 0 (always mapped memory) with probability 0
+            const V* vp = reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
+            float v[ACC];
+            unpack(vp[lig], v);
+            if (VPL > 1) unpack(vp[lig + LPR], v + VN); else { for (int i = VN; i < ACC; ++i) v[i] = 0.f; }
+            if (rj < 0) {                 // whatever row 0 holds must not reach the sum (0 * inf)
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int d = lane + 32 * i;
-                if (d < hd) {
-                    const float v = to_f32(vp[d]);
+                for (int i = 0; i < ACC; ++i) v[i] = 0.f;
+            }
 #pragma unroll
-                    for (int g = 0; g < G; ++g) acc[g][i] += my_ps[g * 32 + jj] * v;
-                }
+            for (int g = 0; g < G; ++g) {
+                const float pj = rj < 0 ? 0.f : my_ps[g * 32 + (jj & 31)];
+#pragma unroll
+                for (int i = 0; i < ACC; ++i) acc[g][i] += pj * v[i];
             }
         }
         __syncwarp();
     }
-    // fold the warps, in warp order
+    // fold the lane groups and the warps, in that order
+    float* my_acc = wacc + (size_t)(warp * KPI + (pv_lane ? grp : 0)) * G * hd;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
+        if (pv_lane) {
+            for (int u = 0; u < VPL; ++u)
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int d = lane + 32 * i;
-            if (d < hd) wacc[((size_t)warp * G + g) * hd + d] = acc[g][i];
+                for (int i = 0; i < ACC; ++i)
+                    if (i < VN) my_acc[(size_t)g * hd + (lig + u * LPR) * VN + i] = acc[g][u * VN + i];
         }
     }
     __syncthreads();
@@ -169,7 +195,9 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
             for (int w = 0; w < SPLIT_WARPS; ++w) {
                 const float mw = wm[w * G + g];
                 const float f = mw == -INFINITY ? 0.f : expf(mw - M);
-                a += wacc[((size_t)w * G + g) * hd + d] * f;
+                float aw = 0.f;
+                for (int k = 0; k < KPI; ++k) aw += wacc[((size_t)(w * KPI + k) * G + g) * hd + d];
+                a += aw * f;
                 L += wl[w * G + g] * f;
             }
         }
@@ -206,8 +234,9 @@ int launch_partial(const void* q, const void* k_cache, const void* v_cache, cons
                    const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
                    float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
                    int* status, cudaStream_t stream) {
+    const int vecs = hd / KVec<T>::N, lpr = vecs < 32 ? vecs : 32, kpi = 32 / lpr;
     const size_t smem = sizeof(float) * ((size_t)G * hd + SPLIT_WARPS * G * 32 + SPLIT_WARPS * 32 + 2 * SPLIT_WARPS * G +
-                                         (size_t)SPLIT_WARPS * G * hd);
+                                         (size_t)SPLIT_WARPS * kpi * G * hd);
     auto kern = attn_split_partial_kernel<T, G>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
