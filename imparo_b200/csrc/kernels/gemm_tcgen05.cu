@@ -1,0 +1,426 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//     out[T, N] (+)= X[T, K] * W[N, K]^T        (both operands K-major, 32-bit accumulation)
+//
+// The weight tile is the MMA's M operand (128 rows of W per CTA) and the tokens are its N
+// operand (16..256 tokens per CTA), so a decode step of a few tokens still fills the
+// 128-row instruction and the kernel's job is to stream W from HBM once: TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) fills a ring of shared-memory
+// stages, one elected thread issues tcgen05.mma with the accumulator in tensor memory,
+// tcgen05.commit hands stages back to the producer, and four warps read the accumulator with
+// tcgen05.ld and write out[token, n] (32 lanes = 32 consecutive n: coalesced).
+//
+// Few output tiles (N small) are cut along K as well (split-K): every split writes its
+// partial tile to scratch, the split that arrives last for a tile adds the partials in split
+// order and runs the epilogue, so the result does not depend on which split came last.
+//
+// Epilogues: store bfloat16 | store float32 | add into float32 (the residual stream) |
+// SwiGLU: the CTA's 128 rows are 64 gate rows and the 64 up rows of the same features,
+// h = silu(gate) * up is written as bfloat16 [T, F]  (imparo-cpu/src/ops.rs:73-78;
+// imparo-model/src/lfm2/workflow_cpu.rs:307-313).
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records
+// IMPARO_ST_WAIT_LIMIT in the status word, stops waiting, frees its tensor memory and
+// returns (the output of that launch is then garbage, and the host raises).
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace imparo {
+namespace tc {
+
+constexpr int BM = 128;            // rows of W per CTA (MMA M)
+constexpr int BK = 64;             // bfloat16 elements per stage along K: 128 bytes, one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr uint32_t WAIT_LIMIT = 4000000u;
+
+enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU_BF16 = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// false when the wait ran out
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups
+// are 1024 bytes apart (SBO); the leading-dimension offset is unused for this layout.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                    // LBO (ignored for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;          // SBO
+    d |= (uint64_t)1 << 46;                    // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+// kind::f16, A and B bfloat16 K-major, D float32
+__device__ __forceinline__ uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Params {
+    void* out;               // [T, ldo]
+    float* scratch;          // split-K partials [splits][T][N]
+    int* counters;           // one per (token tile, row tile); zero before the launch, zero after
+    int* status;
+    int T, N, K, ldo;        // N = rows of W (for SWIGLU: F, W has 2F rows)
+    int splits, kblocks;     // kblocks = ceil(K / BK)
+};
+
+// shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
+// buffer of the SwiGLU epilogue.  Tiles are 1024-byte aligned (128-byte swizzle).
+template <int NT, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    int* flags = reinterpret_cast<int*>(tmem_slot + 1);            // [0]: this CTA folds the splits
+    float* exch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // SwiGLU: [64][17], one 16-token chunk at a time
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
+    const int tile_t = blockIdx.y;                 // which NT tokens
+    const int split = blockIdx.z;
+    const int kb_begin = (int)(((long long)p.kblocks * split) / p.splits);
+    const int kb_end = (int)(((long long)p.kblocks * (split + 1)) / p.splits);
+    const int n_kb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        flags[0] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
+                    report(p.status, IMPARO_ST_WAIT_LIMIT, 10, i, s);
+                    break;
+                }
+                uint8_t* a = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                const int k0 = (kb_begin + i) * BK;
+                if (EPI == SWIGLU_BF16) {
+                    tma_load_2d(a, &map_w, &full[s], k0, tile_n * 64);                       // 64 gate rows
+                    tma_load_2d(a + A_BYTES / 2, &map_w, &full[s], k0, p.N + tile_n * 64);   // their 64 up rows
+                } else {
+                    tma_load_2d(a, &map_w, &full[s], k0, tile_n * BM);
+                }
+                tma_load_2d(a + A_BYTES, &map_x, &full[s], k0, tile_t * NT);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BM, NT);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
+                    report(p.status, IMPARO_ST_WAIT_LIMIT, 11, i, s);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements along K = 32 bytes inside the 128-byte swizzle atom
+                    umma(tmem_base, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(b_addr + k * UMMA_K * 2), idesc,
+                         (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);        // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_ready);            // arrives when every MMA issued above is complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +32 ----
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                       // row of the CTA's W tile
+        bool ok = n_kb == 0 || mbar_wait(acc_ready, 0);
+        if (!ok && lane == 0) report(p.status, IMPARO_ST_WAIT_LIMIT, 12, tile_n, split);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const int t0 = tile_t * NT;
+
+        if (EPI == SWIGLU_BF16) {
+            // rows 0..63 hold gate, rows 64..127 hold up of features tile_n*64 + (row % 64)
+            const int f = tile_n * 64 + (row & 63);
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+            for (int c = 0; c < NT; c += 16) {
+                float v[16];
+                tmem_ld16(taddr + c, v);
+                if (row >= 64) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) exch[(row - 64) * 17 + j] = v[j];
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (row < 64 && f < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        if (t < p.T) out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(v[j]) * exch[row * 17 + j]);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        } else {
+            const int n = tile_n * BM + row;
+            const bool fold_here = p.splits == 1;
+            if (!fold_here) {
+                // write this split's partial tile, then see whether it is the last to arrive
+                float* part = p.scratch + (size_t)split * p.T * p.N;
+#pragma unroll 1
+                for (int c = 0; c < NT; c += 16) {
+                    float v[16];
+                    if (n_kb > 0) tmem_ld16(taddr + c, v);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < p.T) part[(size_t)t * p.N + n] = v[j];
+                        }
+                    }
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    int* counter = p.counters + (size_t)tile_t * gridDim.x + tile_n;
+                    const int prev = atomicAdd(counter, 1);
+                    if (prev == p.splits - 1) { flags[0] = 1; *counter = 0; }     // leave it clean for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                __threadfence();
+            }
+            if (fold_here || flags[0]) {
+#pragma unroll 1
+                for (int c = 0; c < NT; c += 16) {
+                    float v[16];
+                    if (fold_here) {
+                        if (n_kb > 0) tmem_ld16(taddr + c, v);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        if (n < p.N) {
+                            for (int s = 0; s < p.splits; ++s) {            // split order: the same sum every time
+                                const float* part = p.scratch + (size_t)s * p.T * p.N;
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) {
+                                    const int t = t0 + c + j;
+                                    if (t < p.T) v[j] += __ldcg(part + (size_t)t * p.N + n);
+                                }
+                            }
+                        }
+                    }
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t >= p.T) continue;
+                            const size_t o = (size_t)t * p.ldo + n;
+                            if (EPI == STORE_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v[j]);
+                            else if (EPI == STORE_F32) reinterpret_cast<float*>(p.out)[o] = v[j];
+                            else reinterpret_cast<float*>(p.out)[o] += v[j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+static std::mutex g_mutex;
+struct MapKey {
+    const void* ptr; uint64_t rows, cols, ld; uint32_t box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (k.rows * 1315423911u) ^ (k.cols << 20) ^ (k.ld << 7) ^ k.box_rows;
+    }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -20;
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+    if (g_maps.size() > 4096) g_maps.clear();
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -21;
+    g_maps.emplace(key, m);
+    *out = m;
+    return 0;
+}
+
+template <int NT, int STAGES, int EPI>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
+    static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
+    auto kern = gemm_kernel<NT, STAGES, EPI>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, THREADS, smem, stream>>>(mw, mx, p);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+template <int EPI>
+static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+    switch (nt) {
+        case 16: return launch<16, 8, EPI>(mw, mx, p, grid, stream);
+        case 32: return launch<32, 8, EPI>(mw, mx, p, grid, stream);
+        case 64: return launch<64, 8, EPI>(mw, mx, p, grid, stream);
+        case 128: return launch<128, 6, EPI>(mw, mx, p, grid, stream);
+        case 256: return launch<256, 4, EPI>(mw, mx, p, grid, stream);
+    }
+    return -22;
+}
+
+}  // namespace tc
+}  // namespace imparo
+
+using namespace imparo::tc;
+
+// How the launcher would cut a product: token tile, splits along K, scratch floats and
+// counters it needs.  epilogue: 0 store bf16, 1 store f32, 2 add f32, 3 SwiGLU (N = F).
+extern "C" int imparo_gemm_tc_plan(int T, int N, int K, int epilogue, int* token_tile, int* splits,
+                                   long long* scratch_floats, int* n_counters) {
+    if (T <= 0 || N <= 0 || K <= 0) return -2;
+    const int nt = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
+    const int tok_tiles = (T + nt - 1) / nt;
+    const int kblocks = (K + BK - 1) / BK;
+    int s = 1;
+    if (epilogue != SWIGLU_BF16) {
+        // aim at one CTA per SM (148); never cut K below 4 blocks per split
+        const int tiles = row_tiles * tok_tiles;
+        s = tiles >= 148 ? 1 : 148 / tiles;
+        if (s > kblocks / 4) s = kblocks / 4;
+        if (s < 1) s = 1;
+        if (s > 32) s = 32;
+    }
+    *token_tile = nt;
+    *splits = s;
+    *scratch_floats = s > 1 ? (long long)s * T * N : 0;
+    *n_counters = s > 1 ? row_tiles * tok_tiles : 0;
+    return 0;
+}
+
+// x: [T, K] bfloat16 with row stride ldx (elements), inside a buffer of x_rows_alloc rows.
+// w: [N, K] bfloat16 dense (SwiGLU: [2N, K], gate rows then up rows).  out: [T, ldo].
+// scratch / counters: from imparo_gemm_tc_plan; counters must be zero (they are left zero).
+extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const void* w, void* out, int ldo,
+                              int T, int N, int K, int epilogue, float* scratch, int* counters, int* status,
+                              cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return -23;                   // TMA: 16-byte rows
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return -23;
+    int nt, splits, ncnt;
+    long long sfl;
+    imparo_gemm_tc_plan(T, N, K, epilogue, &nt, &splits, &sfl, &ncnt);
+    if (splits > 1 && (!scratch || !counters)) return -24;
+    const int w_rows = epilogue == SWIGLU_BF16 ? 2 * N : N;
+    CUtensorMap mw, mx;
+    int rc = get_map(w, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, epilogue == SWIGLU_BF16 ? 64u : (uint32_t)BM, &mw);
+    if (rc) return rc;
+    rc = get_map(x, (uint64_t)(x_rows_alloc > T ? x_rows_alloc : T), (uint64_t)K, (uint64_t)ldx, (uint32_t)nt, &mx);
+    if (rc) return rc;
+    Params p;
+    p.out = out; p.scratch = scratch; p.counters = counters; p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
+    const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
+    dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
+    if (grid.y > 65535) return -2;
+    switch (epilogue) {
+        case STORE_BF16: return launch_nt<STORE_BF16>(nt, mw, mx, p, grid, stream);
+        case STORE_F32: return launch_nt<STORE_F32>(nt, mw, mx, p, grid, stream);
+        case ADD_F32: return launch_nt<ADD_F32>(nt, mw, mx, p, grid, stream);
+        case SWIGLU_BF16: return launch_nt<SWIGLU_BF16>(nt, mw, mx, p, grid, stream);
+    }
+    return -22;
+}

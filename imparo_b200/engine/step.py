@@ -151,15 +151,16 @@ class StepFunction:
         (imparo-cuda/native/imparo_cuda.cu:7509-7660).  Index data (tokens, positions,
         tables, wanted rows) is read from the descriptor buffer, whose address is fixed."""
         ws = self.rt.workspace
+        generation = (ws.generation, ops.TC_GENERATION)
         key = batch.host["key"]
         entry = self._graphs.get(key)
-        if entry is not None and entry[4] != ws.generation:
+        if entry is not None and entry[4] != generation:
             self._graphs.clear()
             entry = None
         if entry is None:
             if len(self._graphs) >= 64:
                 self._graphs.pop(next(iter(self._graphs)))
-            self._graphs[key] = [1, None, None, None, ws.generation]
+            self._graphs[key] = [1, None, None, None, generation]
             return self._forward(batch)
         if entry[1] is None:
             before = dict(ops.COUNTS)
@@ -169,7 +170,7 @@ class StepFunction:
             entry[1], entry[2] = g, logits
             entry[3] = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
             ops.COUNTS.update(before)          # capture launched nothing
-            if entry[4] != ws.generation:      # a buffer moved during the capture run
+            if entry[4] != (ws.generation, ops.TC_GENERATION):      # a buffer moved during the capture run
                 self._graphs.clear()
                 return self._forward(batch)
         entry[0] += 1

@@ -74,9 +74,8 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros(4, dtype=torch.int32, device=device)
 
 
-_STATUS_TEXT = {1: "token id out of the vocabulary", 2: "cache write to a page out of range",
-                3: "cache read from a page out of range", 4: "state slot out of range",
-                5: "a bounded device wait gave up"}
+_STATUS_TEXT = {1: "token id out of the vocabulary", 2: "cache page out of range (unmapped block or bad table)",
+                3: "state slot out of range", 4: "a bounded device wait gave up (tensor-core product)"}
 
 
 def read_status(status: torch.Tensor) -> None:
@@ -136,7 +135,100 @@ def _gemm_lib_ready(device) -> None:
         _gemm_ws[key] = ws
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+# ---- tcgen05 product ---------------------------------------------------------------------
+EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+_tc_scratch = {}
+_tc_plans = {}
+_status_fallback = {}
+
+
+def gemm_backend() -> str:
+    """"tcgen05" (default) or "library" (cuBLAS), chosen by IMPARO_GEMM."""
+    import os
+    v = os.environ.get("IMPARO_GEMM", "tcgen05").lower()
+    return "library" if v in ("library", "lib", "cublas") else "tcgen05"
+
+
+def _tc_plan(T, N, K, epi):
+    key = (T, N, K, epi)
+    plan = _tc_plans.get(key)
+    if plan is None:
+        import ctypes
+        nt, sp, sf, nc = ctypes.c_int(), ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
+        rc = _lib.kernels().imparo_gemm_tc_plan(T, N, K, epi, ctypes.byref(nt), ctypes.byref(sp), ctypes.byref(sf), ctypes.byref(nc))
+        if rc != 0:
+            raise KernelError(f"gemm_tc_plan({T}, {N}, {K}) refused: {rc}")
+        plan = _tc_plans[key] = (nt.value, sp.value, sf.value, nc.value)
+    return plan
+
+
+def _tc_buffers(device, floats: int, counters: int):
+    """Split-K scratch and tile counters, shared by all products of a device (they run one
+    after the other on the stream).  Grown outside graph capture only."""
+    key = torch.device(device).index or 0
+    buf = _tc_scratch.get(key)
+    if buf is None or buf[0].numel() < floats or buf[1].numel() < counters:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("split-K scratch would grow during graph capture")
+        old_f = buf[0].numel() if buf else 0
+        old_c = buf[1].numel() if buf else 0
+        buf = (torch.empty(max(floats, old_f, 1 << 20), dtype=torch.float32, device=device),
+               torch.zeros(max(counters, old_c, 4096), dtype=torch.int32, device=device))
+        _tc_scratch[key] = buf
+        global TC_GENERATION
+        TC_GENERATION += 1
+    return buf
+
+
+TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that used it are stale
+
+
+def tc_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None) -> None:
+    """The hand-written tensor-core product (csrc/kernels/gemm_tcgen05.cu).
+    epilogue: EPI_STORE_BF16 | EPI_STORE_F32 | EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU
+    (w = [gate rows; up rows] of shape [2F, K], out = silu(x gate^T) * (x up^T), [T, F])."""
+    _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    _need(tc_usable(x, w), "gemm_tc: bfloat16 operands, K a multiple of 8, 16-byte aligned rows")
+    T, K = x.shape
+    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    _need(w.shape[1] == K and (epilogue != EPI_SWIGLU or w.shape[0] % 2 == 0), "gemm_tc: weight shape")
+    _need(out.shape == (T, N) and out.stride(1) == 1, f"gemm_tc: out must be [{T}, {N}]")
+    want_dtype = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32
+    _need(out.dtype == want_dtype, f"gemm_tc: this epilogue writes {want_dtype}")
+    nt, splits, floats, counters = _tc_plan(T, N, K, epilogue)
+    scratch, cnt = _tc_buffers(x.device, floats, counters)
+    if status is None:
+        key = torch.device(x.device).index or 0
+        status = _status_fallback.get(key)
+        if status is None:
+            status = _status_fallback[key] = new_status(x.device)
+    rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
+    rows_alloc = max(T, min(rows_alloc, 1 << 30))
+    _check(_lib.kernels().imparo_gemm_tc(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K, epilogue,
+                                         _ptr(scratch), _ptr(cnt), _ptr(status), _stream()), "gemm_tc")
+
+
+def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
+                  tmp: Optional[torch.Tensor] = None) -> None:
+    """out[T, F] = silu(x gate^T) * (x up^T) with w_gu = [gate; up] of shape [2F, K].
+    bfloat16 on the tensor-core kernel: one launch, the activation in the epilogue.
+    Otherwise: the product into tmp [T, 2F], then the activation kernel."""
+    if x.dtype == torch.bfloat16 and gemm_backend() == "tcgen05" and tc_usable(x, w_gu):
+        gemm_tc(x, w_gu, out, EPI_SWIGLU, status)
+        return
+    _need(tmp is not None and tmp.shape == (x.shape[0], w_gu.shape[0]), "linear_swiglu: tmp [T, 2F] needed on this path")
+    linear(x, w_gu, tmp)
+    swiglu_act(tmp, out)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+           status: Optional[torch.Tensor] = None) -> None:
     """out[M,N] (+)= x[M,K] @ w[N,K]^T.  float32 x/w -> the FFMA kernel (true 32-bit);
     bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16."""
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
@@ -151,6 +243,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
                                               _stream()), "sgemm_nt")
     elif x.dtype == torch.bfloat16:
         _need(not accumulate or out.dtype == torch.float32, "linear: accumulate needs a float32 output")
+        if gemm_backend() == "tcgen05" and tc_usable(x, w):
+            epi = EPI_ADD_F32 if accumulate else (EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16)
+            gemm_tc(x, w, out, epi, status)
+            return
         _gemm_lib_ready(x.device)
         _check(_lib.kernels().imparo_gemm_bf16_nt(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), N,
                                                   int(accumulate), _stream()), "gemm_bf16_nt", "library")

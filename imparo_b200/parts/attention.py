@@ -70,7 +70,7 @@ class AttentionMixer(Part):
         nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only
         width = (nh + 2 * nkv) * hd
         qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype)
-        ops.linear(x, self.w_qkv[:width], qkv)
+        ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype)
         rot = self.position.rotary()
         table = batch.tables[kv.group]
@@ -90,4 +90,4 @@ class AttentionMixer(Part):
         if not done:
             ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
                                 self.window, self.scale, out, nh, self.nkv, hd, rt.status)
-        ops.linear(out, self.w_o, residual, accumulate=True)
+        ops.linear(out, self.w_o, residual, accumulate=True, status=rt.status)

@@ -53,5 +53,5 @@ class LinearHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32)
-        ops.linear(h, self.table, logits)
+        ops.linear(h, self.table, logits, status=self.rt.status)
         return logits

@@ -34,8 +34,10 @@ class SwiGLU(Part):
 
     def forward(self, x, batch, residual):
         rt, T, F = self.rt, x.shape[0], self.ff
-        gu = rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype)
-        ops.linear(x, self.w_gu, gu)
         h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype)
-        ops.swiglu_act(gu, h)
-        ops.linear(h, self.w_down, residual, accumulate=True)
+        if x.dtype == torch.bfloat16 and ops.gemm_backend() == "tcgen05" and ops.tc_usable(x, self.w_gu):
+            ops.linear_swiglu(x, self.w_gu, h, rt.status)        # gate/up product with silu(gate)*up in its epilogue
+        else:
+            gu = rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype)
+            ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=gu)
+        ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)

@@ -53,12 +53,12 @@ class ShortConvMixer(Part):
         st = caches[0]
         rt, T, H = self.rt, x.shape[0], self.hidden
         bcx = rt.workspace.get("conv_bcx", (T, 3 * H), rt.act_dtype)
-        ops.linear(x, self.w_in, bcx)
+        ops.linear(x, self.w_in, bcx, status=rt.status)
         if self.b_in is not None:
             ops.add_bias(bcx, self.b_in)
         y = rt.workspace.get("conv_y", (T, H), rt.act_dtype)
         ops.gated_conv(bcx, self.w_conv, self.b_conv, st.state, batch.item_row_start, batch.item_of_token,
                        batch.item_slot, y, self.taps, rt.status)
-        ops.linear(y, self.w_out, residual, accumulate=True)
+        ops.linear(y, self.w_out, residual, accumulate=True, status=rt.status)
         if self.b_out is not None:
             ops.add_bias(residual, self.b_out)
