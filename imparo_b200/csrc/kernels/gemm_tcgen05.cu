@@ -9,9 +9,11 @@
 // tcgen05.commit hands stages back to the producer, and four warps read the accumulator with
 // tcgen05.ld and write out[token, n] (32 lanes = 32 consecutive n: coalesced).
 //
-// Few output tiles (N small) are cut along K as well (split-K): every split writes its
-// partial tile to scratch, the split that arrives last for a tile adds the partials in split
-// order and runs the epilogue, so the result does not depend on which split came last.
+// Few output tiles (N small) are cut along K as well (split-K): the splits of one tile are the
+// CTAs of one thread-block cluster.  Each leaves its partial tile in its own shared memory;
+// after a cluster barrier every CTA folds a share of the tile's tokens, reading the partials
+// of all splits through distributed shared memory in split order, and runs the epilogue for
+// them.  No global scratch, and the same sum every time.
 //
 // Epilogues: store bfloat16 | store float32 | add into float32 (the residual stream) |
 // SwiGLU: the CTA's 128 rows are 64 gate rows and the 64 up rows of the same features,
@@ -95,6 +97,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+template <int EPI>
+__device__ __forceinline__ void store_out(void* out, size_t o, float v) {
+    if (EPI == STORE_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+    else if (EPI == STORE_F32) reinterpret_cast<float*>(out)[o] = v;
+    else reinterpret_cast<float*>(out)[o] += v;
+}
+
 struct Params {
     void* out;               // [T, ldo]
     float* scratch;          // split-K partials [splits][T][N]
@@ -123,7 +132,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
     const int tile_t = blockIdx.y;                 // which NT tokens
-    const int split = blockIdx.z;
+    int split = blockIdx.z;                        // with split-K: this CTA's rank in its cluster
+    if (p.splits > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
     const int kb_begin = (int)(((long long)p.kblocks * split) / p.splits);
     const int kb_end = (int)(((long long)p.kblocks * (split + 1)) / p.splits);
     const int n_kb = kb_end - kb_begin;
@@ -220,74 +230,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             }
         } else {
             const int n = tile_n * BM + row;
-            const bool fold_here = p.splits == 1;
-            if (!fold_here) {
-                // write this split's partial tile, then see whether it is the last to arrive
-                float* part = p.scratch + (size_t)split * p.T * p.N;
+            if (p.splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < NT; c += 16) {
                     float v[16];
-                    if (n_kb > 0) tmem_ld16(taddr + c, v);
-                    else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                    }
+                    tmem_ld16(taddr + c, v);
                     if (n < p.N) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int t = t0 + c + j;
-                            if (t < p.T) part[(size_t)t * p.N + n] = v[j];
+                            if (t < p.T) store_out<EPI>(p.out, (size_t)t * p.ldo + n, v[j]);
                         }
                     }
                 }
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (warp == 2 && lane == 0) {
-                    int* counter = p.counters + (size_t)tile_t * gridDim.x + tile_n;
-                    const int prev = atomicAdd(counter, 1);
-                    if (prev == p.splits - 1) { flags[0] = 1; *counter = 0; }     // leave it clean for the next launch
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                __threadfence();
-            }
-            if (fold_here || flags[0]) {
+            } else {
+                // this split's partial tile -> own shared memory, [token][row] (the stage ring is idle now)
+                float* part = reinterpret_cast<float*>(smem);
 #pragma unroll 1
                 for (int c = 0; c < NT; c += 16) {
                     float v[16];
-                    if (fold_here) {
-                        if (n_kb > 0) tmem_ld16(taddr + c, v);
-                        else {
+                    tmem_ld16(taddr + c, v);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                        if (n < p.N) {
-                            for (int s = 0; s < p.splits; ++s) {            // split order: the same sum every time
-                                const float* part = p.scratch + (size_t)s * p.T * p.N;
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) {
-                                    const int t = t0 + c + j;
-                                    if (t < p.T) v[j] += __ldcg(part + (size_t)t * p.N + n);
-                                }
-                            }
-                        }
-                    }
-                    if (n < p.N) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t >= p.T) continue;
-                            const size_t o = (size_t)t * p.ldo + n;
-                            if (EPI == STORE_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v[j]);
-                            else if (EPI == STORE_F32) reinterpret_cast<float*>(p.out)[o] = v[j];
-                            else reinterpret_cast<float*>(p.out)[o] += v[j];
-                        }
-                    }
+                    for (int j = 0; j < 16; ++j) part[(c + j) * BM + row] = v[j];
                 }
             }
         }
+    }
+    if (p.splits > 1) {
+        // every thread of every CTA of the cluster: partials are written / may be read
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2) {
+            const int quad = warp & 3;
+            const int row = quad * 32 + lane;
+            const int n = tile_n * BM + row;
+            const int t0 = tile_t * NT;
+            const uint32_t my = smem_u32(smem) + (uint32_t)row * 4;
+            // CTA `split` folds token columns split, split + splits, ...: the sum runs over the
+            // splits in order 0, 1, 2, ... whichever CTA does it
+            for (int c = split; c < NT; c += p.splits) {
+                const int t = t0 + c;
+                if (t >= p.T) break;
+                float acc = 0.f;
+                for (int sidx = 0; sidx < p.splits; ++sidx) {
+                    uint32_t remote;
+                    float v;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(my + (uint32_t)c * BM * 4), "r"(sidx));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+                    acc += v;
+                }
+                if (n < p.N) store_out<EPI>(p.out, (size_t)t * p.ldo + n, acc);
+            }
+        }
+        // nobody leaves while its shared memory may still be read
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -342,29 +339,95 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
     static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
     auto kern = gemm_kernel<NT, STAGES, EPI>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    kern<<<grid, THREADS, smem, stream>>>(mw, mx, p);
-    e = cudaGetLastError();
+    static bool configured = false;             // per instantiation
+    cudaError_t e;
+    if (!configured) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;          // the splits of a tile are one cluster
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, mw, mx, p);
     return e == cudaSuccess ? 0 : (int)e;
 }
+
+// How many clusters of `cluster` CTAs of this kernel the device holds at once (0 on error).
+template <int NT, int STAGES, int EPI>
+static int max_clusters(int cluster) {
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
+    auto kern = gemm_kernel<NT, STAGES, EPI>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, cluster);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = cluster;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+// Ring depth per token tile.  Small token tiles keep the ring shallow enough for two or three
+// CTAs per SM: one CTA's prologue and epilogue then overlap another's streaming, and more
+// clusters are resident at once.
+constexpr int stages_for(int nt) { return nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 
 template <int EPI>
 static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
     switch (nt) {
-        case 16: return launch<16, 8, EPI>(mw, mx, p, grid, stream);
-        case 32: return launch<32, 8, EPI>(mw, mx, p, grid, stream);
-        case 64: return launch<64, 8, EPI>(mw, mx, p, grid, stream);
-        case 128: return launch<128, 6, EPI>(mw, mx, p, grid, stream);
-        case 256: return launch<256, 4, EPI>(mw, mx, p, grid, stream);
+        case 16: return launch<16, stages_for(16), EPI>(mw, mx, p, grid, stream);
+        case 32: return launch<32, stages_for(32), EPI>(mw, mx, p, grid, stream);
+        case 64: return launch<64, stages_for(64), EPI>(mw, mx, p, grid, stream);
+        case 128: return launch<128, stages_for(128), EPI>(mw, mx, p, grid, stream);
+        case 256: return launch<256, stages_for(256), EPI>(mw, mx, p, grid, stream);
     }
     return -22;
+}
+
+// resident clusters by (token tile, cluster size), asked of the runtime once
+static int resident_clusters(int nt, int cluster) {
+    static int table[5][9];
+    static bool known[5][9];
+    const int i = nt == 16 ? 0 : nt == 32 ? 1 : nt == 64 ? 2 : nt == 128 ? 3 : 4;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!known[i][cluster]) {
+        int n = 0;
+        switch (nt) {
+            case 16: n = max_clusters<16, stages_for(16), ADD_F32>(cluster); break;
+            case 32: n = max_clusters<32, stages_for(32), ADD_F32>(cluster); break;
+            case 64: n = max_clusters<64, stages_for(64), ADD_F32>(cluster); break;
+            case 128: n = max_clusters<128, stages_for(128), ADD_F32>(cluster); break;
+            default: n = max_clusters<256, stages_for(256), ADD_F32>(cluster); break;
+        }
+        table[i][cluster] = n;
+        known[i][cluster] = true;
+    }
+    return table[i][cluster];
 }
 
 }  // namespace tc
 }  // namespace imparo
 
 using namespace imparo::tc;
+
+extern "C" int imparo_gemm_tc_max_clusters(int nt, int cluster) {
+    if (cluster < 1 || cluster > 8) return -1;
+    return resident_clusters(nt, cluster);
+}
 
 // How the launcher would cut a product: token tile, splits along K, scratch floats and
 // counters it needs.  epilogue: 0 store bf16, 1 store f32, 2 add f32, 3 SwiGLU (N = F).
@@ -377,17 +440,21 @@ extern "C" int imparo_gemm_tc_plan(int T, int N, int K, int epilogue, int* token
     const int kblocks = (K + BK - 1) / BK;
     int s = 1;
     if (epilogue != SWIGLU_BF16) {
-        // aim at one CTA per SM (148); never cut K below 4 blocks per split
+        // The splits of a tile are one cluster (at most 8 CTAs, the portable size).  Take the
+        // cluster size that puts the most CTAs on the device in ONE wave: all the tiles'
+        // clusters must be resident together.  Never cut K below 4 blocks per split.
         const int tiles = row_tiles * tok_tiles;
-        s = tiles >= 148 ? 1 : 148 / tiles;
-        if (s > kblocks / 4) s = kblocks / 4;
-        if (s < 1) s = 1;
-        if (s > 32) s = 32;
+        int best = 1;
+        if (tiles < 120) {
+            for (int c = 2; c <= 8 && c <= kblocks / 4; ++c)
+                if (tiles <= resident_clusters(nt, c) && tiles * c > tiles * best) best = c;
+        }
+        s = best;
     }
     *token_tile = nt;
     *splits = s;
-    *scratch_floats = s > 1 ? (long long)s * T * N : 0;
-    *n_counters = s > 1 ? row_tiles * tok_tiles : 0;
+    *scratch_floats = 0;                        // partials live in the cluster's shared memory
+    *n_counters = 0;
     return 0;
 }
 
@@ -403,7 +470,6 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
     int nt, splits, ncnt;
     long long sfl;
     imparo_gemm_tc_plan(T, N, K, epilogue, &nt, &splits, &sfl, &ncnt);
-    if (splits > 1 && (!scratch || !counters)) return -24;
     const int w_rows = epilogue == SWIGLU_BF16 ? 2 * N : N;
     CUtensorMap mw, mx;
     int rc = get_map(w, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, epilogue == SWIGLU_BF16 ? 64u : (uint32_t)BM, &mw);
