@@ -27,6 +27,8 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
                           const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
                           int nh, int nkv, int hd, int* status) {
     __shared__ float rowbuf[WARPS][MAX_HEAD];
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int hh = blockIdx.y * WARPS + warp;
@@ -108,6 +110,8 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
                        int window, float scale, T* __restrict__ out, int nh, int nkv, int hd, int* status) {
     __shared__ __align__(16) float qbuf[WARPS][MAX_HEAD];
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * WARPS + warp;
@@ -191,11 +195,11 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
     if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
     if (dtype == IMPARO_DT_F32)
-        qk_norm_rope_store_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+        launch(qk_norm_rope_store_kernel<float>, grid, dim3(WARPS * 32), 0, stream,
             (const float*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (float*)q_out,
             (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
     else if (dtype == IMPARO_DT_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+        launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream,
             (const __nv_bfloat16*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
     else return -1;
@@ -213,11 +217,11 @@ extern "C" int imparo_paged_attention(const void* q, const void* k_cache, const 
     if (nkv <= 0 || nh % nkv != 0) return -5;
     dim3 grid(n_tok, (nh + WARPS - 1) / WARPS);
     if (dtype == IMPARO_DT_F32)
-        paged_attention_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+        launch(paged_attention_kernel<float>, grid, dim3(WARPS * 32), 0, stream,
             (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, item_of_token, table,
             max_blocks, page_size, n_pages, window, scale, (float*)out, nh, nkv, hd, status);
     else if (dtype == IMPARO_DT_BF16)
-        paged_attention_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+        launch(paged_attention_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream,
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions,
             item_of_token, table, max_blocks, page_size, n_pages, window, scale, (__nv_bfloat16*)out, nh, nkv, hd, status);
     else return -1;

@@ -63,6 +63,8 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
                           float scale, float* __restrict__ part_acc, float* __restrict__ part_ml,
                           int nh, int nkv, int hd, int chunk, int n_splits, int* status) {
     extern __shared__ __align__(16) float smem[];
+    pdl_wait();
+    pdl_trigger();
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* qs = smem;
@@ -125,7 +127,14 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
             } else {
                 rowi = page * page_size + (j % page_size);
                 const V* kp = reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
-                for (int c = 0; c < vecs; ++c) dot_group<G>(kp[c], qs, hd, c * VN, s);
+                // eight independent 16-byte loads in flight before any arithmetic
+                for (int c0 = 0; c0 < vecs; c0 += 8) {
+                    V kv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) if (c0 + u < vecs) kv[u] = kp[c0 + u];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) if (c0 + u < vecs) dot_group<G>(kv[u], qs, hd, (c0 + u) * VN, s);
+                }
             }
         }
         my_rows[lane] = rowi;
@@ -148,25 +157,37 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
         const int cnt = min(32, end - base);
         // all loads of a round are independent of the arithmetic: the compiler keeps several
         // rounds in flight
-#pragma unroll 4
-        for (int r = 0; r * KPI < cnt; ++r) {
-            const int jj = r * KPI + grp;
-            const bool live = pv_lane && jj < cnt;
-            const int rj = live ? my_rows[jj] : -1;
-            // branch-free: a dead lane reads row 0 (always mapped memory) with probability 0
-            const V* vp = reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
-            float v[ACC];
-            unpack(vp[lig], v);
-            if (VPL > 1) unpack(vp[lig + LPR], v + VN); else { for (int i = VN; i < ACC; ++i) v[i] = 0.f; }
-            if (rj < 0) {                 // whatever row 0 holds must not reach the sum (0 * inf)
+        // four rounds of value loads in flight at a time; a dead lane reads row 0 (always
+        // mapped memory) and contributes with probability 0
+        for (int r0 = 0; r0 * KPI < cnt; r0 += 4) {
+            V vv[4][2];
+            int rjs[4], jjs[4];
 #pragma unroll
-                for (int i = 0; i < ACC; ++i) v[i] = 0.f;
+            for (int u = 0; u < 4; ++u) {
+                const int jj = (r0 + u) * KPI + grp;
+                const bool live = pv_lane && jj < cnt;
+                const int rj = live ? my_rows[jj] : -1;
+                rjs[u] = rj;
+                jjs[u] = jj & 31;
+                const V* vp = reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
+                vv[u][0] = vp[lig];
+                if (VPL > 1) vv[u][1] = vp[lig + LPR];
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pj = rj < 0 ? 0.f : my_ps[g * 32 + (jj & 31)];
+            for (int u = 0; u < 4; ++u) {
+                float v[ACC];
+                unpack(vv[u][0], v);
+                if (VPL > 1) unpack(vv[u][1], v + VN); else { for (int i = VN; i < ACC; ++i) v[i] = 0.f; }
+                if (rjs[u] < 0) {             // whatever row 0 holds must not reach the sum (0 * inf)
 #pragma unroll
-                for (int i = 0; i < ACC; ++i) acc[g][i] += pj * v[i];
+                    for (int i = 0; i < ACC; ++i) v[i] = 0.f;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pj = rjs[u] < 0 ? 0.f : my_ps[g * 32 + jjs[u]];
+#pragma unroll
+                    for (int i = 0; i < ACC; ++i) acc[g][i] += pj * v[i];
+                }
             }
         }
         __syncwarp();
@@ -211,6 +232,8 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
 template <typename T>
 __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                           T* __restrict__ out, int hd, int n_splits) {
+    pdl_wait();
+    pdl_trigger();
     const size_t th = blockIdx.x;                         // token * nh + head
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
@@ -243,7 +266,7 @@ int launch_partial(const void* q, const void* k_cache, const void* v_cache, cons
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_splits, nkv, n_tok);
-    kern<<<grid, SPLIT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, positions, item_of_token,
+    launch(kern, grid, dim3(SPLIT_WARPS * 32), smem, stream, (const T*)q, (const T*)k_cache, (const T*)v_cache, positions, item_of_token,
                                                    table, max_blocks, page_size, n_pages, window, scale, part_acc, part_ml,
                                                    nh, nkv, hd, chunk, n_splits, status);
     IMPARO_CHECK_LAUNCH();
@@ -291,9 +314,9 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
     if (rc != 0) return rc;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == IMPARO_DT_F32)
-        attn_split_combine_kernel<float><<<n_tok * nh, threads, 0, stream>>>(part_acc, part_ml, (float*)out, hd, n_splits);
+        launch(attn_split_combine_kernel<float>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits);
     else
-        attn_split_combine_kernel<__nv_bfloat16><<<n_tok * nh, threads, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+        launch(attn_split_combine_kernel<__nv_bfloat16>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, hd, n_splits);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -89,4 +89,30 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
 }  // namespace imparo
 
+// ---- programmatic dependent launch ----------------------------------------------------
+// Every kernel of this engine starts with pdl_wait() before it reads or writes anything an
+// earlier kernel may touch, and calls pdl_trigger() so that the next kernel's CTAs may be
+// scheduled early: their launch latency and prologue (and, for the products, the first
+// weight tiles, which no kernel writes) then overlap this kernel's tail.  Without the launch
+// attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern "C" int imparo_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = imparo_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define IMPARO_CHECK_LAUNCH() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)

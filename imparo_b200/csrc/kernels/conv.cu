@@ -25,6 +25,8 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
                                   const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                   const int* __restrict__ item_slot, T* __restrict__ y,
                                   int n_tok, int width, int taps, int n_slots, int* status) {
+    pdl_wait();
+    pdl_trigger();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tok * width) return;
     const int t = (int)(idx / width), ch = (int)(idx % width);
@@ -106,10 +108,10 @@ extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, con
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == IMPARO_DT_F32)
-        gated_conv_kernel<float><<<blocks, threads, 0, stream>>>((const float*)bcx, w, bias, state, item_row_start,
+        launch(gated_conv_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)bcx, w, bias, state, item_row_start,
                                                                 item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
     else if (dtype == IMPARO_DT_BF16)
-        gated_conv_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)bcx, w, bias, state, item_row_start,
+        launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)bcx, w, bias, state, item_row_start,
                                                                          item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();

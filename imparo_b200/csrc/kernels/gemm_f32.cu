@@ -16,6 +16,8 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
                 int M, int N, int K, int lda, int ldc, int accumulate) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_wait();
+    pdl_trigger();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;        // 16 x 16 threads, each 4 x 4 outputs
@@ -72,7 +74,7 @@ extern "C" int imparo_sgemm_nt(const float* A, const float* W, float* C, int M, 
     if (K <= 0) return -1;
     dim3 grid((N + imparo::BN - 1) / imparo::BN, (M + imparo::BM - 1) / imparo::BM);
     if (grid.y > 65535) return -2;
-    imparo::sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldc, accumulate);
+    launch(imparo::sgemm_nt_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldc, accumulate);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

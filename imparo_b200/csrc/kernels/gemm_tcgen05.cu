@@ -155,12 +155,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // Weights are written by no kernel: the first ring of W tiles is requested before
+            // waiting for the previous kernel, so it streams in while that kernel finishes.
+            auto load_w = [&](int i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
-                    report(p.status, IMPARO_ST_WAIT_LIMIT, 10, i, s);
-                    break;
-                }
                 uint8_t* a = smem + s * STAGE_BYTES;
                 mbar_expect_tx(&full[s], STAGE_BYTES);
                 const int k0 = (kb_begin + i) * BK;
@@ -170,7 +168,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 } else {
                     tma_load_2d(a, &map_w, &full[s], k0, tile_n * BM);
                 }
-                tma_load_2d(a + A_BYTES, &map_x, &full[s], k0, tile_t * NT);
+            };
+            auto load_x = [&](int i) {
+                const int s = i % STAGES;
+                tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_x, &full[s], (kb_begin + i) * BK, tile_t * NT);
+            };
+            const int early = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < early; ++i) load_w(i);
+            pdl_wait();
+            pdl_trigger();
+            for (int i = 0; i < early; ++i) load_x(i);
+            for (int i = early; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&empty[s], ((i / STAGES) - 1) & 1)) {
+                    report(p.status, IMPARO_ST_WAIT_LIMIT, 10, i, s);
+                    break;
+                }
+                load_w(i);
+                load_x(i);
             }
         }
     } else if (warp == 1) {
@@ -200,6 +215,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +32 ----
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                       // row of the CTA's W tile
+        pdl_wait();                                             // before any global write or residual read
         bool ok = n_kb == 0 || mbar_wait(acc_ready, 0);
         if (!ok && lane == 0) report(p.status, IMPARO_ST_WAIT_LIMIT, 12, tile_n, split);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -351,13 +367,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = grid.z;          // the splits of a tile are one cluster
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = imparo_pdl_enabled() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kern, mw, mx, p);
     return e == cudaSuccess ? 0 : (int)e;
 }

@@ -12,6 +12,8 @@ namespace imparo {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int width, int vocab, int* status) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) {
@@ -32,6 +34,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                const float* __restrict__ w, float eps, TOut* __restrict__ out,
                                int width) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
     float ss = 0.f;
@@ -46,6 +50,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // gu: [T, 2F] rows = [gate | up]; out: [T, F]
 template <typename T>
 __global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tok, int F) {
+    pdl_wait();
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_tok * F) return;
     const size_t t = i / F, f = i % F;
@@ -57,6 +63,8 @@ __global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out,
 // ---- out[t, :] += bias ----------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n_tok, int width) {
+    pdl_wait();
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_tok * width) return;
     out[i] = from_f32<T>(to_f32(out[i]) + bias[i % width]);
@@ -66,14 +74,19 @@ __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ b
 
 using namespace imparo;
 
+// Programmatic dependent launch for every kernel of the engine: on by default.
+static int g_pdl = 1;
+extern "C" int imparo_pdl_enabled() { return g_pdl; }
+extern "C" void imparo_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 extern "C" int imparo_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
                                    int n_tok, int width, int vocab, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == IMPARO_DT_F32)
-        embed_gather_kernel<float><<<n_tok, threads, 0, stream>>>((const float*)table, ids, out, width, vocab, status);
+        launch(embed_gather_kernel<float>, dim3(n_tok), dim3(threads), 0, stream, (const float*)table, ids, out, width, vocab, status);
     else if (table_dtype == IMPARO_DT_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<n_tok, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab, status);
+        launch(embed_gather_kernel<__nv_bfloat16>, dim3(n_tok), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, width, vocab, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
@@ -84,9 +97,9 @@ extern "C" int imparo_rmsnorm(const float* x, const int* rows, const float* w, f
     if (n_rows <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (out_dtype == IMPARO_DT_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, w, eps, (float*)out, width);
+        launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, w, eps, (float*)out, width);
     else if (out_dtype == IMPARO_DT_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, rows, w, eps, (__nv_bfloat16*)out, width);
+        launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, w, eps, (__nv_bfloat16*)out, width);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
@@ -98,9 +111,9 @@ extern "C" int imparo_swiglu_act(const void* gu, void* out, int dtype, int n_tok
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == IMPARO_DT_F32)
-        swiglu_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tok, F);
+        launch(swiglu_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, n_tok, F);
     else if (dtype == IMPARO_DT_BF16)
-        swiglu_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
+        launch(swiglu_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
@@ -112,9 +125,9 @@ extern "C" int imparo_add_bias(void* out, int dtype, const float* bias, int n_to
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == IMPARO_DT_F32)
-        add_bias_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, bias, n_tok, width);
+        launch(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out, bias, n_tok, width);
     else if (dtype == IMPARO_DT_BF16)
-        add_bias_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, bias, n_tok, width);
+        launch(add_bias_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, bias, n_tok, width);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

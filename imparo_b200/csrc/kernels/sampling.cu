@@ -53,6 +53,8 @@ sample_rows_kernel(const float* __restrict__ logits, const float* __restrict__ t
     __shared__ float fscratch[33];
     __shared__ float part[SAMPLE_THREADS];
     __shared__ int pick;
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const int per = (vocab + blockDim.x - 1) / blockDim.x;
@@ -107,13 +109,63 @@ sample_rows_kernel(const float* __restrict__ logits, const float* __restrict__ t
     }
 }
 
+// Greedy only, for many rows or a large vocabulary: ARGMAX_PARTS blocks per row each find
+// the best of a contiguous stretch, then one warp per row folds them (same rule: larger
+// value, then smaller index).
+constexpr int ARGMAX_PARTS = 32;
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx,
+                      int vocab, int ld) {
+    __shared__ MaxIdx scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.y, part = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+    const int lo = min(vocab, part * per), hi = min(vocab, lo + per);
+    MaxIdx m{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > m.v || (v == m.v && i < m.i)) { m.v = v; m.i = i; }
+    }
+    m = block_argmax(m, scratch);
+    if (threadIdx.x == 0) { part_val[r * ARGMAX_PARTS + part] = m.v; part_idx[r * ARGMAX_PARTS + part] = m.i; }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, lane = threadIdx.x;
+    MaxIdx m{part_val[r * ARGMAX_PARTS + lane], part_idx[r * ARGMAX_PARTS + lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxIdx other{__shfl_xor_sync(0xffffffffu, m.v, o), __shfl_xor_sync(0xffffffffu, m.i, o)};
+        m = better(m, other);
+    }
+    if (lane == 0) out[r] = m.i == 0x7fffffff ? 0 : m.i;
+}
+
 }  // namespace imparo
+
+// part_val / part_idx: scratch of n_rows * 32 entries each.
+extern "C" int imparo_argmax_rows(const float* logits, int* out, float* part_val, int* part_idx,
+                                  int n_rows, int vocab, int ld, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 65535) return -2;
+    dim3 grid(imparo::ARGMAX_PARTS, n_rows);
+    launch(imparo::argmax_partial_kernel, grid, dim3(256), 0, stream, logits, part_val, part_idx, vocab, ld);
+    launch(imparo::argmax_final_kernel, dim3(n_rows), dim3(32), 0, stream, part_val, part_idx, out);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
 
 extern "C" int imparo_sample_rows(const float* logits, const float* temperature, const float* uniform, int* out,
                                   int n_rows, int vocab, int ld, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (temperature && !uniform) return -7;
-    imparo::sample_rows_kernel<<<n_rows, imparo::SAMPLE_THREADS, 0, stream>>>(logits, temperature, uniform, out, vocab, ld);
+    launch(imparo::sample_rows_kernel, dim3(n_rows), dim3(imparo::SAMPLE_THREADS), 0, stream, logits, temperature, uniform, out, vocab, ld);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -295,10 +295,10 @@ def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_s
 
 def split_plan(n_tok: int, nkv: int, upper_context: int):
     """(chunk, n_splits) for the split-key attention kernel: the largest chunk of 512, 256, 128
-    or 64 keys that still gives about two CTAs per SM; a function of the launch's shape only."""
+    or 64 keys that still gives about four CTAs per SM; a function of the launch's shape only."""
     chunk = 64
     for c in (512, 256, 128):
-        if n_tok * nkv * -(-upper_context // c) >= 296:
+        if n_tok * nkv * -(-upper_context // c) >= 592:
             chunk = c
             break
     return chunk, max(1, -(-upper_context // chunk))
@@ -342,12 +342,27 @@ def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y,
         _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], _ptr(status), _stream()), "gated_conv")
 
 
+_argmax_scratch = {}
+
+
 def sample_rows(logits, temperature, uniform, out) -> None:
     """out[r] = greedy pick where temperature[r] <= 0 (or temperature is None), else the
     inverse-CDF pick of softmax(logits[r] / temperature[r]) at uniform[r]."""
     _cuda(logits, temperature, uniform, out)
     n, vocab = logits.shape
     _need(logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= n, "sample_rows: dtypes")
+    if temperature is None and vocab >= 4096 and n <= 65535:
+        # greedy over a large vocabulary: 32 blocks per row, then one warp per row
+        key = torch.device(logits.device).index or 0
+        buf = _argmax_scratch.get(key)
+        if buf is None or buf[0].numel() < n * 32:
+            _need(not torch.cuda.is_current_stream_capturing(), "argmax scratch would grow during graph capture")
+            buf = _argmax_scratch[key] = (torch.empty(max(n, 256) * 32, dtype=torch.float32, device=logits.device),
+                                          torch.empty(max(n, 256) * 32, dtype=torch.int32, device=logits.device))
+        _check(_lib.kernels().imparo_argmax_rows(_ptr(logits), _ptr(out), _ptr(buf[0]), _ptr(buf[1]), n, vocab,
+                                                 logits.stride(0), _stream()), "argmax_rows")
+        COUNTS["own"] += 1
+        return
     if temperature is not None:
         _need(temperature.dtype == torch.float32 and uniform is not None and uniform.dtype == torch.float32
               and temperature.numel() >= n and uniform.numel() >= n, "sample_rows: temperature/uniform float32 per row")
