@@ -1,0 +1,301 @@
+// Attention for prompt portions over the paged cache on tensor cores (bfloat16, head size
+// 64 or 128): a CTA owns up to 64 query rows = (64 / G) consecutive tokens of ONE request
+// times the G query heads that share a kv head, walks the keys 64 at a time in position
+// order, scores with mma.sync m16n8k16 (bfloat16 in, 32-bit out), keeps the running max and
+// sum per row in 32-bit, and accumulates P*V with the same instruction.  Keys and values of a
+// block are read once for the whole group.  The reference's prefill kernel has the same
+// shape for its f16 cache (imparo-cuda/native/sm80/attention_prefill_mma_d64_f16.cuh:29:
+// "CTA = 16 query tokens x 4 GQA heads x 1 KV head, walks 64-key updates in order").
+//
+// Formulas: scores q.k * scale for lo <= key <= position, lo = 0 or position+1-window, no
+// mask tensor, softmax with the max subtracted (imparo-model/src/cpu_support.rs:402-445).
+// Which tokens form a tile is derived on the device from the batch's row starts, so a tile
+// never holds rows of two requests; a token's result does not depend on its neighbours in
+// the tile (every row has its own max, sum and mask).
+#include "common.cuh"
+
+namespace imparo {
+namespace pf {
+
+constexpr int ROWS = 64;          // query rows per CTA
+constexpr int KEYS = 64;          // keys per step
+constexpr int THREADS = 128;      // 4 warps x 16 rows
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                 // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of 16-byte chunk c of row r in a [rows][HD] bfloat16 tile, XOR-swizzled so that
+// the eight rows an ldmatrix reads fall into distinct banks
+template <int HD>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)r * (HD * 2) + (uint32_t)((c ^ (r & 7)) << 4); }
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ item_row_start,
+                    const int* __restrict__ item_start_pos, int n_items, const int* __restrict__ table, int max_blocks,
+                    int page_size, int n_pages, int window, float scale, __nv_bfloat16* __restrict__ out,
+                    int nh, int nkv, int* status) {
+    constexpr int CH = HD / 8;                    // 16-byte chunks per row
+    constexpr int KT = HD / 16;                   // k-steps of the score product
+    constexpr int NT_O = HD / 8;                  // n-tiles of the output
+    extern __shared__ __align__(128) uint8_t pf_smem[];
+    uint8_t* q_s = pf_smem;
+    uint8_t* k_s[2] = {q_s + ROWS * HD * 2, q_s + ROWS * HD * 2 + KEYS * HD * 2};
+    uint8_t* v_s[2] = {k_s[1] + KEYS * HD * 2, k_s[1] + 2 * KEYS * HD * 2};
+    pdl_wait();
+    pdl_trigger();
+
+    const int G = nh / nkv;
+    const int TQ = ROWS / G;                      // tokens per tile
+    const int kvh = blockIdx.y;
+    // which request and which of its tokens: tiles are numbered request by request
+    int item = 0, tile = blockIdx.x, n_item = 0, row0 = 0;
+    for (; item < n_items; ++item) {
+        row0 = item_row_start[item];
+        n_item = item_row_start[item + 1] - row0;
+        const int tiles = (n_item + TQ - 1) / TQ;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (item >= n_items) return;
+    const int tok0 = tile * TQ;                               // first token of the tile within its request's portion
+    const int n_tok = min(TQ, n_item - tok0);
+    const int n_rows = n_tok * G;
+    const int pos0 = item_start_pos[item] + tok0;             // position of the tile's first token
+    const int pos_last = pos0 + n_tok - 1;
+    const int* tab = table + (size_t)item * max_blocks;
+    const size_t kvw = (size_t)nkv * HD;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
+
+    // ---- queries -> shared memory (row r = token r / G, head kvh*G + r % G) ----
+    for (int i = tid; i < ROWS * CH; i += THREADS) {
+        const int r = i / CH, c = i % CH;
+        const bool valid = r < n_rows;
+        const size_t t = (size_t)row0 + tok0 + (valid ? r / G : 0);
+        const __nv_bfloat16* src = q + (t * nh + (size_t)kvh * G + (valid ? r % G : 0)) * HD + c * 8;
+        cp_async16(q_s + tile_off<HD>(r, c), src, valid);
+    }
+    cp_commit();
+
+    const int lo_min = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int kb_first = lo_min / KEYS, kb_last = pos_last / KEYS;
+
+    auto load_kv = [&](int kb, int buf) {
+        for (int i = tid; i < KEYS * CH; i += THREADS) {
+            const int r = i / CH, c = i % CH;
+            const int j = kb * KEYS + r;
+            bool valid = j <= pos_last && j >= lo_min;
+            size_t rowi = 0;
+            if (valid) {
+                const int blk = j / page_size;
+                const int page = blk < max_blocks ? tab[blk] : -1;
+                if (page < 0 || page >= n_pages) {
+                    if (c == 0) report(status, IMPARO_ST_PAGE_RANGE, 6, item, page);
+                    valid = false;
+                } else {
+                    rowi = (size_t)page * page_size + (j % page_size);
+                }
+            }
+            const size_t off = rowi * kvw + (size_t)kvh * HD + c * 8;
+            cp_async16(k_s[buf] + tile_off<HD>(r, c), k_cache + off, valid);
+            cp_async16(v_s[buf] + tile_off<HD>(r, c), v_cache + off, valid);
+        }
+        cp_commit();
+    };
+    load_kv(kb_first, 0);
+
+    // ---- this warp's query fragments ----
+    cp_wait<1>();
+    __syncthreads();
+    uint32_t qf[KT][4];
+    {
+        const int m = lane >> 3, rin = lane & 7;
+        const int r = warp * 16 + (m & 1) * 8 + rin;
+#pragma unroll
+        for (int kt = 0; kt < KT; ++kt) ldmatrix4(qf[kt], smem_addr(q_s + tile_off<HD>(r, kt * 2 + (m >> 1))));
+    }
+    // rows of this thread: warp*16 + g and + 8; their positions and window starts
+    const int r_a = warp * 16 + g, r_b = r_a + 8;
+    const int pos_a = pos0 + r_a / G, pos_b = pos0 + r_b / G;
+    const int lo_a = (window > 0 && pos_a + 1 > window) ? pos_a + 1 - window : 0;
+    const int lo_b = (window > 0 && pos_b + 1 > window) ? pos_b + 1 - window : 0;
+
+    float o[NT_O][4];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const float sl2 = scale * 1.4426950408889634f;            // scores in units of log2(e)
+
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int buf = (kb - kb_first) & 1;
+        if (kb < kb_last) load_kv(kb + 1, buf ^ 1);
+        if (kb < kb_last) cp_wait<1>(); else cp_wait<0>();
+        __syncthreads();
+
+        // ---- scores: 16 rows x 64 keys per warp ----
+        float s[KEYS / 8][4];
+#pragma unroll
+        for (int n = 0; n < KEYS / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        {
+            const int m = lane >> 3, rin = lane & 7;
+#pragma unroll
+            for (int np = 0; np < KEYS / 16; ++np) {                 // pairs of 8-key tiles
+                const int key = np * 16 + (m >> 1) * 8 + rin;
+#pragma unroll
+                for (int kt = 0; kt < KT; ++kt) {
+                    uint32_t b[4];
+                    ldmatrix4(b, smem_addr(k_s[buf] + tile_off<HD>(key, kt * 2 + (m & 1))));
+                    mma16816(s[2 * np], qf[kt], b[0], b[1]);
+                    mma16816(s[2 * np + 1], qf[kt], b[2], b[3]);
+                }
+            }
+        }
+        // ---- mask by position, running max and sum ----
+        const int key0 = kb * KEYS + 2 * tg;
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = key0 + n * 8 + e;
+                const bool ok_a = j <= pos_a && j >= lo_a, ok_b = j <= pos_b && j >= lo_b;
+                s[n][e] = ok_a ? s[n][e] * sl2 : -INFINITY;
+                s[n][2 + e] = ok_b ? s[n][2 + e] * sl2 : -INFINITY;
+                mx_a = fmaxf(mx_a, s[n][e]);
+                mx_b = fmaxf(mx_b, s[n][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ca = (m_a == -INFINITY) ? 0.f : exp2f(m_a - mn_a);
+        const float cb = (m_b == -INFINITY) ? 0.f : exp2f(m_b - mn_b);
+        const float ba = (mn_a == -INFINITY) ? 0.f : mn_a, bb = (mn_b == -INFINITY) ? 0.f : mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                s[n][e] = exp2f(s[n][e] - ba);               // exp2(-inf) = 0 for masked keys
+                s[n][2 + e] = exp2f(s[n][2 + e] - bb);
+                sum_a += s[n][e];
+                sum_b += s[n][2 + e];
+            }
+        }
+        l_a = l_a * ca + sum_a;                               // per-thread partial sums; folded across the quad at the end
+        l_b = l_b * cb + sum_b;
+        m_a = mn_a;
+        m_b = mn_b;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) { o[n][0] *= ca; o[n][1] *= ca; o[n][2] *= cb; o[n][3] *= cb; }
+
+        // ---- O += P * V ----
+        {
+            const int m = lane >> 3, rin = lane & 7;
+#pragma unroll
+            for (int kt = 0; kt < KEYS / 16; ++kt) {                 // 16 keys per step
+                uint32_t a[4];
+                a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+                a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+                a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+                a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+                const int key = kt * 16 + (m & 1) * 8 + rin;
+#pragma unroll
+                for (int np = 0; np < NT_O / 2; ++np) {               // pairs of 8-dim tiles
+                    uint32_t b[4];
+                    ldmatrix4_trans(b, smem_addr(v_s[buf] + tile_off<HD>(key, np * 2 + (m >> 1))));
+                    mma16816(o[2 * np], a, b[0], b[1]);
+                    mma16816(o[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                       // the buffer is refilled two steps on
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float ia = l_a > 0.f ? 1.0f / l_a : 0.f, ib = l_b > 0.f ? 1.0f / l_b : 0.f;
+    // ---- write out[token, head, dim] ----
+    if (r_a < n_rows) {
+        __nv_bfloat16* dst = out + (((size_t)row0 + tok0 + r_a / G) * nh + (size_t)kvh * G + r_a % G) * HD;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tg) = pack_bf16(o[n][0] * ia, o[n][1] * ia);
+    }
+    if (r_b < n_rows) {
+        __nv_bfloat16* dst = out + (((size_t)row0 + tok0 + r_b / G) * nh + (size_t)kvh * G + r_b % G) * HD;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tg) = pack_bf16(o[n][2] * ib, o[n][3] * ib);
+    }
+}
+
+}  // namespace pf
+}  // namespace imparo
+
+using namespace imparo;
+
+// bfloat16, head size 64 or 128, at most 8 query heads per kv head; else -8 (the caller uses
+// another kernel).  n_tok is the batch's token count, n_items its requests.
+extern "C" int imparo_attention_prefill(const void* q, const void* k_cache, const void* v_cache,
+                                        const int* item_row_start, const int* item_start_pos, int n_items,
+                                        const int* table, int max_blocks, int page_size, int n_pages,
+                                        int window, float scale, void* out, int n_tok, int nh, int nkv, int hd,
+                                        int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    const int G = nh / nkv;
+    if (G > 8 || (hd != 64 && hd != 128)) return -8;
+    const int TQ = pf::ROWS / G;
+    const long long tiles = (n_tok + TQ - 1) / TQ + n_items;          // an upper bound: every request may end a tile early
+    if (tiles > 0x7fffffffLL || nkv > 65535) return -2;
+    dim3 grid((unsigned)tiles, nkv);
+    cudaError_t e;
+    const size_t smem = (size_t)(pf::ROWS + 4 * pf::KEYS) * hd * 2;
+    static bool configured = false;
+    if (!configured) {
+        e = cudaFuncSetAttribute(pf::attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (pf::ROWS + 4 * pf::KEYS) * 128 * 2);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    if (hd == 64)
+        e = launch(pf::attn_prefill_kernel<64>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
+                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, item_row_start, item_start_pos, n_items, table,
+                   max_blocks, page_size, n_pages, window, scale, (__nv_bfloat16*)out, nh, nkv, status);
+    else
+        e = launch(pf::attn_prefill_kernel<128>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
+                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, item_row_start, item_start_pos, n_items, table,
+                   max_blocks, page_size, n_pages, window, scale, (__nv_bfloat16*)out, nh, nkv, status);
+    return e == cudaSuccess ? 0 : (int)e;
+}

@@ -183,8 +183,21 @@ def _tc_buffers(device, floats: int, counters: int):
 TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that used it are stale
 
 
-def tc_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+# Above this many tokens the library product is faster than the hand-written kernel as it
+# stands (no overlap of epilogue and main loop yet): measured on B200, T = 64 and 2048.
+TC_MAX_TOKENS = 32
+
+
+def tc_max_tokens() -> int:
+    import os
+    v = os.environ.get("IMPARO_TC_MAX_TOKENS")
+    return int(v) if v else TC_MAX_TOKENS
+
+
+def tc_usable(x: torch.Tensor, w: torch.Tensor, any_size: bool = False) -> bool:
     K = x.shape[1]
+    if not any_size and x.shape[0] > tc_max_tokens():
+        return False
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
@@ -194,7 +207,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     epilogue: EPI_STORE_BF16 | EPI_STORE_F32 | EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU
     (w = [gate rows; up rows] of shape [2F, K], out = silu(x gate^T) * (x up^T), [T, F])."""
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
-    _need(tc_usable(x, w), "gemm_tc: bfloat16 operands, K a multiple of 8, 16-byte aligned rows")
+    _need(tc_usable(x, w, any_size=True), "gemm_tc: bfloat16 operands, K a multiple of 8, 16-byte aligned rows")
     T, K = x.shape
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     _need(w.shape[1] == K and (epilogue != EPI_SWIGLU or w.shape[0] % 2 == 0), "gemm_tc: weight shape")
@@ -325,6 +338,26 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
         T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
     _check(rc, "paged_attention_split")
     COUNTS["own"] += 1          # partial + combine
+    return True
+
+
+def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
+                      scale, out, nh, nkv, hd, status) -> bool:
+    """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
+    query heads per kv head).  Returns False, having launched nothing, for other shapes."""
+    if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
+        return False
+    _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status)
+    T = q.shape[0]
+    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "attention_prefill: q/out shapes")
+    _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.shape[0] >= n_items, "block table must be int32 [items, blocks]")
+    _need(item_row_start.numel() >= n_items + 1 and item_start_pos.numel() >= n_items, "attention_prefill: item arrays")
+    _check(_lib.kernels().imparo_attention_prefill(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
+        _stream()), "attention_prefill")
     return True
 
 

@@ -79,7 +79,11 @@ class AttentionMixer(Part):
                                self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
         out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype)
         done = False
-        if nh // self.nkv <= 8 and T <= 65535:
+        if batch.max_tokens_per_item >= 8:
+            # prompt portions: the tensor-core kernel (bfloat16, head size 64 or 128), tiles of one request each
+            done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start, batch.item_start_pos, batch.n_items, table,
+                                         kv.page_size, kv.n_pages, self.window, self.scale, out, nh, self.nkv, hd, rt.status)
+        if not done and nh // self.nkv <= 8 and T <= 65535:
             # keys cut into chunks; the cut depends on the launch's shape (tokens, table width) only
             chunk, n_splits = ops.split_plan(T, self.nkv, table.shape[1] * kv.page_size)
             part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32)
