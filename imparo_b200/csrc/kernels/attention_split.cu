@@ -320,3 +320,59 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
+
+// ---- the variant that allocates nothing (see no_alloc.h) -----------------------------------
+#include "no_alloc.h"
+#include <mutex>
+
+// The scratch of the static variant: partial accumulators, then (max, sum) pairs.  In host
+// code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_scratch[IMPARO_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mutex;
+
+// Device address of the array on the current device; resolved once per device.
+int static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return IMPARO_ERR_STATIC_SCRATCH_ADDRESS;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return IMPARO_ERR_STATIC_SCRATCH_ADDRESS;
+        g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" long long imparo_paged_attention_split_static_need(int n_tok, int nh, int hd, int n_splits) {
+    if (n_tok <= 0 || nh <= 0 || hd <= 0 || n_splits <= 0) return 0;
+    return (long long)n_tok * nh * n_splits * (hd + 2);
+}
+
+extern "C" int imparo_paged_attention_split_static(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                                   const int* positions, const int* item_of_token,
+                                                   const int* table, int max_blocks, int page_size, int n_pages,
+                                                   int window, float scale, void* out,
+                                                   int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                                                   int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    const long long need = imparo_paged_attention_split_static_need(n_tok, nh, hd, n_splits);
+    if (need <= 0 || need > (long long)IMPARO_STATIC_SCRATCH_FLOATS) return IMPARO_ERR_STATIC_SCRATCH_TOO_SMALL;
+    float* base = nullptr;
+    const int rc = static_scratch(&base);
+    if (rc != 0) return rc;
+    float* part_acc = base;
+    float* part_ml = base + (size_t)n_tok * nh * n_splits * hd;     // hd is a multiple of 16: stays 64-byte aligned
+    return imparo_paged_attention_split(q, k_cache, v_cache, dtype, positions, item_of_token, table, max_blocks, page_size,
+                                        n_pages, window, scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits,
+                                        status, stream);
+}
