@@ -205,6 +205,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
+    ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "zeraix/imparo is a Rust workspace (no setup.py or pyproject.toml: "
@@ -224,12 +225,18 @@ def main():
         cfg["num_hidden_layers"] = args.layers
     steps, warmup = args.steps, max(args.warmup, 3)
     rng = np.random.default_rng(0)
-    max_batch = args.batch if (args.skip_points or args.only_decode) else max(64, args.batch)
+    max_batch = args.batch if (args.skip_points or args.only_decode or args.only_prefill) else max(64, args.batch)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=max_batch, page_size=PAGE,
                     max_step_tokens=PROMPT, random_init={"norm_jitter": 0.0})
     pk = peaks()
     weight_bytes, kv_per_token, prefill_flops, n_params = model_numbers(engine)
 
+    if args.only_prefill:
+        pre_ms = measure_prefill(engine, reps=max(1, steps), warmup=warmup, rng=rng)
+        print(json.dumps({"metric": "prefill only", "tokens": PROMPT, "ms": round(pre_ms, 3),
+                          "value": round(PROMPT * 1000.0 / pre_ms, 1),
+                          "frac": round(prefill_flops(PROMPT) / (pre_ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}))
+        return 0
     with ClockSampler() as clocks:
         ms, launches, library, ctx = measure_decode(engine, args.batch, steps, warmup, rng)
     value = args.batch * 1000.0 / ms
