@@ -260,6 +260,194 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     }
 }
 
+
+// ---- single query tokens (decode rows), split over key chunks, on tensor cores -----------
+// One CTA per (key chunk, kv head, token).  The token's G query heads are rows 0..G-1 of a
+// 16-row MMA tile (the rest is padding).  The chunk's keys are staged 64 at a time with
+// cp.async (double buffer); each of the four warps scores 16 of the 64 keys, keeps its own
+// running max / sum / accumulator, and the warps are folded in warp order at the end.  The
+// result is an unnormalised partial per (token, head, chunk) for the ordered combine kernel
+// of attention_split.cu (same scratch layout: part_acc [T, nh, S, HD], part_ml [T, nh, S, 2]).
+// The general-purpose version of this kernel (any head size, 32-bit) is attention_split.cu;
+// this one exists because the scalar version is bound by instruction issue, not by memory.
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                       const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
+                       const int* __restrict__ item_of_token, const int* __restrict__ table, int max_blocks,
+                       int page_size, int n_pages, int window, float scale, float* __restrict__ part_acc,
+                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int* status) {
+    constexpr int CH = HD / 8, KT = HD / 16, NT_O = HD / 8;
+    extern __shared__ __align__(128) uint8_t pf_smem[];
+    uint8_t* q_s = pf_smem;                                            // [16][HD]
+    uint8_t* k_s[2] = {q_s + 16 * HD * 2, q_s + 16 * HD * 2 + KEYS * HD * 2};
+    uint8_t* v_s[2] = {k_s[1] + KEYS * HD * 2, k_s[1] + 2 * KEYS * HD * 2};
+    float* wm = reinterpret_cast<float*>(v_s[1] + KEYS * HD * 2);     // [4][8]
+    float* wl = wm + 32;                                               // [4][8]
+    float* wacc = wl + 32;                                             // [4][8][HD]
+    pdl_wait();
+    pdl_trigger();
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int G = nh / nkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
+    const int pos = positions[t];
+    const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int begin = max(lo, split * chunk), end = min(pos + 1, (split + 1) * chunk);
+    const int h0 = kvh * G;
+    const size_t part_base = ((size_t)t * nh + h0) * n_splits + split;         // + g * n_splits
+    if (begin >= end) {
+        if (tid < G) {
+            part_ml[(part_base + (size_t)tid * n_splits) * 2] = -INFINITY;
+            part_ml[(part_base + (size_t)tid * n_splits) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
+    const size_t kvw = (size_t)nkv * HD;
+
+    for (int i = tid; i < 16 * CH; i += THREADS) {
+        const int r = i / CH, c = i % CH;
+        const bool valid = r < G;
+        cp_async16(q_s + tile_off<HD>(r, c), q + ((size_t)t * nh + h0 + (valid ? r : 0)) * HD + c * 8, valid);
+    }
+    cp_commit();
+    const int kb_first = begin / KEYS, kb_last = (end - 1) / KEYS;
+    auto load_kv = [&](int kb, int buf) {
+        for (int i = tid; i < KEYS * CH; i += THREADS) {
+            const int r = i / CH, c = i % CH;
+            const int j = kb * KEYS + r;
+            bool valid = j >= begin && j < end;
+            size_t rowi = 0;
+            if (valid) {
+                const int blk = j / page_size;
+                const int page = blk < max_blocks ? tab[blk] : -1;
+                if (page < 0 || page >= n_pages) {
+                    if (c == 0) report(status, IMPARO_ST_PAGE_RANGE, 7, t, page);
+                    valid = false;
+                } else {
+                    rowi = (size_t)page * page_size + (j % page_size);
+                }
+            }
+            const size_t off = rowi * kvw + (size_t)kvh * HD + c * 8;
+            cp_async16(k_s[buf] + tile_off<HD>(r, c), k_cache + off, valid);
+            cp_async16(v_s[buf] + tile_off<HD>(r, c), v_cache + off, valid);
+        }
+        cp_commit();
+    };
+    load_kv(kb_first, 0);
+    cp_wait<1>();
+    __syncthreads();
+    uint32_t qf[KT][4];
+    {
+        const int m = lane >> 3, rin = lane & 7;
+        const int r = (m & 1) * 8 + rin;
+#pragma unroll
+        for (int kt = 0; kt < KT; ++kt) ldmatrix4(qf[kt], smem_addr(q_s + tile_off<HD>(r, kt * 2 + (m >> 1))));
+    }
+    float o[NT_O][2];                                                   // rows 0..7 only (G <= 8)
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sl2 = scale * 1.4426950408889634f;
+
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int buf = (kb - kb_first) & 1;
+        if (kb < kb_last) load_kv(kb + 1, buf ^ 1);
+        if (kb < kb_last) cp_wait<1>(); else cp_wait<0>();
+        __syncthreads();
+        const int mi = lane >> 3, rin = lane & 7;
+        // this warp's 16 keys of the tile
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        {
+            const int key = warp * 16 + (mi >> 1) * 8 + rin;
+#pragma unroll
+            for (int kt = 0; kt < KT; ++kt) {
+                uint32_t b[4];
+                ldmatrix4(b, smem_addr(k_s[buf] + tile_off<HD>(key, kt * 2 + (mi & 1))));
+                mma16816(s[0], qf[kt], b[0], b[1]);
+                mma16816(s[1], qf[kt], b[2], b[3]);
+            }
+        }
+        const int key0 = kb * KEYS + warp * 16 + 2 * tg;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = key0 + n * 8 + e;
+                s[n][e] = (j >= begin && j < end) ? s[n][e] * sl2 : -INFINITY;
+                mx = fmaxf(mx, s[n][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m_run, mx);
+        const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mn);
+        const float base = (mn == -INFINITY) ? 0.f : mn;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) { s[n][e] = exp2f(s[n][e] - base); sum += s[n][e]; }
+        l_run = l_run * corr + sum;
+        m_run = mn;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+        {
+            uint32_t a[4];
+            a[0] = pack_bf16(s[0][0], s[0][1]);
+            a[1] = 0u;                                                  // rows 8..15 are padding
+            a[2] = pack_bf16(s[1][0], s[1][1]);
+            a[3] = 0u;
+            const int key = warp * 16 + (mi & 1) * 8 + rin;
+#pragma unroll
+            for (int np = 0; np < NT_O / 2; ++np) {
+                uint32_t b[4];
+                ldmatrix4_trans(b, smem_addr(v_s[buf] + tile_off<HD>(key, np * 2 + (mi >> 1))));
+                float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f};
+                float c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
+                mma16816(c0, a, b[0], b[1]);
+                mma16816(c1, a, b[2], b[3]);
+                o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1];
+                o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
+            }
+        }
+        __syncthreads();
+    }
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    // ---- fold the four warps (row g = head h0 + g), in warp order ----
+    if (tg == 0) { wm[warp * 8 + g] = m_run; wl[warp * 8 + g] = l_run; }
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+        wacc[((size_t)warp * 8 + g) * HD + n * 8 + 2 * tg] = o[n][0];
+        wacc[((size_t)warp * 8 + g) * HD + n * 8 + 2 * tg + 1] = o[n][1];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += THREADS) {
+        const int gg = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 8 + gg]);
+        float acc = 0.f, L = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = wm[w * 8 + gg];
+                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                acc += wacc[((size_t)w * 8 + gg) * HD + d] * f;
+                L += wl[w * 8 + gg] * f;
+            }
+        }
+        const size_t pb = part_base + (size_t)gg * n_splits;
+        part_acc[pb * HD + d] = acc;
+        // the combine kernel works in natural-log units
+        if (d == 0) { part_ml[pb * 2] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; part_ml[pb * 2 + 1] = L; }
+    }
+}
+
 }  // namespace pf
 }  // namespace imparo
 
@@ -298,4 +486,43 @@ extern "C" int imparo_attention_prefill(const void* q, const void* k_cache, cons
                    (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, item_row_start, item_start_pos, n_items, table,
                    max_blocks, page_size, n_pages, window, scale, (__nv_bfloat16*)out, nh, nkv, status);
     return e == cudaSuccess ? 0 : (int)e;
+}
+
+
+// Implemented in attention_split.cu: the ordered combine of split partials.
+extern "C" int imparo_attention_split_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
+                                              int n_rows, int hd, int n_splits, cudaStream_t stream);
+
+// Single query tokens on tensor cores: bfloat16, head size 64 or 128, at most 8 query heads per
+// kv head; else -8.  Scratch as for imparo_paged_attention_split.
+extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* positions, const int* item_of_token,
+                                           const int* table, int max_blocks, int page_size, int n_pages,
+                                           int window, float scale, void* out, float* part_acc, float* part_ml,
+                                           int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                                           int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
+    if (n_tok > 65535 || nkv > 65535 || chunk < 64 || n_splits < 1) return -2;
+    dim3 grid(n_splits, nkv, n_tok);
+    const size_t smem = (size_t)(16 + 4 * pf::KEYS) * hd * 2 + 64 * 4 + (size_t)4 * 8 * hd * 4;
+    static bool configured = false;
+    cudaError_t e;
+    if (!configured) {
+        e = cudaFuncSetAttribute(pf::attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (16 + 4 * pf::KEYS) * 128 * 2 + 64 * 4 + 4 * 8 * 128 * 4);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    if (hd == 64)
+        e = launch(pf::attn_decode_mma_kernel<64>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
+                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
+                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, status);
+    else
+        e = launch(pf::attn_decode_mma_kernel<128>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
+                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
+                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, status);
+    if (e != cudaSuccess) return (int)e;
+    return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, stream);
 }

@@ -399,18 +399,21 @@ static int max_clusters(int cluster) {
     return n;
 }
 
-// Ring depth per token tile.  Small token tiles keep the ring shallow enough for two or three
-// CTAs per SM: one CTA's prologue and epilogue then overlap another's streaming, and more
-// clusters are resident at once.
+// Ring depth.  A launch whose CTAs all fit on the device at once (one per SM: decode products)
+// runs a deep ring, so that one CTA alone keeps enough bytes in flight to cover the memory
+// latency; a launch with several CTAs per SM gets a shallow ring per CTA (the CTAs together
+// cover the latency, and one CTA's epilogue overlaps another's streaming).
+constexpr int deep_stages_for(int nt) { return nt <= 16 ? 11 : nt <= 32 ? 10 : nt <= 64 ? 8 : nt == 128 ? 6 : 4; }
 constexpr int stages_for(int nt) { return nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 
 template <int EPI>
 static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+    const bool deep = (long long)grid.x * grid.y * grid.z <= 148;
     switch (nt) {
-        case 16: return launch<16, stages_for(16), EPI>(mw, mx, p, grid, stream);
-        case 32: return launch<32, stages_for(32), EPI>(mw, mx, p, grid, stream);
-        case 64: return launch<64, stages_for(64), EPI>(mw, mx, p, grid, stream);
-        case 128: return launch<128, stages_for(128), EPI>(mw, mx, p, grid, stream);
+        case 16: return deep ? launch<16, deep_stages_for(16), EPI>(mw, mx, p, grid, stream) : launch<16, stages_for(16), EPI>(mw, mx, p, grid, stream);
+        case 32: return deep ? launch<32, deep_stages_for(32), EPI>(mw, mx, p, grid, stream) : launch<32, stages_for(32), EPI>(mw, mx, p, grid, stream);
+        case 64: return deep ? launch<64, deep_stages_for(64), EPI>(mw, mx, p, grid, stream) : launch<64, stages_for(64), EPI>(mw, mx, p, grid, stream);
+        case 128: return deep ? launch<128, deep_stages_for(128), EPI>(mw, mx, p, grid, stream) : launch<128, stages_for(128), EPI>(mw, mx, p, grid, stream);
         case 256: return launch<256, stages_for(256), EPI>(mw, mx, p, grid, stream);
     }
     return -22;
@@ -425,10 +428,10 @@ static int resident_clusters(int nt, int cluster) {
     if (!known[i][cluster]) {
         int n = 0;
         switch (nt) {
-            case 16: n = max_clusters<16, stages_for(16), ADD_F32>(cluster); break;
-            case 32: n = max_clusters<32, stages_for(32), ADD_F32>(cluster); break;
-            case 64: n = max_clusters<64, stages_for(64), ADD_F32>(cluster); break;
-            case 128: n = max_clusters<128, stages_for(128), ADD_F32>(cluster); break;
+            case 16: n = max_clusters<16, deep_stages_for(16), ADD_F32>(cluster); break;
+            case 32: n = max_clusters<32, deep_stages_for(32), ADD_F32>(cluster); break;
+            case 64: n = max_clusters<64, deep_stages_for(64), ADD_F32>(cluster); break;
+            case 128: n = max_clusters<128, deep_stages_for(128), ADD_F32>(cluster); break;
             default: n = max_clusters<256, stages_for(256), ADD_F32>(cluster); break;
         }
         table[i][cluster] = n;

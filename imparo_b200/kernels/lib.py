@@ -80,6 +80,8 @@ def _declare_kernels(lib):
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_paged_attention_split",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_attention_decode_mma",
+             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, P, S])

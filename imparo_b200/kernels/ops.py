@@ -318,12 +318,13 @@ def split_plan(n_tok: int, nkv: int, upper_context: int):
 
 
 def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
-                          out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status) -> bool:
+                          out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True) -> bool:
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
     combine).  Returns False, having launched nothing, when the group size is above 8."""
     if nh // nkv > 8:
         return False
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
+    use_mma = mma and q.dtype == torch.bfloat16 and hd in (64, 128) and chunk >= 64
     T = q.shape[0]
     _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "paged_attention_split: q/out shapes")
     _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
@@ -332,10 +333,17 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     _need(part_acc.dtype == torch.float32 and part_acc.numel() >= T * nh * n_splits * hd
           and part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * n_splits * 2, "split scratch too small")
     _need(T <= 65535, "paged_attention_split: at most 65535 query tokens per launch")
-    rc = _lib.kernels().imparo_paged_attention_split(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
-        table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
-        T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
+    if use_mma:
+        # bfloat16, head 64/128: the tensor-core version (the scalar one is bound by instruction issue)
+        rc = _lib.kernels().imparo_attention_decode_mma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table),
+            table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
+            T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
+    else:
+        rc = _lib.kernels().imparo_paged_attention_split(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
+            table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
+            T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
     _check(rc, "paged_attention_split")
     COUNTS["own"] += 1          # partial + combine
     return True

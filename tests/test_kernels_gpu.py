@@ -234,10 +234,13 @@ def run_attention(kind, q, kc, vc, positions, items, table, page, n_pages, windo
     part_acc = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
     part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
     assert o.paged_attention_split(q, kc, vc, positions, items, table, page, n_pages, window, scale, out, part_acc, part_ml,
-                                   chunk, n_splits, nh, nkv, hd, status)
+                                   chunk, n_splits, nh, nkv, hd, status, mma=(kind == "split_mma"))
 
 
-KINDS = [("general", None), ("split", None), ("split", 64), ("split", 512)]
+# "split": the scalar split-key kernel; "split_mma": its tensor-core version where it applies
+# (bfloat16, head 64 or 128), else the scalar one again
+KINDS = [("general", None), ("split", None), ("split", 64), ("split", 512), ("split_mma", None), ("split_mma", 64),
+         ("split_mma", 512)]
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256), (8, 1, 64)])

@@ -72,7 +72,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(dtype):
         part_ml = torch.empty(T * nh * n_splits * 2, device=DEV)
         assert ops.paged_attention_split(c["q"], c["kc"], c["vc"], c["positions"], c["items"], c["table"], c["page"],
                                          c["n_pages"], None, scale, out_plain, part_acc, part_ml, chunk, n_splits, nh, nkv, hd,
-                                         status)
+                                         status, mma=False)          # the same scalar kernel the static entry point runs
         torch.cuda.synchronize()
         ops.read_status(status)
         assert torch.equal(out_static, out_plain), f"call {call}: the two entry points disagree"
