@@ -111,23 +111,38 @@ struct Params {
     int* status;
     int T, N, K, ldo;        // N = rows of W (for SWIGLU: F, W has 2F rows)
     int splits, kblocks;     // kblocks = ceil(K / BK)
+    // fused RMS norm of the input (NORM kernels): X is the 32-bit stream, normalised here
+    const float* x32;        // [rows, ldx32]
+    const float* norm_w;     // [K]
+    const int* norm_rows;    // optional row gather (token t reads row norm_rows[t])
+    float eps;
+    int ldx32;
 };
 
 // shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
 // buffer of the SwiGLU epilogue.  Tiles are 1024-byte aligned (128-byte swizzle).
-template <int NT, int STAGES, int EPI>
+// NORM: the input is the 32-bit residual stream and its RMS norm is computed here: the four
+// epilogue warps (idle during the main loop otherwise) normalise the CTA's token rows,
+// y = x * 1/sqrt(mean(x^2)+eps) * w (imparo-cpu/src/ops.rs:6-22), round to bfloat16 and write
+// them into shared memory in the MMA's swizzled K-major layout for ALL k-blocks of this CTA;
+// the ring then carries W tiles only.  One kernel less per product and no round trip of the
+// normed activations through global memory.
+template <int NT, int STAGES, int EPI, bool NORM>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = NORM ? A_BYTES : A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* bres = smem + STAGES * STAGE_BYTES;                               // NORM: [kblocks][NT][128 B]
+    uint8_t* aux = bres + (NORM ? (size_t)p.kblocks * B_BYTES : 0);
+    uint64_t* full = reinterpret_cast<uint64_t*>(aux);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* b_ready = acc_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 1);
     int* flags = reinterpret_cast<int*>(tmem_slot + 1);            // [0]: this CTA folds the splits
-    float* exch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // SwiGLU: [64][17], one 16-token chunk at a time
+    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: [64][17], one 16-token chunk at a time
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
@@ -141,6 +156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
+        mbar_init(b_ready, 128);
         flags[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -160,7 +176,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             auto load_w = [&](int i) {
                 const int s = i % STAGES;
                 uint8_t* a = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
+                mbar_expect_tx(&full[s], STAGE_BYTES);          // NORM: the W tile only
                 const int k0 = (kb_begin + i) * BK;
                 if (EPI == SWIGLU_BF16) {
                     tma_load_2d(a, &map_w, &full[s], k0, tile_n * 64);                       // 64 gate rows
@@ -170,12 +186,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 }
             };
             auto load_x = [&](int i) {
+                if (NORM) return;                                // the input rows are made in place by the epilogue warps
                 const int s = i % STAGES;
                 tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_x, &full[s], (kb_begin + i) * BK, tile_t * NT);
             };
             const int early = n_kb < STAGES ? n_kb : STAGES;
             for (int i = 0; i < early; ++i) load_w(i);
-            pdl_wait();
+            if (!NORM) pdl_wait();
             pdl_trigger();
             for (int i = 0; i < early; ++i) load_x(i);
             for (int i = early; i < n_kb; ++i) {
@@ -192,6 +209,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, NT);
             bool ok = true;
+            if (NORM && !mbar_wait(b_ready, 0)) {
+                report(p.status, IMPARO_ST_WAIT_LIMIT, 13, tile_n, split);
+                ok = false;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
@@ -200,7 +222,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                const uint32_t b_addr = NORM ? smem_u32(bres + (size_t)i * B_BYTES) : a_addr + A_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     // 16 elements along K = 32 bytes inside the 128-byte swizzle atom
@@ -216,6 +239,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                       // row of the CTA's W tile
         pdl_wait();                                             // before any global write or residual read
+        if (NORM) {
+            // rows ew, ew+4, ... of the CTA's NT token rows; a warp per row, a lane per 16-byte
+            // chunk (8 elements) of the output, all loads 16 bytes wide
+            const int ew = warp - 2;
+            const int k_lo = kb_begin * BK, k_hi = min(p.K, kb_end * BK);
+            for (int r = ew; r < NT; r += 4) {
+                const int t = tile_t * NT + r;
+                uint8_t* dst_row = bres + (size_t)r * 128;
+                if (t < p.T) {
+                    const float* xr = p.x32 + (size_t)(p.norm_rows ? p.norm_rows[t] : t) * p.ldx32;
+                    float ss = 0.f;
+                    for (int k = lane * 4; k < p.K; k += 128) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + k));
+                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                    }
+                    ss = warp_sum(ss);
+                    const float scale = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+                    for (int k = k_lo + lane * 8; k < kb_end * BK; k += 256) {
+                        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+                        if (k < k_hi) {                                       // K is a multiple of 8: whole chunks only
+                            const float4 x0 = __ldg(reinterpret_cast<const float4*>(xr + k));
+                            const float4 x1 = __ldg(reinterpret_cast<const float4*>(xr + k + 4));
+                            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
+                            const float4 w1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k + 4));
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * scale * w0.x, x0.y * scale * w0.y);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * scale * w0.z, x0.w * scale * w0.w);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * scale * w1.x, x1.y * scale * w1.y);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * scale * w1.z, x1.w * scale * w1.w);
+                            packed = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                                *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+                        }
+                        const int i = k / BK - kb_begin, chunk = (k % BK) >> 3;
+                        *reinterpret_cast<uint4*>(dst_row + (size_t)i * B_BYTES + ((chunk ^ (r & 7)) << 4)) = packed;
+                    }
+                } else {
+                    for (int k = k_lo + lane * 8; k < kb_end * BK; k += 256) {
+                        const int i = k / BK - kb_begin, chunk = (k % BK) >> 3;
+                        *reinterpret_cast<uint4*>(dst_row + (size_t)i * B_BYTES + (chunk << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // generic-proxy writes -> visible to the MMA
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b_ready)) : "memory");
+        }
         bool ok = n_kb == 0 || mbar_wait(acc_ready, 0);
         if (!ok && lane == 0) report(p.status, IMPARO_ST_WAIT_LIMIT, 12, tile_n, split);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -350,17 +417,19 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
     return 0;
 }
 
-template <int NT, int STAGES, int EPI>
+template <int NT, int STAGES, int EPI, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
-    static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
-    auto kern = gemm_kernel<NT, STAGES, EPI>;
-    static bool configured = false;             // per instantiation
+    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
+    static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
+    const size_t smem = fixed + (NORM ? (size_t)p.kblocks * NT * BK * 2 : 0);
+    if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller norms separately
+    auto kern = gemm_kernel<NT, STAGES, EPI, NORM>;
+    static size_t configured = 0;               // per instantiation: the largest size asked for so far
     cudaError_t e;
-    if (!configured) {
+    if (smem > configured) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -384,7 +453,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 template <int NT, int STAGES, int EPI>
 static int max_clusters(int cluster) {
     constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
-    auto kern = gemm_kernel<NT, STAGES, EPI>;
+    auto kern = gemm_kernel<NT, STAGES, EPI, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, cluster);
@@ -399,11 +468,11 @@ static int max_clusters(int cluster) {
     return n;
 }
 
-// Ring depth.  A launch whose CTAs all fit on the device at once (one per SM: decode products)
-// runs a deep ring, so that one CTA alone keeps enough bytes in flight to cover the memory
-// latency; a launch with several CTAs per SM gets a shallow ring per CTA (the CTAs together
-// cover the latency, and one CTA's epilogue overlaps another's streaming).
-constexpr int deep_stages_for(int nt) { return nt <= 16 ? 11 : nt <= 32 ? 10 : nt <= 64 ? 8 : nt == 128 ? 6 : 4; }
+// Ring depth.  Measured in the decode step (batch 8): 11 stages 1.050 ms, 5 stages 1.038 ms,
+// 3 stages 1.076 ms.  A ring of 5 leaves room for a second CTA per SM, and with programmatic
+// dependent launch that second CTA is the NEXT product's: it fills its ring with weights while
+// this one is still streaming, which is worth more than a deeper ring of one's own.
+constexpr int deep_stages_for(int nt) { return nt <= 32 ? 5 : nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 constexpr int stages_for(int nt) { return nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 
 template <int EPI>
@@ -510,4 +579,45 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
         case SWIGLU_BF16: return launch_nt<SWIGLU_BF16>(nt, mw, mx, p, grid, stream);
     }
     return -22;
+}
+
+
+// The same product with the RMS norm of its input fused in: X is the 32-bit stream x32[rows, ldx32]
+// (token t reads row norm_rows[t] when norm_rows is given), normalised with norm_w and eps inside
+// the kernel.  For T <= 32 tokens and K small enough that the CTA's normalised rows stay in shared
+// memory; returns -25 when that does not hold (the caller then norms with its own kernel).
+// epilogue: 0 store bf16, 1 store f32, 3 SwiGLU.
+extern "C" int imparo_gemm_tc_norm(const float* x32, int ldx32, const float* norm_w, const int* norm_rows, float eps,
+                                   const void* w, void* out, int ldo, int T, int N, int K, int epilogue,
+                                   int* status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (T > 32) return -25;
+    if (K <= 0 || K % 8 != 0 || ldx32 % 4 != 0) return -23;
+    if ((((uintptr_t)w) & 15) || (((uintptr_t)x32) & 15)) return -23;
+    if (epilogue != STORE_BF16 && epilogue != STORE_F32 && epilogue != SWIGLU_BF16) return -22;
+    int nt, splits, ncnt;
+    long long sfl;
+    imparo_gemm_tc_plan(T, N, K, epilogue, &nt, &splits, &sfl, &ncnt);
+    const int w_rows = epilogue == SWIGLU_BF16 ? 2 * N : N;
+    CUtensorMap mw;
+    int rc = get_map(w, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, epilogue == SWIGLU_BF16 ? 64u : (uint32_t)BM, &mw);
+    if (rc) return rc;
+    Params p = {};
+    p.out = out; p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
+    p.x32 = x32; p.norm_w = norm_w; p.norm_rows = norm_rows; p.eps = eps; p.ldx32 = ldx32;
+    const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
+    dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
+    if (nt == 16) {
+        switch (epilogue) {
+            case STORE_BF16: return launch<16, 9, STORE_BF16, true>(mw, mw, p, grid, stream);
+            case STORE_F32: return launch<16, 9, STORE_F32, true>(mw, mw, p, grid, stream);
+            default: return launch<16, 9, SWIGLU_BF16, true>(mw, mw, p, grid, stream);
+        }
+    }
+    switch (epilogue) {
+        case STORE_BF16: return launch<32, 5, STORE_BF16, true>(mw, mw, p, grid, stream);
+        case STORE_F32: return launch<32, 5, STORE_F32, true>(mw, mw, p, grid, stream);
+        default: return launch<32, 5, SWIGLU_BF16, true>(mw, mw, p, grid, stream);
+    }
 }

@@ -227,11 +227,78 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
                                          _ptr(scratch), _ptr(cnt), _ptr(status), _stream()), "gemm_tc")
 
 
-def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
+class NormedInput:
+    """The RMS norm of rows of the 32-bit stream, not computed yet: a product that can fuse the
+    norm into its own kernel takes it as it is (gemm_tc_norm); anything else calls tensor(),
+    which runs the norm kernel once into the given buffer."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None):
+        self.x, self.weight, self.eps, self.rows, self._out = x, weight, float(eps), rows, out
+        self._done = False
+
+    @property
+    def shape(self):
+        return self._out.shape
+
+    @property
+    def dtype(self):
+        return self._out.dtype
+
+    @property
+    def device(self):
+        return self._out.device
+
+    def tensor(self) -> torch.Tensor:
+        if not self._done:
+            rmsnorm(self.x, self.weight, self.eps, self._out, self.rows)
+            self._done = True
+        return self._out
+
+
+def as_tensor(x) -> torch.Tensor:
+    return x.tensor() if isinstance(x, NormedInput) else x
+
+
+def fuse_norm() -> bool:
+    """Whether products fuse the RMS norm of their input (IMPARO_FUSE_NORM=1).  Off by default:
+    measured on B200 the fused form is slower in the decode step (1.11 ms against 1.05 ms at
+    batch 8): every CTA redoes the norm of all token rows, and the separate norm kernel already
+    runs while the product prefetches its weights."""
+    import os
+    return os.environ.get("IMPARO_FUSE_NORM", "0") == "1"
+
+
+def _try_fused_norm(x: "NormedInput", w: torch.Tensor, out: torch.Tensor, epilogue: int, status) -> bool:
+    """Run the product with the norm fused in when the kernel takes the case."""
+    if not fuse_norm() or x._done or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or gemm_backend() != "tcgen05":
+        return False
+    T, K = x.shape
+    if T > min(32, tc_max_tokens()) or K % 8 or not w.is_contiguous() or w.data_ptr() % 16 or x.x.stride(0) % 4:
+        return False
+    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    if status is None:
+        key = torch.device(out.device).index or 0
+        status = _status_fallback.get(key)
+        if status is None:
+            status = _status_fallback[key] = new_status(out.device)
+    rc = _lib.kernels().imparo_gemm_tc_norm(_ptr(x.x), x.x.stride(0), _ptr(x.weight), _ptr(x.rows), x.eps, _ptr(w), _ptr(out),
+                                            out.stride(0), T, N, K, epilogue, _ptr(status), _stream())
+    if rc == -25:
+        return False
+    _check(rc, "gemm_tc_norm")
+    return True
+
+
+def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
                   tmp: Optional[torch.Tensor] = None) -> None:
     """out[T, F] = silu(x gate^T) * (x up^T) with w_gu = [gate; up] of shape [2F, K].
     bfloat16 on the tensor-core kernel: one launch, the activation in the epilogue.
     Otherwise: the product into tmp [T, 2F], then the activation kernel."""
+    if isinstance(x, NormedInput):
+        if _try_fused_norm(x, w_gu, out, EPI_SWIGLU, status):
+            return
+        x = x.tensor()
     if x.dtype == torch.bfloat16 and gemm_backend() == "tcgen05" and tc_usable(x, w_gu):
         gemm_tc(x, w_gu, out, EPI_SWIGLU, status)
         return
@@ -240,10 +307,16 @@ def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, out: torch.Tensor, status
     swiglu_act(tmp, out)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
            status: Optional[torch.Tensor] = None) -> None:
     """out[M,N] (+)= x[M,K] @ w[N,K]^T.  float32 x/w -> the FFMA kernel (true 32-bit);
-    bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16."""
+    bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16.
+    x may be a NormedInput: its norm is then fused into the product where the kernel allows."""
+    if isinstance(x, NormedInput):
+        if not accumulate and out.is_contiguous() and out.dtype in (torch.bfloat16, torch.float32) and \
+                _try_fused_norm(x, w, out, EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16, status):
+            return
+        x = x.tensor()
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     M, K = x.shape
     N = w.shape[0]

@@ -20,6 +20,8 @@ from .spec import PagedKV, PartSpec, WeightSpec
 class AttentionMixer(Part):
     """params: hidden, n_heads, n_kv_heads, head_dim, eps, window (None or int), position
     (PartSpec), qk_norm (bool, default True), names (optional dict of tensor names)."""
+    accepts_lazy_input = True
+
 
     NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
              "o": "self_attn.out_proj.weight", "q_norm": "self_attn.q_layernorm.weight",

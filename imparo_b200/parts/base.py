@@ -84,6 +84,10 @@ class Part:
     # tables, slots) from the batch's DEVICE arrays, so a step of single tokens can be captured
     # once and replayed.  A part that reads batch.host in forward() must set this to False.
     graph_safe = True
+    # True when forward() hands its input x straight to ops.linear / ops.linear_swiglu and
+    # never touches it otherwise: the block may then pass the norm unevaluated
+    # (ops.NormedInput) so that the product fuses it.  Parts that read x as a tensor keep False.
+    accepts_lazy_input = False
 
     def __init__(self, params: dict, prefix: str, rt: Runtime):
         self.params = dict(params)

@@ -31,5 +31,11 @@ class PreNormResidualBlock(Part):
 
     def forward(self, x, batch, caches):
         """x: the 32-bit residual stream [tokens, width], updated in place."""
-        self.mixer.forward(self.mixer_norm.forward(x), batch, caches, x)
-        self.ff.forward(self.ff_norm.forward(x), batch, x)
+        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x), batch, caches, x)
+        self.ff.forward(self._normed(self.ff_norm, self.ff, x), batch, x)
+
+    @staticmethod
+    def _normed(norm, consumer, x):
+        if consumer.accepts_lazy_input and hasattr(norm, "lazy"):
+            return norm.lazy(x)
+        return norm.forward(x)

@@ -12,6 +12,8 @@ from .spec import WeightSpec
 
 class SwiGLU(Part):
     """params: hidden, ff, names (optional)."""
+    accepts_lazy_input = True
+
 
     NAMES = {"gate": "feed_forward.w1.weight", "up": "feed_forward.w3.weight", "down": "feed_forward.w2.weight"}
 
@@ -35,9 +37,10 @@ class SwiGLU(Part):
     def forward(self, x, batch, residual):
         rt, T, F = self.rt, x.shape[0], self.ff
         h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype)
-        if x.dtype == torch.bfloat16 and ops.gemm_backend() == "tcgen05" and ops.tc_usable(x, self.w_gu):
-            ops.linear_swiglu(x, self.w_gu, h, rt.status)        # gate/up product with silu(gate)*up in its epilogue
+        if T <= ops.tc_max_tokens() and x.dtype == torch.bfloat16 and ops.gemm_backend() == "tcgen05" \
+                and self.hidden % 8 == 0:
+            gu = None                                            # gate/up product with silu(gate)*up in its epilogue
         else:
             gu = rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype)
-            ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=gu)
+        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=gu)
         ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)

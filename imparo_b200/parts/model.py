@@ -71,5 +71,8 @@ class Model:
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
         """Final norm and head at the wanted rows only: [n_rows, vocab] in 32-bit."""
-        h = self.final_norm.forward(x, rows=rows, n_rows=n_rows, tag="final_normed")
+        if getattr(self.head, "accepts_lazy_input", False) and hasattr(self.final_norm, "lazy"):
+            h = self.final_norm.lazy(x, rows=rows, n_rows=n_rows, tag="final_normed")
+        else:
+            h = self.final_norm.forward(x, rows=rows, n_rows=n_rows, tag="final_normed")
         return self.head.forward(h)

@@ -12,6 +12,8 @@ from .spec import SlotState, WeightSpec
 
 class ShortConvMixer(Part):
     """params: hidden, taps, bias (bool), names (optional)."""
+    accepts_lazy_input = True
+
 
     NAMES = {"in": "conv.in_proj.weight", "conv": "conv.conv.weight", "out": "conv.out_proj.weight",
              "conv_bias": "conv.conv.bias", "in_bias": "conv.in_proj.bias", "out_bias": "conv.out_proj.bias"}

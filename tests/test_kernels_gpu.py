@@ -493,3 +493,47 @@ def test_attention_prefill_far_key_and_refusals():
     assert not o.attention_prefill(z, z, z, None, None, 1, None, 4, 1, None, 1.0, z, 1, 1, 48, None)
     zf = torch.zeros(4, 64, device=DEV)
     assert not o.attention_prefill(zf, zf, zf, None, None, 1, None, 4, 1, None, 1.0, zf, 1, 1, 64, None)
+
+
+@pytest.mark.parametrize("T,N,K,epi", [(1, 2048, 2048, "bf16"), (8, 6144, 2048, "bf16"), (8, 3072, 2048, "bf16"), (8, 8192, 2048, "swiglu"),
+                                       (16, 512, 192, "swiglu"), (5, 331, 144, "f32"), (32, 1000, 264, "bf16"), (17, 640, 2048, "f32"),
+                                       (3, 65536, 2048, "f32")])
+def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
+    """ops.linear / ops.linear_swiglu on a NormedInput: the RMS norm of the 32-bit rows is
+    computed inside the tensor-core product.  Against float64, and against the unfused path."""
+    monkeypatch.setenv("IMPARO_FUSE_NORM", "1")
+    o = ops()
+    g = torch.Generator().manual_seed(T * 7 + N)
+    x = torch.randn(40, K, generator=g) * 2
+    wn = 1 + 0.1 * torch.randn(K, generator=g)
+    rows = torch.randperm(40, generator=g)[:T].to(torch.int32)
+    w = bf16_round(torch.randn(2 * N if epi == "swiglu" else N, K, generator=g) * 0.05)
+    eps = 1e-5
+    xs = x[rows.long()].double()
+    normed = (xs * (1.0 / torch.sqrt((xs ** 2).mean(-1, keepdim=True) + eps)) * wn.double()).float()
+    normed = bf16_round(normed).double()                    # what the tensor cores are fed
+    ref = normed @ w.double().T
+    if epi == "swiglu":
+        gate, up = ref[:, :N], ref[:, N:]
+        ref = gate / (1 + torch.exp(-gate)) * up
+    out_dtype = torch.float32 if epi == "f32" else torch.bfloat16
+    results = []
+    for fused in (True, False):
+        buf = torch.empty(T, K, dtype=torch.bfloat16, device=DEV)
+        ni = o.NormedInput(x.to(DEV), wn.to(DEV), eps, buf, rows.to(DEV))
+        if not fused:
+            ni.tensor()                                     # evaluated: the product can no longer fuse it
+        out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+        status = o.new_status(DEV)
+        if epi == "swiglu":
+            o.linear_swiglu(ni, w.to(torch.bfloat16).to(DEV), out, status)
+        else:
+            o.linear(ni, w.to(torch.bfloat16).to(DEV), out, status=status)
+        o.read_status(status)
+        assert ni._done == (not fused)
+        results.append(out.float().cpu().double())
+    tol = 2e-5 if epi == "f32" else 8e-3
+    for r in results:
+        assert (r - ref).abs().max() <= tol * max(1.0, ref.abs().max())
+    # same rounding of the normed rows in both paths: the two results agree far inside bf16 noise
+    assert (results[0] - results[1]).abs().max() <= 1e-2 * max(1.0, ref.abs().max())
