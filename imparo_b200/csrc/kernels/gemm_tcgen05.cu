@@ -117,6 +117,13 @@ struct Params {
     const int* norm_rows;    // optional row gather (token t reads row norm_rows[t])
     float eps;
     int ldx32;
+    // ADD_F32 with the NEXT norm fused behind it: once every CTA of the launch has added its
+    // share into the 32-bit stream `out`, the CTA that finishes last writes
+    // after_out[t, :] = bfloat16(rms_norm(out[t, :], after_w, after_eps)) for every token.
+    __nv_bfloat16* after_out;    // [T, N] or nullptr
+    const float* after_w;        // [N]
+    float after_eps;
+    int* after_counter;          // zero before the launch, left zero
 };
 
 // shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
@@ -158,6 +165,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         mbar_init(acc_ready, 1);
         mbar_init(b_ready, 128);
         flags[0] = 0;
+        flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -369,6 +377,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
+    if (EPI == ADD_F32 && p.after_out != nullptr && warp >= 2) {
+        // The reference fuses the same pair, residual add then the next RMS norm
+        // (imparo-backend/src/lib.rs:2609-2623 add_rms_norm).  Here the product's last CTA does it.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+            const int total = gridDim.x * gridDim.y * gridDim.z;
+            const int prev = atomicAdd(p.after_counter, 1);
+            flags[1] = prev == total - 1;
+            if (prev == total - 1) *p.after_counter = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (flags[1]) {
+            __threadfence();
+            const float* x = reinterpret_cast<const float*>(p.out);
+            for (int t = warp - 2; t < p.T; t += 4) {                 // a warp per token row
+                const float* xr = x + (size_t)t * p.ldo;
+                float ss = 0.f;
+                for (int k = lane * 4; k < p.N; k += 128) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+                ss = warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)p.N + p.after_eps);
+                __nv_bfloat16* orow = p.after_out + (size_t)t * p.N;
+                for (int k = lane * 4; k < p.N; k += 128) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
+                    const float4 w = __ldg(reinterpret_cast<const float4*>(p.after_w + k));
+                    __nv_bfloat162 a = __floats2bfloat162_rn(v.x * scale * w.x, v.y * scale * w.y);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(v.z * scale * w.z, v.w * scale * w.w);
+                    *reinterpret_cast<uint2*>(orow + k) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+                }
+            }
+        }
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -566,7 +609,7 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
     if (rc) return rc;
     rc = get_map(x, (uint64_t)(x_rows_alloc > T ? x_rows_alloc : T), (uint64_t)K, (uint64_t)ldx, (uint32_t)nt, &mx);
     if (rc) return rc;
-    Params p;
+    Params p = {};
     p.out = out; p.scratch = scratch; p.counters = counters; p.status = status;
     p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
     const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
@@ -581,6 +624,32 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
     return -22;
 }
 
+
+// out (32-bit stream) += X W^T, then after_out = bfloat16(rms_norm(out, after_w, after_eps)) by the
+// CTA that finishes last.  N must be a multiple of 4; counter: one int, zero (left zero).
+extern "C" int imparo_gemm_tc_add_norm(const void* x, int ldx, int x_rows_alloc, const void* w, float* out, int ldo,
+                                       int T, int N, int K, const float* after_w, float after_eps, void* after_out,
+                                       int* counter, int* status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || N % 4 != 0 || ldo % 4 != 0) return -23;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)after_out | (uintptr_t)after_w) & 15) return -23;
+    if (!after_w || !after_out || !counter) return -24;
+    int nt, splits, ncnt;
+    long long sfl;
+    imparo_gemm_tc_plan(T, N, K, ADD_F32, &nt, &splits, &sfl, &ncnt);
+    CUtensorMap mw, mx;
+    int rc = get_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BM, &mw);
+    if (rc) return rc;
+    rc = get_map(x, (uint64_t)(x_rows_alloc > T ? x_rows_alloc : T), (uint64_t)K, (uint64_t)ldx, (uint32_t)nt, &mx);
+    if (rc) return rc;
+    Params p = {};
+    p.out = out; p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
+    p.after_out = reinterpret_cast<__nv_bfloat16*>(after_out); p.after_w = after_w; p.after_eps = after_eps; p.after_counter = counter;
+    dim3 grid((N + BM - 1) / BM, (T + nt - 1) / nt, splits);
+    if (grid.y > 65535) return -2;
+    return launch_nt<ADD_F32>(nt, mw, mx, p, grid, stream);
+}
 
 // The same product with the RMS norm of its input fused in: X is the 32-bit stream x32[rows, ldx32]
 // (token t reads row norm_rows[t] when norm_rows is given), normalised with norm_w and eps inside

@@ -21,6 +21,7 @@ class AttentionMixer(Part):
     """params: hidden, n_heads, n_kv_heads, head_dim, eps, window (None or int), position
     (PartSpec), qk_norm (bool, default True), names (optional dict of tensor names)."""
     accepts_lazy_input = True
+    adds_with_linear = True
 
 
     NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",

@@ -88,6 +88,10 @@ class Part:
     # never touches it otherwise: the block may then pass the norm unevaluated
     # (ops.NormedInput) so that the product fuses it.  Parts that read x as a tensor keep False.
     accepts_lazy_input = False
+    # True when the part's LAST write to the residual is ops.linear(..., residual, accumulate=True)
+    # (ops.add_bias after it is fine): the block may then ask that product to compute the next
+    # norm in its own kernel (ops.arm_norm).  A part that writes the residual any other way keeps False.
+    adds_with_linear = False
 
     def __init__(self, params: dict, prefix: str, rt: Runtime):
         self.params = dict(params)

@@ -29,13 +29,39 @@ class PreNormResidualBlock(Part):
     def cache_specs(self):
         return self.mixer.cache_specs()
 
-    def forward(self, x, batch, caches):
-        """x: the 32-bit residual stream [tokens, width], updated in place."""
-        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x), batch, caches, x)
-        self.ff.forward(self._normed(self.ff_norm, self.ff, x), batch, x)
+    def forward(self, x, batch, caches, ready=None, next_norm=None):
+        """x: the 32-bit residual stream [tokens, width], updated in place.
+        ready: this block's mixer-norm input when the block before already produced it.
+        next_norm: the norm part that reads x after this block (the next block's mixer norm);
+        returns its unevaluated/filled input for that block, or None."""
+        from ..kernels import ops
+        h = ready if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
+            self._normed(self.mixer_norm, self.mixer, x, "normed_mixer")
+        ff_in = None
+        if self.mixer.adds_with_linear and self.ff.accepts_lazy_input and self._defers(self.ff_norm):
+            ff_in = self.ff_norm.lazy(x, tag="normed_ff")     # unevaluated: the mixer's output product may fill it
+            ops.arm_norm(x, ff_in)
+        self.mixer.forward(h, batch, caches, x)
+        if ff_in is not None:
+            ops.disarm_norm(x)
+        else:
+            ff_in = self._normed(self.ff_norm, self.ff, x, "normed_ff")
+        nxt = None
+        if next_norm is not None and self.ff.adds_with_linear and self._defers(next_norm):
+            nxt = next_norm.lazy(x, tag="normed_mixer")
+            nxt.owner = next_norm
+            ops.arm_norm(x, nxt)                             # the feed-forward's output product may fill it
+        self.ff.forward(ff_in, batch, x)
+        if nxt is not None:
+            ops.disarm_norm(x)
+        return nxt
 
     @staticmethod
-    def _normed(norm, consumer, x):
+    def _defers(norm) -> bool:
+        return hasattr(norm, "lazy") and getattr(norm, "can_defer", lambda: False)()
+
+    @staticmethod
+    def _normed(norm, consumer, x, tag):
         if consumer.accepts_lazy_input and hasattr(norm, "lazy"):
-            return norm.lazy(x)
-        return norm.forward(x)
+            return norm.lazy(x, tag=tag)
+        return norm.forward(x, tag=tag)

@@ -13,6 +13,7 @@ from .spec import WeightSpec
 class SwiGLU(Part):
     """params: hidden, ff, names (optional)."""
     accepts_lazy_input = True
+    adds_with_linear = True
 
 
     NAMES = {"gate": "feed_forward.w1.weight", "up": "feed_forward.w3.weight", "down": "feed_forward.w2.weight"}

@@ -65,8 +65,17 @@ class Model:
         """Runs the batch's tokens through every schedule entry.  cache_views(entry) gives
         the tuple of bound cache views for that entry.  Returns the residual stream."""
         x = self.embedding.forward(batch.token_ids, batch.n_tokens)
+        ready = None
         for i, e in enumerate(self.schedule):
-            self.layers[e.layer].forward(x, batch, cache_views(i))
+            layer = self.layers[e.layer]
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            if hasattr(layer, "mixer_norm"):
+                # a block may hand the next block its (already computed) norm input
+                ready = layer.forward(x, batch, cache_views(i), ready=ready,
+                                      next_norm=getattr(nxt, "mixer_norm", None) if nxt is not None else None)
+            else:
+                layer.forward(x, batch, cache_views(i))
+                ready = None
         return x
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:

@@ -36,6 +36,10 @@ class RMSNorm(Part):
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
 
+    def can_defer(self) -> bool:
+        """Whether lazy() returns an unevaluated norm (bfloat16 path) rather than computing it."""
+        return self.rt.act_dtype == torch.bfloat16
+
     def lazy(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
              tag: str = "normed"):
         """The norm as an ops.NormedInput: a product that can fuse it does, anything else gets

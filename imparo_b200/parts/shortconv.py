@@ -13,6 +13,7 @@ from .spec import SlotState, WeightSpec
 class ShortConvMixer(Part):
     """params: hidden, taps, bias (bool), names (optional)."""
     accepts_lazy_input = True
+    adds_with_linear = True
 
 
     NAMES = {"in": "conv.in_proj.weight", "conv": "conv.conv.weight", "out": "conv.out_proj.weight",

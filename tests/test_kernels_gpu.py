@@ -537,3 +537,44 @@ def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
         assert (r - ref).abs().max() <= tol * max(1.0, ref.abs().max())
     # same rounding of the normed rows in both paths: the two results agree far inside bf16 noise
     assert (results[0] - results[1]).abs().max() <= 1e-2 * max(1.0, ref.abs().max())
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (8, 2048, 8192), (8, 192, 512), (20, 144, 200), (32, 2048, 2048)])
+def test_product_with_the_next_norm_behind_it(T, N, K, monkeypatch):
+    """linear(..., accumulate=True) into an armed stream: out += x w^T and, in the same kernel,
+    the RMS norm of the updated rows.  Against float64 and against the separate norm kernel."""
+    monkeypatch.setenv("IMPARO_FUSE_ADD_NORM", "1")
+    o = ops()
+    g = torch.Generator().manual_seed(T + N + K)
+    x = bf16_round(torch.randn(T, K, generator=g))
+    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
+    base = torch.randn(T, N, generator=g)
+    wn = 1 + 0.1 * torch.randn(N, generator=g)
+    eps = 1e-6
+    stream = base.to(DEV).clone()
+    buf = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ni = o.NormedInput(stream, wn.to(DEV), eps, buf)
+    o.arm_norm(stream, ni)
+    status = o.new_status(DEV)
+    o.linear(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), stream, accumulate=True, status=status)
+    o.read_status(status)
+    assert ni._done                                             # filled by the product's own kernel
+    ref_stream = base.double() + x.double() @ w.double().T
+    assert (stream.cpu().double() - ref_stream).abs().max() <= 1e-5 * max(1.0, ref_stream.abs().max())
+    s64 = stream.cpu().double()
+    ref_norm = s64 * (1.0 / torch.sqrt((s64 ** 2).mean(-1, keepdim=True) + eps)) * wn.double()
+    assert (buf.float().cpu().double() - ref_norm).abs().max() <= 8e-3 * ref_norm.abs().max()
+    sep = torch.empty_like(buf)
+    o.rmsnorm(stream, wn.to(DEV), eps, sep)
+    assert (buf.float() - sep.float()).abs().max() <= 1.6e-2 * ref_norm.abs().max()
+    # a later write to the stream voids the filled norm
+    o.add_bias(stream, torch.ones(N, device=DEV))
+    assert not ni._done
+    # a second product into the same stream: the counter was left clean
+    ni2 = o.NormedInput(stream, wn.to(DEV), eps, buf)
+    o.arm_norm(stream, ni2)
+    o.linear(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), stream, accumulate=True, status=status)
+    o.read_status(status)
+    assert ni2._done
+    o.rmsnorm(stream, wn.to(DEV), eps, sep)
+    assert (buf.float() - sep.float()).abs().max() <= 1.6e-2 * ref_norm.abs().max() + 0.1
