@@ -132,37 +132,79 @@ class Engine:
             index[rid] = i
         failed: List[int] = []
         t0 = time.perf_counter()
+        gen = {rid: 0 for rid in tokens}        # tokens sampled so far per request (values may still be on the device)
+        dead = set()                            # ended by a stop token
+        zombies = set()                         # ended, but still part of the step in flight: aborted after it
+        carry = None                            # (wanting entries, PendingSample): sampled, values not read yet
+
+        def settle(c) -> None:
+            """Read a step's sampled ids and book them.  The scheduler was already told that
+            these requests go on; one that hit a stop token is ended now (or after the step in
+            flight, if it is part of it)."""
+            entries, pending = c
+            for e, tok in zip(entries, pending.result()):
+                r = e.request
+                if r in dead:
+                    continue
+                if tok in stops:
+                    dead.add(r)
+                    if sched.abort(r) == -2:
+                        zombies.add(r)
+                else:
+                    out[index[r]].append(tok)
+                    tokens[r].append(tok)
+
         idle = 0
-        while sched.has_work():
-            plan = sched.plan()
+        while carry is not None or sched.has_work():
+            plan = sched.plan() if sched.has_work() else []
             for rid in sched.take_failed():
                 failed.append(index[rid])
             if not plan:
+                if carry is not None:
+                    settle(carry)
+                    carry = None
+                    continue
                 idle += 1
                 if idle > 2:
                     raise RuntimeError("the scheduler has requests but plans no step")
                 continue
             idle = 0
-            items = [StepItem(e.request, tokens[e.request][e.start:e.start + e.count],
-                              [e.count - 1] if e.want else []) for e in plan]
+            # A step of single tokens for exactly the requests whose ids were just sampled takes
+            # them on the device; anything else needs the values on the host first.
+            fed = (carry is not None and all(e.count == 1 and e.want for e in plan)
+                   and [e.request for e in plan] == [e.request for e in carry[0]])
+            if carry is not None and not fed:
+                settle(carry)
+                carry = None
+            if fed:
+                items = [StepItem(e.request, [0], [0]) for e in plan]
+                device_tokens = carry[1].dev_ids
+            else:
+                items = [StepItem(e.request, tokens[e.request][e.start:e.start + e.count],
+                                  [e.count - 1] if e.want else []) for e in plan]
+                device_tokens = None
             try:
-                logits = self.step_fn(items, manage_cache=False)
+                logits = self.step_fn(items, manage_cache=False, device_tokens=device_tokens)
             except Exception:
                 sched.step_done(False)
                 raise
             sched.step_done(True)
-            wanting = [e for e in plan if e.want]
-            if wanting:
-                ids = self.sampler.sample(logits, [temps[index[e.request]] for e in wanting],
-                                          [seeds[index[e.request]] for e in wanting],
-                                          [len(out[index[e.request]]) for e in wanting])
-                for e, tok in zip(wanting, ids):
-                    i = index[e.request]
-                    eos = tok in stops
-                    if not eos:
-                        out[i].append(tok)
-                        tokens[e.request].append(tok)
-                    sched.on_token(e.request, eos)
+            if fed:
+                settle(carry)                   # while the step just launched runs
+                carry = None
+            for r in [z for z in zombies]:
+                if sched.abort(r) != -2:
+                    zombies.discard(r)
+            wanting = [e for e in plan if e.want and e.request not in dead]
+            all_wanting = [e for e in plan if e.want]
+            if all_wanting:
+                pending = self.sampler.sample_async(logits, [temps[index[e.request]] for e in all_wanting],
+                                                    [seeds[index[e.request]] for e in all_wanting],
+                                                    [gen[e.request] for e in all_wanting])
+                for e in wanting:
+                    gen[e.request] += 1
+                    sched.on_token(e.request, False)          # optimistic: a stop token is booked when it is read
+                carry = (all_wanting, pending)
             self._stats["steps"] += 1
             self._stats["prompt_tokens"] += sum(e.count for e in plan if e.count > 1 or e.start == 0)
             self._stats["decode_tokens"] += len(wanting)

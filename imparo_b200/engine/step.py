@@ -200,14 +200,20 @@ class StepFunction:
         if total > self.max_step_tokens:
             raise ValueError(f"a step holds at most {self.max_step_tokens} tokens, found {total}")
 
-    def __call__(self, items: Sequence[StepItem], manage_cache: bool = True) -> Optional[torch.Tensor]:
+    def __call__(self, items: Sequence[StepItem], manage_cache: bool = True,
+                 device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the step.  Returns logits [wanted, vocab] (float32, on the device) in the
         order of items and of want, or None when nothing was wanted.
 
         manage_cache=True: pages for the new tokens are taken here (all items or none;
         CacheFull leaves everything as it was), and the cache advances once the step has
         been issued without error.  manage_cache=False: the caller (the scheduler) has
-        reserved the pages and commits or abandons the step itself."""
+        reserved the pages and commits or abandons the step itself.
+
+        device_tokens: int32 ids on the device, one per token of the batch in order; they replace
+        the items' token values (which are then placeholders).  This is how a decode step takes
+        the ids the previous step sampled without a round trip through the host (the reference's
+        pipelined decode does the same: imparo-model/src/lib.rs:2457-2537 queue_step / argmax_feed)."""
         self.check_items(items)
         cache = self.cache
         if manage_cache:
@@ -222,6 +228,8 @@ class StepFunction:
                 raise
         try:
             batch = self.build_batch(items)
+            if device_tokens is not None:
+                batch.token_ids.copy_(device_tokens[:batch.n_tokens])
             fresh = [int(s) for s, p in zip(batch.host["slots"], batch.host["start_pos"]) if p == 0]
             if fresh and cache.state:
                 idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)

@@ -28,39 +28,62 @@ def uniform_for(seed: int, step: int) -> float:
     return (z >> 40) / float(1 << 24)
 
 
+class PendingSample:
+    """Ids sampled on the device whose copy to the host is under way.  dev_ids can feed the
+    next step on the device at once; result() waits for the copy and returns the ids."""
+
+    def __init__(self, dev_ids: torch.Tensor, host_ids: torch.Tensor, event: torch.cuda.Event):
+        self.dev_ids, self._host, self._event = dev_ids, host_ids, event
+
+    def result(self) -> List[int]:
+        self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
+    RING = 3        # a step's ids stay valid while the next two steps sample
+
     def __init__(self, device, max_rows: int = 1024):
         self.device = device
         self._cap = 0
+        self._turn = 0
         self._grow(max_rows)
 
     def _grow(self, n: int) -> None:
         if n <= self._cap:
             return
         self._cap = n
-        self._host_in = torch.empty((2, n), dtype=torch.float32, pin_memory=True)
+        self._host_in = [torch.empty((2, n), dtype=torch.float32, pin_memory=True) for _ in range(self.RING)]
         self._dev_in = torch.empty((2, n), dtype=torch.float32, device=self.device)
-        self._dev_out = torch.empty(n, dtype=torch.int32, device=self.device)
-        self._host_out = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        self._dev_outs = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(self.RING)]
+        self._host_outs = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(self.RING)]
 
     def sample(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
                seeds: Optional[Sequence[int]] = None, steps: Optional[Sequence[int]] = None) -> List[int]:
         """One token id per row of logits.  temperatures None or all 0: greedy.  Row r with
         temperature > 0 uses uniform_for(seeds[r], steps[r]).  Reads the ids back (this is
         the step's device-to-host copy) and returns them as a list."""
+        return self.sample_async(logits, temperatures, seeds, steps).result()
+
+    def sample_async(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
+                     seeds: Optional[Sequence[int]] = None, steps: Optional[Sequence[int]] = None) -> PendingSample:
+        """Like sample(), without waiting: the kernel and the device-to-host copy are queued."""
         n = logits.shape[0]
         self._grow(n)
-        out = self._dev_out[:n]
+        self._turn = (self._turn + 1) % self.RING
+        out = self._dev_outs[self._turn][:n]
         if temperatures is None or not any(t > 0 for t in temperatures):
             ops.sample_rows(logits, None, None, out)
         else:
-            h = self._host_in
+            h = self._host_in[self._turn]
             for r in range(n):
                 t = float(temperatures[r])
                 h[0, r] = t
                 h[1, r] = uniform_for(seeds[r], steps[r]) if t > 0 else 0.0
             self._dev_in[:, :n].copy_(h[:, :n], non_blocking=True)
             ops.sample_rows(logits, self._dev_in[0, :n], self._dev_in[1, :n], out)
-        self._host_out[:n].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._host_out[:n].tolist()
+        host = self._host_outs[self._turn][:n]
+        host.copy_(out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return PendingSample(out, host, ev)
