@@ -11,8 +11,8 @@ from tests.tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
 
-PAGE = {"A": 16, "B": 4, "C": 8}
-LENGTHS = {"A": [70, 45, 96, 33, 64, 51, 80], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58]}
+PAGE = {"A": 16, "B": 4, "C": 8, "D": 32}
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51, 80], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [44, 71, 36, 60]}
 
 
 def engine_for(name, dtype, steps, parallel=4):
@@ -24,7 +24,7 @@ def engine_for(name, dtype, steps, parallel=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
 def test_family(name, dtype, family):
     reqs = make_requests(name, LENGTHS[name])
@@ -95,3 +95,42 @@ def test_state_slots_and_pages_start_clean_when_used_again():
     reqs = dict(a, **b)
     eng = engine_for(name, "float32", steps, parallel=1)       # one slot: it must be reused
     check_trace(eng, steps, name, reqs, "float32")
+
+
+def test_full_width_layers_bfloat16_against_32_bit():
+    """Four layers of LFM2-1.2B width (hidden 2048, 32 heads in 8 groups, head 64, ff 8192,
+    vocabulary 65536): the sizes the tensor-core kernels are tuned for, which the tiny models
+    never reach (split-K clusters, 128-row weight tiles, 64-key attention tiles, several key
+    chunks).  The bfloat16 path (tensor cores) against the 32-bit path (FFMA product, scalar
+    attention): different kernels, same weights up to rounding."""
+    import torch
+    from imparo_b200.engine import Engine, StepItem
+    cfg = {"architectures": ["Lfm2ForCausalLM"], "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 4,
+           "layer_types": ["conv", "full_attention", "conv", "full_attention"], "num_attention_heads": 32,
+           "num_key_value_heads": 8, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+           "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_embedding": True}
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, 65536, 700).tolist()
+    tail = rng.integers(0, 65536, 6).tolist()
+    results = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(config=cfg, seed=7, dtype=dtype, ctx=1024, parallel=2, page_size=16, max_step_tokens=1024,
+                     random_init={"norm_jitter": 0.1, "matrix_std": 0.02})
+        eng.add_request(1)
+        rows = [eng.step([StepItem(1, prompt[:300], [0, 150, 299])]).cpu().numpy()]
+        rows.append(eng.step([StepItem(1, prompt[300:], [0, 399])]).cpu().numpy())
+        for t in tail:                                    # single tokens: the decode kernels
+            rows.append(eng.step([StepItem(1, [t], [0])]).cpu().numpy())
+        eng.check_device_status()
+        eng.end_request(1)
+        results[dtype] = np.concatenate(rows)
+        del eng
+        torch.cuda.empty_cache()
+    ref, got = results["float32"], results["bfloat16"]
+    assert np.isfinite(ref).all() and np.isfinite(got).all()
+    scale = np.abs(ref).max()
+    assert scale > 0.1
+    err = np.abs(got - ref).max()
+    assert err <= 4e-2 * scale, (err, scale)
+    # and the rows are not all alike (a kernel that ignored its input would pass the bound above)
+    assert np.abs(ref[0] - ref[-1]).max() > 0.2 * scale

@@ -33,4 +33,16 @@ TINY_C = {
     "tie_embedding": True, "max_position_embeddings": 4096, "sliding_window": 24,
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# a width that is no multiple of 8 (no 16-byte rows for the tensor-core product: the library
+# product takes over), a prime vocabulary, as many kv heads as heads, head size set by its own key
+TINY_D = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 257, "hidden_size": 100, "num_hidden_layers": 3,
+    "layer_types": ["full_attention", "conv", "full_attention"],
+    "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 16,
+    "block_ff_dim": 118, "block_auto_adjust_ff_dim": False,
+    "conv_L_cache": 5, "conv_bias": True, "rope_theta": 10000.0, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 4096,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
