@@ -38,7 +38,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr uint32_t WAIT_LIMIT = 4000000u;
 
-enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU_BF16 = 3 };
+enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU_BF16 = 3, PARTIAL_F32 = 4 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -155,7 +155,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
     const int tile_t = blockIdx.y;                 // which NT tokens
     int split = blockIdx.z;                        // with split-K: this CTA's rank in its cluster
-    if (p.splits > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
+    // PARTIAL_F32: the splits are plain CTAs (blockIdx.z), each stores its partial tile and is done
+    const bool clustered = EPI != PARTIAL_F32 && p.splits > 1;
+    if (clustered) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(split));
     const int kb_begin = (int)(((long long)p.kblocks * split) / p.splits);
     const int kb_end = (int)(((long long)p.kblocks * (split + 1)) / p.splits);
     const int n_kb = kb_end - kb_begin;
@@ -321,7 +323,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             }
         } else {
             const int n = tile_n * BM + row;
-            if (p.splits == 1) {
+            if (EPI == PARTIAL_F32) {
+                // this split's partial tile -> scratch[split][token][n]; whoever reads the stream next
+                // adds the splits in order (rows.cu: add_partials_rmsnorm)
+                float* part = p.scratch + (size_t)split * p.T * p.N;
+#pragma unroll 1
+                for (int c = 0; c < NT; c += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c, v);
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < p.T) part[(size_t)t * p.N + n] = v[j];
+                        }
+                    }
+                }
+            } else if (p.splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < NT; c += 16) {
                     float v[16];
@@ -347,7 +365,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             }
         }
     }
-    if (p.splits > 1) {
+    if (clustered) {
         // every thread of every CTA of the cluster: partials are written / may be read
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -483,7 +501,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = grid.z;          // the splits of a tile are one cluster
+    attr[0].val.clusterDim.z = EPI == PARTIAL_F32 ? 1 : grid.z;     // the splits of a tile are one cluster
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
@@ -572,7 +590,14 @@ extern "C" int imparo_gemm_tc_plan(int T, int N, int K, int epilogue, int* token
     const int tok_tiles = (T + nt - 1) / nt;
     const int kblocks = (K + BK - 1) / BK;
     int s = 1;
-    if (epilogue != SWIGLU_BF16) {
+    if (epilogue == PARTIAL_F32) {
+        // plain CTAs, no cluster: as many splits as fill the device once, at least 4 k-blocks each
+        const int tiles = row_tiles * tok_tiles;
+        s = tiles >= 148 ? 1 : 148 / tiles;
+        if (s > kblocks / 4) s = kblocks / 4;
+        if (s < 1) s = 1;
+        if (s > 16) s = 16;
+    } else if (epilogue != SWIGLU_BF16) {
         // The splits of a tile are one cluster (at most 8 CTAs, the portable size).  Take the
         // cluster size that puts the most CTAs on the device in ONE wave: all the tiles'
         // clusters must be resident together.  Never cut K below 4 blocks per split.
@@ -586,7 +611,7 @@ extern "C" int imparo_gemm_tc_plan(int T, int N, int K, int epilogue, int* token
     }
     *token_tile = nt;
     *splits = s;
-    *scratch_floats = 0;                        // partials live in the cluster's shared memory
+    *scratch_floats = epilogue == PARTIAL_F32 ? (long long)s * T * N : 0;   // else partials live in the cluster's shared memory
     *n_counters = 0;
     return 0;
 }
@@ -620,6 +645,9 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
         case STORE_F32: return launch_nt<STORE_F32>(nt, mw, mx, p, grid, stream);
         case ADD_F32: return launch_nt<ADD_F32>(nt, mw, mx, p, grid, stream);
         case SWIGLU_BF16: return launch_nt<SWIGLU_BF16>(nt, mw, mx, p, grid, stream);
+        case PARTIAL_F32:
+            if (!scratch) return -24;
+            return launch_nt<PARTIAL_F32>(nt, mw, mx, p, grid, stream);
     }
     return -22;
 }

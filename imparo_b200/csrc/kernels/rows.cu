@@ -46,6 +46,36 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
+// ---- stream += split partials, then RMS norm ----------------------------------------------
+// A product that was cut along K leaves its partial results part[s][row][:] (s = 0..S-1) instead
+// of adding them into the 32-bit stream itself.  This kernel adds them in split order (the same
+// sum every time), writes the stream back, and — when out is given — norms the updated row in the
+// same pass.  The reference fuses the same pair, residual add then norm
+// (imparo-backend/src/lib.rs:2609-2623 add_rms_norm).
+template <typename TOut>
+__global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part, int n_splits,
+                                            size_t split_stride, const float* __restrict__ w, float eps,
+                                            TOut* __restrict__ out, int width) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * width;
+    const float* pr = part + (size_t)r * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = xr[i];
+        for (int s = 0; s < n_splits; ++s) v += pr[(size_t)s * split_stride + i];
+        xr[i] = v;
+        ss += v * v;
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TOut* o = out + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);   // own writes
+}
+
 // ---- silu(gate) * up ----------------------------------------------------------------
 // gu: [T, 2F] rows = [gate | up]; out: [T, F]
 template <typename T>
@@ -128,6 +158,23 @@ extern "C" int imparo_add_bias(void* out, int dtype, const float* bias, int n_to
         launch(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out, bias, n_tok, width);
     else if (dtype == IMPARO_DT_BF16)
         launch(add_bias_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, bias, n_tok, width);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// x[r, :] += sum over s of part[s][r][:] (in order), and out = rms_norm(x) when out is not null.
+extern "C" int imparo_add_partials_rmsnorm(float* x, const float* part, int n_splits, long long split_stride,
+                                           const float* w, float eps, void* out, int out_dtype, int n_rows, int width,
+                                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (out == nullptr || out_dtype == IMPARO_DT_F32)
+        launch(add_partials_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, part, n_splits, (size_t)split_stride,
+               w, eps, (float*)out, width);
+    else if (out_dtype == IMPARO_DT_BF16)
+        launch(add_partials_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, part, n_splits,
+               (size_t)split_stride, w, eps, (__nv_bfloat16*)out, width);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -66,6 +66,7 @@ def _declare_kernels(lib):
     S = c_void_p  # cudaStream_t
     _declare(lib, "imparo_embed_gather", [P, I, P, P, I, I, I, P, S])
     _declare(lib, "imparo_rmsnorm", [P, P, P, c_float, P, I, I, I, S])
+    _declare(lib, "imparo_add_partials_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_swiglu_act", [P, P, I, I, I, S])
     _declare(lib, "imparo_add_bias", [P, I, P, I, I, S])
     _declare(lib, "imparo_sgemm_nt", [P, P, P, I, I, I, I, I, I, S])

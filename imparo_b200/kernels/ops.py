@@ -89,6 +89,7 @@ def read_status(status: torch.Tensor) -> None:
 
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
     _cuda(table, ids, out, status)
+    _pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void
     n, width = out.shape
     _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
     _need(out.dtype == torch.float32 and table.shape[1] == width, "embedding output is float32 [tokens, width]")
@@ -96,9 +97,53 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
                                               table.shape[0], _ptr(status), _stream()), "embed_gather")
 
 
+# ---- adds into the 32-bit stream that are still split partials ---------------------------------
+# A decode-sized product into the stream is cut along K over many CTAs.  Instead of folding the
+# splits itself it may leave them in scratch ("pending"); the next reader of the stream — nearly
+# always the RMS norm — adds them in split order and goes on in the same kernel.
+_deferrable = set()      # data_ptr of streams whose next accumulate-product may stay pending
+_pending = {}            # data_ptr -> (scratch, n_splits, rows, width)
+_partials = {}           # device index -> scratch tensor
+
+
+def defer_adds() -> bool:
+    import os
+    return os.environ.get("IMPARO_DEFER_ADDS", "1") == "1"
+
+
+def allow_deferred_add(stream: torch.Tensor) -> None:
+    """The caller promises that whatever reads `stream` next goes through ops.rmsnorm,
+    ops.settle, ops.add_bias or another ops.linear(accumulate=True)."""
+    if defer_adds():
+        _deferrable.add(stream.data_ptr())
+
+
+def disallow_deferred_add(stream: torch.Tensor) -> None:
+    _deferrable.discard(stream.data_ptr())
+
+
+def settle(stream: torch.Tensor) -> None:
+    """Fold pending partials into the stream (no-op when there are none)."""
+    p = _pending.pop(stream.data_ptr(), None)
+    if p is not None:
+        scratch, S, T, N = p
+        _check(_lib.kernels().imparo_add_partials_rmsnorm(_ptr(stream), _ptr(scratch), S, T * N, None, 0.0, None, 0, T, N,
+                                                          _stream()), "add_partials")
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
     _cuda(x, w, out, rows)
+    pend = _pending.get(x.data_ptr())
+    if pend is not None:
+        scratch, S, T, N = pend
+        if rows is None and out.shape == (T, N) and x.shape[1] == N and w.numel() == N and w.dtype == torch.float32:
+            # the stream's pending partials are added and the updated rows normed in one kernel
+            _pending.pop(x.data_ptr())
+            _check(_lib.kernels().imparo_add_partials_rmsnorm(_ptr(x), _ptr(scratch), S, T * N, _ptr(w), float(eps), _ptr(out),
+                                                              _code(out), T, N, _stream()), "add_partials_rmsnorm")
+            return
+        settle(x)
     n, width = out.shape
     _need(x.dtype == torch.float32 and w.dtype == torch.float32, "rmsnorm reads a float32 stream and float32 weights")
     _need(x.shape[1] == width and w.numel() == width, "rmsnorm width mismatch")
@@ -119,6 +164,7 @@ def swiglu_act(gu: torch.Tensor, out: torch.Tensor) -> None:
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     _cuda(out, bias)
+    settle(out)
     _void_filled(out)                # a norm computed before this write is stale
     n, width = out.shape
     _need(bias.dtype == torch.float32 and bias.numel() == width, "bias must be float32 [width]")
@@ -137,7 +183,7 @@ def _gemm_lib_ready(device) -> None:
 
 
 # ---- tcgen05 product ---------------------------------------------------------------------
-EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2, 3, 4
 _tc_scratch = {}
 _tc_plans = {}
 _status_fallback = {}
@@ -203,7 +249,8 @@ def tc_usable(x: torch.Tensor, w: torch.Tensor, any_size: bool = False) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None,
+            scratch: Optional[torch.Tensor] = None) -> None:
     """The hand-written tensor-core product (csrc/kernels/gemm_tcgen05.cu).
     epilogue: EPI_STORE_BF16 | EPI_STORE_F32 | EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU
     (w = [gate rows; up rows] of shape [2F, K], out = silu(x gate^T) * (x up^T), [T, F])."""
@@ -216,7 +263,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     want_dtype = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32
     _need(out.dtype == want_dtype, f"gemm_tc: this epilogue writes {want_dtype}")
     nt, splits, floats, counters = _tc_plan(T, N, K, epilogue)
-    scratch, cnt = _tc_buffers(x.device, floats, counters)
+    if epilogue == EPI_PARTIAL:
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= floats, "gemm_tc: partials scratch")
+        cnt = scratch
+    else:
+        scratch, cnt = _tc_buffers(x.device, floats, counters)
     if status is None:
         key = torch.device(x.device).index or 0
         status = _status_fallback.get(key)
@@ -381,12 +432,32 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
     _need(x.dtype == w.dtype, "linear: x and w must share a dtype")
     if x.dtype == torch.float32:
         _need(out.dtype == torch.float32, "linear: float32 product writes float32")
+        if accumulate:
+            settle(out)
         _check(_lib.kernels().imparo_sgemm_nt(_ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), N, int(accumulate),
                                               _stream()), "sgemm_nt")
     elif x.dtype == torch.bfloat16:
         _need(not accumulate or out.dtype == torch.float32, "linear: accumulate needs a float32 output")
         if gemm_backend() == "tcgen05" and tc_usable(x, w):
             epi = EPI_ADD_F32 if accumulate else (EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16)
+            if accumulate and out.data_ptr() in _deferrable and out.is_contiguous():
+                settle(out)                                       # one set of partials at a time
+                nt, splits, floats, _ = _tc_plan(M, N, K, EPI_PARTIAL)
+                if splits > 1:
+                    key = torch.device(x.device).index or 0
+                    buf = _partials.get(key)
+                    if buf is None or buf.numel() < floats:
+                        _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                        buf = _partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                        global TC_GENERATION
+                        TC_GENERATION += 1
+                    _void_filled(out)
+                    _armed.pop(out.data_ptr(), None)
+                    gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
+                    _pending[out.data_ptr()] = (buf, splits, M, N)
+                    return
+            if accumulate:
+                settle(out)
             ni = _armed.pop(out.data_ptr(), None) if accumulate else None
             if ni is not None and fuse_add_norm() and not ni._done and tuple(ni.shape) == (M, N) and N % 4 == 0 \
                     and ni._out.is_contiguous() and ni.dtype == torch.bfloat16:
@@ -398,6 +469,7 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
             gemm_tc(x, w, out, epi, status)
             return
         if accumulate:
+            settle(out)
             _armed.pop(out.data_ptr(), None)
             _void_filled(out)
         _gemm_lib_ready(x.device)

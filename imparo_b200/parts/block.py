@@ -41,7 +41,7 @@ class PreNormResidualBlock(Part):
         if self.mixer.adds_with_linear and self.ff.accepts_lazy_input and self._defers(self.ff_norm):
             ff_in = self.ff_norm.lazy(x, tag="normed_ff")     # unevaluated: the mixer's output product may fill it
             ops.arm_norm(x, ff_in)
-        self.mixer.forward(h, batch, caches, x)
+        self._run(self.mixer, x, lambda: self.mixer.forward(h, batch, caches, x))
         if ff_in is not None:
             ops.disarm_norm(x)
         else:
@@ -51,10 +51,26 @@ class PreNormResidualBlock(Part):
             nxt = next_norm.lazy(x, tag="normed_mixer")
             nxt.owner = next_norm
             ops.arm_norm(x, nxt)                             # the feed-forward's output product may fill it
-        self.ff.forward(ff_in, batch, x)
+        self._run(self.ff, x, lambda: self.ff.forward(ff_in, batch, x))
         if nxt is not None:
             ops.disarm_norm(x)
         return nxt
+
+    @staticmethod
+    def _run(part, x, call) -> None:
+        """A part whose last write to the stream is an accumulate-product may leave that add as
+        split partials for the next norm to fold (ops.allow_deferred_add); any other part gets
+        and leaves a stream that is whole."""
+        from ..kernels import ops
+        if part.adds_with_linear:
+            ops.allow_deferred_add(x)
+            try:
+                call()
+            finally:
+                ops.disallow_deferred_add(x)
+        else:
+            ops.settle(x)
+            call()
 
     @staticmethod
     def _defers(norm) -> bool:

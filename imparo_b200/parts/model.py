@@ -78,6 +78,12 @@ class Model:
                 ready = None
         return x
 
+    def settle(self, x: torch.Tensor) -> None:
+        """Make the stream whole (fold split partials a product may have left) for a reader that
+        does not go through the ops launchers."""
+        from ..kernels import ops
+        ops.settle(x)
+
     def logits(self, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
         """Final norm and head at the wanted rows only: [n_rows, vocab] in 32-bit."""
         if getattr(self.head, "accepts_lazy_input", False) and hasattr(self.final_norm, "lazy"):
