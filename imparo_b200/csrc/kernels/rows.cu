@@ -63,17 +63,36 @@ __global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* 
     float* xr = x + (size_t)r * width;
     const float* pr = part + (size_t)r * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = xr[i];
-        for (int s = 0; s < n_splits; ++s) v += pr[(size_t)s * split_stride + i];
-        xr[i] = v;
-        ss += v * v;
+    if ((width & 3) == 0 && (split_stride & 3) == 0) {
+        // 16-byte loads, and all of a chunk's split loads in flight before the (ordered) adds
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(xr + i);
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+                float4 p[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < n_splits) p[u] = __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(s0 + u) * split_stride + i));
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < n_splits) { v.x += p[u].x; v.y += p[u].y; v.z += p[u].z; v.w += p[u].w; }
+            }
+            *reinterpret_cast<float4*>(xr + i) = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float v = xr[i];
+            for (int s = 0; s < n_splits; ++s) v += pr[(size_t)s * split_stride + i];
+            xr[i] = v;
+            ss += v * v;
+        }
     }
     if (out == nullptr) return;
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
     TOut* o = out + (size_t)r * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);   // own writes
+    __syncthreads();                                  // other threads' writes of this row (block scope)
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
 // ---- silu(gate) * up ----------------------------------------------------------------
