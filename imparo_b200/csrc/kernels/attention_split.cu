@@ -294,15 +294,28 @@ __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, co
     const size_t th = blockIdx.x;                         // token * nh + head
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+    for (int s = 0; s < n_splits; ++s) if (__ldcg(ml + 2 * s + 1) > 0.f) M = fmaxf(M, __ldcg(ml + 2 * s));
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.f, L = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ls = ml[2 * s + 1];
-            if (ls > 0.f) {
-                const float f = expf(ml[2 * s] - M);
-                a += part_acc[(th * n_splits + s) * hd + d] * f;
-                L += ls * f;
+        // eight splits' loads in flight at a time; the adds stay in split order
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float pa[8], pm[8], pl[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int s = s0 + u;
+                if (s < n_splits) {
+                    pm[u] = __ldcg(ml + 2 * s);
+                    pl[u] = __ldcg(ml + 2 * s + 1);
+                    pa[u] = __ldcg(part_acc + (th * n_splits + s) * hd + d);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (s0 + u < n_splits && pl[u] > 0.f) {
+                    const float f = expf(pm[u] - M);
+                    a += pa[u] * f;
+                    L += pl[u] * f;
+                }
             }
         }
         out[th * hd + d] = from_f32<T>(L > 0.f ? a / L : 0.f);
