@@ -123,3 +123,159 @@ def test_toy_mixer_is_registered_built_and_stepped(schedule):
             assert np.abs(other[k] - results[0][k]).max() <= 1e-5, k
     # and the state matters: the same token at another position gives other logits
     assert np.abs(results[0][("r0", 5)] - results[0][("r0", 6)]).max() > 1e-3
+
+
+# ---------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, as toy parts
+# ---------------------------------------------------------------------------------------------
+
+def register_routed_toy():
+    from imparo_b200.config.base import KeyReader
+    from imparo_b200.config.registry import Architecture, register_architecture
+    from imparo_b200.kernels import ops
+    from imparo_b200.parts.base import Part, register_part
+    from imparo_b200.parts.position import PositionEncoding
+    from imparo_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, WeightSpec
+
+    class RoutedFeedForward(Part):
+        """Top-1 of E small SwiGLU experts per token; router logits and the choice in 32-bit."""
+        graph_safe = False       # the shapes it launches depend on the routing: not for capture and replay
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            self.H, self.F, self.E = int(params["hidden"]), int(params["ff"]), int(params["experts"])
+            self.names = {"router": prefix + "moe.router.weight",
+                          **{f"w{k}_{e}": prefix + f"moe.experts.{e}.w{k}.weight" for e in range(self.E) for k in (1, 2, 3)}}
+
+        def weight_specs(self):
+            specs = [WeightSpec(self.names["router"], ((self.E, self.H),), role="vector", init=("bias",))]
+            for e in range(self.E):
+                specs += [WeightSpec(self.names[f"w1_{e}"], ((self.F, self.H),)), WeightSpec(self.names[f"w3_{e}"], ((self.F, self.H),)),
+                          WeightSpec(self.names[f"w2_{e}"], ((self.H, self.F),))]
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors[self.names["router"]]
+            self.w13 = [torch.cat([tensors[self.names[f"w1_{e}"]], tensors[self.names[f"w3_{e}"]]]).contiguous() for e in range(self.E)]
+            self.w2 = [tensors[self.names[f"w2_{e}"]] for e in range(self.E)]
+
+        def forward(self, x, batch, residual):
+            choice = (x.float() @ self.router.T).argmax(-1)              # router in 32-bit
+            for e in range(self.E):
+                idx = (choice == e).nonzero().flatten()
+                if idx.numel() == 0:
+                    continue
+                xe = x[idx].contiguous()
+                gu = torch.empty(idx.numel(), 2 * self.F, dtype=x.dtype, device=x.device)
+                ops.linear(xe, self.w13[e], gu)                          # the framework's own product and activation kernels
+                h = torch.empty(idx.numel(), self.F, dtype=x.dtype, device=x.device)
+                ops.swiglu_act(gu, h)
+                out = torch.zeros(idx.numel(), self.H, device=x.device)
+                ops.linear(h, self.w2[e], out, accumulate=True)
+                residual.index_add_(0, idx, out)
+
+    class ScaledRotary(PositionEncoding):
+        """Half-split rotation of the first n_rot dimensions with frequencies divided by a factor
+        that grows with the pair index (another table, same kernel)."""
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            n_rot, theta, factor = int(params["n_rot"]), float(params["theta"]), float(params["factor"])
+            i = torch.arange(n_rot // 2, dtype=torch.float64)
+            inv = theta ** (-2.0 * i / n_rot) / (1.0 + factor * i)
+            self.inv, self.n_rot = inv.to(torch.float32).to(rt.device), n_rot
+
+        def rotary(self):
+            return self.inv, self.n_rot
+
+    register_part("feed_forward", "toy_routed", RoutedFeedForward, replace=True)
+    register_part("position", "toy_scaled_rotary", ScaledRotary, replace=True)
+
+    def parse(values):
+        r = KeyReader(values)
+        return {k: values[k] for k in ("vocab_size", "hidden_size", "n_layers", "heads", "kv_heads", "ff", "experts", "n_rot", "theta", "factor", "eps")}
+
+    def spec(c):
+        H, hd = c["hidden_size"], c["hidden_size"] // c["heads"]
+        pos = PartSpec("toy_scaled_rotary", {"n_rot": c["n_rot"], "theta": c["theta"], "factor": c["factor"]})
+        layers = tuple(LayerSpec(
+            prefix=f"m.layers.{i}.",
+            mixer=PartSpec("attention", {"hidden": H, "n_heads": c["heads"], "n_kv_heads": c["kv_heads"], "head_dim": hd,
+                                         "eps": c["eps"], "window": None, "position": pos}),
+            feed_forward=PartSpec("toy_routed", {"hidden": H, "ff": c["ff"], "experts": c["experts"]}),
+            mixer_norm=PartSpec("rmsnorm", {"width": H, "eps": c["eps"], "name": "n1.weight"}),
+            feed_forward_norm=PartSpec("rmsnorm", {"width": H, "eps": c["eps"], "name": "n2.weight"})) for i in range(c["n_layers"]))
+        return ModelSpec(architecture="RoutedToyForCausalLM", vocab_size=c["vocab_size"], hidden_size=H,
+                         embedding=PartSpec("token_table", {"vocab": c["vocab_size"], "width": H, "name": "m.embed.weight"}),
+                         layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(c["n_layers"])),
+                         final_norm=PartSpec("rmsnorm", {"width": H, "eps": c["eps"], "name": "m.norm.weight"}),
+                         head=PartSpec("linear", {"vocab": c["vocab_size"], "width": H, "name": "m.embed.weight"}), max_positions=4096)
+
+    register_architecture(Architecture("RoutedToyForCausalLM", ("routed_toy",), parse, spec), replace=True)
+
+
+ROUTED = {"architectures": ["RoutedToyForCausalLM"], "vocab_size": 211, "hidden_size": 96, "n_layers": 3, "heads": 3, "kv_heads": 1,
+          "ff": 72, "experts": 4, "n_rot": 16, "theta": 5000.0, "factor": 0.25, "eps": 1e-5}
+
+
+def plain_routed_logits(folder, toks):
+    """The routed toy in numpy float64, whole sequence, with the plain implementation's parts."""
+    from tests.plain import lfm2_plain as P
+    t = {k: v.astype(np.float64) for k, v in P.read_safetensors(folder + "/model.safetensors").items()}
+    c = ROUTED
+    H, nh, nkv = c["hidden_size"], c["heads"], c["kv_heads"]
+    hd = H // nh
+    T = len(toks)
+    pos = np.arange(T)
+    i = np.arange(c["n_rot"] // 2, dtype=np.float64)
+    inv = (c["theta"] ** (-2.0 * i / c["n_rot"]) / (1.0 + c["factor"] * i)).astype(np.float32)
+    ang = (pos[:, None].astype(np.float64) * inv[None, :].astype(np.float64)).astype(np.float32).astype(np.float64)
+
+    def rope(x):                                    # x [T, heads, hd]; first n_rot dims, half-split
+        half = c["n_rot"] // 2
+        out = x.copy()
+        x0, x1 = x[..., :half], x[..., half:c["n_rot"]]
+        out[..., :half] = x0 * np.cos(ang)[:, None] - x1 * np.sin(ang)[:, None]
+        out[..., half:c["n_rot"]] = x0 * np.sin(ang)[:, None] + x1 * np.cos(ang)[:, None]
+        return out
+    x = t["m.embed.weight"][np.asarray(toks)]
+    for l in range(c["n_layers"]):
+        p = f"m.layers.{l}."
+        cur = P.rms_norm(x, t[p + "n1.weight"], c["eps"])
+        q = P.rms_norm((cur @ t[p + "self_attn.q_proj.weight"].T).reshape(T, nh, hd), t[p + "self_attn.q_layernorm.weight"], c["eps"])
+        k = P.rms_norm((cur @ t[p + "self_attn.k_proj.weight"].T).reshape(T, nkv, hd), t[p + "self_attn.k_layernorm.weight"], c["eps"])
+        v = (cur @ t[p + "self_attn.v_proj.weight"].T).reshape(T, nkv, hd)
+        o = P.attend(rope(q), rope(k), v, 1.0 / np.sqrt(hd))
+        x = x + o.reshape(T, H) @ t[p + "self_attn.out_proj.weight"].T
+        n = P.rms_norm(x, t[p + "n2.weight"], c["eps"])
+        choice = (n @ t[p + "moe.router.weight"].T).argmax(-1)
+        ff = np.zeros_like(x)
+        for tok in range(T):
+            e = choice[tok]
+            ff[tok] = P.swiglu(n[tok:tok + 1], {"w1": t[p + f"moe.experts.{e}.w1.weight"], "w2": t[p + f"moe.experts.{e}.w2.weight"],
+                                                "w3": t[p + f"moe.experts.{e}.w3.weight"]})[0]
+        x = x + ff
+    return P.rms_norm(x, t["m.norm.weight"], c["eps"]) @ t["m.embed.weight"].T
+
+
+def test_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward that routes each token to one of four experts and a rotary table of its own,
+    both defined in this test, in a registered toy architecture: written to a model folder by the
+    random-weights mode, loaded, stepped whole / in portions / mixed, and compared with numpy."""
+    from imparo_b200.engine import Engine
+    from imparo_b200.weights import write_random_model
+    register_routed_toy()
+    folder = str(tmp_path / "routed")
+    write_random_model(folder, ROUTED, seed=4, dtype="float32", matrix_std=0.15)
+    rng = np.random.default_rng(1)
+    reqs = {f"r{i}": rng.integers(0, ROUTED["vocab_size"], n).tolist() for i, n in enumerate([37, 20, 29])}
+    ref = {k: plain_routed_logits(folder, v) for k, v in reqs.items()}
+    scale = max(np.abs(v).max() for v in ref.values())
+    for build in (traces.whole, traces.portions, lambda r: traces.mixed(r, seed=5, tail=6, max_portion=8)):
+        steps = build(reqs)
+        eng = Engine(folder, dtype="float32", ctx=64, parallel=3, page_size=8, num_pages=24)
+        got = logits_by_position(steps, run_trace(eng, steps))
+        for (rid, pos), row in got.items():
+            assert np.abs(row - ref[rid][pos]).max() <= 5e-5 * scale, (rid, pos)
+    # the routing is real: tokens go to different experts
+    assert len({int(x) for x in np.argmax(np.random.default_rng(0).standard_normal((50, 4)), -1)}) > 1
