@@ -102,3 +102,26 @@ def test_command_line_generates_the_same_tokens(tmp_path):
                         "-c", "64", "-t", str(tf), "--json"], cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert json.loads(r.stdout.strip().splitlines()[-1])["tokens"] == [want]
+
+
+def test_many_requests_few_pages_every_request_gets_its_own_tokens():
+    """24 requests of random lengths through 5 slots and a pool far smaller than their sum:
+    portions beside decode rows, slots and pages used again, preemptions.  Every request must
+    get the tokens it gets alone (32-bit, greedy)."""
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(9)
+    lens = [int(x) for x in rng.integers(3, 60, 24)]
+    reqs = make_requests("B", lens, seed=13)
+    prompts = list(reqs.values())
+    news = [int(x) for x in rng.integers(1, 20, 24)]
+    eng = Engine(model_dir("B"), dtype="float32", ctx=96, parallel=5, page_size=4, num_pages=70, max_step_tokens=24)
+    seen = []
+    got = eng.generate(prompts, max_tokens=news, on_step=lambda plan: seen.append(plan))
+    for i, p in enumerate(prompts):
+        want, margins = P.generate(plain_model("B"), p, news[i])
+        agree(got[i], want, margins, 1e-5)
+    assert max(len(plan) for plan in seen) == 5                      # all slots were in use at once
+    assert all(sum(e.count for e in plan) <= 24 for plan in seen)
+    assert eng.stats()["failed"] == []
+    assert eng.cache.free_pages(0) == 70 and eng.cache.free_slots() == 5 and eng.cache.n_requests() == 0
+    eng.cache.check()

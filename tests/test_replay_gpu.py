@@ -134,3 +134,43 @@ def test_full_width_layers_bfloat16_against_32_bit():
     assert err <= 4e-2 * scale, (err, scale)
     # and the rows are not all alike (a kernel that ignored its input would pass the bound above)
     assert np.abs(ref[0] - ref[-1]).max() > 0.2 * scale
+
+
+def test_long_context_whole_against_portions():
+    """6,000 positions: hundreds of pages per request, table rows of several hundred blocks, key
+    chunks and tiles far from position 0.  Whole prompt against 1,024-token portions and single
+    tokens, at LFM2-350M width with two attention layers (bfloat16: the tensor-core kernels)."""
+    import torch
+    from imparo_b200.engine import Engine, StepItem
+    cfg = {"architectures": ["Lfm2ForCausalLM"], "vocab_size": 4096, "hidden_size": 1024, "num_hidden_layers": 3,
+           "layer_types": ["full_attention", "conv", "full_attention"], "num_attention_heads": 16,
+           "num_key_value_heads": 8, "block_ff_dim": 6656, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+           "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_embedding": True}
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, 4096, 6000).tolist()
+    tail = rng.integers(0, 4096, 5).tolist()
+    want = [0, 1023, 1024, 3000, 5999]
+    eng = Engine(config=cfg, seed=3, dtype="bfloat16", ctx=8192, parallel=2, page_size=16, max_step_tokens=6000,
+                 random_init={"norm_jitter": 0.1})
+    eng.add_request(1)
+    whole = [eng.step([StepItem(1, toks, want)]).float().cpu().numpy()]
+    for t in tail:
+        whole.append(eng.step([StepItem(1, [t], [0])]).float().cpu().numpy())
+    eng.add_request(2)
+    parts = []
+    for a in range(0, 6000, 1024):
+        chunk = toks[a:a + 1024]
+        w = [p - a for p in want if a <= p < a + len(chunk)]
+        out = eng.step([StepItem(2, chunk, w)])
+        if out is not None:
+            parts.append(out.float().cpu().numpy())
+    for t in tail:
+        parts.append(eng.step([StepItem(2, [t], [0])]).float().cpu().numpy())
+    eng.check_device_status()
+    a, b = np.concatenate(whole), np.concatenate(parts)
+    assert a.shape == b.shape == (10, 4096) and np.isfinite(a).all()
+    scale = np.abs(a).max()
+    assert np.abs(a - b).max() <= 3e-2 * scale, (np.abs(a - b).max(), scale)
+    assert np.abs(a[0] - a[4]).max() > 0.1 * scale
+    eng.end_request(1); eng.end_request(2)
+    eng.cache.check()
