@@ -49,29 +49,16 @@ __device__ __forceinline__ void unpack(const uint4& v, float* o) {
     for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(p[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
 }
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-    const int n = valid ? 16 : 0;                 // 0: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-
-constexpr int STAGE_PAD = 16;      // bytes after each staged row: lanes that read different rows hit different banks
-constexpr int N_STAGES = 2;
-
 // dynamic shared memory layout (floats):
 //   qs   [G][hd]                 the group's queries
 //   ps   [WARPS][G][32]          a warp's probabilities for its 32 keys
 //   rows [WARPS][32] (int)       their cache rows
 //   wm, wl [WARPS][G]            per-warp running max / sum
 //   wacc [WARPS][KPI][G][hd]     per-warp, per-lane-group accumulators (KPI = keys per load instruction)
-//   STAGED only: per warp N_STAGES x (rows[32] | K[32][hd + pad] | V[32][hd + pad])
-// STAGED: a warp copies the keys and values of its next 32-key step into shared memory with
-// cp.async while it works on the current one, so the memory system always has the next step
-// in flight; the arithmetic then reads shared memory.  Not STAGED (rows too wide for that):
-// the arithmetic reads global memory in batches of independent loads.
-template <typename T, int G, bool STAGED>
+// The arithmetic reads global memory in batches of independent loads.  (Staging the loads
+// through shared memory with cp.async was tried and changed nothing: this kernel is bound by
+// instruction issue; its tensor-core version is attn_decode_mma_kernel in attention_prefill.cu.)
+template <typename T, int G>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                           const int* __restrict__ positions, const int* __restrict__ item_of_token,
@@ -129,10 +116,6 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
     float* my_ps = ps + warp * G * 32;
     int* my_rows = rows + warp * 32;
 
-    // ---- staging (STAGED only) ----
-    const int rowb = hd * (int)sizeof(T) + STAGE_PAD;
-    const int stage_bytes = 32 * 4 + 2 * 32 * rowb;
-    uint8_t* my_stage = reinterpret_cast<uint8_t*>(wacc + (size_t)SPLIT_WARPS * KPI * G * hd) + (size_t)warp * N_STAGES * stage_bytes;
     auto lookup = [&](int j) -> int {
         if (j >= end) return -1;
         const int blk = j / page_size;
@@ -140,49 +123,16 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
         if (page < 0 || page >= n_pages) { report(status, IMPARO_ST_PAGE_RANGE, 5, t, page); return -1; }
         return page * page_size + (j % page_size);
     };
-    auto issue = [&](int step) {
-        const int base = begin + warp * 32 + step * SPLIT_WARPS * 32;
-        if (base < end) {
-            uint8_t* st = my_stage + (size_t)(step % N_STAGES) * stage_bytes;
-            const int rowi = lookup(base + lane);
-            reinterpret_cast<int*>(st)[lane] = rowi;
-            uint8_t* ks = st + 32 * 4;
-            uint8_t* vs = ks + 32 * rowb;
-            for (int it = 0; it < vecs; ++it) {                    // 32 keys x vecs chunks, 32 chunks per round
-                const int i = it * 32 + lane;
-                const int key = i / vecs, c = i % vecs;
-                const int r = __shfl_sync(0xffffffffu, rowi, key);
-                const size_t off = (size_t)(r < 0 ? 0 : r) * kvw + (size_t)kvh * hd + (size_t)c * VN;
-                cp_async16(ks + key * rowb + c * 16, k_cache + off, r >= 0);
-                cp_async16(vs + key * rowb + c * 16, v_cache + off, r >= 0);
-            }
-        }
-        cp_commit();                                               // an empty group keeps the count in step
-    };
-    if (STAGED) issue(0);
 
-    int step = 0;
-    for (int base = begin + warp * 32; base < end; base += SPLIT_WARPS * 32, ++step) {
+    for (int base = begin + warp * 32; base < end; base += SPLIT_WARPS * 32) {
         const int j = base + lane;
-        int rowi = -1;
         float s[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) s[g] = 0.f;
-        const uint8_t* st = my_stage + (size_t)(step % N_STAGES) * stage_bytes;
-        const uint8_t* st_k = st + 32 * 4;
-        const uint8_t* st_v = st_k + 32 * rowb;
-        if (STAGED) {
-            issue(step + 1);
-            cp_wait_1();                                           // this step's copies have landed
-            __syncwarp();
-            rowi = reinterpret_cast<const int*>(st)[lane];
-        } else {
-            rowi = lookup(j);
-        }
+        const int rowi = lookup(j);
         {
             if (rowi >= 0) {
-                const V* kp = STAGED ? reinterpret_cast<const V*>(st_k + lane * rowb)
-                                     : reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
+                const V* kp = reinterpret_cast<const V*>(k_cache + (size_t)rowi * kvw + (size_t)kvh * hd);
                 // eight independent 16-byte loads in flight before any arithmetic
                 for (int c0 = 0; c0 < vecs; c0 += 8) {
                     V kv[8];
@@ -225,8 +175,7 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
                 const int rj = live ? my_rows[jj] : -1;
                 rjs[u] = rj;
                 jjs[u] = jj & 31;
-                const V* vp = STAGED ? reinterpret_cast<const V*>(st_v + (jj & 31) * rowb)
-                                     : reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
+                const V* vp = reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
                 vv[u][0] = vp[lig];
                 if (VPL > 1) vv[u][1] = vp[lig + LPR];
             }
@@ -322,16 +271,15 @@ __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, co
     }
 }
 
-template <typename T, int G, bool STAGED>
-int launch_partial_as(const void* q, const void* k_cache, const void* v_cache, const int* positions, const int* item_of_token,
-                      const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
-                      float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
-                      int* status, cudaStream_t stream) {
+template <typename T, int G>
+int launch_partial(const void* q, const void* k_cache, const void* v_cache, const int* positions, const int* item_of_token,
+                   const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
+                   float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                   int* status, cudaStream_t stream) {
     const int vecs = hd / KVec<T>::N, lpr = vecs < 32 ? vecs : 32, kpi = 32 / lpr;
-    size_t smem = sizeof(float) * ((size_t)G * hd + SPLIT_WARPS * G * 32 + SPLIT_WARPS * 32 + 2 * SPLIT_WARPS * G +
-                                   (size_t)SPLIT_WARPS * kpi * G * hd);
-    if (STAGED) smem += (size_t)SPLIT_WARPS * N_STAGES * (32 * 4 + 2 * 32 * (hd * sizeof(T) + STAGE_PAD));
-    auto kern = attn_split_partial_kernel<T, G, STAGED>;
+    const size_t smem = sizeof(float) * ((size_t)G * hd + SPLIT_WARPS * G * 32 + SPLIT_WARPS * 32 + 2 * SPLIT_WARPS * G +
+                                         (size_t)SPLIT_WARPS * kpi * G * hd);
+    auto kern = attn_split_partial_kernel<T, G>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -342,19 +290,6 @@ int launch_partial_as(const void* q, const void* k_cache, const void* v_cache, c
            nh, nkv, hd, chunk, n_splits, status);
     IMPARO_CHECK_LAUNCH();
     return 0;
-}
-
-template <typename T, int G>
-int launch_partial(const void* q, const void* k_cache, const void* v_cache, const int* positions, const int* item_of_token,
-                   const int* table, int max_blocks, int page_size, int n_pages, int window, float scale,
-                   float* part_acc, float* part_ml, int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
-                   int* status, cudaStream_t stream) {
-    // rows of up to 256 bytes are staged through shared memory; wider ones are read directly
-    if (hd * sizeof(T) <= 256)
-        return launch_partial_as<T, G, true>(q, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages,
-                                             window, scale, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, status, stream);
-    return launch_partial_as<T, G, false>(q, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages,
-                                          window, scale, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, status, stream);
 }
 
 template <typename T>

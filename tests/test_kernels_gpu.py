@@ -432,7 +432,8 @@ def test_temperature_sampling_is_the_inverse_cdf(V):
     assert np.abs(freq - p).max() < 2e-3
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (6, 2, 128), (3, 1, 64), (8, 1, 64), (2, 1, 128), (32, 8, 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (6, 2, 128), (3, 1, 64), (8, 1, 64), (2, 1, 128), (32, 8, 64), (4, 2, 64),
+                                       (5, 1, 64), (6, 1, 128), (7, 1, 64)])
 @pytest.mark.parametrize("page,window", [(4, None), (16, None), (16, 50), (64, 7)])
 def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window):
     """Prompt portions of several requests in one launch: a long portion that starts in the
