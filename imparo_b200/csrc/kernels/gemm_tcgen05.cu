@@ -345,10 +345,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                     float v[16];
                     tmem_ld16(taddr + c, v);
                     if (n < p.N) {
+                        if (EPI == ADD_F32) {
+                            // all sixteen reads of the stream before any write: the compiler must not
+                            // chain load-add-store sixteen times (it cannot prove the addresses differ)
+                            float old[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < p.T) store_out<EPI>(p.out, (size_t)t * p.ldo + n, v[j]);
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = t0 + c + j;
+                                old[j] = t < p.T ? reinterpret_cast<const float*>(p.out)[(size_t)t * p.ldo + n] : 0.f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = t0 + c + j;
+                                if (t < p.T) reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = old[j] + v[j];
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = t0 + c + j;
+                                if (t < p.T) store_out<EPI>(p.out, (size_t)t * p.ldo + n, v[j]);
+                            }
                         }
                     }
                 }
