@@ -19,43 +19,15 @@ namespace imparo {
 
 constexpr int MAX_TAPS = 16;
 
+// The thread of a portion's first token, for one channel: outputs of the first min(n, taps-1)
+// tokens from the old state, then the new state.
 template <typename T>
-__global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ w,
-                                  const float* __restrict__ bias, float* __restrict__ state,
-                                  const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
-                                  const int* __restrict__ item_slot, T* __restrict__ y,
-                                  int n_tok, int width, int taps, int n_slots, int* status) {
-    pdl_wait();
-    pdl_trigger();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_tok * width) return;
-    const int t = (int)(idx / width), ch = (int)(idx % width);
-    const int item = item_of_token[t];
-    const int start = item_row_start[item];
-    const int n = item_row_start[item + 1] - start;
-    const int rel = t - start;
+__device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, const float* __restrict__ w, float b0,
+                                                  float* __restrict__ state, const int* __restrict__ item_slot,
+                                                  T* __restrict__ y, int item, int start, int n, int ch,
+                                                  int width, int taps, int n_slots, int* status) {
     const int hist = taps - 1;
     const size_t stride = (size_t)3 * width;
-    float wk[MAX_TAPS];
-#pragma unroll
-    for (int k = 0; k < MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)ch * taps + k] : 0.f;
-    const float b0 = bias ? bias[ch] : 0.f;
-
-    if (rel >= hist) {
-        float acc = 0.f;
-#pragma unroll
-        for (int k = 0; k < MAX_TAPS; ++k) {
-            if (k < taps) {
-                const T* r = bcx + (size_t)(t - hist + k) * stride;
-                acc += wk[k] * (to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]));
-            }
-        }
-        acc += b0;
-        y[(size_t)t * width + ch] = from_f32<T>(to_f32(bcx[(size_t)t * stride + width + ch]) * acc);
-        return;
-    }
-    if (rel != 0) return;
-
     const int slot = item_slot[item];
     if (slot < 0 || slot >= n_slots) {
         if (ch == 0) report(status, IMPARO_ST_SLOT_RANGE, 4, item, slot);
@@ -94,6 +66,99 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
     }
 }
 
+template <typename T>
+__global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ w,
+                                  const float* __restrict__ bias, float* __restrict__ state,
+                                  const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
+                                  const int* __restrict__ item_slot, T* __restrict__ y,
+                                  int n_tok, int width, int taps, int n_slots, int* status) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tok * width) return;
+    const int t = (int)(idx / width), ch = (int)(idx % width);
+    const int item = item_of_token[t];
+    const int start = item_row_start[item];
+    const int n = item_row_start[item + 1] - start;
+    const int rel = t - start;
+    const int hist = taps - 1;
+    const size_t stride = (size_t)3 * width;
+    const float b0 = bias ? bias[ch] : 0.f;
+
+    if (rel >= hist) {
+        float acc = 0.f;
+        for (int k = 0; k < taps; ++k) {
+            const T* r = bcx + (size_t)(t - hist + k) * stride;
+            acc += w[(size_t)ch * taps + k] * (to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]));
+        }
+        acc += b0;
+        y[(size_t)t * width + ch] = from_f32<T>(to_f32(bcx[(size_t)t * stride + width + ch]) * acc);
+        return;
+    }
+    if (rel != 0) return;
+    conv_portion_head<T>(bcx, w, b0, state, item_slot, y, item, start, n, ch, width, taps, n_slots, status);
+}
+
+// bfloat16 with a width that is a multiple of 8, for prompt-sized batches: a thread owns eight
+// consecutive channels of one token and moves 16 bytes at a time.  Same sums in the same order
+// as gated_conv_kernel; the thread of a portion's first token walks its eight channels through
+// conv_portion_head.
+__global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, const float* __restrict__ w,
+                                         const float* __restrict__ bias, float* __restrict__ state,
+                                         const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
+                                         const int* __restrict__ item_slot, __nv_bfloat16* __restrict__ y,
+                                         int n_tok, int width, int taps, int n_slots, int* status) {
+    pdl_wait();
+    pdl_trigger();
+    const int per_row = width >> 3;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tok * per_row) return;
+    const int t = (int)(idx / per_row), ch = (int)(idx % per_row) << 3;
+    const int hist = taps - 1;
+    const int item = item_of_token[t];
+    const int start = item_row_start[item];
+    const int rel = t - start;
+    if (rel < hist) {
+        if (rel != 0) return;
+        const int n = item_row_start[item + 1] - start;
+        for (int i = 0; i < 8; ++i)
+            conv_portion_head<__nv_bfloat16>(bcx, w, bias ? bias[ch + i] : 0.f, state, item_slot, y, item, start, n,
+                                             ch + i, width, taps, n_slots, status);
+        return;
+    }
+    const size_t stride = (size_t)3 * width;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const __nv_bfloat16* r = bcx + (size_t)(t - hist + k) * stride;
+        const uint4 b = *reinterpret_cast<const uint4*>(r + ch);
+        const uint4 x = *reinterpret_cast<const uint4*>(r + 2 * (size_t)width + ch);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 bf = __bfloat1622float2(bp[i]), xf = __bfloat1622float2(xp[i]);
+            acc[2 * i] += w[(size_t)(ch + 2 * i) * taps + k] * (bf.x * xf.x);
+            acc[2 * i + 1] += w[(size_t)(ch + 2 * i + 1) * taps + k] * (bf.y * xf.y);
+        }
+    }
+    if (bias) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += bias[ch + i];
+    }
+    const uint4 c = *reinterpret_cast<const uint4*>(bcx + (size_t)t * stride + width + ch);
+    const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&c);
+    uint4 out;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 cf = __bfloat1622float2(cp[i]);
+        op[i] = __floats2bfloat162_rn(cf.x * acc[2 * i], cf.y * acc[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)t * width + ch) = out;
+}
+
 }  // namespace imparo
 
 using namespace imparo;
@@ -110,10 +175,18 @@ extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, con
     if (dtype == IMPARO_DT_F32)
         launch(gated_conv_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)bcx, w, bias, state, item_row_start,
                                                                 item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
-    else if (dtype == IMPARO_DT_BF16)
-        launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)bcx, w, bias, state, item_row_start,
-                                                                         item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
-    else return -1;
+    else if (dtype == IMPARO_DT_BF16) {
+        const bool wide = n_tok >= 64 && (width & 7) == 0 && (((uintptr_t)bcx | (uintptr_t)y) & 15) == 0;
+        if (wide) {
+            const size_t n8 = (size_t)n_tok * (width >> 3);
+            launch(gated_conv_bf16x8_kernel, dim3((unsigned)((n8 + threads - 1) / threads)), dim3(threads), 0, stream,
+                   (const __nv_bfloat16*)bcx, w, bias, state, item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y,
+                   n_tok, width, taps, n_slots, status);
+        } else {
+            launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)bcx, w, bias, state,
+                   item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
+        }
+    } else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -30,6 +30,18 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 // row rows[r].  The sum of squares is a fixed tree over blockDim threads, so a row's
 // result never depends on which other rows are in the launch.
 template <typename TOut>
+__device__ __forceinline__ void store4(TOut* o, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* o, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* o, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ w, float eps, TOut* __restrict__ out,
                                int width) {
@@ -38,11 +50,25 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     pdl_trigger();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+    TOut* o = out + (size_t)r * width;
     float ss = 0.f;
+    if ((width & 3) == 0) {                       // 16-byte loads; the second pass re-reads from L1/L2
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + i);
+            const float4 g = *reinterpret_cast<const float4*>(w + i);
+            store4<TOut>(o + i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) { float v = xr[i]; ss += v * v; }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
-    TOut* o = out + (size_t)r * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
@@ -109,6 +135,28 @@ __global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out,
     out[i] = from_f32<T>(silu(g) * u);
 }
 
+// eight features per thread, 16-byte loads and stores (F a multiple of 8)
+__global__ void swiglu_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n_tok, int F) {
+    pdl_wait();
+    pdl_trigger();
+    const int per_row = F >> 3;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_tok * per_row) return;
+    const size_t t = i / per_row, f = (i % per_row) << 3;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * F + f);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * F + F + f);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 r;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
+        rp[k] = __floats2bfloat162_rn(silu(a.x) * b.x, silu(a.y) * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * F + f) = r;
+}
+
 // ---- out[t, :] += bias ----------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n_tok, int width) {
@@ -161,6 +209,9 @@ extern "C" int imparo_swiglu_act(const void* gu, void* out, int dtype, int n_tok
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == IMPARO_DT_F32)
         launch(swiglu_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, n_tok, F);
+    else if (dtype == IMPARO_DT_BF16 && (F & 7) == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0)
+        launch(swiglu_act_bf16x8_kernel, dim3((unsigned)((n / 8 + threads - 1) / threads)), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
     else if (dtype == IMPARO_DT_BF16)
         launch(swiglu_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tok, F);
     else return -1;

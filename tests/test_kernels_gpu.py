@@ -43,7 +43,7 @@ def test_embed_gather(width, vocab, dtype):
         o.read_status(st)
 
 
-@pytest.mark.parametrize("width", [100, 144, 2048, 3000])
+@pytest.mark.parametrize("width", [100, 144, 2048, 3000, 101, 1026])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(width, out_dtype):
     o = ops()
@@ -98,13 +98,14 @@ def test_gemm_bf16(M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu_act(dtype):
+@pytest.mark.parametrize("rows,F", [(11, 200), (11, 204), (3, 77), (130, 1016)])     # 16-byte path and not
+def test_swiglu_act(dtype, rows, F):
     o = ops()
     g = torch.Generator().manual_seed(4)
-    gu = (torch.randn(11, 2 * 200, generator=g) * 4).to(dtype)
-    out = torch.empty(11, 200, dtype=dtype, device=DEV)
+    gu = (torch.randn(rows, 2 * F, generator=g) * 4).to(dtype)
+    out = torch.empty(rows, F, dtype=dtype, device=DEV)
     o.swiglu_act(gu.to(DEV), out)
-    gate, up = gu[:, :200].double(), gu[:, 200:].double()
+    gate, up = gu[:, :F].double(), gu[:, F:].double()
     ref = gate / (1 + torch.exp(-gate)) * up
     tol = 1e-6 if dtype == torch.float32 else 8e-3
     assert (out.float().cpu().double() - ref).abs().max() <= tol * ref.abs().max()
@@ -128,10 +129,12 @@ def conv_reference(bcx, w, bias, state):
 @pytest.mark.parametrize("taps", [2, 3, 4, 7])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("bias", [False, True])
-def test_gated_conv_ragged_batch(taps, dtype, bias):
+@pytest.mark.parametrize("H,lens", [(72, [1, 9, 2, 1, 5]),          # shorter than taps-1, equal, longer
+                                    (72, [40, 1, 3, 57, 6]),        # enough tokens for the 16-byte kernel
+                                    (76, [33, 2, 70, 1, 1])])       # a width it does not take
+def test_gated_conv_ragged_batch(taps, dtype, bias, H, lens):
     o = ops()
-    H, n_slots = 72, 5
-    lens = [1, 9, 2, 1, 5]          # shorter than taps-1, equal, longer
+    n_slots = 5
     slots = [3, 0, 4, 1, 2]
     g = torch.Generator().manual_seed(taps)
     T = sum(lens)
@@ -503,6 +506,7 @@ def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
     """ops.linear / ops.linear_swiglu on a NormedInput: the RMS norm of the 32-bit rows is
     computed inside the tensor-core product.  Against float64, and against the unfused path."""
     monkeypatch.setenv("IMPARO_FUSE_NORM", "1")
+    monkeypatch.setenv("IMPARO_TC_MAX_TOKENS", "64")        # the own product for every T of this test
     o = ops()
     g = torch.Generator().manual_seed(T * 7 + N)
     x = torch.randn(40, K, generator=g) * 2
@@ -545,6 +549,7 @@ def test_product_with_the_next_norm_behind_it(T, N, K, monkeypatch):
     """linear(..., accumulate=True) into an armed stream: out += x w^T and, in the same kernel,
     the RMS norm of the updated rows.  Against float64 and against the separate norm kernel."""
     monkeypatch.setenv("IMPARO_FUSE_ADD_NORM", "1")
+    monkeypatch.setenv("IMPARO_TC_MAX_TOKENS", "64")
     o = ops()
     g = torch.Generator().manual_seed(T + N + K)
     x = bf16_round(torch.randn(T, K, generator=g))
