@@ -17,6 +17,10 @@ namespace imparo {
 constexpr int MAX_HEAD = 256;
 constexpr int WARPS = 4;
 
+// What does not depend on the previous kernel is done before the wait on it: the token's
+// position, the norm weights, the rotation's sines and cosines and the cache row (the batch
+// description comes from the host before the step).  After the wait: one load of the head's
+// values, the norm, the rotation, the store.
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
@@ -27,7 +31,7 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
                           const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
                           int nh, int nkv, int hd, int* status) {
     __shared__ float rowbuf[WARPS][MAX_HEAD];
-    pdl_wait();
+    constexpr int PER = MAX_HEAD / 32, PAIRS = MAX_HEAD / 64;
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -39,30 +43,24 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
     float* row = rowbuf[warp];
     const int pos = positions[t];
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+    const int half = n_rot >> 1;
 
-    float ss = 0.f;
-    for (int d = lane; d < hd; d += 32) { float v = to_f32(src[d]); row[d] = v; ss += v * v; }
+    float wreg[PER], sn[PAIRS], cs[PAIRS];
     if (is_q || is_k) {
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
         const float* w = is_q ? q_w : k_w;
-        __syncwarp();
-        for (int d = lane; d < hd; d += 32) row[d] = row[d] * scale * w[d];
-        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; wreg[j] = d < hd ? w[d] : 0.f; }
         if (inv_freq) {
-            const int half = n_rot >> 1;
-            for (int i = lane; i < half; i += 32) {
-                const float ang = (float)pos * inv_freq[i];
-                float sn, cs;
-                sincosf(ang, &sn, &cs);
-                const float x0 = row[i], x1 = row[i + half];
-                row[i] = x0 * cs - x1 * sn;
-                row[i + half] = x0 * sn + x1 * cs;
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int i = lane + 32 * j;
+                sn[j] = 0.f; cs[j] = 1.f;
+                if (i < half) sincosf((float)pos * inv_freq[i], &sn[j], &cs[j]);
             }
         }
     }
-    __syncwarp();
-    T* dst;
+    T* dst = nullptr;
+    int bad_page = 0;
     if (is_q) {
         dst = q_out + (size_t)t * nh * hd + (size_t)hh * hd;
     } else {
@@ -71,13 +69,50 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
         int page = -1;
         if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
         if (page < 0 || page >= n_pages) {
-            if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);
-            return;
+            bad_page = page;                                 // reported after the wait
+        } else {
+            const size_t r = (size_t)page * page_size + (pos % page_size);
+            dst = (is_k ? k_cache : v_cache) + r * ((size_t)nkv * hd) + (size_t)kvh * hd;
         }
-        const size_t r = (size_t)page * page_size + (pos % page_size);
-        dst = (is_k ? k_cache : v_cache) + r * ((size_t)nkv * hd) + (size_t)kvh * hd;
     }
-    for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(row[d]);
+    pdl_wait();
+    if (dst == nullptr) {
+        if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 2, t, bad_page);
+        return;
+    }
+
+    float val[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int d = lane + 32 * j;
+        val[j] = d < hd ? to_f32(src[d]) : 0.f;
+        ss += val[j] * val[j];
+    }
+    if (is_q || is_k) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; if (d < hd) row[d] = val[j] * scale * wreg[j]; }
+        __syncwarp();
+        if (inv_freq) {
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int i = lane + 32 * j;
+                if (i < half) {
+                    const float x0 = row[i], x1 = row[i + half];
+                    row[i] = x0 * cs[j] - x1 * sn[j];
+                    row[i + half] = x0 * sn[j] + x1 * cs[j];
+                }
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; if (d < hd) dst[d] = from_f32<T>(row[d]); }
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; if (d < hd) dst[d] = from_f32<T>(val[j]); }
+    }
 }
 
 // ---- general paged attention ---------------------------------------------------------
@@ -110,8 +145,8 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
                        int window, float scale, T* __restrict__ out, int nh, int nkv, int hd, int* status) {
     __shared__ __align__(16) float qbuf[WARPS][MAX_HEAD];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * WARPS + warp;

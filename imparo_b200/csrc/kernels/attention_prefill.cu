@@ -67,7 +67,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     uint8_t* q_s = pf_smem;
     uint8_t* k_s[2] = {q_s + ROWS * HD * 2, q_s + ROWS * HD * 2 + KEYS * HD * 2};
     uint8_t* v_s[2] = {k_s[1] + KEYS * HD * 2, k_s[1] + 2 * KEYS * HD * 2};
-    pdl_wait();
     pdl_trigger();
 
     const int G = nh / nkv;
@@ -93,6 +92,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
+
+    pdl_wait();          // up to here only the batch description was read, which the host wrote before the step
 
     // ---- queries -> shared memory (row r = token r / G, head kvh*G + r % G) ----
     for (int i = tid; i < ROWS * CH; i += THREADS) {
@@ -285,9 +286,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     float* wm = reinterpret_cast<float*>(v_s[1] + KEYS * HD * 2);     // [4][8]
     float* wl = wm + 32;                                               // [4][8]
     float* wacc = wl + 32;                                             // [4][8][HD]
-    pdl_wait();
     pdl_trigger();
 
+    // the batch description (positions, block table) comes from the host before the step: it is
+    // read, and the chunk's table entries are pulled into the L1, before the wait on the previous kernel
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nh / nkv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -297,6 +299,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int begin = max(lo, split * chunk), end = min(pos + 1, (split + 1) * chunk);
     const int h0 = kvh * G;
     const size_t part_base = ((size_t)t * nh + h0) * n_splits + split;         // + g * n_splits
+    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
+    if (begin < end) {
+        const int b0 = begin / page_size, b1 = min((end - 1) / page_size, max_blocks - 1);
+        for (int b = b0 + tid * 32; b <= b1; b += THREADS * 32)                // one touch per 128-byte line
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + b));
+    }
+    pdl_wait();
     if (begin >= end) {
         if (tid < G) {
             part_ml[(part_base + (size_t)tid * n_splits) * 2] = -INFINITY;
@@ -304,7 +313,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         return;
     }
-    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
     const size_t kvw = (size_t)nkv * HD;
 
     for (int i = tid; i < 16 * CH; i += THREADS) {

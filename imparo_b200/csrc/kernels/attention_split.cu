@@ -66,8 +66,8 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
                           float scale, float* __restrict__ part_acc, float* __restrict__ part_ml,
                           int nh, int nkv, int hd, int chunk, int n_splits, int* status) {
     extern __shared__ __align__(16) float smem[];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* qs = smem;
@@ -238,8 +238,8 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
 template <typename T>
 __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                           T* __restrict__ out, int hd, int n_splits) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const size_t th = blockIdx.x;                         // token * nh + head
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;

@@ -90,11 +90,16 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 }  // namespace imparo
 
 // ---- programmatic dependent launch ----------------------------------------------------
-// Every kernel of this engine starts with pdl_wait() before it reads or writes anything an
-// earlier kernel may touch, and calls pdl_trigger() so that the next kernel's CTAs may be
-// scheduled early: their launch latency and prologue (and, for the products, the first
-// weight tiles, which no kernel writes) then overlap this kernel's tail.  Without the launch
-// attribute both are no-ops.
+// Every kernel of this engine calls pdl_trigger() first and then pdl_wait(), before it reads
+// or writes anything an earlier kernel may touch.  The trigger lets the next kernel's CTAs be
+// scheduled as soon as this kernel's CTAs are all resident; the wait returns when the previous
+// kernel has completed, and that kernel only completes after its own wait, so completion is
+// ordered along the whole chain.  Several kernels of the chain are thus resident ahead of the
+// running one, their launch latency and prologues hidden; the products use the time to request
+// their weight tiles (which no kernel writes).  Without the launch attribute both are no-ops.
+// Before its wait a kernel may read only what no kernel of the chain writes: weights, and the
+// batch description of the step (positions, request of a token, portion starts, state slots,
+// block tables), which the host copies to the device before the step's first kernel.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -20,22 +20,23 @@ namespace imparo {
 constexpr int MAX_TAPS = 16;
 
 // The thread of a portion's first token, for one channel: outputs of the first min(n, taps-1)
-// tokens from the old state, then the new state.
+// tokens from the old state, then the new state.  wk: this channel's taps (loaded by the caller,
+// before it waited for the previous kernel).  Everything the outputs need is requested in one
+// batch of loads: a decode token costs one round trip to memory after the wait.
 template <typename T>
-__device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, const float* __restrict__ w, float b0,
-                                                  float* __restrict__ state, const int* __restrict__ item_slot,
+__device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, const float* wk, float b0,
+                                                  float* __restrict__ state, int slot,
                                                   T* __restrict__ y, int item, int start, int n, int ch,
                                                   int width, int taps, int n_slots, int* status) {
     const int hist = taps - 1;
     const size_t stride = (size_t)3 * width;
-    const int slot = item_slot[item];
     if (slot < 0 || slot >= n_slots) {
         if (ch == 0) report(status, IMPARO_ST_SLOT_RANGE, 4, item, slot);
         return;
     }
     float* st = state + (size_t)slot * hist * width + ch;
     // seq[e], e in [0, hist + m): the old state then the first m values of this portion
-    float seq[2 * MAX_TAPS];
+    float seq[2 * MAX_TAPS], gate[MAX_TAPS];
     const int m = min(n, hist);
 #pragma unroll
     for (int e = 0; e < MAX_TAPS; ++e) if (e < hist) seq[e] = st[(size_t)e * width];
@@ -44,13 +45,14 @@ __device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, con
         if (e < m) {
             const T* r = bcx + (size_t)(start + e) * stride;
             seq[hist + e] = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+            gate[e] = to_f32(r[width + ch]);
         }
     }
     for (int e = 0; e < m; ++e) {
         float acc = 0.f;
-        for (int k = 0; k < taps; ++k) acc += w[(size_t)ch * taps + k] * seq[e + k];
+        for (int k = 0; k < taps; ++k) acc += wk[k] * seq[e + k];
         acc += b0;
-        y[(size_t)(start + e) * width + ch] = from_f32<T>(to_f32(bcx[(size_t)(start + e) * stride + width + ch]) * acc);
+        y[(size_t)(start + e) * width + ch] = from_f32<T>(gate[e] * acc);
     }
     // new state slot s = seq_full[n + s]
     for (int s = 0; s < hist; ++s) {
@@ -66,13 +68,15 @@ __device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, con
     }
 }
 
+// The batch description (which request a token belongs to, where its portion starts, its state
+// slot) comes from the host before the step and the taps are weights: both are read before the
+// wait on the previous kernel, so that after it only activations and state remain to be fetched.
 template <typename T>
 __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ w,
                                   const float* __restrict__ bias, float* __restrict__ state,
                                   const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                   const int* __restrict__ item_slot, T* __restrict__ y,
                                   int n_tok, int width, int taps, int n_slots, int* status) {
-    pdl_wait();
     pdl_trigger();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tok * width) return;
@@ -82,21 +86,33 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
     const int n = item_row_start[item + 1] - start;
     const int rel = t - start;
     const int hist = taps - 1;
+    if (rel > 0 && rel < hist) return;           // written by the thread of the portion's first token
+    const int slot = rel == 0 ? item_slot[item] : 0;
     const size_t stride = (size_t)3 * width;
+    float wk[MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) wk[k] = k < taps ? w[(size_t)ch * taps + k] : 0.f;
     const float b0 = bias ? bias[ch] : 0.f;
+    pdl_wait();
 
     if (rel >= hist) {
-        float acc = 0.f;
-        for (int k = 0; k < taps; ++k) {
-            const T* r = bcx + (size_t)(t - hist + k) * stride;
-            acc += w[(size_t)ch * taps + k] * (to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]));
+        float v[MAX_TAPS];
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) {
+            if (k < taps) {
+                const T* r = bcx + (size_t)(t - hist + k) * stride;
+                v[k] = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+            }
         }
+        const float gate = to_f32(bcx[(size_t)t * stride + width + ch]);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) if (k < taps) acc += wk[k] * v[k];
         acc += b0;
-        y[(size_t)t * width + ch] = from_f32<T>(to_f32(bcx[(size_t)t * stride + width + ch]) * acc);
+        y[(size_t)t * width + ch] = from_f32<T>(gate * acc);
         return;
     }
-    if (rel != 0) return;
-    conv_portion_head<T>(bcx, w, b0, state, item_slot, y, item, start, n, ch, width, taps, n_slots, status);
+    conv_portion_head<T>(bcx, wk, b0, state, slot, y, item, start, n, ch, width, taps, n_slots, status);
 }
 
 // bfloat16 with a width that is a multiple of 8, for prompt-sized batches: a thread owns eight
@@ -108,8 +124,8 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
                                          const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                          const int* __restrict__ item_slot, __nv_bfloat16* __restrict__ y,
                                          int n_tok, int width, int taps, int n_slots, int* status) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int per_row = width >> 3;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tok * per_row) return;
@@ -121,9 +137,13 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
     if (rel < hist) {
         if (rel != 0) return;
         const int n = item_row_start[item + 1] - start;
-        for (int i = 0; i < 8; ++i)
-            conv_portion_head<__nv_bfloat16>(bcx, w, bias ? bias[ch + i] : 0.f, state, item_slot, y, item, start, n,
+        const int slot = item_slot[item];
+        for (int i = 0; i < 8; ++i) {
+            float wk[MAX_TAPS];
+            for (int k = 0; k < taps; ++k) wk[k] = w[(size_t)(ch + i) * taps + k];
+            conv_portion_head<__nv_bfloat16>(bcx, wk, bias ? bias[ch + i] : 0.f, state, slot, y, item, start, n,
                                              ch + i, width, taps, n_slots, status);
+        }
         return;
     }
     const size_t stride = (size_t)3 * width;

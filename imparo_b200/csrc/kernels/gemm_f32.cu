@@ -16,8 +16,8 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
                 int M, int N, int K, int lda, int ldc, int accumulate) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;        // 16 x 16 threads, each 4 x 4 outputs

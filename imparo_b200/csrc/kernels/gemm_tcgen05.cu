@@ -201,9 +201,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_x, &full[s], (kb_begin + i) * BK, tile_t * NT);
             };
             const int early = n_kb < STAGES ? n_kb : STAGES;
+            pdl_trigger();
             for (int i = 0; i < early; ++i) load_w(i);
             if (!NORM) pdl_wait();
-            pdl_trigger();
             for (int i = 0; i < early; ++i) load_x(i);
             for (int i = early; i < n_kb; ++i) {
                 const int s = i % STAGES;

@@ -12,8 +12,8 @@ namespace imparo {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int width, int vocab, int* status) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) {
@@ -46,8 +46,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                const float* __restrict__ w, float eps, TOut* __restrict__ out,
                                int width) {
     __shared__ float scratch[33];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
     TOut* o = out + (size_t)r * width;
@@ -83,12 +83,42 @@ __global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* 
                                             size_t split_stride, const float* __restrict__ w, float eps,
                                             TOut* __restrict__ out, int width) {
     __shared__ float scratch[33];
-    pdl_wait();
     pdl_trigger();
     const int r = blockIdx.x;
     float* xr = x + (size_t)r * width;
     const float* pr = part + (size_t)r * width;
     float ss = 0.f;
+    if ((width & 3) == 0 && (split_stride & 3) == 0 && width <= (int)blockDim.x * 4) {
+        // A thread owns four columns and keeps them in registers.  The norm weight (written by no
+        // kernel) is fetched before the wait; after it the row and all its partials are requested
+        // at once, so the kernel costs one round trip to memory, a block sum and the stores.
+        const int i = threadIdx.x * 4;
+        const bool mine = i < width;
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mine && out) g = __ldg(reinterpret_cast<const float4*>(w + i));
+        pdl_wait();
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mine) {
+            v = *reinterpret_cast<const float4*>(xr + i);
+            for (int s0 = 0; s0 < n_splits; s0 += 16) {
+                float4 p[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (s0 + u < n_splits) p[u] = __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(s0 + u) * split_stride + i));
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (s0 + u < n_splits) { v.x += p[u].x; v.y += p[u].y; v.z += p[u].z; v.w += p[u].w; }
+            }
+            *reinterpret_cast<float4*>(xr + i) = v;
+            ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        if (out == nullptr) return;
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+        if (mine) store4<TOut>(out + (size_t)r * width + i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        return;
+    }
+    pdl_wait();
     if ((width & 3) == 0 && (split_stride & 3) == 0) {
         // 16-byte loads, and all of a chunk's split loads in flight before the (ordered) adds
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
@@ -125,8 +155,8 @@ __global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* 
 // gu: [T, 2F] rows = [gate | up]; out: [T, F]
 template <typename T>
 __global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tok, int F) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_tok * F) return;
     const size_t t = i / F, f = i % F;
@@ -137,8 +167,8 @@ __global__ void swiglu_act_kernel(const T* __restrict__ gu, T* __restrict__ out,
 
 // eight features per thread, 16-byte loads and stores (F a multiple of 8)
 __global__ void swiglu_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n_tok, int F) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int per_row = F >> 3;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_tok * per_row) return;
@@ -160,8 +190,8 @@ __global__ void swiglu_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, _
 // ---- out[t, :] += bias ----------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n_tok, int width) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_tok * width) return;
     out[i] = from_f32<T>(to_f32(out[i]) + bias[i % width]);

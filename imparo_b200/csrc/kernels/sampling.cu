@@ -53,8 +53,8 @@ sample_rows_kernel(const float* __restrict__ logits, const float* __restrict__ t
     __shared__ float fscratch[33];
     __shared__ float part[SAMPLE_THREADS];
     __shared__ int pick;
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const int per = (vocab + blockDim.x - 1) / blockDim.x;
@@ -118,8 +118,8 @@ __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx,
                       int vocab, int ld) {
     __shared__ MaxIdx scratch[33];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.y, part = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
@@ -135,8 +135,8 @@ argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     int* __restrict__ out) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, lane = threadIdx.x;
     MaxIdx m{part_val[r * ARGMAX_PARTS + lane], part_idx[r * ARGMAX_PARTS + lane]};
 #pragma unroll
