@@ -25,16 +25,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LFM2_1_2B = {
-    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
-    "vocab_size": 65536, "hidden_size": 2048, "num_hidden_layers": 16,
-    "layer_types": ["conv", "conv", "full_attention", "conv", "conv", "full_attention", "conv", "conv",
-                    "full_attention", "conv", "full_attention", "conv", "full_attention", "conv", "full_attention", "conv"],
-    "num_attention_heads": 32, "num_key_value_heads": 8,
-    "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
-    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5,
-    "tie_embedding": True, "max_position_embeddings": 128000,
-}
+# the config.json of LFM2-1.2B (the sizes the headline is quoted on); weights are random
+with open(os.path.join(ROOT, "imparo_b200", "config", "presets", "lfm2_1.2b.json")) as _f:
+    LFM2_1_2B = json.load(_f)
 PROMPT = 2048
 CTX = 4096
 PAGE = 16

@@ -264,26 +264,30 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
 // ---- single query tokens (decode rows), split over key chunks, on tensor cores -----------
 // One CTA per (key chunk, kv head, token).  The token's G query heads are rows 0..G-1 of a
-// 16-row MMA tile (the rest is padding).  The chunk's keys are staged 64 at a time with
-// cp.async (double buffer); each of the four warps scores 16 of the 64 keys, keeps its own
-// running max / sum / accumulator, and the warps are folded in warp order at the end.  The
-// result is an unnormalised partial per (token, head, chunk) for the ordered combine kernel
-// of attention_split.cu (same scratch layout: part_acc [T, nh, S, HD], part_ml [T, nh, S, 2]).
-// The general-purpose version of this kernel (any head size, 32-bit) is attention_split.cu;
-// this one exists because the scalar version is bound by instruction issue, not by memory.
+// 16-row MMA tile (the rest is padding) and are read straight into registers.  The chunk's keys
+// are staged 64 at a time with cp.async (double buffer); each of the four warps scores 16 of the
+// 64 keys, keeps its own running max / sum / accumulator, and the warps are folded in warp order
+// at the end.  The result is an unnormalised partial per (token, head, chunk) for the ordered
+// combine kernel of attention_split.cu (same scratch layout: part_acc [T, nh, S, HD], part_ml
+// [T, nh, S, 2]).  Tiles of keys that earlier steps wrote are requested before the wait on the
+// previous kernel.  The general-purpose version of this kernel (any head size, 32-bit) is
+// attention_split.cu; this one exists because the scalar version is bound by instruction issue,
+// not by memory.
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
                        const int* __restrict__ item_of_token, const int* __restrict__ table, int max_blocks,
                        int page_size, int n_pages, int window, float scale, float* __restrict__ part_acc,
-                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int* status) {
+                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int fresh, int* status) {
     constexpr int CH = HD / 8, KT = HD / 16, NT_O = HD / 8;
     extern __shared__ __align__(128) uint8_t pf_smem[];
-    uint8_t* q_s = pf_smem;                                            // [16][HD]
-    uint8_t* k_s[2] = {q_s + 16 * HD * 2, q_s + 16 * HD * 2 + KEYS * HD * 2};
+    // shared memory: two buffers of 64 keys and 64 values (32 KB at head size 64, so that four
+    // CTAs fit beside a resident product CTA); after the key loop the same bytes hold the warps'
+    // partial results for the fold
+    uint8_t* k_s[2] = {pf_smem, pf_smem + KEYS * HD * 2};
     uint8_t* v_s[2] = {k_s[1] + KEYS * HD * 2, k_s[1] + 2 * KEYS * HD * 2};
-    float* wm = reinterpret_cast<float*>(v_s[1] + KEYS * HD * 2);     // [4][8]
+    float* wm = reinterpret_cast<float*>(pf_smem);                     // [4][8]
     float* wl = wm + 32;                                               // [4][8]
     float* wacc = wl + 32;                                             // [4][8][HD]
     pdl_trigger();
@@ -300,27 +304,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int h0 = kvh * G;
     const size_t part_base = ((size_t)t * nh + h0) * n_splits + split;         // + g * n_splits
     const int* tab = table + (size_t)item_of_token[t] * max_blocks;
-    if (begin < end) {
-        const int b0 = begin / page_size, b1 = min((end - 1) / page_size, max_blocks - 1);
-        for (int b = b0 + tid * 32; b <= b1; b += THREADS * 32)                // one touch per 128-byte line
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(tab + b));
-    }
-    pdl_wait();
-    if (begin >= end) {
-        if (tid < G) {
-            part_ml[(part_base + (size_t)tid * n_splits) * 2] = -INFINITY;
-            part_ml[(part_base + (size_t)tid * n_splits) * 2 + 1] = 0.f;
-        }
-        return;
-    }
     const size_t kvw = (size_t)nkv * HD;
-
-    for (int i = tid; i < 16 * CH; i += THREADS) {
-        const int r = i / CH, c = i % CH;
-        const bool valid = r < G;
-        cp_async16(q_s + tile_off<HD>(r, c), q + ((size_t)t * nh + h0 + (valid ? r : 0)) * HD + c * 8, valid);
-    }
-    cp_commit();
     const int kb_first = begin / KEYS, kb_last = (end - 1) / KEYS;
     auto load_kv = [&](int kb, int buf) {
         for (int i = tid; i < KEYS * CH; i += THREADS) {
@@ -344,16 +328,43 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         cp_commit();
     };
-    load_kv(kb_first, 0);
-    cp_wait<1>();
-    __syncthreads();
+    // Keys and values at positions below pos + 1 - fresh were written by earlier steps, not by a
+    // kernel this one may overlap with (fresh = the most tokens one request brings to this step; 0 =
+    // not known): the first two tiles are requested before the wait when they lie there entirely.
+    const int old_end = fresh > 0 ? pos + 1 - fresh : -1;
+    int requested = kb_first - 1;                                       // tiles asked for so far
+    if (begin < end) {
+        for (int u = 0; u < 2; ++u) {
+            const int kb = kb_first + u;
+            if (kb <= kb_last && min(end, (kb + 1) * KEYS) <= old_end) { load_kv(kb, u); requested = kb; } else break;
+        }
+    }
+    pdl_wait();
+    if (begin >= end) {
+        if (tid < G) {
+            part_ml[(part_base + (size_t)tid * n_splits) * 2] = -INFINITY;
+            part_ml[(part_base + (size_t)tid * n_splits) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+
+    // the queries go straight to registers in the MMA's A layout: row g of the 16-row tile is head
+    // h0 + g (rows from G up are padding)
     uint32_t qf[KT][4];
     {
-        const int m = lane >> 3, rin = lane & 7;
-        const int r = (m & 1) * 8 + rin;
+        const __nv_bfloat16* qrow = q + ((size_t)t * nh + h0 + (g < G ? g : 0)) * HD + 2 * tg;
 #pragma unroll
-        for (int kt = 0; kt < KT; ++kt) ldmatrix4(qf[kt], smem_addr(q_s + tile_off<HD>(r, kt * 2 + (m >> 1))));
+        for (int kt = 0; kt < KT; ++kt) {
+            qf[kt][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16) : 0u;
+            qf[kt][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 8) : 0u;
+            qf[kt][1] = qf[kt][3] = 0u;
+        }
     }
+    if (requested < kb_first) {
+        load_kv(kb_first, 0);
+        requested = kb_first;
+    }
+    if (tid == 0) timeline_mark(0);
     float o[NT_O][2];                                                   // rows 0..7 only (G <= 8)
 #pragma unroll
     for (int n = 0; n < NT_O; ++n) { o[n][0] = o[n][1] = 0.f; }
@@ -362,8 +373,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     for (int kb = kb_first; kb <= kb_last; ++kb) {
         const int buf = (kb - kb_first) & 1;
-        if (kb < kb_last) load_kv(kb + 1, buf ^ 1);
-        if (kb < kb_last) cp_wait<1>(); else cp_wait<0>();
+        if (kb < kb_last && requested < kb + 1) {
+            load_kv(kb + 1, buf ^ 1);
+            requested = kb + 1;
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
+        }
         __syncthreads();
         const int mi = lane >> 3, rin = lane & 7;
         // this warp's 16 keys of the tile
@@ -424,6 +440,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         __syncthreads();
     }
+    if (tid == 0) timeline_mark(1);                                     // the key loop is done
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     // ---- fold the four warps (row g = head h0 + g), in warp order ----
@@ -507,30 +524,30 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
                                            const int* positions, const int* item_of_token,
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, float* part_acc, float* part_ml,
-                                           int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
+                                           int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
                                            int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
     if (n_tok > 65535 || nkv > 65535 || chunk < 64 || n_splits < 1) return -2;
     dim3 grid(n_splits, nkv, n_tok);
-    const size_t smem = (size_t)(16 + 4 * pf::KEYS) * hd * 2 + 64 * 4 + (size_t)4 * 8 * hd * 4;
+    const size_t smem = (size_t)4 * pf::KEYS * hd * 2;          // the fold's 256 + 128 * hd bytes fit inside
     static bool configured = false;
     cudaError_t e;
     if (!configured) {
         e = cudaFuncSetAttribute(pf::attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (16 + 4 * pf::KEYS) * 128 * 2 + 64 * 4 + 4 * 8 * 128 * 4);
+                                 4 * pf::KEYS * 128 * 2);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     if (hd == 64)
         e = launch(pf::attn_decode_mma_kernel<64>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
                    (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
-                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, status);
+                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status);
     else
         e = launch(pf::attn_decode_mma_kernel<128>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
                    (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
-                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, status);
+                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status);
     if (e != cudaSuccess) return (int)e;
     return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, stream);
 }

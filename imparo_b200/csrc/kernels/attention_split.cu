@@ -234,36 +234,53 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
     }
 }
 
-// One block per (token, head): fold the splits in order.
+// One block per (token, head): fold the splits in order.  The splits' (max, sum) pairs go
+// through shared memory and the first sixteen splits' accumulators are requested at the same
+// time, so the usual launch costs one round trip to memory.
+constexpr int COMBINE_MAX_SPLITS = 2048;
 template <typename T>
 __global__ void attn_split_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                           T* __restrict__ out, int hd, int n_splits) {
+    __shared__ float f_s[COMBINE_MAX_SPLITS];             // exp(max_s - M), 0 for an empty split
+    __shared__ float l_s[COMBINE_MAX_SPLITS];
+    __shared__ float m_all;
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;                         // token * nh + head
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) if (__ldcg(ml + 2 * s + 1) > 0.f) M = fmaxf(M, __ldcg(ml + 2 * s));
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float a = 0.f, L = 0.f;
-        // eight splits' loads in flight at a time; the adds stay in split order
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {
-            float pa[8], pm[8], pl[8];
+    const float* acc = part_acc + th * n_splits * hd;
+    const int d0 = threadIdx.x;
+    float pa[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int s = s0 + u;
-                if (s < n_splits) {
-                    pm[u] = __ldcg(ml + 2 * s);
-                    pl[u] = __ldcg(ml + 2 * s + 1);
-                    pa[u] = __ldcg(part_acc + (th * n_splits + s) * hd + d);
-                }
+    for (int u = 0; u < 16; ++u) pa[u] = (u < n_splits && d0 < hd) ? __ldcg(acc + (size_t)u * hd + d0) : 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(ml) + s);
+        f_s[s] = v.x;
+        l_s[s] = v.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int s = threadIdx.x; s < n_splits; s += 32) if (l_s[s] > 0.f) M = fmaxf(M, f_s[s]);
+        M = warp_max(M);
+        if (threadIdx.x == 0) m_all = M;
+    }
+    __syncthreads();
+    const float M = m_all;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) f_s[s] = l_s[s] > 0.f ? expf(f_s[s] - M) : 0.f;
+    __syncthreads();
+    for (int d = d0; d < hd; d += blockDim.x) {
+        float a = 0.f, L = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 16) {
+            if (s0 > 0 || d != d0) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) pa[u] = s0 + u < n_splits ? __ldcg(acc + (size_t)(s0 + u) * hd + d) : 0.f;
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (s0 + u < n_splits && pl[u] > 0.f) {
-                    const float f = expf(pm[u] - M);
-                    a += pa[u] * f;
-                    L += pl[u] * f;
+            for (int u = 0; u < 16; ++u) {
+                if (s0 + u < n_splits && l_s[s0 + u] > 0.f) {
+                    a += pa[u] * f_s[s0 + u];
+                    L += l_s[s0 + u] * f_s[s0 + u];
                 }
             }
         }
@@ -344,6 +361,7 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
 extern "C" int imparo_attention_split_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
                                               int n_rows, int hd, int n_splits, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return -2;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == IMPARO_DT_F32)
         launch(attn_split_combine_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits);

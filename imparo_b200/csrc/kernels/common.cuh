@@ -100,13 +100,87 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 // Before its wait a kernel may read only what no kernel of the chain writes: weights, and the
 // batch description of the step (positions, request of a token, portion starts, state slots,
 // block tables), which the host copies to the device before the step's first kernel.
+#ifndef IMPARO_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// A kernel that wants the SMs to itself for a while triggers late: timeline_begin() where it
+// starts, pdl_trigger_late() where the dependents may come.
+__device__ __forceinline__ void pdl_trigger_late() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void timeline_begin() {}
+__device__ __forceinline__ void timeline_mark(int) {}
+#else
+// ---- device timeline (a build of its own, -DIMPARO_TIMELINE) ----------------------------
+// Thread 0 of block (0,0,0) of every launch takes the next record of a device buffer and stamps
+// the global nanosecond timer when the kernel's first block starts (at pdl_trigger), when its
+// wait on the previous kernel returns (at pdl_wait) and at up to two marks of the kernel's own.
+// buffer: [0] next record, [1] capacity, then records of four 64-bit words.  Records are taken in
+// launch order: a kernel's dependents cannot start before its blocks have all passed pdl_trigger.
+// Each translation unit holds its own copy of the buffer address (set at its first launch after
+// imparo_timeline_start); the host list of launched functions is shared.
+#include <vector>
+static __device__ unsigned long long* g_timeline = nullptr;
+inline unsigned long long* g_timeline_host = nullptr;
+inline int g_timeline_epoch = 0;
+inline std::vector<const void*> g_timeline_funcs;
+static int g_timeline_bound = -1;
+
+__device__ __forceinline__ unsigned long long timeline_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ int* timeline_slot() { __shared__ int slot; return &slot; }
+__device__ __forceinline__ bool timeline_thread() {
+    return g_timeline != nullptr && threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+}
+__device__ __forceinline__ void timeline_stamp(int word) {
+    const int slot = *timeline_slot();
+    if (slot >= 0) g_timeline[2 + (size_t)slot * 4 + word] = timeline_ns();
+}
+__device__ __forceinline__ void timeline_begin() {
+    if (timeline_thread()) {
+        const unsigned long long slot = atomicAdd(g_timeline, 1ULL);
+        *timeline_slot() = slot < g_timeline[1] ? (int)slot : -1;
+        timeline_stamp(0);
+    }
+}
+__device__ __forceinline__ void pdl_trigger() {
+    timeline_begin();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_trigger_late() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (timeline_thread()) timeline_stamp(1);
+}
+// which = 0 or 1; call it from ONE thread of the launch's blocks; only block (0,0,0) records
+__device__ __forceinline__ void timeline_mark(int which) {
+    if (g_timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) timeline_stamp(2 + which);
+}
+// host: remember the launched function and make sure this unit knows the buffer
+static inline cudaError_t timeline_note(const void* kernel) {
+    if (g_timeline_host == nullptr) return cudaSuccess;
+    if (g_timeline_bound != g_timeline_epoch) {
+        cudaError_t e = cudaMemcpyToSymbol(g_timeline, &g_timeline_host, sizeof(g_timeline_host));
+        if (e != cudaSuccess) return e;
+        g_timeline_bound = g_timeline_epoch;
+    }
+    g_timeline_funcs.push_back(kernel);
+    return cudaSuccess;
+}
+#endif
+#ifndef IMPARO_TIMELINE
+static inline cudaError_t timeline_note(const void*) { return cudaSuccess; }
+#endif
 
 extern "C" int imparo_pdl_enabled();
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+static inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    {
+        cudaError_t e = timeline_note(reinterpret_cast<const void*>(kernel));
+        if (e != cudaSuccess) return e;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

@@ -112,6 +112,28 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
         y[(size_t)t * width + ch] = from_f32<T>(gate * acc);
         return;
     }
+    if (n == 1 && slot >= 0 && slot < n_slots) {
+        // a decode token: everything in registers, one batch of loads
+        float* st = state + (size_t)slot * hist * width + ch;
+        float sv[MAX_TAPS];
+#pragma unroll
+        for (int e = 0; e < MAX_TAPS - 1; ++e) sv[e] = e < hist ? st[(size_t)e * width] : 0.f;
+        const T* r = bcx + (size_t)t * stride;
+        const float bx = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+        const float gate = to_f32(r[width + ch]);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) {
+            if (k < hist) acc += wk[k] * sv[k];
+            else if (k == hist) acc += wk[k] * bx;
+        }
+        acc += b0;
+        y[(size_t)t * width + ch] = from_f32<T>(gate * acc);
+#pragma unroll
+        for (int e = 0; e < MAX_TAPS - 1; ++e)
+            if (e < hist) st[(size_t)e * width] = (e + 1 < hist) ? sv[e + 1] : bx;
+        return;
+    }
     conv_portion_head<T>(bcx, wk, b0, state, slot, y, item, start, n, ch, width, taps, n_slots, status);
 }
 

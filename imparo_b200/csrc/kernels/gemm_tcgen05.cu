@@ -294,6 +294,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b_ready)) : "memory");
         }
         bool ok = n_kb == 0 || mbar_wait(acc_ready, 0);
+        if (threadIdx.x == 64) timeline_mark(0);                // the accumulator is complete
         if (!ok && lane == 0) report(p.status, IMPARO_ST_WAIT_LIMIT, 12, tile_n, split);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -448,6 +449,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) timeline_mark(1);                     // this CTA's epilogue is done
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
@@ -508,6 +510,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
+    e = timeline_note(reinterpret_cast<const void*>(kern));
+    if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(THREADS);

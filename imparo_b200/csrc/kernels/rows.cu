@@ -206,6 +206,49 @@ static int g_pdl = 1;
 extern "C" int imparo_pdl_enabled() { return g_pdl; }
 extern "C" void imparo_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+// ---- device timeline: host side (see common.cuh) -------------------------------------------
+// buffer: device memory of (2 + 4 * capacity) 64-bit words.  Returns -1 when the library was
+// built without IMPARO_TIMELINE.
+extern "C" int imparo_timeline_start(unsigned long long* buffer, long long capacity) {
+#ifdef IMPARO_TIMELINE
+    if (buffer == nullptr || capacity <= 0) { g_timeline_host = nullptr; ++g_timeline_epoch; return 0; }
+    const unsigned long long head[2] = {0ULL, (unsigned long long)capacity};
+    cudaError_t e = cudaMemcpy(buffer, head, sizeof(head), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return (int)e;
+    g_timeline_host = buffer;
+    ++g_timeline_epoch;
+    g_timeline_funcs.clear();
+    return 0;
+#else
+    (void)buffer; (void)capacity;
+    return -1;
+#endif
+}
+// launches noted on the host since imparo_timeline_start (stream captures included), and the
+// name of the i-th one
+extern "C" long long imparo_timeline_launches() {
+#ifdef IMPARO_TIMELINE
+    return (long long)g_timeline_funcs.size();
+#else
+    return -1;
+#endif
+}
+extern "C" int imparo_timeline_name(long long i, char* out, int n) {
+#ifdef IMPARO_TIMELINE
+    if (i < 0 || i >= (long long)g_timeline_funcs.size() || n <= 0) return -2;
+    const char* name = nullptr;
+    cudaError_t e = cudaFuncGetName(&name, g_timeline_funcs[(size_t)i]);
+    if (e != cudaSuccess || name == nullptr) return (int)e;
+    int k = 0;
+    for (; k < n - 1 && name[k]; ++k) out[k] = name[k];
+    out[k] = 0;
+    return 0;
+#else
+    (void)i; (void)out; (void)n;
+    return -1;
+#endif
+}
+
 extern "C" int imparo_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
                                    int n_tok, int width, int vocab, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;

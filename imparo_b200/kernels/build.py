@@ -94,7 +94,7 @@ def _run(cmd, what: str) -> None:
         raise BuildError(f"compiling {what} failed:\n$ {' '.join(cmd)}\n{r.stdout}")
 
 
-def _build(name: str, sub: str, ext: str, compiler: str, cflags, link_cmd_tail) -> str:
+def _build(name: str, sub: str, ext: str, compiler: str, cflags, link_cmd_tail, variant: str = "") -> str:
     out_dir = build_dir()
     lib = os.path.join(out_dir, f"lib{name}.so")
     srcs, hdrs = _sources(sub, ext)
@@ -120,7 +120,7 @@ def _build(name: str, sub: str, ext: str, compiler: str, cflags, link_cmd_tail) 
         objs = []
 
         def one(src):
-            obj = os.path.join(out_dir, os.path.basename(src) + ".o")
+            obj = os.path.join(out_dir, os.path.basename(src) + variant + ".o")
             # per-file digest: only changed files are recompiled
             d = _digest([src] + hdrs, [compiler] + list(cflags))
             ostamp = obj + ".stamp"
@@ -146,13 +146,22 @@ def _build(name: str, sub: str, ext: str, compiler: str, cflags, link_cmd_tail) 
     return lib
 
 
+def timeline_build() -> bool:
+    """IMPARO_TIMELINE=1 selects a second build of the kernels that stamps a device timeline
+    (kernels/timeline.py); it has its own objects and library name."""
+    return os.environ.get("IMPARO_TIMELINE", "") not in ("", "0")
+
+
 def build_kernels() -> str:
     """-> path of the CUDA kernel library (sm_100a)."""
     nvcc = _find_nvcc()
     cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
     tail = ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "shared", "-Xcompiler", "-fPIC",
             f"-L{cuda_lib}", "-lcublas", "-Xlinker", f"-rpath={cuda_lib}"]
-    return _build("imparo_b200_kernels", "kernels", ".cu", nvcc, NVCC_FLAGS + ["-I", os.path.join(CSRC, "kernels")], tail)
+    flags = NVCC_FLAGS + ["-I", os.path.join(CSRC, "kernels")]
+    if timeline_build():
+        return _build("imparo_b200_kernels_timeline", "kernels", ".cu", nvcc, flags + ["-DIMPARO_TIMELINE"], tail, variant=".tl")
+    return _build("imparo_b200_kernels", "kernels", ".cu", nvcc, flags, tail)
 
 
 def build_host() -> str:

@@ -64,6 +64,9 @@ def host():
 
 def _declare_kernels(lib):
     S = c_void_p  # cudaStream_t
+    _declare(lib, "imparo_timeline_start", [P, c_int64])
+    _declare(lib, "imparo_timeline_launches", [], c_int64)
+    _declare(lib, "imparo_timeline_name", [c_int64, ctypes.c_char_p, I])
     _declare(lib, "imparo_embed_gather", [P, I, P, P, I, I, I, P, S])
     _declare(lib, "imparo_rmsnorm", [P, P, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_add_partials_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, S])
@@ -84,7 +87,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_paged_attention_split",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_decode_mma",
-             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
+             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, P, S])

@@ -535,9 +535,15 @@ def split_plan(n_tok: int, nkv: int, upper_context: int):
 
 
 def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
-                          out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True) -> bool:
+                          out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True,
+                          fresh: int = 0) -> bool:
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
-    combine).  Returns False, having launched nothing, when the group size is above 8."""
+    combine).  Returns False, having launched nothing, when the group size is above 8.
+
+    fresh: the most tokens one request brings to this step, when the caller knows that cache rows
+    below `position + 1 - fresh` were written before the stream's last copy or foreign kernel (the
+    engine's steps start with such a copy).  The tensor-core kernel then requests its first key
+    tiles while the kernels before it still run.  0: nothing is assumed."""
     if nh // nkv > 8:
         return False
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
@@ -555,7 +561,7 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
         rc = _lib.kernels().imparo_attention_decode_mma(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table),
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
-            T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
+            T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), _ptr(status), _stream())
     else:
         rc = _lib.kernels().imparo_paged_attention_split(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),

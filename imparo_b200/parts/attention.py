@@ -93,7 +93,7 @@ class AttentionMixer(Part):
             part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32)
             done = ops.paged_attention_split(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size,
                                              kv.n_pages, self.window, self.scale, out, part_acc, part_ml, chunk,
-                                             n_splits, nh, self.nkv, hd, rt.status)
+                                             n_splits, nh, self.nkv, hd, rt.status, fresh=batch.max_tokens_per_item)
         if not done:
             ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
                                 self.window, self.scale, out, nh, self.nkv, hd, rt.status)

@@ -237,13 +237,17 @@ def run_attention(kind, q, kc, vc, positions, items, table, page, n_pages, windo
     part_acc = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
     part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
     assert o.paged_attention_split(q, kc, vc, positions, items, table, page, n_pages, window, scale, out, part_acc, part_ml,
-                                   chunk, n_splits, nh, nkv, hd, status, mma=(kind == "split_mma"))
+                                   chunk, n_splits, nh, nkv, hd, status, mma=kind.startswith("split_mma"),
+                                   fresh=1 if kind == "split_mma_early" else 0)
 
 
 # "split": the scalar split-key kernel; "split_mma": its tensor-core version where it applies
 # (bfloat16, head 64 or 128), else the scalar one again
+# "split_mma_early": the same, told that every cache row but a token's own was written before the
+# launch's stream last synchronised (true here: the caches are copied to the device), so that it
+# requests its first key tiles before waiting for the previous kernel
 KINDS = [("general", None), ("split", None), ("split", 64), ("split", 512), ("split_mma", None), ("split_mma", 64),
-         ("split_mma", 512)]
+         ("split_mma", 512), ("split_mma_early", None), ("split_mma_early", 64), ("split_mma_early", 128)]
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256), (8, 1, 64)])
