@@ -29,7 +29,8 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
                           const float* __restrict__ inv_freq, int n_rot, float eps,
                           T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                           const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                          int nh, int nkv, int hd, int* status) {
+                          int nh, int nkv, int hd, const float* __restrict__ part, int parts, size_t part_stride,
+                          int* status) {
     __shared__ float rowbuf[WARPS][MAX_HEAD];
     constexpr int PER = MAX_HEAD / 32, PAIRS = MAX_HEAD / 64;
     pdl_trigger();
@@ -83,11 +84,33 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
 
     float val[PER];
     float ss = 0.f;
+    if (parts > 0) {
+        // the product before this kernel was cut along K and left its partial results
+        // [parts][tokens][width]: summed here in split order and rounded as a stored tensor would be
+        const float* ps = part + (size_t)t * in_width + (size_t)hh * hd;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const int d = lane + 32 * j;
-        val[j] = d < hd ? to_f32(src[d]) : 0.f;
-        ss += val[j] * val[j];
+        for (int j = 0; j < PER; ++j) {
+            const int d = lane + 32 * j;
+            float acc = 0.f;
+            if (d < hd) {
+                for (int s0 = 0; s0 < parts; s0 += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = s0 + u < parts ? __ldcg(ps + (size_t)(s0 + u) * part_stride + d) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) if (s0 + u < parts) acc += v[u];
+                }
+            }
+            val[j] = to_f32(from_f32<T>(acc));
+            ss += val[j] * val[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int d = lane + 32 * j;
+            val[j] = d < hd ? to_f32(src[d]) : 0.f;
+            ss += val[j] * val[j];
+        }
     }
     if (is_q || is_k) {
         ss = warp_sum(ss);
@@ -220,23 +243,30 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 
 using namespace imparo;
 
+// qkv: [n_tok, (nh + 2 nkv) * hd] of the dtype; or, when parts > 0, float partial results
+// [parts][n_tok][width] (split s at qkv + s * part_stride floats) of a product cut along K.
 extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* positions, const int* item_of_token,
                                          const float* q_w, const float* k_w, const float* inv_freq, int n_rot, float eps,
                                          void* q_out, void* k_cache, void* v_cache,
                                          const int* table, int max_blocks, int page_size, int n_pages,
-                                         int n_tok, int nh, int nkv, int hd, int* status, cudaStream_t stream) {
+                                         int n_tok, int nh, int nkv, int hd, int parts, long long part_stride,
+                                         int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (hd < 16 || hd > MAX_HEAD || hd % 16 != 0) return -3;
     if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
+    if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * (nh + 2 * nkv) * hd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
+    const float* part = parts > 0 ? (const float*)qkv : nullptr;
     if (dtype == IMPARO_DT_F32)
         launch(qk_norm_rope_store_kernel<float>, grid, dim3(WARPS * 32), 0, stream,
             (const float*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (float*)q_out,
-            (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
+            (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts,
+            (size_t)part_stride, status);
     else if (dtype == IMPARO_DT_BF16)
         launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream,
             (const __nv_bfloat16*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (__nv_bfloat16*)q_out,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, status);
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts,
+            (size_t)part_stride, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -19,12 +19,43 @@ namespace imparo {
 
 constexpr int MAX_TAPS = 16;
 
+// The input rows [b | c | x]: a stored tensor of T, or the partial results of a product that was
+// cut along K (float [parts][tokens][3 * width]).  Partials are summed in split order and rounded
+// to T, which is what the product's own fold would have stored.
+template <typename T>
+struct ConvIn {
+    const T* rows;
+    const float* part;
+    int parts;
+    size_t part_stride;
+    __device__ __forceinline__ float at(size_t idx) const {
+        if (parts <= 0) return to_f32(rows[idx]);
+        float acc = 0.f;
+        if (parts <= 4) {                       // straight-line: the loads of several values overlap
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = u < parts ? __ldcg(part + (size_t)u * part_stride + idx) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (u < parts) acc += v[u];
+        } else {
+            for (int s0 = 0; s0 < parts; s0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = s0 + u < parts ? __ldcg(part + (size_t)(s0 + u) * part_stride + idx) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) if (s0 + u < parts) acc += v[u];
+            }
+        }
+        return to_f32(from_f32<T>(acc));
+    }
+};
+
 // The thread of a portion's first token, for one channel: outputs of the first min(n, taps-1)
 // tokens from the old state, then the new state.  wk: this channel's taps (loaded by the caller,
 // before it waited for the previous kernel).  Everything the outputs need is requested in one
 // batch of loads: a decode token costs one round trip to memory after the wait.
 template <typename T>
-__device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, const float* wk, float b0,
+__device__ __forceinline__ void conv_portion_head(const ConvIn<T>& bcx, const float* wk, float b0,
                                                   float* __restrict__ state, int slot,
                                                   T* __restrict__ y, int item, int start, int n, int ch,
                                                   int width, int taps, int n_slots, int* status) {
@@ -43,9 +74,9 @@ __device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, con
 #pragma unroll
     for (int e = 0; e < MAX_TAPS; ++e) {
         if (e < m) {
-            const T* r = bcx + (size_t)(start + e) * stride;
-            seq[hist + e] = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
-            gate[e] = to_f32(r[width + ch]);
+            const size_t r = (size_t)(start + e) * stride;
+            seq[hist + e] = bcx.at(r + ch) * bcx.at(r + 2 * (size_t)width + ch);
+            gate[e] = bcx.at(r + width + ch);
         }
     }
     for (int e = 0; e < m; ++e) {
@@ -61,8 +92,8 @@ __device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, con
         if (e < hist + m) {
             v = seq[e];
         } else {
-            const T* r = bcx + (size_t)(start + e - hist) * stride;
-            v = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+            const size_t r = (size_t)(start + e - hist) * stride;
+            v = bcx.at(r + ch) * bcx.at(r + 2 * (size_t)width + ch);
         }
         st[(size_t)s * width] = v;
     }
@@ -72,7 +103,7 @@ __device__ __forceinline__ void conv_portion_head(const T* __restrict__ bcx, con
 // slot) comes from the host before the step and the taps are weights: both are read before the
 // wait on the previous kernel, so that after it only activations and state remain to be fetched.
 template <typename T>
-__global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ w,
+__global__ void gated_conv_kernel(const ConvIn<T> bcx, const float* __restrict__ w,
                                   const float* __restrict__ bias, float* __restrict__ state,
                                   const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                   const int* __restrict__ item_slot, T* __restrict__ y,
@@ -100,11 +131,11 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
 #pragma unroll
         for (int k = 0; k < MAX_TAPS; ++k) {
             if (k < taps) {
-                const T* r = bcx + (size_t)(t - hist + k) * stride;
-                v[k] = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
+                const size_t r = (size_t)(t - hist + k) * stride;
+                v[k] = bcx.at(r + ch) * bcx.at(r + 2 * (size_t)width + ch);
             }
         }
-        const float gate = to_f32(bcx[(size_t)t * stride + width + ch]);
+        const float gate = bcx.at((size_t)t * stride + width + ch);
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < MAX_TAPS; ++k) if (k < taps) acc += wk[k] * v[k];
@@ -118,9 +149,9 @@ __global__ void gated_conv_kernel(const T* __restrict__ bcx, const float* __rest
         float sv[MAX_TAPS];
 #pragma unroll
         for (int e = 0; e < MAX_TAPS - 1; ++e) sv[e] = e < hist ? st[(size_t)e * width] : 0.f;
-        const T* r = bcx + (size_t)t * stride;
-        const float bx = to_f32(r[ch]) * to_f32(r[2 * (size_t)width + ch]);
-        const float gate = to_f32(r[width + ch]);
+        const size_t r = (size_t)t * stride;
+        const float bx = bcx.at(r + ch) * bcx.at(r + 2 * (size_t)width + ch);
+        const float gate = bcx.at(r + width + ch);
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < MAX_TAPS; ++k) {
@@ -163,7 +194,7 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
         for (int i = 0; i < 8; ++i) {
             float wk[MAX_TAPS];
             for (int k = 0; k < taps; ++k) wk[k] = w[(size_t)(ch + i) * taps + k];
-            conv_portion_head<__nv_bfloat16>(bcx, wk, bias ? bias[ch + i] : 0.f, state, slot, y, item, start, n,
+            conv_portion_head<__nv_bfloat16>(ConvIn<__nv_bfloat16>{bcx, nullptr, 0, 0}, wk, bias ? bias[ch + i] : 0.f, state, slot, y, item, start, n,
                                              ch + i, width, taps, n_slots, status);
         }
         return;
@@ -205,27 +236,34 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
 
 using namespace imparo;
 
+// bcx: [n_tok, 3 * width] of the dtype; or, when parts > 0, float partial results
+// [parts][n_tok][3 * width] (split s at bcx + s * part_stride floats) of a product cut along K,
+// which this kernel sums (the dtype then names the output and the rounding of the sum).
 extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, const float* bias, float* state,
                                  const int* item_row_start, const int* item_of_token, const int* item_slot,
-                                 void* y, int n_tok, int width, int taps, int n_slots, int* status,
-                                 cudaStream_t stream) {
+                                 void* y, int n_tok, int width, int taps, int n_slots, int parts, long long part_stride,
+                                 int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (taps < 2 || taps > MAX_TAPS) return -6;
+    if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * 3 * width)) return -2;
     const size_t n = (size_t)n_tok * width;
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
-    if (dtype == IMPARO_DT_F32)
-        launch(gated_conv_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)bcx, w, bias, state, item_row_start,
-                                                                item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
-    else if (dtype == IMPARO_DT_BF16) {
-        const bool wide = n_tok >= 64 && (width & 7) == 0 && (((uintptr_t)bcx | (uintptr_t)y) & 15) == 0;
+    const float* part = parts > 0 ? (const float*)bcx : nullptr;
+    if (dtype == IMPARO_DT_F32) {
+        ConvIn<float> in{(const float*)bcx, part, parts, (size_t)part_stride};
+        launch(gated_conv_kernel<float>, dim3(blocks), dim3(threads), 0, stream, in, w, bias, state, item_row_start,
+               item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
+    } else if (dtype == IMPARO_DT_BF16) {
+        const bool wide = parts == 0 && n_tok >= 64 && (width & 7) == 0 && (((uintptr_t)bcx | (uintptr_t)y) & 15) == 0;
         if (wide) {
             const size_t n8 = (size_t)n_tok * (width >> 3);
             launch(gated_conv_bf16x8_kernel, dim3((unsigned)((n8 + threads - 1) / threads)), dim3(threads), 0, stream,
                    (const __nv_bfloat16*)bcx, w, bias, state, item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y,
                    n_tok, width, taps, n_slots, status);
         } else {
-            launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)bcx, w, bias, state,
+            ConvIn<__nv_bfloat16> in{(const __nv_bfloat16*)bcx, part, parts, (size_t)part_stride};
+            launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, in, w, bias, state,
                    item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
         }
     } else return -1;

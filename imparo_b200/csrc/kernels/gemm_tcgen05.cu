@@ -149,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     uint64_t* b_ready = acc_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 1);
     int* flags = reinterpret_cast<int*>(tmem_slot + 1);            // [0]: this CTA folds the splits
-    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: [64][17], one 16-token chunk at a time
+    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: [128][17], one 16-token chunk at a time
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
@@ -301,23 +301,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         const int t0 = tile_t * NT;
 
         if (EPI == SWIGLU_BF16) {
-            // rows 0..63 hold gate, rows 64..127 hold up of features tile_n*64 + (row % 64)
-            const int f = tile_n * 64 + (row & 63);
+            // rows 0..63 hold gate, rows 64..127 hold up of features tile_n*64 + (row % 64).  Both go
+            // through shared memory, and the 128 threads then share the (feature, token) pairs: a
+            // lone warp doing sixteen silus in a row is bound by instruction latency
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+            const int e = (int)threadIdx.x - 64;
+            const int ff = e & 63, parity = e >> 6;
+            const int f = tile_n * 64 + ff;
 #pragma unroll 1
             for (int c = 0; c < NT; c += 16) {
                 float v[16];
                 tmem_ld16(taddr + c, v);
-                if (row >= 64) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) exch[(row - 64) * 17 + j] = v[j];
-                }
+                for (int j = 0; j < 16; ++j) exch[row * 17 + j] = v[j];
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (row < 64 && f < p.N) {
+                if (f < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c + j;
-                        if (t < p.T) out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(v[j]) * exch[row * 17 + j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        const int t = t0 + c + j + parity;
+                        if (t < p.T)
+                            out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(exch[ff * 17 + j + parity]) * exch[(64 + ff) * 17 + j + parity]);
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -398,12 +401,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 const int t = t0 + c;
                 if (t >= p.T) break;
                 float acc = 0.f;
-                for (int sidx = 0; sidx < p.splits; ++sidx) {
-                    uint32_t remote;
-                    float v;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(my + (uint32_t)c * BM * 4), "r"(sidx));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-                    acc += v;
+                for (int s0 = 0; s0 < p.splits; s0 += 8) {            // eight remote loads in flight, adds in split order
+                    float v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        v[u] = 0.f;
+                        if (s0 + u < p.splits) {
+                            uint32_t remote;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(my + (uint32_t)c * BM * 4), "r"(s0 + u));
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[u]) : "r"(remote));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) if (s0 + u < p.splits) acc += v[u];
                 }
                 if (n < p.N) store_out<EPI>(p.out, (size_t)t * p.ldo + n, acc);
             }
@@ -498,7 +508,7 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 
 template <int NT, int STAGES, int EPI, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
+    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 128 * 17 * 4 : 0);
     static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
     const size_t smem = fixed + (NORM ? (size_t)p.kblocks * NT * BK * 2 : 0);
     if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller norms separately
@@ -533,7 +543,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 // How many clusters of `cluster` CTAs of this kernel the device holds at once (0 on error).
 template <int NT, int STAGES, int EPI>
 static int max_clusters(int cluster) {
-    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 64 * 17 * 4 : 0);
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 128 * 17 * 4 : 0);
     auto kern = gemm_kernel<NT, STAGES, EPI, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};

@@ -151,6 +151,26 @@ __global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* 
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
+// ---- out = sum of split partials ----------------------------------------------------------
+// For a consumer that cannot read partials itself: out[i] = part[0][i] + part[1][i] + ... in order.
+template <typename TOut>
+__global__ void fold_partials_kernel(const float* __restrict__ part, int n_splits, size_t split_stride,
+                                     TOut* __restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = s0 + u < n_splits ? __ldcg(part + (size_t)(s0 + u) * split_stride + i) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) if (s0 + u < n_splits) acc += v[u];
+    }
+    out[i] = from_f32<TOut>(acc);
+}
+
 // ---- silu(gate) * up ----------------------------------------------------------------
 // gu: [T, 2F] rows = [gate | up]; out: [T, F]
 template <typename T>
@@ -307,6 +327,22 @@ extern "C" int imparo_add_bias(void* out, int dtype, const float* bias, int n_to
 }
 
 // x[r, :] += sum over s of part[s][r][:] (in order), and out = rms_norm(x) when out is not null.
+extern "C" int imparo_fold_partials(const float* part, int n_splits, long long split_stride, void* out, int out_dtype,
+                                    long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n_splits < 1 || split_stride < n) return -2;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (out_dtype == IMPARO_DT_F32)
+        launch(fold_partials_kernel<float>, dim3(blocks), dim3(threads), 0, stream, part, n_splits, (size_t)split_stride, (float*)out, (size_t)n);
+    else if (out_dtype == IMPARO_DT_BF16)
+        launch(fold_partials_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, part, n_splits, (size_t)split_stride,
+               (__nv_bfloat16*)out, (size_t)n);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" int imparo_add_partials_rmsnorm(float* x, const float* part, int n_splits, long long split_stride,
                                            const float* w, float eps, void* out, int out_dtype, int n_rows, int width,
                                            cudaStream_t stream) {

@@ -81,7 +81,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gemm_tc_norm", [P, I, P, P, c_float, P, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_gemm_tc", [P, I, I, P, P, I, I, I, I, I, P, P, P, S])
     _declare(lib, "imparo_qk_norm_rope_store",
-             [P, I, P, P, P, P, P, I, c_float, P, P, P, P, I, I, I, I, I, I, I, P, S])
+             [P, I, P, P, P, P, P, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_paged_attention",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_paged_attention_split",
@@ -90,7 +90,8 @@ def _declare_kernels(lib):
              [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
-    _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, P, S])
+    _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, c_int64, P, S])
+    _declare(lib, "imparo_fold_partials", [P, I, c_int64, P, I, c_int64, S])
     _declare(lib, "imparo_argmax_rows", [P, P, P, P, I, I, I, S])
     _declare(lib, "imparo_sample_rows", [P, P, P, P, I, I, I, S])
 

@@ -266,7 +266,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     _need(w.shape[1] == K and (epilogue != EPI_SWIGLU or w.shape[0] % 2 == 0), "gemm_tc: weight shape")
     _need(out.shape == (T, N) and out.stride(1) == 1, f"gemm_tc: out must be [{T}, {N}]")
     want_dtype = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32
-    _need(out.dtype == want_dtype, f"gemm_tc: this epilogue writes {want_dtype}")
+    _need(epilogue == EPI_PARTIAL or out.dtype == want_dtype, f"gemm_tc: this epilogue writes {want_dtype}")
     nt, splits, floats, counters = _tc_plan(T, N, K, epilogue)
     if epilogue == EPI_PARTIAL:
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= floats, "gemm_tc: partials scratch")
@@ -484,13 +484,78 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
 
 
+class PartialProduct:
+    """A product x w^T that was cut along K and not folded: parts[s] (float32 [T, N], split s at
+    offset s * stride floats) sum to the result.  gated_conv and qk_norm_rope_store read it as it is
+    (they sum in split order and round to `dtype`, what the product's own fold would have stored);
+    anything else calls tensor(), which folds it into the buffer the product would have written."""
+
+    def __init__(self, parts: torch.Tensor, splits: int, shape, out: torch.Tensor):
+        self.parts, self.splits, self.shape, self._out = parts, int(splits), tuple(shape), out
+        self.stride = self.shape[0] * self.shape[1]
+        self.dtype, self.device = out.dtype, out.device
+        self._done = False
+
+    def tensor(self) -> torch.Tensor:
+        if not self._done:
+            _check(_lib.kernels().imparo_fold_partials(_ptr(self.parts), self.splits, self.stride, _ptr(self._out),
+                                                       _code(self._out), self.stride, _stream()), "fold_partials")
+            self._done = True
+        return self._out
+
+
+_consumer_parts = {}
+
+
+def unfolded_products() -> bool:
+    """Whether linear_unfolded may leave split partials to its consumer (IMPARO_UNFOLDED=0 turns it off)."""
+    import os
+    return os.environ.get("IMPARO_UNFOLDED", "1") != "0"
+
+
+def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """out = x w^T for a consumer that can read split partials (gated_conv, qk_norm_rope_store).
+    Returns `out`, filled; or, when the tensor-core product is cut along K (few tokens), a
+    PartialProduct: each split's CTAs store their tile and are done, with no fold across CTAs inside
+    the product, and the consumer adds the splits while it reads."""
+    if isinstance(x, NormedInput):
+        x = x.tensor()
+    if unfolded_products() and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous() \
+            and gemm_backend() == "tcgen05" and tc_usable(x, w):
+        M, K = x.shape
+        N = w.shape[0]
+        nt, splits, floats, _ = _tc_plan(M, N, K, EPI_PARTIAL)
+        if splits > 1:
+            key = torch.device(x.device).index or 0
+            buf = _consumer_parts.get(key)
+            if buf is None or buf.numel() < floats:
+                _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                buf = _consumer_parts[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                global TC_GENERATION
+                TC_GENERATION += 1
+            gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
+            return PartialProduct(buf, splits, (M, N), out)
+    linear(x, w, out, status=status)
+    return out
+
+
+def _parts_of(x):
+    """(pointer tensor, parts, stride) of a kernel input that is a tensor or a PartialProduct."""
+    if isinstance(x, PartialProduct):
+        return x.parts, x.splits, x.stride
+    return x, 0, 0
+
+
 def qk_norm_rope_store(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, q_out,
                        k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, status) -> None:
-    """qkv [T, (nh+2*nkv)*hd] -> q_out [T, nh*hd] normed and rotated; k (normed, rotated)
-    and v written into their pages.  nkv == 0: q only (a layer that reads another's cache)."""
-    _cuda(qkv, positions, item_of_token, q_w, k_w, inv_freq, q_out, k_cache, v_cache, table, status)
+    """qkv [T, (nh+2*nkv)*hd] (a tensor or a PartialProduct) -> q_out [T, nh*hd] normed and rotated;
+    k (normed, rotated) and v written into their pages.  nkv == 0: q only (a layer that reads
+    another's cache)."""
+    src, parts, part_stride = _parts_of(qkv)
+    _cuda(src, positions, item_of_token, q_w, k_w, inv_freq, q_out, k_cache, v_cache, table, status)
     T = q_out.shape[0]
-    _need(qkv.shape == (T, (nh + 2 * nkv) * hd) and q_out.shape[1] == nh * hd, "qk_norm_rope_store: widths")
+    _need(tuple(qkv.shape) == (T, (nh + 2 * nkv) * hd) and q_out.shape[1] == nh * hd, "qk_norm_rope_store: widths")
+    _need(qkv.dtype == q_out.dtype, "qk_norm_rope_store: q_out must have the activations' dtype")
     _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
           and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
     _need(q_w.dtype == torch.float32 and q_w.numel() == hd, "q norm weight must be float32 [head]")
@@ -504,9 +569,9 @@ def qk_norm_rope_store(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot,
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= n_rot // 2, "inv_freq must be float32 [n_rot/2]")
     max_blocks = table.shape[1] if table is not None else 0
     _check(_lib.kernels().imparo_qk_norm_rope_store(
-        _ptr(qkv), _code(qkv), _ptr(positions), _ptr(item_of_token), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), n_rot,
+        _ptr(src), _code(q_out), _ptr(positions), _ptr(item_of_token), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), n_rot,
         float(eps), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(table), max_blocks, page_size, n_pages,
-        T, nh, nkv, hd, _ptr(status), _stream()), "qk_norm_rope_store")
+        T, nh, nkv, hd, parts, part_stride, _ptr(status), _stream()), "qk_norm_rope_store")
 
 
 def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
@@ -593,17 +658,19 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
 
 
 def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, taps, status) -> None:
-    _cuda(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y, status)
+    """bcx: [tokens, 3*width] rows [b | c | x], a tensor of y's dtype or a PartialProduct."""
+    src, parts, part_stride = _parts_of(bcx)
+    _cuda(src, w, bias, state, item_row_start, item_of_token, item_slot, y, status)
     T, width = y.shape
-    _need(bcx.shape == (T, 3 * width) and bcx.dtype == y.dtype, "gated_conv: bcx must be [tokens, 3*width]")
+    _need(tuple(bcx.shape) == (T, 3 * width) and bcx.dtype == y.dtype, "gated_conv: bcx must be [tokens, 3*width]")
     _need(w.dtype == torch.float32 and w.shape == (width, taps), "gated_conv: taps must be float32 [width, taps]")
     _need(state.dtype == torch.float32 and state.dim() == 3 and state.shape[1:] == (taps - 1, width),
           "gated_conv: state must be float32 [slots, taps-1, width]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == width, "gated_conv: bias must be float32 [width]")
     _check(_lib.kernels().imparo_gated_conv(
-        _ptr(bcx), _code(bcx), _ptr(w), _ptr(bias), _ptr(state), _ptr(item_row_start), _ptr(item_of_token),
-        _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], _ptr(status), _stream()), "gated_conv")
+        _ptr(src), _code(y), _ptr(w), _ptr(bias), _ptr(state), _ptr(item_row_start), _ptr(item_of_token),
+        _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], parts, part_stride, _ptr(status), _stream()), "gated_conv")
 
 
 _argmax_scratch = {}

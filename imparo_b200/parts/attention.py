@@ -73,7 +73,7 @@ class AttentionMixer(Part):
         nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only
         width = (nh + 2 * nkv) * hd
         qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype)
-        ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+        qkv = ops.linear_unfolded(x, self.w_qkv[:width], qkv, status=rt.status)    # the kernel below can add split partials
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype)
         rot = self.position.rotary()
         table = batch.tables[kv.group]

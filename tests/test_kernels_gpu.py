@@ -376,6 +376,82 @@ def test_qk_norm_rope_store(nh, nkv, hd, n_rot, dtype):
         o.read_status(status)
 
 
+@pytest.mark.parametrize("splits", [2, 3, 6, 11])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_consumers_of_unfolded_products(splits, dtype):
+    """gated_conv and qk_norm_rope_store on the split partials of a product give what they give on the
+    folded tensor (sum in split order, rounded to the activations' dtype), bit for bit."""
+    o = ops()
+    g = torch.Generator().manual_seed(splits)
+    # --- conv: lengths around taps - 1, a decode token among them
+    H, taps, lens, slots = 40, 3, [1, 5, 2, 1], [2, 0, 3, 1]
+    T = sum(lens)
+    parts = torch.randn(splits, T, 3 * H, generator=g).to(DEV)
+    folded = torch.zeros(T, 3 * H, device=DEV)
+    for s_ in range(splits):
+        folded += parts[s_]
+    folded = folded.to(dtype)
+    w = torch.randn(H, taps, generator=g).to(DEV)
+    state0 = torch.randn(4, taps - 1, H, generator=g).to(DEV)
+    row_start = torch.tensor(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32), device=DEV)
+    iot = torch.tensor(np.repeat(np.arange(len(lens)), lens).astype(np.int32), device=DEV)
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    status = o.new_status(DEV)
+    outs = []
+    for src in ("tensor", "parts"):
+        y = torch.empty(T, H, dtype=dtype, device=DEV)
+        st = state0.clone()
+        bcx = folded if src == "tensor" else o.PartialProduct(parts.reshape(-1), splits, (T, 3 * H), torch.empty(T, 3 * H, dtype=dtype, device=DEV))
+        o.gated_conv(bcx, w, None, st, row_start, iot, slot_t, y, taps, status)
+        outs.append((y, st))
+    o.read_status(status)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    pp = o.PartialProduct(parts.reshape(-1), splits, (T, 3 * H), torch.empty(T, 3 * H, dtype=dtype, device=DEV))
+    assert torch.equal(pp.tensor(), folded)                  # the fold kernel, for consumers that want a tensor
+    # --- q/k norm, rotation, cache write
+    nh, nkv, hd, page, n_pages = 3, 1, 32, 4, 8
+    width = (nh + 2 * nkv) * hd
+    parts = torch.randn(splits, T, width, generator=g).to(DEV)
+    folded = torch.zeros(T, width, device=DEV)
+    for s_ in range(splits):
+        folded += parts[s_]
+    folded = folded.to(dtype)
+    positions = torch.arange(T, dtype=torch.int32, device=DEV)
+    items = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).flip(0).reshape(1, n_pages).contiguous()
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+    inv = torch.tensor((10000.0 ** (-2.0 * np.arange(hd // 2) / hd)).astype(np.float32), device=DEV)
+    res = []
+    for src in ("tensor", "parts"):
+        q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+        kc = torch.zeros(n_pages, page, nkv * hd, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        qkv = folded if src == "tensor" else o.PartialProduct(parts.reshape(-1), splits, (T, width), torch.empty(T, width, dtype=dtype, device=DEV))
+        o.qk_norm_rope_store(qkv, positions, items, qw, kw, inv, hd, 1e-5, q_out, kc, vc, table, page, n_pages, nh, nkv, hd, status)
+        res.append((q_out, kc, vc))
+    o.read_status(status)
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("T,N,K", [(8, 6144, 2048), (3, 3072, 2048), (16, 384, 512), (5, 200, 136)])
+def test_linear_unfolded_sums_to_the_product(T, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(N + T)
+    x = bf16_round(torch.randn(T, K, generator=g))
+    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    status = o.new_status(DEV)
+    r = o.linear_unfolded(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), out, status)
+    o.read_status(status)
+    if N >= 3072:
+        assert isinstance(r, o.PartialProduct) and r.splits > 1        # the decode products of the model's sizes are cut
+    got = (r.tensor() if isinstance(r, o.PartialProduct) else r).float().cpu().double()
+    ref = x.double() @ w.double().T
+    assert (got - ref).abs().max() <= 8e-3 * max(1.0, ref.abs().max())
+
+
 def test_kernels_refuse_sizes_they_do_not_take():
     o = ops()
     st = o.new_status(DEV)
