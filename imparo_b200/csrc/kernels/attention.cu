@@ -21,7 +21,8 @@ constexpr int WARPS = 4;
 // position, the norm weights, the rotation's sines and cosines and the cache row (the batch
 // description comes from the host before the step).  After the wait: one load of the head's
 // values, the norm, the rotation, the store.
-template <typename T>
+// FEW: at most eight partials (or none): straight-line loads, all of a head's values in flight together
+template <typename T, bool FEW>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
                           const int* __restrict__ item_of_token,
@@ -93,12 +94,20 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
             const int d = lane + 32 * j;
             float acc = 0.f;
             if (d < hd) {
-                for (int s0 = 0; s0 < parts; s0 += 8) {
+                if (FEW) {
                     float v[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) v[u] = s0 + u < parts ? __ldcg(ps + (size_t)(s0 + u) * part_stride + d) : 0.f;
+                    for (int u = 0; u < 8; ++u) v[u] = u < parts ? __ldcg(ps + (size_t)u * part_stride + d) : 0.f;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) if (s0 + u < parts) acc += v[u];
+                    for (int u = 0; u < 8; ++u) if (u < parts) acc += v[u];
+                } else {
+                    for (int s0 = 0; s0 < parts; s0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) v[u] = s0 + u < parts ? __ldcg(ps + (size_t)(s0 + u) * part_stride + d) : 0.f;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) if (s0 + u < parts) acc += v[u];
+                    }
                 }
             }
             val[j] = to_f32(from_f32<T>(acc));
@@ -257,16 +266,15 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
     if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * (nh + 2 * nkv) * hd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
     const float* part = parts > 0 ? (const float*)qkv : nullptr;
-    if (dtype == IMPARO_DT_F32)
-        launch(qk_norm_rope_store_kernel<float>, grid, dim3(WARPS * 32), 0, stream,
-            (const float*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (float*)q_out,
-            (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts,
-            (size_t)part_stride, status);
-    else if (dtype == IMPARO_DT_BF16)
-        launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), 0, stream,
-            (const __nv_bfloat16*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (__nv_bfloat16*)q_out,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts,
-            (size_t)part_stride, status);
+#define IMPARO_QK(T_, FEW_) launch(qk_norm_rope_store_kernel<T_, FEW_>, grid, dim3(WARPS * 32), 0, stream, \
+            (const T_*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (T_*)q_out, (T_*)k_cache, (T_*)v_cache, \
+            table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts, (size_t)part_stride, status)
+    if (dtype == IMPARO_DT_F32) {
+        if (parts <= 8) IMPARO_QK(float, true); else IMPARO_QK(float, false);
+    } else if (dtype == IMPARO_DT_BF16) {
+        if (parts <= 8) IMPARO_QK(__nv_bfloat16, true); else IMPARO_QK(__nv_bfloat16, false);
+    }
+#undef IMPARO_QK
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -22,16 +22,18 @@ constexpr int MAX_TAPS = 16;
 // The input rows [b | c | x]: a stored tensor of T, or the partial results of a product that was
 // cut along K (float [parts][tokens][3 * width]).  Partials are summed in split order and rounded
 // to T, which is what the product's own fold would have stored.
-template <typename T>
+// MODE 0: a tensor; 1: at most four partials (straight-line code, so that the loads of the
+// several values a thread needs are all in flight together); 2: any number of partials.
+template <typename T, int MODE>
 struct ConvIn {
     const T* rows;
     const float* part;
     int parts;
     size_t part_stride;
     __device__ __forceinline__ float at(size_t idx) const {
-        if (parts <= 0) return to_f32(rows[idx]);
+        if (MODE == 0) return to_f32(rows[idx]);
         float acc = 0.f;
-        if (parts <= 4) {                       // straight-line: the loads of several values overlap
+        if (MODE == 1) {
             float v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = u < parts ? __ldcg(part + (size_t)u * part_stride + idx) : 0.f;
@@ -54,8 +56,8 @@ struct ConvIn {
 // tokens from the old state, then the new state.  wk: this channel's taps (loaded by the caller,
 // before it waited for the previous kernel).  Everything the outputs need is requested in one
 // batch of loads: a decode token costs one round trip to memory after the wait.
-template <typename T>
-__device__ __forceinline__ void conv_portion_head(const ConvIn<T>& bcx, const float* wk, float b0,
+template <typename T, int MODE>
+__device__ __forceinline__ void conv_portion_head(const ConvIn<T, MODE>& bcx, const float* wk, float b0,
                                                   float* __restrict__ state, int slot,
                                                   T* __restrict__ y, int item, int start, int n, int ch,
                                                   int width, int taps, int n_slots, int* status) {
@@ -102,8 +104,8 @@ __device__ __forceinline__ void conv_portion_head(const ConvIn<T>& bcx, const fl
 // The batch description (which request a token belongs to, where its portion starts, its state
 // slot) comes from the host before the step and the taps are weights: both are read before the
 // wait on the previous kernel, so that after it only activations and state remain to be fetched.
-template <typename T>
-__global__ void gated_conv_kernel(const ConvIn<T> bcx, const float* __restrict__ w,
+template <typename T, int MODE>
+__global__ void gated_conv_kernel(const ConvIn<T, MODE> bcx, const float* __restrict__ w,
                                   const float* __restrict__ bias, float* __restrict__ state,
                                   const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                   const int* __restrict__ item_slot, T* __restrict__ y,
@@ -165,7 +167,7 @@ __global__ void gated_conv_kernel(const ConvIn<T> bcx, const float* __restrict__
             if (e < hist) st[(size_t)e * width] = (e + 1 < hist) ? sv[e + 1] : bx;
         return;
     }
-    conv_portion_head<T>(bcx, wk, b0, state, slot, y, item, start, n, ch, width, taps, n_slots, status);
+    conv_portion_head<T, MODE>(bcx, wk, b0, state, slot, y, item, start, n, ch, width, taps, n_slots, status);
 }
 
 // bfloat16 with a width that is a multiple of 8, for prompt-sized batches: a thread owns eight
@@ -194,7 +196,7 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
         for (int i = 0; i < 8; ++i) {
             float wk[MAX_TAPS];
             for (int k = 0; k < taps; ++k) wk[k] = w[(size_t)(ch + i) * taps + k];
-            conv_portion_head<__nv_bfloat16>(ConvIn<__nv_bfloat16>{bcx, nullptr, 0, 0}, wk, bias ? bias[ch + i] : 0.f, state, slot, y, item, start, n,
+            conv_portion_head<__nv_bfloat16, 0>(ConvIn<__nv_bfloat16, 0>{bcx, nullptr, 0, 0}, wk, bias ? bias[ch + i] : 0.f, state, slot, y, item, start, n,
                                              ch + i, width, taps, n_slots, status);
         }
         return;
@@ -250,10 +252,13 @@ extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, con
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     const float* part = parts > 0 ? (const float*)bcx : nullptr;
+    const int mode = parts == 0 ? 0 : (parts <= 4 ? 1 : 2);
+#define IMPARO_CONV(T_, M_) do { \
+        ConvIn<T_, M_> in{(const T_*)bcx, part, parts, (size_t)part_stride}; \
+        launch(gated_conv_kernel<T_, M_>, dim3(blocks), dim3(threads), 0, stream, in, w, bias, state, item_row_start, \
+               item_of_token, item_slot, (T_*)y, n_tok, width, taps, n_slots, status); } while (0)
     if (dtype == IMPARO_DT_F32) {
-        ConvIn<float> in{(const float*)bcx, part, parts, (size_t)part_stride};
-        launch(gated_conv_kernel<float>, dim3(blocks), dim3(threads), 0, stream, in, w, bias, state, item_row_start,
-               item_of_token, item_slot, (float*)y, n_tok, width, taps, n_slots, status);
+        if (mode == 0) IMPARO_CONV(float, 0); else if (mode == 1) IMPARO_CONV(float, 1); else IMPARO_CONV(float, 2);
     } else if (dtype == IMPARO_DT_BF16) {
         const bool wide = parts == 0 && n_tok >= 64 && (width & 7) == 0 && (((uintptr_t)bcx | (uintptr_t)y) & 15) == 0;
         if (wide) {
@@ -261,11 +266,10 @@ extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, con
             launch(gated_conv_bf16x8_kernel, dim3((unsigned)((n8 + threads - 1) / threads)), dim3(threads), 0, stream,
                    (const __nv_bfloat16*)bcx, w, bias, state, item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y,
                    n_tok, width, taps, n_slots, status);
-        } else {
-            ConvIn<__nv_bfloat16> in{(const __nv_bfloat16*)bcx, part, parts, (size_t)part_stride};
-            launch(gated_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, in, w, bias, state,
-                   item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status);
-        }
+        } else if (mode == 0) IMPARO_CONV(__nv_bfloat16, 0);
+        else if (mode == 1) IMPARO_CONV(__nv_bfloat16, 1);
+        else IMPARO_CONV(__nv_bfloat16, 2);
+#undef IMPARO_CONV
     } else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
