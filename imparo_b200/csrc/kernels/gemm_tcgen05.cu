@@ -97,6 +97,29 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// CH chunks of 16 accumulator columns with one wait: the loads are issued back to back, and the
+// empty statements after the wait keep every use of the values behind it.
+template <int CH>
+__device__ __forceinline__ void tmem_ld_chunks(uint32_t taddr, float (&v)[CH][16]) {
+    uint32_t r[CH][16];
+#pragma unroll
+    for (int u = 0; u < CH; ++u)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(r[u][0]), "=r"(r[u][1]), "=r"(r[u][2]), "=r"(r[u][3]), "=r"(r[u][4]), "=r"(r[u][5]), "=r"(r[u][6]),
+                       "=r"(r[u][7]), "=r"(r[u][8]), "=r"(r[u][9]), "=r"(r[u][10]), "=r"(r[u][11]), "=r"(r[u][12]),
+                       "=r"(r[u][13]), "=r"(r[u][14]), "=r"(r[u][15])
+                     : "r"(taddr + 16 * u));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int u = 0; u < CH; ++u) {
+        asm volatile("" : "+r"(r[u][0]), "+r"(r[u][1]), "+r"(r[u][2]), "+r"(r[u][3]), "+r"(r[u][4]), "+r"(r[u][5]), "+r"(r[u][6]),
+                          "+r"(r[u][7]), "+r"(r[u][8]), "+r"(r[u][9]), "+r"(r[u][10]), "+r"(r[u][11]), "+r"(r[u][12]),
+                          "+r"(r[u][13]), "+r"(r[u][14]), "+r"(r[u][15]) :: "memory");
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[u][i] = __uint_as_float(r[u][i]);
+    }
+}
+
 template <int EPI>
 __device__ __forceinline__ void store_out(void* out, size_t o, float v) {
     if (EPI == STORE_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
@@ -149,7 +172,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     uint64_t* b_ready = acc_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 1);
     int* flags = reinterpret_cast<int*>(tmem_slot + 1);            // [0]: this CTA folds the splits
-    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: [128][17], one 16-token chunk at a time
+    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: 2 x [128][17], a 16-token chunk each
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
@@ -299,6 +322,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const int t0 = tile_t * NT;
+        constexpr int CH = NT >= 64 ? 4 : NT / 16;              // accumulator chunks fetched per wait
 
         if (EPI == SWIGLU_BF16) {
             // rows 0..63 hold gate, rows 64..127 hold up of features tile_n*64 + (row % 64).  Both go
@@ -309,21 +333,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             const int ff = e & 63, parity = e >> 6;
             const int f = tile_n * 64 + ff;
 #pragma unroll 1
-            for (int c = 0; c < NT; c += 16) {
-                float v[16];
-                tmem_ld16(taddr + c, v);
+            for (int c = 0; c < NT; c += 16 * CH) {
+                float v[CH][16];
+                tmem_ld_chunks<CH>(taddr + c, v);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) exch[row * 17 + j] = v[j];
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (f < p.N) {
+                for (int u = 0; u < CH; ++u) {
+                    // two exchange buffers in turn: one barrier per 16 tokens (a buffer is rewritten only
+                    // after the barrier of the chunk between, which every thread passes after reading it)
+                    float* ex = exch + (u & 1) * (128 * 17);
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const int t = t0 + c + j + parity;
-                        if (t < p.T)
-                            out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(exch[ff * 17 + j + parity]) * exch[(64 + ff) * 17 + j + parity]);
+                    for (int j = 0; j < 16; ++j) ex[row * 17 + j] = v[u][j];
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (f < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            const int t = t0 + c + 16 * u + j + parity;
+                            if (t < p.T)
+                                out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(ex[ff * 17 + j + parity]) * ex[(64 + ff) * 17 + j + parity]);
+                        }
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (CH == 1 || c + 16 * CH < NT) asm volatile("bar.sync 1, 128;" ::: "memory");
             }
         } else {
             const int n = tile_n * BM + row;
@@ -332,15 +362,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 // adds the splits in order (rows.cu: add_partials_rmsnorm)
                 float* part = p.scratch + (size_t)split * p.T * p.N;
 #pragma unroll 1
-                for (int c = 0; c < NT; c += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c, v);
+                for (int c = 0; c < NT; c += 16 * CH) {
+                    float v[CH][16];
+                    tmem_ld_chunks<CH>(taddr + c, v);
                     if (n < p.N) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < p.T) part[(size_t)t * p.N + n] = v[j];
-                        }
+                        for (int u = 0; u < CH; ++u)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = t0 + c + 16 * u + j;
+                                if (t < p.T) part[(size_t)t * p.N + n] = v[u][j];
+                            }
                     }
                 }
             } else if (p.splits == 1) {
@@ -508,7 +540,7 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 
 template <int NT, int STAGES, int EPI, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 128 * 17 * 4 : 0);
+    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
     static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
     const size_t smem = fixed + (NORM ? (size_t)p.kblocks * NT * BK * 2 : 0);
     if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller norms separately
@@ -543,7 +575,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 // How many clusters of `cluster` CTAs of this kernel the device holds at once (0 on error).
 template <int NT, int STAGES, int EPI>
 static int max_clusters(int cluster) {
-    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 128 * 17 * 4 : 0);
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
     auto kern = gemm_kernel<NT, STAGES, EPI, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};

@@ -237,7 +237,7 @@ TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that us
 #   T=16  gate+up 15.7 / 14.2+act, down 12.5 / 12.6, in_proj 11.0 / 7.1, out_proj 7.1 / 5.2, qkv 7.1 / 5.4
 #   T=64  gate+up 20.9 / 15.6+act, down 19.4 / 12.9, in_proj 17.3 / 6.8
 #   T=2048 down 66 / 50, gate+up 275 / 160 (the epilogue dominates a 32-k-block main loop)
-TC_MAX_TOKENS = 16
+TC_MAX_TOKENS = 64
 
 
 def tc_max_tokens() -> int:
