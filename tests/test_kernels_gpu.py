@@ -62,6 +62,26 @@ def test_rmsnorm(width, out_dtype):
     assert torch.equal(out2, out[rows.long()])
 
 
+@pytest.mark.parametrize("width", [128, 1024, 2048, 2176, 144])
+def test_rmsnorm_many_rows(width):
+    """A prompt portion's worth of rows (another kernel from 256 rows on, where the width allows it)."""
+    o = ops()
+    g = torch.Generator().manual_seed(width)
+    n = 300
+    x = torch.randn(n + 20, width, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    eps = 1e-5
+    rows = torch.randperm(n + 20, generator=g)[:n].to(torch.int32)
+    xs = x[rows.long()].double()
+    ref = xs * (1.0 / torch.sqrt((xs ** 2).mean(-1, keepdim=True) + eps)) * w.double()
+    out = torch.full((n, width), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
+    assert (out.float().cpu().double() - ref).abs().max() <= 8e-3 * ref.abs().max()
+    out2 = torch.full((n + 20, width), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), eps, out2)
+    assert torch.equal(out2[rows.long().to(DEV)], out)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 53, 71), (37, 130, 64), (64, 64, 16), (130, 1, 5), (7, 331, 144)])
 def test_sgemm_is_true_float32(M, N, K):
     o = ops()
@@ -320,12 +340,16 @@ def test_one_far_key_stands_out(dtype, far, window, kind, chunk):
 
 @pytest.mark.parametrize("nh,nkv,hd,n_rot", [(4, 2, 16, 16), (6, 2, 32, 32), (3, 1, 48, 48), (2, 2, 64, 32), (1, 1, 256, 256)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_store(nh, nkv, hd, n_rot, dtype):
+@pytest.mark.parametrize("many", [False, True])
+def test_qk_norm_rope_store(nh, nkv, hd, n_rot, dtype, many):
     o = ops()
     rng = np.random.default_rng(hd)
-    page, n_pages, eps, theta = 4, 40, 1e-6, 50000.0
+    page, n_pages, eps, theta = 4, 40 if not many else 120, 1e-6, 50000.0
     positions = np.array([0, 1, 2, 3, 4, 17, 900, 4095, 100000, 7], dtype=np.int32)
     items = np.array([0, 0, 0, 0, 0, 1, 2, 3, 4, 5], dtype=np.int32)
+    if many:        # a prompt portion beside them: the launch then gives a warp several heads
+        positions = np.concatenate([positions, np.arange(20, 320, dtype=np.int32)])
+        items = np.concatenate([items, np.full(300, 5, dtype=np.int32)])
     T = len(positions)
     table = -np.ones((6, 100000 // page + 2), dtype=np.int32)
     perm = rng.permutation(n_pages)
