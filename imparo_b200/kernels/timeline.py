@@ -85,7 +85,7 @@ def _short(mangled: str) -> str:
     if i < len(mangled) and mangled[i] == "I":
         k = mangled.find("EEv", i)
         args = mangled[i + 1:k if k > 0 else i + 1]
-        args = args.replace("13__nv_bfloat16", "bf16,").replace("Lb0E", "").replace("Lb1E", "norm,")
+        args = args.replace("13__nv_bfloat16", "bf16,").replace("Lb0E", "0,").replace("Lb1E", "1,")
         args = re.sub(r"Li(\d+)E", lambda g: g.group(1) + ",", args)
         args = "f32" if args == "f" else args.rstrip(",")
     return name + (f"<{args}>" if args else "")
