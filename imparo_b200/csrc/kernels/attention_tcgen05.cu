@@ -1,0 +1,419 @@
+// Attention for prompt portions over the paged cache on the 5th-generation tensor cores
+// (bfloat16, head size 64 or 128, pages of 16, 32, 64 or 128 positions).
+//
+// A CTA owns up to 128 query rows: (128 / G) consecutive tokens of ONE request times the G query
+// heads that share a kv head (the tile shape of the reference's prefill kernel, "query tokens x GQA
+// heads x 1 KV head", imparo-cuda/native/sm80/attention_prefill_mma_d64_f16.cuh:29, at eight times
+// its rows).  It walks the keys 128 at a time in position order:
+//
+//   warp 0      TMA: the step's keys and values, page by page (one tile load per page and 64-dim
+//               block, 128-byte swizzle), into a ring of two stages
+//   warp 1      tcgen05.mma: S = Q K^T into tensor memory (M = 128 rows, N = 128 keys), and, once
+//               the softmax warps have written P, O_step = P V (M = 128, N = head size), the values
+//               read as they lie in the cache (MN-major operand)
+//   warps 2-5   one thread per row: read S from tensor memory, mask by position and window, running
+//               max and sum in 32-bit, P = exp2(s - max) as bfloat16 into shared memory in the MMA's
+//               swizzled layout; read O_step and fold it into the row's 32-bit output registers
+//
+// Formulas: scores q.k * scale for lo <= key <= position, lo = 0 or position + 1 - window, no mask
+// tensor, softmax with the max subtracted (imparo-model/src/cpu_support.rs:402-445).  Which tokens
+// form a tile is derived on the device from the batch's row starts, so a tile never holds rows of
+// two requests; a row's result does not depend on its neighbours in the tile.
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records IMPARO_ST_WAIT_LIMIT in
+// the status word, stops waiting, frees its tensor memory and returns.
+#include "tcgen05.cuh"
+
+namespace imparo {
+namespace fa {
+
+using namespace tc;
+
+constexpr int ROWS = 128;          // query rows per CTA: the MMAs' M
+constexpr int KEYS = 128;          // keys per step: N of the score product, K of P V
+constexpr int THREADS = 192;
+constexpr int STAGES = 2;
+constexpr uint32_t REGION = 128 * 128;      // a [128 rows][128 bytes] block of a tile: 16 KB
+constexpr uint32_t ALIGN_SLACK = 768;       // spare bytes for aligning the tiles to 1024: two CTAs must fit an SM at head size 64
+
+// The values as B operand: [key][dim] with the dims contiguous (MN-major), 128-byte swizzle:
+// groups of 8 keys are 1024 bytes apart (SBO), 64-dim blocks lbo bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, bfloat16 operands, float32 accumulator; b_mn: the B operand is MN-major
+__device__ __forceinline__ uint32_t instr_desc_ab(int m, int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// 2^x for x <= 0 (scores minus their max): the hardware approximation, one instruction
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Args {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* item_row_start;
+    const int* item_start_pos;
+    const int* table;
+    int* status;
+    int n_items, max_blocks, page_size, n_pages, window, nh, nkv;
+    float scale;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 2 : 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a) {
+    constexpr int NB = HD / 64;                              // 64-dim blocks of a head
+    constexpr uint32_t Q_BYTES = NB * REGION, P_BYTES = 2 * REGION, K_BYTES = NB * REGION, V_BYTES = NB * REGION;
+    constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
+    constexpr uint32_t TMEM_COLS = 256;                      // scores: columns 0..127, P V: 128..128+HD-1
+    extern __shared__ __align__(1024) uint8_t fa_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
+    if ((uint32_t)(smem - fa_smem_raw) > ALIGN_SLACK) {      // the launch's shared memory does not cover the aligned tiles
+        if (threadIdx.x == 0) report(a.status, IMPARO_ST_WAIT_LIMIT, 29, (int)(smem - fa_smem_raw), 0);
+        return;
+    }
+    uint8_t* q_s = smem;
+    uint8_t* p_s = q_s + Q_BYTES;
+    uint8_t* kv_s = p_s + P_BYTES;                           // [stage][K | V]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + STAGES * STAGE_BYTES);
+    uint64_t* kv_full = bars;                                // [STAGES]
+    uint64_t* kv_empty = bars + STAGES;                      // [STAGES]
+    uint64_t* q_ready = bars + 2 * STAGES;
+    uint64_t* s_ready = q_ready + 1;
+    uint64_t* p_ready = q_ready + 2;
+    uint64_t* pv_ready = q_ready + 3;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 4);
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = a.nh / a.nkv;
+    const int TQ = ROWS / G;                                 // tokens per tile
+    const int kvh = blockIdx.y;
+    // which request and which of its tokens: tiles are numbered request by request; the last tiles
+    // (most keys under a causal mask) go first
+    int item = 0, tile = (int)gridDim.x - 1 - (int)blockIdx.x, n_item = 0, row0 = 0;
+    for (; item < a.n_items; ++item) {
+        row0 = a.item_row_start[item];
+        n_item = a.item_row_start[item + 1] - row0;
+        const int tiles = (n_item + TQ - 1) / TQ;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (item >= a.n_items) return;                           // the grid is an upper bound (uniform per CTA)
+    const int tok0 = tile * TQ;
+    const int n_tok = min(TQ, n_item - tok0);
+    const int n_rows = n_tok * G;
+    const int pos0 = a.item_start_pos[item] + tok0;
+    const int pos_last = pos0 + n_tok - 1;
+    const int* tab = a.table + (size_t)item * a.max_blocks;
+    const int lo_min = (a.window > 0 && pos0 + 1 > a.window) ? pos0 + 1 - a.window : 0;
+    const int kb_first = lo_min / KEYS, kb_last = pos_last / KEYS;
+    const int n_steps = kb_last - kb_first + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        mbar_init(q_ready, 128);
+        mbar_init(s_ready, 1);
+        mbar_init(p_ready, 128);
+        mbar_init(pv_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- keys and values, page by page ----
+            pdl_wait();                                      // this step's keys were written by the kernel before
+            const int pages_per_step = KEYS / a.page_size;
+            const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
+            for (int i = 0; i < n_steps; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1)) {
+                    report(a.status, IMPARO_ST_WAIT_LIMIT, 20, i, s);
+                    break;
+                }
+                uint8_t* kdst = kv_s + s * STAGE_BYTES;
+                uint8_t* vdst = kdst + K_BYTES;
+                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                const int blk0 = (kb_first + i) * pages_per_step;
+                for (int pg = 0; pg < pages_per_step; ++pg) {
+                    // blocks before every row's window or past the request's last position hold nothing
+                    // this tile may use (a window's old pages may be gone): a mapped page stands in
+                    // for them (their keys are masked, their values finite)
+                    const int blk = min(max(blk0 + pg, first_blk), last_blk);
+                    int page = blk < a.max_blocks ? tab[blk] : -1;
+                    if (page < 0 || page >= a.n_pages) {
+                        report(a.status, IMPARO_ST_PAGE_RANGE, 21, item, page);
+                        page = 0;
+                    }
+                    const int y = page * a.page_size;
+                    const uint32_t off = (uint32_t)pg * a.page_size * 128;
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        tma_load_2d(kdst + nb * REGION + off, &map_k, &kv_full[s], kvh * HD + nb * 64, y);
+                        tma_load_2d(vdst + nb * REGION + off, &map_v, &kv_full[s], kvh * HD + nb * 64, y);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- the two products of every step ----
+            const uint32_t idesc_s = instr_desc_ab(ROWS, KEYS, false);
+            const uint32_t idesc_o = instr_desc_ab(ROWS, HD, true);
+            const uint32_t t_s = tmem_base, t_o = tmem_base + 128;
+            bool ok = mbar_wait(q_ready, 0);
+            if (!ok) report(a.status, IMPARO_ST_WAIT_LIMIT, 22, 0, 0);
+            auto issue_pv = [&](int i) {                      // O_step = P_i V_i
+                const uint32_t vb = smem_u32(kv_s + (i % STAGES) * STAGE_BYTES + K_BYTES), pb = smem_u32(p_s);
+#pragma unroll
+                for (int kk = 0; kk < KEYS / UMMA_K; ++kk)
+                    umma(t_o, smem_desc(pb + (kk >> 2) * REGION + (kk & 3) * 32), smem_desc_mn(vb + kk * (UMMA_K * 128), REGION),
+                         idesc_o, kk > 0 ? 1u : 0u);
+                umma_commit(&kv_empty[i % STAGES]);          // keys (scored earlier) and values of the stage are read
+                umma_commit(pv_ready);
+            };
+            for (int i = 0; i < n_steps && ok; ++i) {
+                // P of the step before is written and its scores are read: the score tile is free again
+                if (i > 0 && !mbar_wait(p_ready, (i - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 23, i, 0); ok = false; break; }
+                const int s = i % STAGES;
+                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 24, i, s); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t qb = smem_u32(q_s), kb = smem_u32(kv_s + s * STAGE_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma(t_s, smem_desc(qb + nb * REGION + k * 32), smem_desc(kb + nb * REGION + k * 32), idesc_s,
+                             (nb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(s_ready);                        // the softmax warps want this first ...
+                if (i > 0) issue_pv(i - 1);                  // ... the step before's P V only when they fold it
+            }
+            if (ok) {
+                if (mbar_wait(p_ready, (n_steps - 1) & 1)) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_pv(n_steps - 1);
+                } else {
+                    report(a.status, IMPARO_ST_WAIT_LIMIT, 25, n_steps, 0);
+                }
+            }
+        }
+    } else {
+        // ---- softmax: thread = row = tensor-memory lane ----
+        const int r = (warp & 3) * 32 + lane;
+        const bool valid = r < n_rows;
+        const int tok = r / G, head = kvh * G + r % G;
+        const int pos_r = pos0 + tok;
+        const int lo_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
+        const int lo_last = (a.window > 0 && pos_last + 1 > a.window) ? pos_last + 1 - a.window : 0;
+        const uint32_t t_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16), t_o = t_s + 128;
+        const size_t row_off = ((size_t)(row0 + tok0 + (valid ? tok : 0)) * a.nh + head) * HD;
+        pdl_wait();
+        // the row's queries -> shared memory, 16-byte chunks swizzled as the MMA reads them
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(a.q + row_off);
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(q_s + (c >> 3) * REGION + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(q_ready)) : "memory");
+        }
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
+        const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
+        bool ok = true;
+        auto fold_pv = [&](float corr) {                     // o = o * corr + O_step
+#pragma unroll
+            for (int c = 0; c < HD; c += 64) {
+                float v[4][16];
+                tmem_ld_chunks<4>(t_o + c, v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) o[c + u * 16 + e] = o[c + u * 16 + e] * corr + v[u][e];
+            }
+        };
+        for (int i = 0; i < n_steps; ++i) {
+            const int key0 = (kb_first + i) * KEYS;
+            if (!mbar_wait(s_ready, i & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 26, i, r); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // which keys of the step this row sees: [j_lo, j_hi] relative to key0 (empty for padding rows).
+            // A step that every row of the tile sees whole (all but the steps at the diagonal and at a
+            // window's edge) skips the per-key tests.
+            const int j_hi = valid ? min(KEYS - 1, pos_r - key0) : -1;
+            const int j_lo = max(0, lo_r - key0);
+            const bool whole = key0 + KEYS - 1 <= pos0 && key0 >= lo_last;
+            // pass 1: the row's max over the step (four running maxima: no 128-long dependent chain)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v[4][16];
+                tmem_ld_chunks<4>(t_s + h * 64, v);
+                if (whole) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[u][e]);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const int j = h * 64 + u * 16 + e;
+                            if (j >= j_lo && j <= j_hi) mx4[e & 3] = fmaxf(mx4[e & 3], v[u][e]);
+                        }
+                }
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            mx *= sl2;                                       // sl2 > 0: the max commutes with the scaling
+            const float m_new = fmaxf(m_run, mx);
+            const float corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
+            const float base = (m_new == -INFINITY) ? 0.f : m_new;
+            // the previous step's P V is complete by now or soon: fold it in before P is overwritten
+            if (i > 0) {
+                if (!mbar_wait(pv_ready, (i - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 27, i, r); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fold_pv(corr_prev);
+            }
+            // pass 2: P = exp2(s - max), bfloat16, into shared memory; the row's sum in 32-bit
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const float nbase = -base;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v[4][16];
+                tmem_ld_chunks<4>(t_s + h * 64, v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t w[8];
+                    if (whole) {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            const float p0 = ex2(fmaf(v[u][e], sl2, nbase)), p1 = ex2(fmaf(v[u][e + 1], sl2, nbase));
+                            sum4[(e >> 1) & 3] += p0 + p1;
+                            w[e >> 1] = pack2(p0, p1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            const int j = h * 64 + u * 16 + e;
+                            const float p0 = (j >= j_lo && j <= j_hi) ? ex2(fmaf(v[u][e], sl2, nbase)) : 0.f;
+                            const float p1 = (j + 1 >= j_lo && j + 1 <= j_hi) ? ex2(fmaf(v[u][e + 1], sl2, nbase)) : 0.f;
+                            sum4[(e >> 1) & 3] += p0 + p1;
+                            w[e >> 1] = pack2(p0, p1);
+                        }
+                    }
+                    // keys u*16 .. u*16+15 of this half: chunks 2u and 2u+1 of the row's 128 bytes
+                    uint8_t* prow = p_s + h * REGION + r * 128;
+                    *reinterpret_cast<uint4*>(prow + (((2 * u) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(prow + (((2 * u + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            l_run = l_run * corr + sum;
+            m_run = m_new;
+            corr_prev = corr;
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(p_ready)) : "memory");
+        }
+        if (ok) {
+            if (mbar_wait(pv_ready, (n_steps - 1) & 1)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                fold_pv(corr_prev);
+                if (valid) {
+                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                    uint4* dst = reinterpret_cast<uint4*>(a.out + row_off);
+#pragma unroll
+                    for (int c = 0; c < HD / 8; ++c)
+                        dst[c] = make_uint4(pack2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                            pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+                }
+            } else {
+                report(a.status, IMPARO_ST_WAIT_LIMIT, 28, n_steps, r);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = ALIGN_SLACK + (size_t)(HD / 64) * REGION + 2 * REGION + (size_t)STAGES * 2 * (HD / 64) * REGION + 128;
+    auto kern = attn_prefill_tc_kernel<HD>;
+    static bool configured = false;
+    cudaError_t e;
+    if (!configured) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    e = launch(kern, grid, dim3(THREADS), smem, stream, mk, mv, a);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // namespace fa
+}  // namespace imparo
+
+using namespace imparo;
+
+// bfloat16, head size 64 or 128, at most 8 query heads per kv head, pages of 16, 32, 64 or 128
+// positions; else -8 (the caller uses another kernel).  n_tok is the batch's token count, n_items
+// its requests.  The caches are [n_pages * page_size rows, nkv * hd] arenas.
+extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* item_row_start, const int* item_start_pos, int n_items,
+                                           const int* table, int max_blocks, int page_size, int n_pages,
+                                           int window, float scale, void* out, int n_tok, int nh, int nkv, int hd,
+                                           int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    const int G = nh / nkv;
+    if (G > 8 || (hd != 64 && hd != 128)) return -8;
+    if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return -8;
+    if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return -8;
+    if (!(scale > 0.f)) return -8;                           // the row max is taken before the scaling
+    const int TQ = fa::ROWS / G;
+    const long long tiles = (n_tok + TQ - 1) / TQ + n_items;          // an upper bound: every request may end a tile early
+    if (tiles > 0x7fffffffLL || nkv > 65535) return -2;
+    CUtensorMap mk, mv;
+    const uint64_t rows = (uint64_t)n_pages * page_size, cols = (uint64_t)nkv * hd;
+    int rc = tc::get_map(k_cache, rows, cols, cols, (uint32_t)page_size, &mk);
+    if (rc) return rc;
+    rc = tc::get_map(v_cache, rows, cols, cols, (uint32_t)page_size, &mv);
+    if (rc) return rc;
+    fa::Args a;
+    a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out;
+    a.item_row_start = item_row_start; a.item_start_pos = item_start_pos; a.table = table; a.status = status;
+    a.n_items = n_items; a.max_blocks = max_blocks; a.page_size = page_size; a.n_pages = n_pages; a.window = window;
+    a.nh = nh; a.nkv = nkv; a.scale = scale;
+    dim3 grid((unsigned)tiles, nkv);
+    return hd == 64 ? fa::launch_tc<64>(mk, mv, a, grid, stream) : fa::launch_tc<128>(mk, mv, a, grid, stream);
+}

@@ -638,22 +638,38 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
 
 
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
-                      scale, out, nh, nkv, hd, status) -> bool:
+                      scale, out, nh, nkv, hd, status, kernel: str = "auto") -> bool:
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
-    query heads per kv head).  Returns False, having launched nothing, for other shapes."""
+    query heads per kv head).  Returns False, having launched nothing, for other shapes.
+
+    kernel: "tcgen05" (TMA + tcgen05.mma with the scores in tensor memory; pages of 16, 32, 64 or
+    128 positions), "mma" (mma.sync, any page size), or "auto": the first where it takes the shape
+    (IMPARO_ATTN_PREFILL=mma in the environment makes "auto" skip it)."""
     if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
         return False
     _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status)
     T = q.shape[0]
     _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "attention_prefill: q/out shapes")
+    _need(q.is_contiguous() and out.is_contiguous(), "attention_prefill: q and out must be dense")
     _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
     _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
     _need(table.dtype == torch.int32 and table.dim() == 2 and table.shape[0] >= n_items, "block table must be int32 [items, blocks]")
     _need(item_row_start.numel() >= n_items + 1 and item_start_pos.numel() >= n_items, "attention_prefill: item arrays")
-    _check(_lib.kernels().imparo_attention_prefill(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
-        table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
-        _stream()), "attention_prefill")
+    _need(kernel in ("auto", "tcgen05", "mma"), "attention_prefill: kernel is auto, tcgen05 or mma")
+    args = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
+            table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
+            _stream())
+    if kernel == "auto":
+        import os
+        kernel = "mma" if os.environ.get("IMPARO_ATTN_PREFILL", "") == "mma" else "auto"
+    if kernel in ("auto", "tcgen05"):
+        rc = _lib.kernels().imparo_attention_prefill_tc(*args)
+        if rc != -8:
+            _check(rc, "attention_prefill_tc")
+            return True
+        if kernel == "tcgen05":
+            return False
+    _check(_lib.kernels().imparo_attention_prefill(*args), "attention_prefill")
     return True
 
 

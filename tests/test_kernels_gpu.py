@@ -541,14 +541,16 @@ def test_temperature_sampling_is_the_inverse_cdf(V):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (6, 2, 128), (3, 1, 64), (8, 1, 64), (2, 1, 128), (32, 8, 64), (4, 2, 64),
                                        (5, 1, 64), (6, 1, 128), (7, 1, 64)])
-@pytest.mark.parametrize("page,window", [(4, None), (16, None), (16, 50), (64, 7)])
-def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window):
+@pytest.mark.parametrize("page,window", [(4, None), (16, None), (16, 50), (64, 7), (32, 200), (128, None)])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window, kernel):
     """Prompt portions of several requests in one launch: a long portion that starts in the
-    middle of its request, a single token, a whole short prompt, a short tail."""
+    middle of its request, a single token, a whole short prompt, a short tail, and one long enough
+    for several key steps with a window's edge inside them."""
     o = ops()
     dtype = torch.bfloat16
     rng = np.random.default_rng(nh * 100 + hd + page)
-    portions = [(37, 130), (0, 1), (0, 70), (200, 9)]            # (start position, tokens)
+    portions = [(37, 130), (0, 1), (0, 70), (200, 9), (115, 300)]            # (start position, tokens)
     lens = [s + n for s, n in portions]
     table, kc, vc, ks, vs, n_pages = make_paged(rng, lens, page, nkv, hd, dtype)
     T = sum(n for _, n in portions)
@@ -558,9 +560,12 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window):
     out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
     status = o.new_status(DEV)
     scale = 1 / math.sqrt(hd)
-    assert o.attention_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), torch.from_numpy(row_start).to(DEV),
+    took = o.attention_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), torch.from_numpy(row_start).to(DEV),
                                torch.from_numpy(start_pos).to(DEV), len(portions), torch.from_numpy(table).to(DEV), page, n_pages,
-                               window, scale, out, nh, nkv, hd, status)
+                               window, scale, out, nh, nkv, hd, status, kernel=kernel)
+    assert took == (kernel == "mma" or page >= 16)           # the tcgen05 kernel declines pages below 16 positions
+    if not took:
+        return
     o.read_status(status)
     got = out.float().cpu().double().numpy()
     assert np.isfinite(got).all()
@@ -574,11 +579,12 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window):
             t += 1
 
 
-def test_attention_prefill_far_key_and_refusals():
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_attention_prefill_far_key_and_refusals(kernel):
     o = ops()
     nh, nkv, hd, page, n = 8, 2, 64, 16, 900
     rng = np.random.default_rng(5)
-    for far in (0, 63, 64, 511, 512, 700, 899):
+    for far in (0, 63, 64, 127, 128, 511, 512, 700, 899):
         table, kc, vc, ks, vs, n_pages = make_paged(rng, [n], page, nkv, hd, torch.bfloat16)
         q = torch.from_numpy(rng.standard_normal((n, nh * hd)).astype(np.float32)).to(torch.bfloat16)
         for kvh in range(nkv):
@@ -590,7 +596,7 @@ def test_attention_prefill_far_key_and_refusals():
         status = o.new_status(DEV)
         assert o.attention_prefill(q.to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([0, n], dtype=torch.int32, device=DEV),
                                    torch.zeros(1, dtype=torch.int32, device=DEV), 1, torch.from_numpy(table).to(DEV), page,
-                                   n_pages, None, 1 / math.sqrt(hd), out, nh, nkv, hd, status)
+                                   n_pages, None, 1 / math.sqrt(hd), out, nh, nkv, hd, status, kernel=kernel)
         o.read_status(status)
         for kvh in range(nkv):
             h = kvh * (nh // nkv)
