@@ -11,9 +11,10 @@
 //   warp 1      tcgen05.mma: S = Q K^T into tensor memory (M = 128 rows, N = 128 keys), and, once
 //               the softmax warps have written P, O_step = P V (M = 128, N = head size), the values
 //               read as they lie in the cache (MN-major operand)
-//   warps 2-5   one thread per row: read S from tensor memory, mask by position and window, running
-//               max and sum in 32-bit, P = exp2(s - max) as bfloat16 into shared memory in the MMA's
-//               swizzled layout; read O_step and fold it into the row's 32-bit output registers
+//   warps 2-9   two threads per row (half of the step's keys and half of the head's dims each): read S
+//               from tensor memory, mask by position and window, running max and sum in 32-bit,
+//               P = exp2(s - max) as bfloat16 into shared memory in the MMA's swizzled layout; read
+//               O_step and fold it into the row's 32-bit output registers
 //
 // Formulas: scores q.k * scale for lo <= key <= position, lo = 0 or position + 1 - window, no mask
 // tensor, softmax with the max subtracted (imparo-model/src/cpu_support.rs:402-445).  Which tokens
@@ -31,7 +32,7 @@ using namespace tc;
 
 constexpr int ROWS = 128;          // query rows per CTA: the MMAs' M
 constexpr int KEYS = 128;          // keys per step: N of the score product, K of P V
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: softmax
 constexpr int STAGES = 2;
 constexpr uint32_t REGION = 128 * 128;      // a [128 rows][128 bytes] block of a tile: 16 KB
 constexpr uint32_t ALIGN_SLACK = 768;       // spare bytes for aligning the tiles to 1024: two CTAs must fit an SM at head size 64
@@ -57,6 +58,19 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// one 32-bit value per lane into a tensor-memory column, and a pair of neighbouring columns back
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(v)) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, float& x, float& y) {
+    uint32_t r0, r1;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile("" : "+r"(r0), "+r"(r1) :: "memory");
+    x = __uint_as_float(r0);
+    y = __uint_as_float(r1);
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -79,7 +93,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     constexpr int NB = HD / 64;                              // 64-dim blocks of a head
     constexpr uint32_t Q_BYTES = NB * REGION, P_BYTES = 2 * REGION, K_BYTES = NB * REGION, V_BYTES = NB * REGION;
     constexpr uint32_t STAGE_BYTES = K_BYTES + V_BYTES;
-    constexpr uint32_t TMEM_COLS = 256;                      // scores: columns 0..127, P V: 128..128+HD-1
+    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;     // scores: columns 0..127, P V: 128..128+HD-1, then four spare
+    constexpr uint32_t XCOL = 128 + HD;                      // columns the two threads of a row exchange through
     extern __shared__ __align__(1024) uint8_t fa_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
     if ((uint32_t)(smem - fa_smem_raw) > ALIGN_SLACK) {      // the launch's shared memory does not cover the aligned tiles
@@ -97,15 +112,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* p_ready = q_ready + 2;
     uint64_t* pv_ready = q_ready + 3;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 4);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);     // a softmax thread's wait ran out
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nh / a.nkv;
     const int TQ = ROWS / G;                                 // tokens per tile
-    const int kvh = blockIdx.y;
-    // which request and which of its tokens: tiles are numbered request by request; the last tiles
-    // (most keys under a causal mask) go first
-    int item = 0, tile = (int)gridDim.x - 1 - (int)blockIdx.x, n_item = 0, row0 = 0;
+    // The kv head is the fast grid index and the tiles run backwards along the slow one: CTAs are
+    // handed out in that order, so the tiles with the most keys under a causal mask start first
+    // and the short ones fill the SMs' last gaps.
+    const int kvh = blockIdx.x;
+    // which request and which of its tokens: tiles are numbered request by request
+    int item = 0, tile = (int)gridDim.y - 1 - (int)blockIdx.y, n_item = 0, row0 = 0;
     for (; item < a.n_items; ++item) {
         row0 = a.item_row_start[item];
         n_item = a.item_row_start[item + 1] - row0;
@@ -126,10 +144,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(q_ready, 128);
+        mbar_init(q_ready, 256);
         mbar_init(s_ready, 1);
-        mbar_init(p_ready, 128);
+        mbar_init(p_ready, 256);
         mbar_init(pv_ready, 1);
+        *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -220,95 +239,111 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
     } else {
-        // ---- softmax: thread = row = tensor-memory lane ----
+        // ---- softmax: two threads per row (= tensor-memory lane), one for each half of the step's keys
+        // and of the head's dims.  Warps 2-5 take keys 0-63, warps 6-9 keys 64-127; the two threads of a
+        // row agree on the row's max through two spare tensor-memory columns.
+        const int half = (warp - 2) >> 2;
         const int r = (warp & 3) * 32 + lane;
         const bool valid = r < n_rows;
         const int tok = r / G, head = kvh * G + r % G;
         const int pos_r = pos0 + tok;
         const int lo_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
         const int lo_last = (a.window > 0 && pos_last + 1 > a.window) ? pos_last + 1 - a.window : 0;
-        const uint32_t t_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16), t_o = t_s + 128;
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t t_s = t_lane + half * 64, t_o = t_lane + 128 + half * (HD / 2), t_x = t_lane + XCOL;
         const size_t row_off = ((size_t)(row0 + tok0 + (valid ? tok : 0)) * a.nh + head) * HD;
+        constexpr int DH = HD / 2;                           // dims of the output this thread keeps
         pdl_wait();
-        // the row's queries -> shared memory, 16-byte chunks swizzled as the MMA reads them
+        // this thread's half of the row's queries -> shared memory, 16-byte chunks swizzled as the MMA reads them
         {
             const uint4* src = reinterpret_cast<const uint4*>(a.q + row_off);
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
+            for (int cc = 0; cc < DH / 8; ++cc) {
+                const int c = half * (DH / 8) + cc;
                 const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
                 *reinterpret_cast<uint4*>(q_s + (c >> 3) * REGION + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(q_ready)) : "memory");
         }
-        float o[HD];
+        float o[DH];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        for (int d = 0; d < DH; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
         bool ok = true;
-        auto fold_pv = [&](float corr) {                     // o = o * corr + O_step
+        auto fold_pv = [&](float corr) {                     // o = o * corr + O_step (this thread's dims)
 #pragma unroll
-            for (int c = 0; c < HD; c += 64) {
-                float v[4][16];
-                tmem_ld_chunks<4>(t_o + c, v);
+            for (int c = 0; c < DH; c += 32) {
+                float v[2][16];
+                tmem_ld_chunks<2>(t_o + c, v);
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 2; ++u)
 #pragma unroll
                     for (int e = 0; e < 16; ++e) o[c + u * 16 + e] = o[c + u * 16 + e] * corr + v[u][e];
             }
         };
         for (int i = 0; i < n_steps; ++i) {
-            const int key0 = (kb_first + i) * KEYS;
-            if (!mbar_wait(s_ready, i & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 26, i, r); ok = false; break; }
+            const int key0 = (kb_first + i) * KEYS + half * 64;          // this thread's first key of the step
+            // A wait that runs out is recorded; every softmax thread still goes through the same named
+            // barriers and all leave together after the next one.
+            if (!mbar_wait(s_ready, i & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 26, i, r); *gave_up = 1; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // which keys of the step this row sees: [j_lo, j_hi] relative to key0 (empty for padding rows).
+            // which of its 64 keys this row sees: [j_lo, j_hi] relative to key0 (empty for padding rows).
             // A step that every row of the tile sees whole (all but the steps at the diagonal and at a
             // window's edge) skips the per-key tests.
-            const int j_hi = valid ? min(KEYS - 1, pos_r - key0) : -1;
+            const int j_hi = valid ? min(63, pos_r - key0) : -1;
             const int j_lo = max(0, lo_r - key0);
-            const bool whole = key0 + KEYS - 1 <= pos0 && key0 >= lo_last;
-            // pass 1: the row's max over the step (four running maxima: no 128-long dependent chain)
+            const bool whole = (kb_first + i) * KEYS + KEYS - 1 <= pos0 && (kb_first + i) * KEYS >= lo_last;
+            // pass 1: the max over this thread's keys (four running maxima: no long dependent chain)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                float v[4][16];
-                tmem_ld_chunks<4>(t_s + h * 64, v);
+                float v[2][16];
+                tmem_ld_chunks<2>(t_s + h * 32, v);
                 if (whole) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
+                    for (int u = 0; u < 2; ++u)
 #pragma unroll
                         for (int e = 0; e < 16; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[u][e]);
                 } else {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
+                    for (int u = 0; u < 2; ++u)
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
-                            const int j = h * 64 + u * 16 + e;
+                            const int j = h * 32 + u * 16 + e;
                             if (j >= j_lo && j <= j_hi) mx4[e & 3] = fmaxf(mx4[e & 3], v[u][e]);
                         }
                 }
             }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= sl2;                                       // sl2 > 0: the max commutes with the scaling
+            // the row's max: both threads of the row leave theirs in tensor memory and read the pair
+            tmem_st1(t_x + half, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (*gave_up) { ok = false; break; }
+            float mx_a, mx_b;
+            tmem_ld2(t_x, mx_a, mx_b);
+            const float mx = fmaxf(mx_a, mx_b) * sl2;        // sl2 > 0: the max commutes with the scaling
             const float m_new = fmaxf(m_run, mx);
             const float corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
             const float base = (m_new == -INFINITY) ? 0.f : m_new;
             // the previous step's P V is complete by now or soon: fold it in before P is overwritten
             if (i > 0) {
-                if (!mbar_wait(pv_ready, (i - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 27, i, r); ok = false; break; }
+                if (!mbar_wait(pv_ready, (i - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 27, i, r); *gave_up = 1; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 fold_pv(corr_prev);
             }
-            // pass 2: P = exp2(s - max), bfloat16, into shared memory; the row's sum in 32-bit
+            // pass 2: P = exp2(s - max), bfloat16, into shared memory; this thread's share of the row's sum
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const float nbase = -base;
+            uint8_t* prow = p_s + half * REGION + r * 128;   // keys 0-63 and 64-127 are the two blocks of P
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                float v[4][16];
-                tmem_ld_chunks<4>(t_s + h * 64, v);
+                float v[2][16];
+                tmem_ld_chunks<2>(t_s + h * 32, v);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 2; ++u) {
                     uint32_t w[8];
                     if (whole) {
 #pragma unroll
@@ -320,41 +355,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     } else {
 #pragma unroll
                         for (int e = 0; e < 16; e += 2) {
-                            const int j = h * 64 + u * 16 + e;
+                            const int j = h * 32 + u * 16 + e;
                             const float p0 = (j >= j_lo && j <= j_hi) ? ex2(fmaf(v[u][e], sl2, nbase)) : 0.f;
                             const float p1 = (j + 1 >= j_lo && j + 1 <= j_hi) ? ex2(fmaf(v[u][e + 1], sl2, nbase)) : 0.f;
                             sum4[(e >> 1) & 3] += p0 + p1;
                             w[e >> 1] = pack2(p0, p1);
                         }
                     }
-                    // keys u*16 .. u*16+15 of this half: chunks 2u and 2u+1 of the row's 128 bytes
-                    uint8_t* prow = p_s + h * REGION + r * 128;
-                    *reinterpret_cast<uint4*>(prow + (((2 * u) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(prow + (((2 * u + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+                    // keys h*32 + u*16 .. +15 of this block: chunks 4h + 2u and 4h + 2u + 1 of the row's 128 bytes
+                    const int c0 = 4 * h + 2 * u;
+                    *reinterpret_cast<uint4*>(prow + ((c0 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(prow + (((c0 + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l_run = l_run * corr + sum;
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m_run = m_new;
             corr_prev = corr;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(p_ready)) : "memory");
         }
-        if (ok) {
-            if (mbar_wait(pv_ready, (n_steps - 1) & 1)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                fold_pv(corr_prev);
-                if (valid) {
-                    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-                    uint4* dst = reinterpret_cast<uint4*>(a.out + row_off);
+        if (ok) {                                            // uniform over the softmax threads (set after a barrier)
+            if (!mbar_wait(pv_ready, (n_steps - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 28, n_steps, r); *gave_up = 1; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            fold_pv(corr_prev);
+            // the row's sum: the two threads' shares, in the order (keys 0-63, keys 64-127)
+            tmem_st1(t_x + 2 + half, l_run);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float l_a, l_b;
+            tmem_ld2(t_x + 2, l_a, l_b);
+            const float l = l_a + l_b;
+            if (valid && !*gave_up) {
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                uint4* dst = reinterpret_cast<uint4*>(a.out + row_off + half * DH);
 #pragma unroll
-                    for (int c = 0; c < HD / 8; ++c)
-                        dst[c] = make_uint4(pack2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
-                                            pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
-                }
-            } else {
-                report(a.status, IMPARO_ST_WAIT_LIMIT, 28, n_steps, r);
+                for (int c = 0; c < DH / 8; ++c)
+                    dst[c] = make_uint4(pack2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                        pack2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
             }
         }
     }
@@ -402,7 +441,7 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     if (!(scale > 0.f)) return -8;                           // the row max is taken before the scaling
     const int TQ = fa::ROWS / G;
     const long long tiles = (n_tok + TQ - 1) / TQ + n_items;          // an upper bound: every request may end a tile early
-    if (tiles > 0x7fffffffLL || nkv > 65535) return -2;
+    if (tiles > 65535) return -8;                            // the tiles are the grid's y extent: the caller uses another kernel
     CUtensorMap mk, mv;
     const uint64_t rows = (uint64_t)n_pages * page_size, cols = (uint64_t)nkv * hd;
     int rc = tc::get_map(k_cache, rows, cols, cols, (uint32_t)page_size, &mk);
@@ -414,6 +453,6 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.item_row_start = item_row_start; a.item_start_pos = item_start_pos; a.table = table; a.status = status;
     a.n_items = n_items; a.max_blocks = max_blocks; a.page_size = page_size; a.n_pages = n_pages; a.window = window;
     a.nh = nh; a.nkv = nkv; a.scale = scale;
-    dim3 grid((unsigned)tiles, nkv);
+    dim3 grid(nkv, (unsigned)tiles);
     return hd == 64 ? fa::launch_tc<64>(mk, mv, a, grid, stream) : fa::launch_tc<128>(mk, mv, a, grid, stream);
 }
