@@ -22,7 +22,9 @@ constexpr int WARPS = 4;
 // description comes from the host before the step).  After the wait: one load of the head's
 // values, the norm, the rotation, the store.
 // FEW: at most eight partials (or none): straight-line loads, all of a head's values in flight together
-template <typename T, bool FEW>
+// PER: elements of a head per lane (head size up to 32 * PER), so that a head of 64 does not pay
+// for the loops of a head of 256.
+template <typename T, bool FEW, int PER>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
                           const int* __restrict__ item_of_token,
@@ -33,7 +35,7 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
                           int nh, int nkv, int hd, const float* __restrict__ part, int parts, size_t part_stride,
                           int* status) {
     __shared__ float rowbuf[WARPS][MAX_HEAD];
-    constexpr int PER = MAX_HEAD / 32, PAIRS = MAX_HEAD / 64;
+    constexpr int PAIRS = (PER + 1) / 2;
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -266,14 +268,17 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
     if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * (nh + 2 * nkv) * hd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
     const float* part = parts > 0 ? (const float*)qkv : nullptr;
-#define IMPARO_QK(T_, FEW_) launch(qk_norm_rope_store_kernel<T_, FEW_>, grid, dim3(WARPS * 32), 0, stream, \
+#define IMPARO_QK3(T_, FEW_, PER_) launch(qk_norm_rope_store_kernel<T_, FEW_, PER_>, grid, dim3(WARPS * 32), 0, stream, \
             (const T_*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (T_*)q_out, (T_*)k_cache, (T_*)v_cache, \
             table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts, (size_t)part_stride, status)
+#define IMPARO_QK(T_, FEW_) do { if (hd <= 64) IMPARO_QK3(T_, FEW_, 2); else if (hd <= 128) IMPARO_QK3(T_, FEW_, 4); \
+                                 else IMPARO_QK3(T_, FEW_, 8); } while (0)
     if (dtype == IMPARO_DT_F32) {
         if (parts <= 8) IMPARO_QK(float, true); else IMPARO_QK(float, false);
     } else if (dtype == IMPARO_DT_BF16) {
         if (parts <= 8) IMPARO_QK(__nv_bfloat16, true); else IMPARO_QK(__nv_bfloat16, false);
     }
+#undef IMPARO_QK3
 #undef IMPARO_QK
     else return -1;
     IMPARO_CHECK_LAUNCH();

@@ -131,7 +131,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (tile < tiles) break;
         tile -= tiles;
     }
-    if (item >= a.n_items) return;                           // the grid is an upper bound (uniform per CTA)
+    if (item >= a.n_items) {                                 // the grid is an upper bound (uniform per CTA)
+        if (threadIdx.x == 0) pdl_wait();                    // (keeps the launch's timeline record whole)
+        return;
+    }
     const int tok0 = tile * TQ;
     const int n_tok = min(TQ, n_item - tok0);
     const int n_rows = n_tok * G;

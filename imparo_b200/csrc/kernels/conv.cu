@@ -173,14 +173,17 @@ __global__ void gated_conv_kernel(const ConvIn<T, MODE> bcx, const float* __rest
 // bfloat16 with a width that is a multiple of 8, for prompt-sized batches: a thread owns eight
 // consecutive channels of one token and moves 16 bytes at a time.  Same sums in the same order
 // as gated_conv_kernel; the thread of a portion's first token walks its eight channels through
-// conv_portion_head.
+// conv_portion_head.  TAPS > 0: the number of taps is fixed at compile time; the thread's 8 * TAPS
+// tap weights are contiguous and come as 16-byte loads, and the loads of all taps' rows are in
+// flight together.  TAPS == 0: any number of taps.
+template <int TAPS>
 __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, const float* __restrict__ w,
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
                                          const int* __restrict__ item_slot, __nv_bfloat16* __restrict__ y,
-                                         int n_tok, int width, int taps, int n_slots, int* status) {
+                                         int n_tok, int width, int taps_rt, int n_slots, int* status) {
     pdl_trigger();
-    pdl_wait();
+    const int taps = TAPS > 0 ? TAPS : taps_rt;
     const int per_row = width >> 3;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tok * per_row) return;
@@ -189,6 +192,18 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
     const int item = item_of_token[t];
     const int start = item_row_start[item];
     const int rel = t - start;
+    // the thread's tap weights: w[(ch + i) * taps + k], 8 * taps consecutive floats
+    constexpr int NW = TAPS > 0 ? 8 * TAPS : 1;
+    float wv[NW];
+    if (TAPS > 0) {
+        const float4* wp = reinterpret_cast<const float4*>(w + (size_t)ch * TAPS);
+#pragma unroll
+        for (int q4 = 0; q4 < 2 * TAPS; ++q4) {
+            const float4 f = __ldg(wp + q4);
+            wv[4 * q4] = f.x; wv[4 * q4 + 1] = f.y; wv[4 * q4 + 2] = f.z; wv[4 * q4 + 3] = f.w;
+        }
+    }
+    pdl_wait();
     if (rel < hist) {
         if (rel != 0) return;
         const int n = item_row_start[item + 1] - start;
@@ -205,24 +220,45 @@ __global__ void gated_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ bcx, 
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int k = 0; k < taps; ++k) {
-        const __nv_bfloat16* r = bcx + (size_t)(t - hist + k) * stride;
-        const uint4 b = *reinterpret_cast<const uint4*>(r + ch);
-        const uint4 x = *reinterpret_cast<const uint4*>(r + 2 * (size_t)width + ch);
-        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
-        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const uint4 c = *reinterpret_cast<const uint4*>(bcx + (size_t)t * stride + width + ch);
+    if (TAPS > 0) {
+        uint4 bq[TAPS > 0 ? TAPS : 1], xq[TAPS > 0 ? TAPS : 1];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 bf = __bfloat1622float2(bp[i]), xf = __bfloat1622float2(xp[i]);
-            acc[2 * i] += w[(size_t)(ch + 2 * i) * taps + k] * (bf.x * xf.x);
-            acc[2 * i + 1] += w[(size_t)(ch + 2 * i + 1) * taps + k] * (bf.y * xf.y);
+        for (int k = 0; k < TAPS; ++k) {
+            const __nv_bfloat16* r = bcx + (size_t)(t - hist + k) * stride;
+            bq[k] = *reinterpret_cast<const uint4*>(r + ch);
+            xq[k] = *reinterpret_cast<const uint4*>(r + 2 * (size_t)width + ch);
+        }
+#pragma unroll
+        for (int k = 0; k < TAPS; ++k) {
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bq[k]);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xq[k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 bf = __bfloat1622float2(bp[i]), xf = __bfloat1622float2(xp[i]);
+                acc[2 * i] += wv[(2 * i) * TAPS + k] * (bf.x * xf.x);
+                acc[2 * i + 1] += wv[(2 * i + 1) * TAPS + k] * (bf.y * xf.y);
+            }
+        }
+    } else {
+        for (int k = 0; k < taps; ++k) {
+            const __nv_bfloat16* r = bcx + (size_t)(t - hist + k) * stride;
+            const uint4 b = *reinterpret_cast<const uint4*>(r + ch);
+            const uint4 x = *reinterpret_cast<const uint4*>(r + 2 * (size_t)width + ch);
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 bf = __bfloat1622float2(bp[i]), xf = __bfloat1622float2(xp[i]);
+                acc[2 * i] += w[(size_t)(ch + 2 * i) * taps + k] * (bf.x * xf.x);
+                acc[2 * i + 1] += w[(size_t)(ch + 2 * i + 1) * taps + k] * (bf.y * xf.y);
+            }
         }
     }
     if (bias) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += bias[ch + i];
     }
-    const uint4 c = *reinterpret_cast<const uint4*>(bcx + (size_t)t * stride + width + ch);
     const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&c);
     uint4 out;
     __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&out);
@@ -263,9 +299,15 @@ extern "C" int imparo_gated_conv(const void* bcx, int dtype, const float* w, con
         const bool wide = parts == 0 && n_tok >= 64 && (width & 7) == 0 && (((uintptr_t)bcx | (uintptr_t)y) & 15) == 0;
         if (wide) {
             const size_t n8 = (size_t)n_tok * (width >> 3);
-            launch(gated_conv_bf16x8_kernel, dim3((unsigned)((n8 + threads - 1) / threads)), dim3(threads), 0, stream,
-                   (const __nv_bfloat16*)bcx, w, bias, state, item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y,
-                   n_tok, width, taps, n_slots, status);
+            const dim3 g8((unsigned)((n8 + threads - 1) / threads));
+            const bool w16 = (((uintptr_t)w) & 15) == 0;         // the fixed-taps versions read the weights 16 bytes at a time
+#define IMPARO_CONV8(TAPS_) launch(gated_conv_bf16x8_kernel<TAPS_>, g8, dim3(threads), 0, stream, (const __nv_bfloat16*)bcx, w, bias, \
+                   state, item_row_start, item_of_token, item_slot, (__nv_bfloat16*)y, n_tok, width, taps, n_slots, status)
+            if (w16 && taps == 2) IMPARO_CONV8(2);
+            else if (w16 && taps == 3) IMPARO_CONV8(3);
+            else if (w16 && taps == 4) IMPARO_CONV8(4);
+            else IMPARO_CONV8(0);
+#undef IMPARO_CONV8
         } else if (mode == 0) IMPARO_CONV(__nv_bfloat16, 0);
         else if (mode == 1) IMPARO_CONV(__nv_bfloat16, 1);
         else IMPARO_CONV(__nv_bfloat16, 2);

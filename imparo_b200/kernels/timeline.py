@@ -113,6 +113,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=12, help="decode steps to run (the last one is printed)")
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--prefill", action="store_true", help="print the step of a whole prompt instead of a decode step "
+                    "(library products are not stamped: their time shows in the share of the kernel before them)")
     ap.add_argument("--json", action="store_true")
     args = ap.parse_args(argv)
     import numpy as np
@@ -135,6 +137,20 @@ def main(argv: Optional[List[str]] = None) -> int:
     tl = Timeline()
     rng = np.random.default_rng(0)
     V = engine.vocab_size
+    if args.prefill:
+        rows = None
+        for rep in range(3):
+            engine.add_request(900 + rep)
+            before = tl.host_launches()
+            n_before = tl.records().shape[0]
+            engine.step([StepItem(900 + rep, rng.integers(0, V, args.prompt_len).tolist(), [args.prompt_len - 1])])
+            rec = tl.records()[n_before:]
+            names = tl.names(before, tl.host_launches())
+            engine.end_request(900 + rep)
+            rows = step_table(names, rec)
+        tl.stop()
+        _print_table(rows, f"prompt of {args.prompt_len} tokens", args.json)
+        return 0
     ids = list(range(args.batch))
     for r in ids:
         engine.add_request(r)
@@ -155,11 +171,17 @@ def main(argv: Optional[List[str]] = None) -> int:
     names = tl.names(first, last)
     n = len(names)
     rows = step_table(names, rec[-n:])
-    if args.json:
+    _print_table(rows, "last decode step", args.json)
+    return 0
+
+
+def _print_table(rows, what: str, as_json: bool) -> None:
+    if as_json:
         print(json.dumps(rows))
-        return 0
-    total = (int(rec[-1, 1]) - int(rec[-n, 1])) / 1e3
-    print(f"last decode step: {n} kernels, {total:.1f} us from the first wait to the last")
+        return
+    n = len(rows)
+    total = rows[-1]["at_us"] - rows[0]["at_us"]
+    print(f"{what}: {n} kernels, {total:.1f} us from the first wait to the last")
     print(f"{'at us':>9} {'resident':>9} {'chain us':>9} {'mark0':>7} {'mark1':>7}  kernel")
     for r in rows:
         f = lambda v: "      -" if v is None else f"{v:7.2f}"
@@ -173,7 +195,6 @@ def main(argv: Optional[List[str]] = None) -> int:
     print("\nchain time by kernel:")
     for k, (c, us) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
         print(f"{us:9.1f} us {100 * us / total:5.1f}%  x{c:<3d} {us / c:6.2f} each  {k}")
-    return 0
 
 
 if __name__ == "__main__":
