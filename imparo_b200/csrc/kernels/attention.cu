@@ -149,6 +149,95 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
     }
 }
 
+// Many tokens (a prompt portion), stored input, and a rotation whose pairs (i, i + n_rot/2) fall
+// into the same lane (n_rot/2 a multiple of 32, e.g. heads of 64 or 128 fully rotated): a block owns
+// one token, its four warps share the token's heads, the sines and cosines of the position are
+// computed once per warp instead of once per head, and norm and rotation stay in registers.
+template <typename T, int PER>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_rows_kernel(const T* __restrict__ qkv, const int* __restrict__ positions,
+                         const int* __restrict__ item_of_token,
+                         const float* __restrict__ q_w, const float* __restrict__ k_w,
+                         const float* __restrict__ inv_freq, int n_rot, float eps,
+                         T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                         const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                         int nh, int nkv, int hd, int* status) {
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total = nh + 2 * nkv;
+    const int pos = positions[t];
+    const int hj = n_rot >> 6;                               // register distance of a rotation pair: (n_rot / 2) / 32
+    float wq[PER], wk[PER], sn[PER], cs[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int d = lane + 32 * j;
+        wq[j] = d < hd ? q_w[d] : 0.f;
+        wk[j] = (d < hd && nkv > 0) ? k_w[d] : 0.f;
+        sn[j] = 0.f; cs[j] = 1.f;
+        if (inv_freq && j < hj) sincosf((float)pos * inv_freq[d], &sn[j], &cs[j]);
+    }
+    size_t cache_row = 0;
+    int page = 0;
+    if (nkv > 0) {
+        const int blk = pos / page_size;
+        page = blk < max_blocks ? table[(size_t)item_of_token[t] * max_blocks + blk] : -1;
+        if (page >= 0 && page < n_pages) cache_row = (size_t)page * page_size + (pos % page_size);
+    }
+    pdl_wait();
+    const T* src = qkv + (size_t)t * total * hd;
+    float nxt[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; nxt[j] = (warp < total && d < hd) ? to_f32(src[(size_t)warp * hd + d]) : 0.f; }
+    for (int hh = warp; hh < total; hh += WARPS) {
+        float val[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) val[j] = nxt[j];
+        if (hh + WARPS < total) {                            // the next head's values are on their way meanwhile
+#pragma unroll
+            for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; nxt[j] = d < hd ? to_f32(src[(size_t)(hh + WARPS) * hd + d]) : 0.f; }
+        }
+        const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+        T* dst;
+        if (is_q) {
+            dst = q_out + (size_t)t * nh * hd + (size_t)hh * hd;
+        } else {
+            if (page < 0 || page >= n_pages) {
+                if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);
+                return;
+            }
+            const int kvh = is_k ? hh - nh : hh - nh - nkv;
+            dst = (is_k ? k_cache : v_cache) + cache_row * ((size_t)nkv * hd) + (size_t)kvh * hd;
+        }
+        if (is_q || is_k) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) ss += val[j] * val[j];
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int j = 0; j < PER; ++j) val[j] = val[j] * scale * (is_q ? wq[j] : wk[j]);
+            if (inv_freq) {
+#pragma unroll
+                for (int j = 0; j < PER / 2; ++j) {
+                    if (j < hj) {
+                        // the pair (lane + 32 j, lane + 32 j + n_rot/2): registers j and j + hj
+                        float x0 = val[j], x1 = 0.f;
+#pragma unroll
+                        for (int q = 0; q < PER; ++q) if (q == j + hj) x1 = val[q];
+                        const float r0 = x0 * cs[j] - x1 * sn[j], r1 = x0 * sn[j] + x1 * cs[j];
+                        val[j] = r0;
+#pragma unroll
+                        for (int q = 0; q < PER; ++q) if (q == j + hj) val[q] = r1;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; if (d < hd) dst[d] = from_f32<T>(val[j]); }
+    }
+}
+
 // ---- general paged attention ---------------------------------------------------------
 template <typename T> struct Vec;
 template <> struct Vec<float> { using type = float4; static constexpr int N = 4; };
@@ -268,6 +357,18 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
     if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * (nh + 2 * nkv) * hd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
     const float* part = parts > 0 ? (const float*)qkv : nullptr;
+    if (n_tok >= 256 && parts == 0 && hd % 32 == 0 && hd <= 128 && (inv_freq == nullptr || (n_rot >= 64 && n_rot % 64 == 0))) {
+        // a prompt portion: the register-only kernel, one block per token
+#define IMPARO_QKR(T_, PER_) launch(qk_norm_rope_rows_kernel<T_, PER_>, dim3(n_tok), dim3(WARPS * 32), 0, stream, (const T_*)qkv, \
+            positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (T_*)q_out, (T_*)k_cache, (T_*)v_cache, table, max_blocks, \
+            page_size, n_pages, nh, nkv, hd, status)
+        if (dtype == IMPARO_DT_F32) { if (hd <= 64) IMPARO_QKR(float, 2); else IMPARO_QKR(float, 4); }
+        else if (dtype == IMPARO_DT_BF16) { if (hd <= 64) IMPARO_QKR(__nv_bfloat16, 2); else IMPARO_QKR(__nv_bfloat16, 4); }
+        else return -1;
+#undef IMPARO_QKR
+        IMPARO_CHECK_LAUNCH();
+        return 0;
+    }
 #define IMPARO_QK3(T_, FEW_, PER_) launch(qk_norm_rope_store_kernel<T_, FEW_, PER_>, grid, dim3(WARPS * 32), 0, stream, \
             (const T_*)qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, (T_*)q_out, (T_*)k_cache, (T_*)v_cache, \
             table, max_blocks, page_size, n_pages, nh, nkv, hd, part, parts, (size_t)part_stride, status)

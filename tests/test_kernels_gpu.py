@@ -338,7 +338,8 @@ def test_one_far_key_stands_out(dtype, far, window, kind, chunk):
     assert np.abs(out[0].float().cpu().double().numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("nh,nkv,hd,n_rot", [(4, 2, 16, 16), (6, 2, 32, 32), (3, 1, 48, 48), (2, 2, 64, 32), (1, 1, 256, 256)])
+@pytest.mark.parametrize("nh,nkv,hd,n_rot", [(4, 2, 16, 16), (6, 2, 32, 32), (3, 1, 48, 48), (2, 2, 64, 32), (1, 1, 256, 256),
+                                             (4, 2, 64, 64), (3, 1, 128, 128), (5, 2, 128, 64), (6, 3, 96, 64)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("many", [False, True])
 def test_qk_norm_rope_store(nh, nkv, hd, n_rot, dtype, many):
