@@ -11,8 +11,9 @@ from tests.tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
 
-PAGE = {"A": 16, "B": 4, "C": 8, "D": 32}
-LENGTHS = {"A": [70, 45, 96, 33, 64, 51, 80], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [44, 71, 36, 60]}
+PAGE = {"A": 16, "B": 4, "C": 8, "D": 32, "E": 16, "F": 64}
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51, 80], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [44, 71, 36, 60],
+           "E": [150, 47, 96, 201, 64], "F": [130, 75, 40, 164]}
 
 
 def engine_for(name, dtype, steps, parallel=4):
@@ -24,7 +25,7 @@ def engine_for(name, dtype, steps, parallel=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
 def test_family(name, dtype, family):
     reqs = make_requests(name, LENGTHS[name])

@@ -1,7 +1,7 @@
 """Tiny LFM2 configurations for tests.  They differ in every size and option: layer
-order, heads and groups (2, 3, 1), head size (16, 32, 48), taps (3, 4, 2), conv bias,
+order, heads and groups (2, 3, 1), head size (16, 32, 48, 64, 128), taps (3, 4, 2, 5), conv bias,
 rope theta, eps, tied or own head, ff auto-adjust, vocabulary and width that are no
-power of two, and a sliding window in C."""
+power of two, and a sliding window in C and E."""
 
 TINY_A = {
     "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
@@ -45,4 +45,27 @@ TINY_D = {
     "tie_embedding": True, "max_position_embeddings": 4096,
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head sizes the tensor-core attention kernels take (64 and 128), so that those kernels (tcgen05
+# prompt attention, split-key decode attention on mma.sync) meet the plain implementation too:
+# E has two query heads per kv head and a sliding window on one layer, F one kv head for three heads
+TINY_E = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 300, "hidden_size": 96, "num_hidden_layers": 4,
+    "layer_types": ["full_attention", "conv", "sliding_attention", "full_attention"],
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "block_ff_dim": 160, "block_auto_adjust_ff_dim": False,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 4096, "sliding_window": 40,
+}
+
+TINY_F = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 270, "hidden_size": 72, "num_hidden_layers": 3,
+    "layer_types": ["conv", "full_attention", "full_attention"],
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128,
+    "block_ff_dim": 136, "block_auto_adjust_ff_dim": False,
+    "conv_L_cache": 4, "conv_bias": True, "rope_theta": 10000.0, "norm_eps": 2e-6,
+    "tie_embedding": False, "max_position_embeddings": 4096,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
