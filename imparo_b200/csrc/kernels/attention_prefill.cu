@@ -296,6 +296,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     // read, and the chunk's table entries are pulled into the L1, before the wait on the previous kernel
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int G = nh / nkv;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
     const int pos = positions[t];
@@ -306,25 +307,31 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int* tab = table + (size_t)item_of_token[t] * max_blocks;
     const size_t kvw = (size_t)nkv * HD;
     const int kb_first = begin / KEYS, kb_last = (end - 1) / KEYS;
+    // a thread fetches half a row of the tile (two threads per key): one page lookup, then CH / 2
+    // 16-byte pieces each of the key and of the value
     auto load_kv = [&](int kb, int buf) {
-        for (int i = tid; i < KEYS * CH; i += THREADS) {
-            const int r = i / CH, c = i % CH;
-            const int j = kb * KEYS + r;
-            bool valid = j >= begin && j < end;
-            size_t rowi = 0;
-            if (valid) {
-                const int blk = j / page_size;
-                const int page = blk < max_blocks ? tab[blk] : -1;
-                if (page < 0 || page >= n_pages) {
-                    if (c == 0) report(status, IMPARO_ST_PAGE_RANGE, 7, t, page);
-                    valid = false;
-                } else {
-                    rowi = (size_t)page * page_size + (j % page_size);
-                }
+        static_assert(THREADS == 2 * KEYS, "two threads per key of a tile");
+        const int r = tid >> 1, c0 = (tid & 1) * (CH / 2);
+        const int j = kb * KEYS + r;
+        bool valid = j >= begin && j < end;
+        size_t rowi = 0;
+        if (valid) {
+            // pages of a power of two: shifts, not integer division
+            const int blk = page_shift >= 0 ? j >> page_shift : j / page_size;
+            const int within = page_shift >= 0 ? j & (page_size - 1) : j % page_size;
+            const int page = blk < max_blocks ? tab[blk] : -1;
+            if (page < 0 || page >= n_pages) {
+                if (c0 == 0) report(status, IMPARO_ST_PAGE_RANGE, 7, t, page);
+                valid = false;
+            } else {
+                rowi = (size_t)page * page_size + within;
             }
-            const size_t off = rowi * kvw + (size_t)kvh * HD + c * 8;
-            cp_async16(k_s[buf] + tile_off<HD>(r, c), k_cache + off, valid);
-            cp_async16(v_s[buf] + tile_off<HD>(r, c), v_cache + off, valid);
+        }
+        const size_t off = rowi * kvw + (size_t)kvh * HD + c0 * 8;
+#pragma unroll
+        for (int c = 0; c < CH / 2; ++c) {
+            cp_async16(k_s[buf] + tile_off<HD>(r, c0 + c), k_cache + off + c * 8, valid);
+            cp_async16(v_s[buf] + tile_off<HD>(r, c0 + c), v_cache + off + c * 8, valid);
         }
         cp_commit();
     };
