@@ -110,8 +110,11 @@ def model_numbers(engine):
     weight_bytes = (matrix_params + V * H) * elt          # every matrix once; the tied table is the head
     kv_per_token = n_attn * 2 * nkv * hd * elt
 
-    def prefill_flops(T):
-        return 2.0 * T * matrix_params + 2.0 * V * H + n_attn * 4.0 * nh * hd * T * (T + 1) / 2
+    def prefill_flops(T, wanted=1):
+        # what the step executes: the last layer's feed-forward runs on the wanted rows only (as
+        # in the reference), every other product on all T tokens; causal attention; the head on the wanted rows
+        return 2.0 * T * (matrix_params - per_layer_ffn) + 2.0 * wanted * per_layer_ffn + 2.0 * wanted * V * H \
+            + n_attn * 4.0 * nh * hd * T * (T + 1) / 2
     return weight_bytes, kv_per_token, prefill_flops, matrix_params + V * H
 
 
@@ -264,7 +267,8 @@ def main():
                    "layers": cfg["num_hidden_layers"], "layers_of_config": LFM2_1_2B["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": 32, "kv_heads": 8, "head_dim": 64, "ff_dim": engine.config.ff_dim,
                    "vocab": cfg["vocab_size"], "conv_L_cache": 3, "page_size": PAGE, "params": n_params,
-                   "l2": "inputs larger than L2 (2.3 GB of weights read per step)", "cuda_graph": True},
+                   "l2": "inputs larger than L2 (2.3 GB of weights read per step)", "cuda_graph": True,
+                   "last_ffn": "wanted rows only"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": int(round(launches * steps)), "own_kernels_per_step": round(launches, 1),
         "library_gemms_per_step": round(library, 1),

@@ -151,6 +151,22 @@ __global__ void add_partials_rmsnorm_kernel(float* __restrict__ x, const float* 
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
+// ---- out[r, :] = x[rows[r], :] ---------------------------------------------------------------
+// Rows of the 32-bit stream picked out (the last layer's feed-forward runs on the wanted rows only).
+__global__ void gather_rows_f32_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                       float* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const float* src = x + (size_t)rows[blockIdx.x] * width;
+    float* dst = out + (size_t)blockIdx.x * width;
+    if ((width & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4)
+            *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 // ---- out = sum of split partials ----------------------------------------------------------
 // For a consumer that cannot read partials itself: out[i] = part[0][i] + part[1][i] + ... in order.
 template <typename TOut>
@@ -327,6 +343,13 @@ extern "C" int imparo_add_bias(void* out, int dtype, const float* bias, int n_to
 }
 
 // x[r, :] += sum over s of part[s][r][:] (in order), and out = rms_norm(x) when out is not null.
+extern "C" int imparo_gather_rows_f32(const float* x, const int* rows, float* out, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    launch(gather_rows_f32_kernel, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), 0, stream, x, rows, out, width);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" int imparo_fold_partials(const float* part, int n_splits, long long split_stride, void* out, int out_dtype,
                                     long long n, cudaStream_t stream) {
     if (n <= 0) return 0;

@@ -141,8 +141,10 @@ class StepFunction:
 
     # -- decode-only steps replay a captured graph ------------------------------------------
     def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
-        x = self.model.forward(batch, self._views)
-        return self.model.logits(x, batch.want_rows, batch.n_want) if batch.n_want else None
+        x, picked = self.model.forward(batch, self._views, wanted=(batch.want_rows, batch.n_want))
+        if not batch.n_want:
+            return None
+        return self.model.logits(x, None if picked else batch.want_rows, batch.n_want)
 
     def _forward_graphed(self, batch: StepBatch) -> Optional[torch.Tensor]:
         """A step of single tokens only has the same launches whenever (requests, wanted

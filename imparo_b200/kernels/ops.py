@@ -484,6 +484,18 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, :] = x[rows[r], :] for a 32-bit stream (folds split partials pending on x first)."""
+    _cuda(x, rows, out)
+    settle(x)
+    n, width = out.shape
+    _need(x.dtype == torch.float32 and out.dtype == torch.float32 and x.shape[1] == width and x.stride(1) == 1
+          and x.stride(0) == width and out.is_contiguous(), "gather_rows: dense float32 [rows, width]")
+    _need(rows.dtype == torch.int32 and rows.numel() >= n, "gather_rows: rows must be int32, one per output row")
+    _check(_lib.kernels().imparo_gather_rows_f32(_ptr(x), _ptr(rows), _ptr(out), n, width, _stream()), "gather_rows")
+    COUNTS["own"] += 1
+
+
 class PartialProduct:
     """A product x w^T that was cut along K and not folded: parts[s] (float32 [T, N], split s at
     offset s * stride floats) sum to the result.  gated_conv and qk_norm_rope_store read it as it is

@@ -18,6 +18,7 @@ class PreNormResidualBlock(Part):
         self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt)
         self.parts = (self.mixer_norm, self.mixer, self.ff_norm, self.ff)
         self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.picks_rows = True         # forward(only_rows=...) is implemented
 
     def weight_specs(self):
         return [w for p in self.parts for w in p.weight_specs()]
@@ -29,19 +30,35 @@ class PreNormResidualBlock(Part):
     def cache_specs(self):
         return self.mixer.cache_specs()
 
-    def forward(self, x, batch, caches, ready=None, next_norm=None):
+    def forward(self, x, batch, caches, ready=None, next_norm=None, only_rows=None):
         """x: the 32-bit residual stream [tokens, width], updated in place.
         ready: this block's mixer-norm input when the block before already produced it.
         next_norm: the norm part that reads x after this block (the next block's mixer norm);
-        returns its unevaluated/filled input for that block, or None."""
+        returns its unevaluated/filled input for that block, or None.
+        only_rows = (rows, n): the caller needs the block's output at these n rows only (the
+        model's last block, whose output feeds nothing but the wanted logits; the reference skips
+        the same work, imparo-model/src/lfm2/workflow_gpu.rs:990-992,1201-1203).  The mixer still
+        runs on every row (its cache and state advance); the feed-forward runs on the picked rows,
+        and their stream [n, width] is returned instead (None when n is 0)."""
         from ..kernels import ops
         h = ready if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
             self._normed(self.mixer_norm, self.mixer, x, "normed_mixer")
         ff_in = None
-        if self.mixer.adds_with_linear and self.ff.accepts_lazy_input and self._defers(self.ff_norm):
+        if only_rows is None and self.mixer.adds_with_linear and self.ff.accepts_lazy_input and self._defers(self.ff_norm):
             ff_in = self.ff_norm.lazy(x, tag="normed_ff")     # unevaluated: the mixer's output product may fill it
             ops.arm_norm(x, ff_in)
         self._run(self.mixer, x, lambda: self.mixer.forward(h, batch, caches, x))
+        if only_rows is not None:
+            ops.disarm_norm(x)
+            rows, n = only_rows
+            if n == 0:
+                ops.settle(x)
+                return None
+            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype)
+            ops.gather_rows(x, rows, xs)
+            picked_in = self._normed(self.ff_norm, self.ff, xs, "normed_ff")
+            self._run(self.ff, xs, lambda: self.ff.forward(picked_in, batch, xs))
+            return xs
         if ff_in is not None:
             ops.disarm_norm(x)
         else:

@@ -2,7 +2,7 @@
 final norm and head.  It holds no architecture-specific code."""
 from __future__ import annotations
 
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -61,22 +61,30 @@ class Model:
         return out
 
     # -- running -----------------------------------------------------------------------
-    def forward(self, batch, cache_views) -> torch.Tensor:
+    def forward(self, batch, cache_views, wanted=None):
         """Runs the batch's tokens through every schedule entry.  cache_views(entry) gives
-        the tuple of bound cache views for that entry.  Returns the residual stream."""
+        the tuple of bound cache views for that entry.  Returns the residual stream.
+
+        wanted = (rows, n): only these n rows of the result will be read (the logits' rows).  When
+        they are fewer than the batch's tokens and the last entry is a block that can run its
+        feed-forward on picked rows, the result is (stream of the picked rows [n, width] or None
+        for n = 0, True); else (the whole stream, False)."""
         x = self.embedding.forward(batch.token_ids, batch.n_tokens)
         ready = None
+        last = len(self.schedule) - 1
         for i, e in enumerate(self.schedule):
             layer = self.layers[e.layer]
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             if hasattr(layer, "mixer_norm"):
+                if i == last and wanted is not None and wanted[1] < batch.n_tokens and getattr(layer, "picks_rows", False):
+                    return layer.forward(x, batch, cache_views(i), ready=ready, only_rows=wanted), True
                 # a block may hand the next block its (already computed) norm input
                 ready = layer.forward(x, batch, cache_views(i), ready=ready,
                                       next_norm=getattr(nxt, "mixer_norm", None) if nxt is not None else None)
             else:
                 layer.forward(x, batch, cache_views(i))
                 ready = None
-        return x
+        return (x, False) if wanted is not None else x
 
     def settle(self, x: torch.Tensor) -> None:
         """Make the stream whole (fold split partials a product may have left) for a reader that
@@ -84,8 +92,9 @@ class Model:
         from ..kernels import ops
         ops.settle(x)
 
-    def logits(self, x: torch.Tensor, rows: torch.Tensor, n_rows: int) -> torch.Tensor:
-        """Final norm and head at the wanted rows only: [n_rows, vocab] in 32-bit."""
+    def logits(self, x: torch.Tensor, rows: Optional[torch.Tensor], n_rows: int) -> torch.Tensor:
+        """Final norm and head at the wanted rows only: [n_rows, vocab] in 32-bit.  rows None: x
+        holds exactly the wanted rows."""
         if getattr(self.head, "accepts_lazy_input", False) and hasattr(self.final_norm, "lazy"):
             h = self.final_norm.lazy(x, rows=rows, n_rows=n_rows, tag="final_normed")
         else:
