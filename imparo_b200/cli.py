@@ -38,6 +38,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--num-pages", type=int, default=None)
     ap.add_argument("--max-step-tokens", type=int, default=2048, help="token budget of one step")
+    ap.add_argument("--probe-layer", type=int, default=None, metavar="I",
+                    help="print rms, sum and first values of the stages of schedule entry I (for comparing engines; slow)")
     ap.add_argument("--json", action="store_true", help="print one JSON line with tokens and timings")
     ap.add_argument("tokens", nargs="*", type=int, help="prompt token ids")
     return ap
@@ -67,7 +69,7 @@ def main(argv=None) -> int:
     parallel = args.parallel or max(1, len(prompts) if prompts else args.batch)
     t0 = time.perf_counter()
     engine = Engine(args.model, config=config, seed=args.seed, dtype=args.dtype, ctx=args.ctx, parallel=parallel,
-                    page_size=args.page_size, num_pages=args.num_pages, max_step_tokens=args.max_step_tokens)
+                    page_size=args.page_size, num_pages=args.num_pages, max_step_tokens=args.max_step_tokens, probe_layer=args.probe_layer)
     load_s = time.perf_counter() - t0
     if not prompts:
         if not args.prompt_len:

@@ -10,6 +10,9 @@ once), the request fields max_tokens and temperature (imparo-server/src/main.rs:
 """
 from __future__ import annotations
 
+import os
+import sys
+
 import time
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -34,12 +37,18 @@ class Engine:
     def __init__(self, model: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
                  dtype: str = "bfloat16", device: Union[str, torch.device] = "cuda:0", ctx: int = 4096,
                  parallel: int = 8, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_step_tokens: int = 2048, random_init: Optional[dict] = None):
+                 max_step_tokens: int = 2048, random_init: Optional[dict] = None,
+                 probe_layer: Optional[int] = None, probe=None):
         """model: a folder with config.json and model.safetensors.  Or config (a config.json
         dictionary) with seed: random weights drawn on the device (random_init may give
         matrix_std, conv_std, norm_jitter).  ctx: the most positions one request may reach.
         parallel: the most requests live at once.  num_pages: pages in each pool (default:
-        enough for parallel requests of ctx positions)."""
+        enough for parallel requests of ctx positions).
+        probe_layer (or IMPARO_PROBE_LAYER in the environment): a schedule entry whose block shows its
+        stages (stream in, mixer norm, stream after the mixer, feed-forward norm, stream out) to
+        probe(name, tensor); the default probe prints rms, sum and the first five values of each to
+        stderr, as the reference's stage probes do (imparo-model/src/cpu_support.rs:26-46).  Probing
+        evaluates every stage on its own and switches graph replay off: for comparing engines, not for timing."""
         if dtype not in _PRECISIONS:
             raise ValueError(f"dtype must be one of {sorted(_PRECISIONS)}")
         self.precision = _PRECISIONS[dtype]
@@ -73,9 +82,23 @@ class Engine:
                                   kv_dtype=self.rt.act_dtype, device=self.device)
         self.max_step_tokens = int(max_step_tokens)
         self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel)
+        if probe_layer is None and os.environ.get("IMPARO_PROBE_LAYER", "") != "":
+            probe_layer = int(os.environ["IMPARO_PROBE_LAYER"])
+        if probe_layer is not None:
+            if not 0 <= int(probe_layer) < len(self.model.schedule):
+                raise ValueError(f"probe_layer {probe_layer} is not one of the model's {len(self.model.schedule)} schedule entries")
+            self.rt.probe_entry = int(probe_layer)
+            self.rt.probe = probe if probe is not None else self._print_probe
+            self.step_fn.use_graphs = False
         self.sampler = Sampler(self.device, max_rows=max(self.parallel, 8))
         self.vocab_size = self.model.spec.vocab_size
         self._stats = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0, "preemptions": 0, "seconds": 0.0}
+
+    def _print_probe(self, name: str, t: torch.Tensor) -> None:
+        v = t.detach().float()
+        head = ", ".join(f"{x:.6g}" for x in v.reshape(-1)[:5].tolist())
+        print(f"probe entry {self.rt.probe_entry} {name} {tuple(t.shape)}: rms {float(v.pow(2).mean().sqrt()):.6g} "
+              f"sum {float(v.sum()):.6g} first [{head}]", file=sys.stderr, flush=True)
 
     # -- the step function, for callers that schedule themselves ---------------------------
     def add_request(self, request: int) -> None:

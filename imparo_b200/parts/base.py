@@ -37,6 +37,12 @@ class Runtime:
     device: torch.device
     status: Optional[torch.Tensor] = None       # int32[4] device word kernels report bad indices into
     workspace: "Workspace" = None
+    # Stage probe (the reference's IMPARO_PROBE_LAYER / IMPARO_GPU_PROBE, imparo-model/src/cpu_support.rs:26-46,
+    # gpu_support.rs:202): when probe_entry names a schedule entry, that entry's block hands named
+    # intermediates (whole tensors) to probe(name, tensor), so that two engines can be compared stage by stage.
+    probe_entry: Optional[int] = None
+    probe: Optional[object] = None
+    probe_now: bool = False                     # set by the model while the probed entry runs
 
     @property
     def act_dtype(self) -> torch.dtype:

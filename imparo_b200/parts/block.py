@@ -41,6 +41,8 @@ class PreNormResidualBlock(Part):
         runs on every row (its cache and state advance); the feed-forward runs on the picked rows,
         and their stream [n, width] is returned instead (None when n is 0)."""
         from ..kernels import ops
+        if self.rt.probe_now:
+            return self._forward_probed(x, batch, caches, ready, only_rows)
         h = ready if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
             self._normed(self.mixer_norm, self.mixer, x, "normed_mixer")
         ff_in = None
@@ -72,6 +74,35 @@ class PreNormResidualBlock(Part):
         if nxt is not None:
             ops.disarm_norm(x)
         return nxt
+
+    def _forward_probed(self, x, batch, caches, ready, only_rows):
+        """The same block with every stage evaluated and shown to the runtime's probe: the stream
+        going in, the mixer's normed input, the stream after the mixer, the feed-forward's normed
+        input, the stream going out.  Nothing is deferred or fused here."""
+        from ..kernels import ops
+        probe = self.rt.probe
+        ops.settle(x)
+        probe("stream_in", x)
+        h = ops.as_tensor(ready) if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
+            self.mixer_norm.forward(x, tag="normed_mixer")
+        probe("mixer_norm", h)
+        ops.settle(x)
+        self.mixer.forward(h, batch, caches, x)
+        ops.settle(x)
+        probe("stream_mixer", x)
+        if only_rows is not None:
+            rows, n = only_rows
+            if n == 0:
+                return None
+            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype)
+            ops.gather_rows(x, rows, xs)
+            x = xs
+        ff_in = self.ff_norm.forward(x, tag="normed_ff")
+        probe("ff_norm", ff_in)
+        self.ff.forward(ff_in, batch, x)
+        ops.settle(x)
+        probe("stream_out", x)
+        return x if only_rows is not None else None
 
     @staticmethod
     def _run(part, x, call) -> None:

@@ -209,16 +209,26 @@ def swiglu(n, w):
     return (silu(n @ w["w1"].T) * (n @ w["w3"].T)) @ w["w2"].T
 
 
-def block(x, lw, cfg, positions):
+def block(x, lw, cfg, positions, probe=None):
     """imparo-model/src/lfm2/workflow_cpu.rs:172-319 — pre-norms only:
-    x += mixer(rms(x, operator_norm)); x += ffn(rms(x, ffn_norm))."""
+    x += mixer(rms(x, operator_norm)); x += ffn(rms(x, ffn_norm)).
+    probe(name, array): shown the stages the reference's probe names
+    (imparo-model/src/cpu_support.rs:26-46), for comparing with another engine."""
+    show = probe if probe is not None else (lambda name, a: None)
+    show("stream_in", x)
     cur = rms_norm(x, lw["operator_norm"], cfg.eps)
+    show("mixer_norm", cur)
     if lw["kind"] == "conv":
         mix = conv_mixer(cur, lw, cfg)
     else:
         mix = attention_mixer(cur, lw, cfg, positions)
     x = x + mix
-    return x + swiglu(rms_norm(x, lw["ffn_norm"], cfg.eps), lw)
+    show("stream_mixer", x)
+    h = rms_norm(x, lw["ffn_norm"], cfg.eps)
+    show("ff_norm", h)
+    x = x + swiglu(h, lw)
+    show("stream_out", x)
+    return x
 
 
 # ----------------------------------------------------------------------------
@@ -266,14 +276,14 @@ class PlainLfm2:
                     lw["window"] = int(cfg.window)
             self.layers.append(lw)
 
-    def hidden_states(self, tokens):
+    def hidden_states(self, tokens, probe_layer=None, probe=None):
         """imparo-model/src/cpu_support.rs:327-342 (rows of the table, no scale), then
-        every block in order."""
+        every block in order.  probe_layer / probe: see block()."""
         tokens = np.asarray(tokens, dtype=np.int64)
         positions = np.arange(len(tokens))
         x = self.embed[tokens].astype(self.dtype)
-        for lw in self.layers:
-            x = block(x, lw, self.cfg, positions)
+        for i, lw in enumerate(self.layers):
+            x = block(x, lw, self.cfg, positions, probe if i == probe_layer else None)
         return x
 
     def logits(self, tokens):

@@ -9,7 +9,7 @@ import sys
 import numpy as np
 import pytest
 
-from tests.gpu_helpers import make_requests, model_dir, plain_model
+from tests.gpu_helpers import TOL, make_requests, model_dir, plain_model
 from tests.plain import lfm2_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -125,3 +125,32 @@ def test_many_requests_few_pages_every_request_gets_its_own_tokens():
     assert eng.stats()["failed"] == []
     assert eng.cache.free_pages(0) == 70 and eng.cache.free_slots() == 5 and eng.cache.n_requests() == 0
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [0, 1, 5])
+def test_stage_probe_against_the_plain_implementation(dtype, layer):
+    """Engine(probe_layer=i) shows the stages of one block; the plain implementation shows the same
+    stages by the same names: a whole prompt, stage by stage."""
+    from imparo_b200.engine import Engine, StepItem
+    name = "B"
+    toks = np.random.default_rng(11).integers(0, 512, 37).tolist()
+    seen = {}
+    eng = Engine(model_dir(name), dtype=dtype, ctx=128, parallel=1, page_size=4, probe_layer=layer,
+                 probe=lambda n, t: seen.__setitem__(n, t.detach().float().cpu().numpy().copy()))
+    eng.add_request(1)
+    got_logits = eng.step([StepItem(1, toks, [len(toks) - 1])]).cpu().numpy()
+    eng.end_request(1)
+    ref = {}
+    plain = plain_model(name)
+    plain.hidden_states(toks, probe_layer=layer, probe=lambda n, a: ref.__setitem__(n, np.asarray(a, dtype=np.float64)))
+    assert list(seen) == ["stream_in", "mixer_norm", "stream_mixer", "ff_norm", "stream_out"] == list(ref)
+    tol = TOL[dtype]
+    for n in ref:
+        a, b = seen[n], ref[n]
+        if a.shape[0] != b.shape[0]:                 # the model's last block shows the wanted rows only from its feed-forward on
+            b = b[-a.shape[0]:]
+        assert a.shape == b.shape, n
+        assert np.abs(a - b).max() <= 4 * tol * max(1.0, np.abs(b).max()), n
+    want = plain.logits(toks)[-1]
+    assert np.abs(got_logits[0] - want).max() <= tol * np.abs(want).max()
