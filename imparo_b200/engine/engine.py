@@ -155,6 +155,8 @@ class Engine:
             index[rid] = i
         failed: List[int] = []
         t0 = time.perf_counter()
+        log = os.environ.get("IMPARO_LOG", "") not in ("", "0")
+        t_log = t0
         gen = {rid: 0 for rid in tokens}        # tokens sampled so far per request (values may still be on the device)
         dead = set()                            # ended by a stop token
         zombies = set()                         # ended, but still part of the step in flight: aborted after it
@@ -229,11 +231,26 @@ class Engine:
                     sched.on_token(e.request, False)          # optimistic: a stop token is booked when it is read
                 carry = (all_wanting, pending)
             self._stats["steps"] += 1
-            self._stats["prompt_tokens"] += sum(e.count for e in plan if e.count > 1 or e.start == 0)
+            n_prompt = sum(e.count for e in plan if e.count > 1 or e.start == 0)
+            self._stats["prompt_tokens"] += n_prompt
             self._stats["decode_tokens"] += len(wanting)
+            if log:
+                # one line per step, as the reference's IMPARO_LOG does for its forward calls
+                # (imparo-model/src/lib.rs:938-946); host time since the previous step was issued,
+                # not GPU time: steps are issued ahead of the device
+                now = time.perf_counter()
+                print(f"imparo step {self._stats['steps']} rows={len(plan)} prompt_tokens={n_prompt} "
+                      f"decode_tokens={len(wanting)} free_pages={[self.cache.free_pages(g) for g in range(self.cache.n_groups)]} "
+                      f"free_slots={self.cache.free_slots()} host_ms={1e3 * (now - t_log):.3f}", file=sys.stderr, flush=True)
+                t_log = now
             if on_step is not None:
                 on_step(plan)
         ops.read_status(self.status)
+        if log:
+            dt = time.perf_counter() - t0
+            n_new = sum(gen.values())
+            print(f"imparo generate: {len(prompts)} requests, {n_new} new tokens in {dt:.3f} s ({n_new / max(dt, 1e-9):.1f} tok/s), "
+                  f"{self._stats['preemptions'] + sched.n_preemptions} preemptions so far", file=sys.stderr, flush=True)
         self._stats["seconds"] += time.perf_counter() - t0
         self._stats["preemptions"] += sched.n_preemptions
         self._stats["failed"] = failed

@@ -154,3 +154,16 @@ def test_stage_probe_against_the_plain_implementation(dtype, layer):
         assert np.abs(a - b).max() <= 4 * tol * max(1.0, np.abs(b).max()), n
     want = plain.logits(toks)[-1]
     assert np.abs(got_logits[0] - want).max() <= tol * np.abs(want).max()
+
+
+def test_log_lines_per_step(capfd, monkeypatch):
+    """IMPARO_LOG=1: one line per step on stderr and a summary at the end."""
+    from imparo_b200.engine import Engine
+    monkeypatch.setenv("IMPARO_LOG", "1")
+    eng = Engine(model_dir("A"), dtype="bfloat16", ctx=128, parallel=2, page_size=16, max_step_tokens=16)
+    out = eng.generate([[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20], [5, 6, 7]], max_tokens=4)
+    err = capfd.readouterr().err
+    lines = [l for l in err.splitlines() if l.startswith("imparo step ")]
+    assert len(lines) == eng.stats()["steps"] and all("prompt_tokens=" in l and "free_pages=" in l for l in lines)
+    assert "imparo generate: 2 requests, 8 new tokens" in err
+    assert [len(o) for o in out] == [4, 4]
