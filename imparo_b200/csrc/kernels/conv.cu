@@ -8,11 +8,12 @@
 //   shorter than taps-1).  A bias, which the reference does not have, is added to sum
 //   before the gate.
 //
-// One launch does output and state.  A thread owns (token, channel).  Tokens at least
-// taps-1 into their portion need only bcx.  The thread of a portion's FIRST token also
-// computes the outputs of the next taps-2 tokens and then writes the new state; it reads
-// the whole old state into registers first, and no other thread touches that state, so
-// the update in place is race-free.
+// One launch does output and state.  A thread owns (token, channel) — or, for prompt portions in
+// bfloat16, (token, eight channels).  Tokens at least taps-1 into their portion need only bcx.
+// The thread of a portion's FIRST token also computes the outputs of the next taps-2 tokens and
+// then writes the new state; it reads the whole old state into registers first, and no other
+// thread touches that state, so the update in place is race-free.  The input may also be the
+// split partials of the product before (summed here), see ConvIn.
 #include "common.cuh"
 
 namespace imparo {

@@ -231,12 +231,11 @@ TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that us
 
 
 # Above this many tokens the library product is faster than the hand-written kernel as it
-# stands (one token tile per CTA, no overlap of epilogue and main loop, cluster fold on the
-# small products).  Measured on B200 inside a CUDA graph, LFM2-1.2B shapes, us (own / cuBLAS):
-#   T=8   gate+up 14.3 / 14.1+act, down 11.6 / 19.8, in_proj 9.0 / 6.5, out_proj 6.4 / 6.8, qkv 6.6 / 7.2
-#   T=16  gate+up 15.7 / 14.2+act, down 12.5 / 12.6, in_proj 11.0 / 7.1, out_proj 7.1 / 5.2, qkv 7.1 / 5.4
-#   T=64  gate+up 20.9 / 15.6+act, down 19.4 / 12.9, in_proj 17.3 / 6.8
-#   T=2048 down 66 / 50, gate+up 275 / 160 (the epilogue dominates a 32-k-block main loop)
+# stands (one token tile per CTA, no overlap of epilogue and main loop).  Measured on B200, whole
+# decode steps of LFM2-1.2B shapes in their CUDA graph, ms per step (own kernel / library product):
+# batch 32: 1.058 / 1.107; batch 64: 1.381 / 1.421 (the own kernels stay in the chain of
+# programmatic dependent launches and prefetch their weights; a library product breaks it).  At
+# 2,048 tokens the library is ahead: down 66 / 50 us, gate+up 275 / 160 us per product.
 TC_MAX_TOKENS = 64
 
 
