@@ -21,6 +21,12 @@ constexpr int ROWS = 64;          // query rows per CTA
 constexpr int KEYS = 64;          // keys per step
 constexpr int THREADS = 128;      // 4 warps x 16 rows
 
+// 2^x by the hardware's approximation (2 ulp; inputs at or below -126 give 0, -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -285,8 +291,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     // shared memory: two buffers of 64 keys and 64 values (32 KB at head size 64, so that four
     // CTAs fit beside a resident product CTA); after the key loop the same bytes hold the warps'
     // partial results for the fold
-    uint8_t* k_s[2] = {pf_smem, pf_smem + KEYS * HD * 2};
-    uint8_t* v_s[2] = {k_s[1] + KEYS * HD * 2, k_s[1] + 2 * KEYS * HD * 2};
+    constexpr int TILE_BYTES = KEYS * HD * 2;
+    auto k_s = [&](int buf) { return pf_smem + buf * TILE_BYTES; };          // computed, not an indexed array:
+    auto v_s = [&](int buf) { return pf_smem + (2 + buf) * TILE_BYTES; };    // that would live in local memory
     float* wm = reinterpret_cast<float*>(pf_smem);                     // [4][8]
     float* wl = wm + 32;                                               // [4][8]
     float* wacc = wl + 32;                                             // [4][8][HD]
@@ -307,11 +314,13 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int* tab = table + (size_t)item_of_token[t] * max_blocks;
     const size_t kvw = (size_t)nkv * HD;
     const int kb_first = begin / KEYS, kb_last = (end - 1) / KEYS;
-    // a thread fetches half a row of the tile (two threads per key): one page lookup, then CH / 2
-    // 16-byte pieces each of the key and of the value
+    // A thread fetches half a row of the tile (two threads per key): one page lookup, then CH / 2
+    // 16-byte pieces each of the key and of the value.  The two threads of a key take alternate
+    // pieces, so that one instruction of the pair covers whole 32-byte sectors.  Warp w fetches keys
+    // 16 w .. 16 w + 15 of the tile, the very keys it scores: the key loop needs no CTA-wide barrier.
     auto load_kv = [&](int kb, int buf) {
         static_assert(THREADS == 2 * KEYS, "two threads per key of a tile");
-        const int r = tid >> 1, c0 = (tid & 1) * (CH / 2);
+        const int r = tid >> 1, c0 = tid & 1;
         const int j = kb * KEYS + r;
         bool valid = j >= begin && j < end;
         size_t rowi = 0;
@@ -328,10 +337,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             }
         }
         const size_t off = rowi * kvw + (size_t)kvh * HD + c0 * 8;
+        uint8_t* const kd = k_s(buf);
+        uint8_t* const vd = v_s(buf);
 #pragma unroll
         for (int c = 0; c < CH / 2; ++c) {
-            cp_async16(k_s[buf] + tile_off<HD>(r, c0 + c), k_cache + off + c * 8, valid);
-            cp_async16(v_s[buf] + tile_off<HD>(r, c0 + c), v_cache + off + c * 8, valid);
+            cp_async16(kd + tile_off<HD>(r, c0 + 2 * c), k_cache + off + c * 16, valid);
+            cp_async16(vd + tile_off<HD>(r, c0 + 2 * c), v_cache + off + c * 16, valid);
         }
         cp_commit();
     };
@@ -387,8 +398,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         } else {
             cp_wait<0>();
         }
-        __syncthreads();
+        __syncwarp();                                          // the warp's own 16 keys have landed
         const int mi = lane >> 3, rin = lane & 7;
+        const uint8_t* const kt_s = k_s(buf);
+        const uint8_t* const vt_s = v_s(buf);
         // this warp's 16 keys of the tile
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
@@ -397,35 +410,45 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
             for (int kt = 0; kt < KT; ++kt) {
                 uint32_t b[4];
-                ldmatrix4(b, smem_addr(k_s[buf] + tile_off<HD>(key, kt * 2 + (mi & 1))));
+                ldmatrix4(b, smem_addr(kt_s + tile_off<HD>(key, kt * 2 + (mi & 1))));
                 mma16816(s[0], qf[kt], b[0], b[1]);
                 mma16816(s[1], qf[kt], b[2], b[3]);
             }
         }
         const int key0 = kb * KEYS + warp * 16 + 2 * tg;
+        const int wk0 = kb * KEYS + warp * 16;
         float mx = -INFINITY;
+        if (wk0 >= begin && wk0 + 16 <= end) {                  // all 16 keys are live: no masks
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = key0 + n * 8 + e;
-                s[n][e] = (j >= begin && j < end) ? s[n][e] * sl2 : -INFINITY;
-                mx = fmaxf(mx, s[n][e]);
-            }
+                for (int e = 0; e < 2; ++e) { s[n][e] *= sl2; mx = fmaxf(mx, s[n][e]); }
+        } else {
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = key0 + n * 8 + e;
+                    s[n][e] = (j >= begin && j < end) ? s[n][e] * sl2 : -INFINITY;
+                    mx = fmaxf(mx, s[n][e]);
+                }
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float mn = fmaxf(m_run, mx);
-        const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - mn);
+        const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mn);
         const float base = (mn == -INFINITY) ? 0.f : mn;
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) { s[n][e] = exp2f(s[n][e] - base); sum += s[n][e]; }
+            for (int e = 0; e < 2; ++e) { s[n][e] = fast_exp2(s[n][e] - base); sum += s[n][e]; }
         l_run = l_run * corr + sum;
         m_run = mn;
+        if (__any_sync(0xffffffffu, corr != 1.f)) {             // the running max moved in some row
 #pragma unroll
-        for (int n = 0; n < NT_O; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+            for (int n = 0; n < NT_O; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+        }
         {
             uint32_t a[4];
             a[0] = pack_bf16(s[0][0], s[0][1]);
@@ -436,7 +459,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
             for (int np = 0; np < NT_O / 2; ++np) {
                 uint32_t b[4];
-                ldmatrix4_trans(b, smem_addr(v_s[buf] + tile_off<HD>(key, np * 2 + (mi >> 1))));
+                ldmatrix4_trans(b, smem_addr(vt_s + tile_off<HD>(key, np * 2 + (mi >> 1))));
                 float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f};
                 float c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
                 mma16816(c0, a, b[0], b[1]);
@@ -445,8 +468,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
             }
         }
-        __syncthreads();
+        __syncwarp();                                          // the warp refills this buffer two steps on
     }
+    __syncthreads();                                           // the tiles' bytes become the fold's scratch
     if (tid == 0) timeline_mark(1);                                     // the key loop is done
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
