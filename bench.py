@@ -184,11 +184,12 @@ def measure_e2e(engine, batch, steps, warmup, rng):
     def on_step(plan):
         if all(e.count == 1 for e in plan) and len(plan) == batch:
             stamps.append(time.perf_counter())
+            h2d.append(engine.step_fn.last_h2d_bytes)       # this step's batch description, as uploaded
     n_new = warmup + steps + 2 + 2 * batch      # requests start decoding up to ~batch steps apart
     out = engine.generate(prompts, max_tokens=n_new, on_step=on_step, stop_token_ids=[])
     assert all(len(o) == n_new for o in out) and len(stamps) > warmup + steps, (len(stamps), warmup + steps)
     dt = stamps[warmup + steps] - stamps[warmup]
-    return batch * steps / dt, engine.step_fn.last_h2d_bytes
+    return batch * steps / dt, max(h2d[warmup:warmup + steps + 1])
 
 
 def main():
