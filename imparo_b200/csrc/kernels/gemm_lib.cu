@@ -21,6 +21,8 @@ namespace {
 cublasHandle_t g_handle = nullptr;
 void* g_workspace = nullptr;
 size_t g_workspace_bytes = 0;
+bool g_bound = false;                 // g_handle is set to g_bound_stream and the workspace
+cudaStream_t g_bound_stream = nullptr;
 }
 
 // workspace: device memory the caller owns for as long as products run (stable address,
@@ -32,6 +34,7 @@ extern "C" int imparo_gemm_lib_init(void* workspace, size_t workspace_bytes) {
     }
     g_workspace = workspace;
     g_workspace_bytes = workspace_bytes;
+    g_bound = false;
     return 0;
 }
 
@@ -41,11 +44,18 @@ extern "C" int imparo_gemm_bf16_nt(const void* A, const void* W, void* C, int c_
     if (M <= 0 || N <= 0) return 0;
     if (!g_handle) return -1;
     if (accumulate && c_dtype != IMPARO_DT_F32) return -2;
-    cublasStatus_t s = cublasSetStream(g_handle, stream);
-    if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
-    if (g_workspace) {
-        s = cublasSetWorkspace(g_handle, g_workspace, g_workspace_bytes);
+    cublasStatus_t s;
+    if (!g_bound || g_bound_stream != stream) {
+        // setting the stream resets the library's workspace to its own, so both are set together,
+        // and only when the stream changes (a step issues dozens of products on one stream)
+        s = cublasSetStream(g_handle, stream);
         if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+        if (g_workspace) {
+            s = cublasSetWorkspace(g_handle, g_workspace, g_workspace_bytes);
+            if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+        }
+        g_bound = true;
+        g_bound_stream = stream;
     }
     const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
     // column-major view: C^T[N,M] = W[N,K] * A^T[K,M]

@@ -136,7 +136,7 @@ class StepFunction:
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
         b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),
-                  "key": (T, R, W, tuple(strides)), "h2d_bytes": n_ints * 4}
+                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item), "h2d_bytes": n_ints * 4}
         return b
 
     # -- decode-only steps replay a captured graph ------------------------------------------
@@ -147,11 +147,14 @@ class StepFunction:
         return self.model.logits(x, None if picked else batch.want_rows, batch.n_want)
 
     def _forward_graphed(self, batch: StepBatch) -> Optional[torch.Tensor]:
-        """A step of single tokens only has the same launches whenever (requests, wanted
-        rows, table widths) repeat: the second time such a step comes it is captured, from
-        then on replayed.  The reference captures its one-token step the same way
-        (imparo-cuda/native/imparo_cuda.cu:7509-7660).  Index data (tokens, positions,
-        tables, wanted rows) is read from the descriptor buffer, whose address is fixed."""
+        """A step has the same launches whenever (tokens, requests, wanted rows, table widths,
+        the longest portion) repeat; which request brings how many tokens, every position, table
+        and wanted row is index data that the kernels read from the descriptor buffer, whose
+        address is fixed.  The second time such a step comes it is captured, from then on
+        replayed: steps of single tokens (the reference captures its one-token step the same way,
+        imparo-cuda/native/imparo_cuda.cu:7509-7660) and also portions of prompts beside them,
+        which a scheduler with a fixed token budget produces again and again.  Issued launch by
+        launch from Python a step of the full-size model costs the host about 2.5 ms."""
         ws = self.rt.workspace
         generation = (ws.generation, ops.TC_GENERATION)
         key = batch.host["key"]
@@ -237,7 +240,7 @@ class StepFunction:
                 idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)
                 for t in cache.state.values():
                     t.index_fill_(0, idx, 0.0)
-            if self.use_graphs and batch.decode_only and not fresh:
+            if self.use_graphs:
                 logits = self._forward_graphed(batch)
             else:
                 logits = self._forward(batch)

@@ -71,7 +71,9 @@ def _digest(paths, flags) -> str:
         h.update(os.path.basename(p).encode())
         with open(p, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(flags).encode())
+    # the checkout's own path (it is in the include flags) is no part of what was compiled:
+    # a tree that was built and then copied elsewhere stays built
+    h.update(" ".join(flags).replace(_PKG, "<package>").encode())
     return h.hexdigest()
 
 

@@ -7,6 +7,7 @@ cobatch_rows.cuh:37-61).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -44,8 +45,29 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current stream's handle.  A step issues well over a hundred launches from Python, so the
+    handle is asked of the runtime directly, not through a Stream object built per call."""
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+_environ_bytes = getattr(os.environ, "_data", None)      # the mapping behind os.environ (bytes keys on POSIX)
+if not isinstance(_environ_bytes, dict) or (_environ_bytes and not isinstance(next(iter(_environ_bytes)), bytes)):
+    _environ_bytes = None
+
+
+def _env(name: str, default: str = "") -> str:
+    """os.environ.get for the switches read on every launch, without its per-call encoding."""
+    if _environ_bytes is not None:
+        v = _environ_bytes.get(name.encode())
+        return default if v is None else v.decode()
+    return os.environ.get(name, default)
 
 
 # Launch counts since import: "own" = this engine's CUDA kernels, "library" = cuBLAS products.
@@ -107,8 +129,7 @@ _partials = {}           # device index -> scratch tensor
 
 
 def defer_adds() -> bool:
-    import os
-    return os.environ.get("IMPARO_DEFER_ADDS", "1") == "1"
+    return _env("IMPARO_DEFER_ADDS", "1") == "1"
 
 
 def allow_deferred_add(stream: torch.Tensor) -> None:
@@ -175,7 +196,7 @@ _gemm_ws = {}
 
 
 def _gemm_lib_ready(device) -> None:
-    key = torch.device(device).index or 0
+    key = device.index or 0
     if key not in _gemm_ws:
         ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
         _check(_lib.kernels().imparo_gemm_lib_init(_ptr(ws), ws.numel()), "gemm_lib_init")
@@ -191,8 +212,7 @@ _status_fallback = {}
 
 def gemm_backend() -> str:
     """"tcgen05" (default) or "library" (cuBLAS), chosen by IMPARO_GEMM."""
-    import os
-    v = os.environ.get("IMPARO_GEMM", "tcgen05").lower()
+    v = _env("IMPARO_GEMM", "tcgen05").lower()
     return "library" if v in ("library", "lib", "cublas") else "tcgen05"
 
 
@@ -240,8 +260,7 @@ TC_MAX_TOKENS = 64
 
 
 def tc_max_tokens() -> int:
-    import os
-    v = os.environ.get("IMPARO_TC_MAX_TOKENS")
+    v = _env("IMPARO_TC_MAX_TOKENS")
     return int(v) if v else TC_MAX_TOKENS
 
 
@@ -263,9 +282,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     T, K = x.shape
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     _need(w.shape[1] == K and (epilogue != EPI_SWIGLU or w.shape[0] % 2 == 0), "gemm_tc: weight shape")
-    _need(out.shape == (T, N) and out.stride(1) == 1, f"gemm_tc: out must be [{T}, {N}]")
+    if not (out.shape == (T, N) and out.stride(1) == 1):
+        raise KernelError(f"gemm_tc: out must be [{T}, {N}]")
     want_dtype = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32
-    _need(epilogue == EPI_PARTIAL or out.dtype == want_dtype, f"gemm_tc: this epilogue writes {want_dtype}")
+    if not (epilogue == EPI_PARTIAL or out.dtype == want_dtype):
+        raise KernelError(f"gemm_tc: this epilogue writes {want_dtype}")
     nt, splits, floats, counters = _tc_plan(T, N, K, epilogue)
     if epilogue == EPI_PARTIAL:
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= floats, "gemm_tc: partials scratch")
@@ -324,8 +345,7 @@ def fuse_add_norm() -> bool:
     1.04 ms without.  The product's last CTA has to wait for every other CTA's writes (fence,
     counter) and then norms all rows alone, which is a longer serial tail than the separate norm
     kernel, whose launch the programmatic dependent launch already overlaps."""
-    import os
-    return os.environ.get("IMPARO_FUSE_ADD_NORM", "0") == "1"
+    return _env("IMPARO_FUSE_ADD_NORM", "0") == "1"
 
 
 def arm_norm(stream: torch.Tensor, normed: "NormedInput") -> None:
@@ -355,8 +375,7 @@ def fuse_norm() -> bool:
     measured on B200 the fused form is slower in the decode step (1.11 ms against 1.05 ms at
     batch 8): every CTA redoes the norm of all token rows, and the separate norm kernel already
     runs while the product prefetches its weights."""
-    import os
-    return os.environ.get("IMPARO_FUSE_NORM", "0") == "1"
+    return _env("IMPARO_FUSE_NORM", "0") == "1"
 
 
 def _try_fused_norm(x: "NormedInput", w: torch.Tensor, out: torch.Tensor, epilogue: int, status) -> bool:
@@ -431,7 +450,8 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     M, K = x.shape
     N = w.shape[0]
-    _need(w.shape[1] == K and out.shape == (M, N), f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if not (w.shape[1] == K and out.shape == (M, N)):
+        raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     _need(x.stride(1) == 1 and out.is_contiguous() and w.is_contiguous(), "linear: rows must be dense")
     _need(x.dtype == w.dtype, "linear: x and w must share a dtype")
     if x.dtype == torch.float32:

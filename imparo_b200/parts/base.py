@@ -68,7 +68,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        key = f"{tag}:{dtype}"
+        key = (tag, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
             if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():

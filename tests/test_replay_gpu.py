@@ -98,6 +98,36 @@ def test_state_slots_and_pages_start_clean_when_used_again():
     check_trace(eng, steps, name, reqs, "float32")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "E"])
+def test_a_captured_step_shape_serves_other_layouts(name, dtype):
+    """Steps with the same totals (tokens, requests, wanted rows, longest portion) are captured
+    once and replayed; which request brings how many tokens changes from step to step, and new
+    requests start inside replayed steps."""
+    lengths = {"a": 52, "b": 52, "c": 52, "d": 16, "e": 16}
+    reqs = {k: v for k, v in zip(lengths, make_requests(name, list(lengths.values()), seed=31).values())}
+    cuts = [{"a": 20, "b": 20, "c": 20},
+            {"a": 1, "b": 5, "c": 10}, {"a": 1, "b": 10, "c": 5}, {"a": 10, "b": 1, "c": 5}, {"a": 5, "b": 10, "c": 1},
+            {"a": 10, "b": 5, "c": 1}, {"a": 5, "b": 1, "c": 10},
+            {"d": 16}, {"e": 16}]                                  # whole new requests, the same shape twice
+    at = {k: 0 for k in reqs}
+    steps = []
+    for cut in cuts:
+        entries = []
+        for k, n in cut.items():
+            entries.append({"id": k, "tokens": reqs[k][at[k]:at[k] + n], "want": [0, n - 1] if n > 1 else [0]})
+            at[k] += n
+        steps.append({"step": len(steps), "entries": entries, "end": [k for k in cut if at[k] == len(reqs[k])]})
+    assert all(at[k] == len(reqs[k]) for k in reqs)
+    # requests d and e: one step each, of one shape; the second is the capture, so add a third
+    extra = make_requests(name, [16], seed=32)["r0"]
+    reqs["f"] = extra
+    steps.append({"step": len(steps), "entries": [{"id": "f", "tokens": extra, "want": [0, 15]}], "end": ["f"]})
+    eng = engine_for(name, dtype, steps)
+    check_trace(eng, steps, name, reqs, dtype)
+    assert eng.step_fn.graph_replays >= 6
+
+
 def test_full_width_layers_bfloat16_against_32_bit():
     """Four layers of LFM2-1.2B width (hidden 2048, 32 heads in 8 groups, head 64, ff 8192,
     vocabulary 65536): the sizes the tensor-core kernels are tuned for, which the tiny models
