@@ -18,7 +18,9 @@ CASES = [(5, 3, 7, 11), (6, 4, 2, 12), (4, 2, 1, 13), (3, 4, 1, 14), (8, 3, 16, 
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_conv_golden.py /path/to/imparo (a checkout of zeraix/imparo)")
+    ref = sys.argv[1]
     inc = os.path.join(ref, "crates", "imparo-cuda", "native")
     with tempfile.TemporaryDirectory() as d:
         exe = os.path.join(d, "conv_harness")
