@@ -192,6 +192,107 @@ def measure_e2e(engine, batch, steps, warmup, rng):
     return batch * steps / dt, max(h2d[warmup:warmup + steps + 1])
 
 
+def _preset(name):
+    with open(os.path.join(ROOT, "imparo_b200", "config", "presets", name + ".json")) as f:
+        return json.load(f)
+
+
+def workload_continuous(args):
+    """LFM2-700M sizes: requests with prompt lengths uniform in [64, 4096] through 32 slots, prompts
+    in portions under a 512-token step budget beside the running decode rows, temperature 0.7
+    (seeded), 128 new tokens each; with more requests than slots, slots and pages are used again."""
+    import numpy as np
+    from imparo_b200.engine import Engine
+    from imparo_b200.kernels import ops
+    rng = np.random.default_rng(1)
+    n, slots, new = args.requests, 32, 128
+    engine = Engine(config=_preset("lfm2_700m"), seed=0, dtype="bfloat16", ctx=4096 + new, parallel=slots, page_size=PAGE,
+                    max_step_tokens=512, random_init={"norm_jitter": 0.0})
+    V = engine.vocab_size
+    lens = [int(x) for x in rng.integers(64, 4097, n)]
+    prompts = [rng.integers(0, V, k).tolist() for k in lens]
+    engine.generate(prompts[:4], max_tokens=8, temperature=0.7, seed=list(range(4)))       # warm-up: buffers, first graphs
+    shapes = {"steps": 0, "mixed": 0, "rows": 0}
+
+    def on_step(plan):
+        shapes["steps"] += 1
+        shapes["mixed"] += any(e.count > 1 for e in plan) and any(e.count == 1 for e in plan)
+        shapes["rows"] += len(plan)
+    before, replays = dict(ops.COUNTS), engine.step_fn.graph_replays
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        out = engine.generate(prompts, max_tokens=new, temperature=0.7, seed=list(range(n)), on_step=on_step, stop_token_ids=[])
+        dt = time.perf_counter() - t0
+    assert all(len(o) == new for o in out)
+    st = engine.stats()
+    print(json.dumps({
+        "metric": "LFM2-700M continuous batching, prompt + generated tokens per second (wall clock, through Engine.generate)",
+        "value": round((sum(lens) + n * new) / dt, 1), "unit": "tokens/s", "generated_per_s": round(n * new / dt, 1),
+        "seconds": round(dt, 3), "requests": n, "slots": slots, "prompt_tokens": sum(lens), "new_tokens": n * new,
+        "step_budget": 512, "steps": shapes["steps"], "steps_with_portions_beside_decode_rows": shapes["mixed"],
+        "mean_rows_per_step": round(shapes["rows"] / max(shapes["steps"], 1), 1),
+        "graph_replays": engine.step_fn.graph_replays - replays, "graph_captures": engine.step_fn.graph_captures,
+        "graph_resets": engine.step_fn.graph_resets, "preemptions": st["preemptions"], "failed": st["failed"],
+        "own_kernel_launches": ops.COUNTS["own"] - before["own"], "library_gemms": ops.COUNTS["library"] - before["library"],
+        "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "clocks": clocks.summary()}))
+    return 0
+
+
+def workload_long(args):
+    """LFM2-350M sizes: 4 requests with 32,768-token prompts and 512 greedy tokens each, in bfloat16
+    and in 32-bit; in 32-bit also the logits at the prompt's last position, whole against portions
+    of 1,024 tokens."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine, StepItem
+    cfg = _preset("lfm2_350m")
+    rng = np.random.default_rng(2)
+    P, new, B = 32768, 512, 4
+    out = {"metric": "LFM2-350M long context: 4 x 32,768-token prompts + 512 greedy tokens", "unit": "tokens/s",
+           "data": "synthetic (random weights, uniform-random token ids)"}
+    prompts = None
+    for dtype in ("bfloat16", "float32"):
+        engine = Engine(config=cfg, seed=0, dtype=dtype, ctx=P + new, parallel=B, page_size=PAGE, max_step_tokens=P,
+                        random_init={"norm_jitter": 0.0})
+        if prompts is None:
+            prompts = [rng.integers(0, engine.vocab_size, P).tolist() for _ in range(B)]
+        n_new = new if dtype == "bfloat16" else 32          # the 32-bit path is for checks: a few decode steps suffice
+        stamps = []
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        got = engine.generate(prompts, max_tokens=n_new, stop_token_ids=[],
+                              on_step=lambda plan: stamps.append((time.perf_counter(), sum(e.count for e in plan))))
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(len(g) == n_new for g in got)
+        t_first_decode = next(t for t, c in stamps if c == B)       # the first step of decode rows only was issued
+        decode_steps = sum(1 for _, c in stamps if c == B)
+        key = "bf16" if dtype == "bfloat16" else "fp32"
+        out[key] = {"seconds": round(dt, 3), "prefill_tokens_per_s": round(B * P / (t_first_decode - t0), 1),
+                    "decode_tokens_per_s": round(B * (decode_steps - 1) / max(stamps[-1][0] - t_first_decode, 1e-9), 1),
+                    "new_tokens_each": n_new}
+        if dtype == "float32":
+            # the same prompt whole and in 1,024-token portions: logits at its last position
+            rows = []
+            for cut in (P, 1024):
+                engine.add_request(900 + cut)
+                at = 0
+                while at < P:
+                    k = min(cut, P - at)
+                    lg = engine.step([StepItem(900 + cut, prompts[0][at:at + k], [k - 1] if at + k == P else [])])
+                    at += k
+                rows.append(lg[0].double().cpu())
+                engine.end_request(900 + cut)
+            scale = float(rows[0].abs().max())
+            out[key]["whole_vs_1024_portions_max_abs_diff"] = float((rows[0] - rows[1]).abs().max())
+            out[key]["logit_scale"] = scale
+            out[key]["same_argmax"] = bool(int(rows[0].argmax()) == int(rows[1].argmax()))
+        del engine
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -203,6 +304,11 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long"],
+                    help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
+                         "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
+                         "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit")
+    ap.add_argument("--requests", type=int, default=64, help="continuous: requests in all")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "zeraix/imparo is a Rust workspace (no setup.py or pyproject.toml: "
@@ -216,6 +322,10 @@ def main():
     from imparo_b200.engine import Engine
     from imparo_b200.kernels import ops
 
+    if args.workload == "continuous":
+        return workload_continuous(args)
+    if args.workload == "long":
+        return workload_long(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

@@ -150,6 +150,29 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
 }  // namespace imparo
 
 // part_val / part_idx: scratch of n_rows * 32 entries each.
+// token_ids[i] = prev[src[i]] where src[i] >= 0: a step takes the ids the step before it sampled
+// straight from that step's output on the device (rows with src < 0 keep the id the host wrote)
+namespace imparo {
+__global__ void take_sampled_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ src,
+                                           const int* __restrict__ prev, int n, int n_prev) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const int s = src[i];
+        if (s >= 0 && s < n_prev) token_ids[i] = prev[s];
+    }
+}
+}  // namespace imparo
+
+extern "C" int imparo_take_sampled_tokens(int* token_ids, const int* src, const int* prev, int n, int n_prev,
+                                          cudaStream_t stream) {
+    if (n <= 0) return 0;
+    launch(imparo::take_sampled_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, token_ids, src, prev, n, n_prev);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" int imparo_argmax_rows(const float* logits, int* out, float* part_val, int* part_idx,
                                   int n_rows, int vocab, int ld, cudaStream_t stream) {
     if (n_rows <= 0) return 0;

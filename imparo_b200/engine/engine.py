@@ -194,20 +194,26 @@ class Engine:
                     raise RuntimeError("the scheduler has requests but plans no step")
                 continue
             idle = 0
-            # A step of single tokens for exactly the requests whose ids were just sampled takes
-            # them on the device; anything else needs the values on the host first.
-            fed = (carry is not None and all(e.count == 1 and e.want for e in plan)
-                   and [e.request for e in plan] == [e.request for e in carry[0]])
+            # Rows whose token is the id the step in flight is sampling take it from that step's output
+            # on the device; prompt portions bring tokens the host knows.  Only a row that needs a
+            # value which is neither makes the host read the pending ids first.
+            pending_at = {e.request: i for i, e in enumerate(carry[0])} if carry is not None else {}
+            unknown = [e for e in plan if e.start + e.count > len(tokens[e.request])]
+            fed = carry is not None and all(e.count == 1 and e.start == len(tokens[e.request]) and e.request in pending_at
+                                            for e in unknown)
             if carry is not None and not fed:
                 settle(carry)
                 carry = None
-            if fed:
-                items = [StepItem(e.request, [0], [0]) for e in plan]
-                device_tokens = carry[1].dev_ids
-            else:
-                items = [StepItem(e.request, tokens[e.request][e.start:e.start + e.count],
-                                  [e.count - 1] if e.want else []) for e in plan]
-                device_tokens = None
+            items, token_src = [], []
+            for e in plan:
+                want = [e.count - 1] if e.want else []
+                if fed and e.start + e.count > len(tokens[e.request]):
+                    items.append(StepItem(e.request, [0], want))
+                    token_src.append(pending_at[e.request])
+                else:
+                    items.append(StepItem(e.request, tokens[e.request][e.start:e.start + e.count], want))
+                    token_src.extend([-1] * e.count)
+            device_tokens = (carry[1].dev_ids, token_src) if fed and unknown else None
             try:
                 logits = self.step_fn(items, manage_cache=False, device_tokens=device_tokens)
             except Exception:

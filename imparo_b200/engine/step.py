@@ -34,7 +34,7 @@ class StepBatch:
     """The step's batch on the device.  All index arrays are int32."""
     __slots__ = ("n_tokens", "n_items", "token_ids", "positions", "item_of_token", "item_row_start",
                  "item_slot", "item_start_pos", "tables", "want_rows", "n_want", "max_tokens_per_item",
-                 "max_context", "decode_only", "host")
+                 "max_context", "decode_only", "host", "token_src")
 
 
 def _round_up(x: int, m: int) -> int:
@@ -46,8 +46,12 @@ class StepFunction:
                  use_graphs: bool = True):
         self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", False)
         self.last_h2d_bytes = 0
-        self._graphs = {}        # key -> [times seen, graph, logits, (own, library) launches, generation]
+        self._graphs = {}        # key -> [times seen, graph, logits, (own, library) launches, generation], in order of use
+        self._capture_stream = None
+        self.max_graphs = 512    # shapes remembered (a continuous batch under a token budget meets a few hundred)
         self.graph_replays = 0
+        self.graph_captures = 0
+        self.graph_resets = 0    # times every graph was dropped because a buffer they use had moved
         self.model = model
         self.cache = cache
         self.rt = model.rt
@@ -76,7 +80,7 @@ class StepFunction:
             slot[1].synchronize()
         return slot[0]
 
-    def build_batch(self, items: Sequence[StepItem]) -> StepBatch:
+    def build_batch(self, items: Sequence[StepItem], token_src: Optional[Sequence[int]] = None) -> StepBatch:
         cache = self.cache
         R = len(items)
         T = sum(len(it.tokens) for it in items)
@@ -86,7 +90,9 @@ class StepFunction:
         for g in range(ng):
             longest = max(cache.table_len(it.request, g) for it in items)
             strides.append(_round_up(max(longest, 1), 32))
-        sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides]
+        # the last array (one source index per token, -1 = the id the host wrote) is there in every
+        # step, so that the layout depends on the step's totals only
+        sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides] + [T]
         offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
         host = self._host_buffer(int(offs[-1]))
         h = host.numpy()
@@ -117,6 +123,11 @@ class StepFunction:
             tab[:] = -1
             for i, it in enumerate(items):
                 cache.fill_table(it.request, g, tab[i])
+        src = h[offs[7 + ng]:offs[7 + ng] + T]
+        if token_src is None:
+            src[:] = -1
+        else:
+            src[:] = np.asarray(token_src, dtype=np.int32)
         n_ints = int(offs[-1])
         self.last_h2d_bytes = n_ints * 4
         self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
@@ -132,6 +143,7 @@ class StepFunction:
         b.item_start_pos = d[offs[5]:offs[5] + R]
         b.want_rows = d[offs[6]:offs[6] + max(W, 1)]
         b.tables = [d[offs[7 + g]:offs[7 + g] + R * strides[g]].view(R, strides[g]) for g in range(ng)]
+        b.token_src = d[offs[7 + ng]:offs[7 + ng] + T]
         b.max_tokens_per_item = max(len(it.tokens) for it in items)
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
@@ -161,22 +173,37 @@ class StepFunction:
         entry = self._graphs.get(key)
         if entry is not None and entry[4] != generation:
             self._graphs.clear()
+            self.graph_resets += 1
             entry = None
         if entry is None:
-            if len(self._graphs) >= 64:
-                self._graphs.pop(next(iter(self._graphs)))
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))          # the shape used longest ago
             self._graphs[key] = [1, None, None, None, generation]
             return self._forward(batch)
+        self._graphs[key] = self._graphs.pop(key)                   # most recently used: to the end
         if entry[1] is None:
             before = dict(ops.COUNTS)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                logits = self._forward(batch)
+            # Captured on a stream of its own, without torch.cuda.graph(): that helper first waits
+            # for the device and empties the allocators' caches, which a serving loop that meets a
+            # new shape every few steps cannot afford.  Nothing is allocated under capture (the
+            # first, uncaptured run of the shape sized every buffer).
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+            self._capture_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._capture_stream):
+                g.capture_begin()
+                try:
+                    logits = self._forward(batch)
+                finally:
+                    g.capture_end()
             entry[1], entry[2] = g, logits
             entry[3] = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
             ops.COUNTS.update(before)          # capture launched nothing
+            self.graph_captures += 1
             if entry[4] != (ws.generation, ops.TC_GENERATION):      # a buffer moved during the capture run
                 self._graphs.clear()
+                self.graph_resets += 1
                 return self._forward(batch)
         entry[0] += 1
         entry[1].replay()
@@ -206,7 +233,7 @@ class StepFunction:
             raise ValueError(f"a step holds at most {self.max_step_tokens} tokens, found {total}")
 
     def __call__(self, items: Sequence[StepItem], manage_cache: bool = True,
-                 device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                 device_tokens: Optional[tuple] = None) -> Optional[torch.Tensor]:
         """Runs the step.  Returns logits [wanted, vocab] (float32, on the device) in the
         order of items and of want, or None when nothing was wanted.
 
@@ -215,10 +242,12 @@ class StepFunction:
         been issued without error.  manage_cache=False: the caller (the scheduler) has
         reserved the pages and commits or abandons the step itself.
 
-        device_tokens: int32 ids on the device, one per token of the batch in order; they replace
-        the items' token values (which are then placeholders).  This is how a decode step takes
-        the ids the previous step sampled without a round trip through the host (the reference's
-        pipelined decode does the same: imparo-model/src/lib.rs:2457-2537 queue_step / argmax_feed)."""
+        device_tokens: (ids, src): int32 ids on the device (what an earlier step sampled) and, per
+        token of the batch in order, the index in ids its value comes from, or -1 for a token whose
+        value the item gives (the others are placeholders).  This is how decode rows take the ids
+        the previous step sampled without a round trip through the host, beside prompt portions
+        whose tokens the host knows (the reference's pipelined decode does the same for its
+        one-token step: imparo-model/src/lib.rs:2457-2537 queue_step / argmax_feed)."""
         self.check_items(items)
         cache = self.cache
         if manage_cache:
@@ -232,9 +261,14 @@ class StepFunction:
                     cache.rollback(it.request)
                 raise
         try:
-            batch = self.build_batch(items)
             if device_tokens is not None:
-                batch.token_ids.copy_(device_tokens[:batch.n_tokens])
+                prev_ids, token_src = device_tokens
+                if len(token_src) != sum(len(it.tokens) for it in items):
+                    raise ValueError("device_tokens: one source index per token of the batch")
+                batch = self.build_batch(items, token_src)
+                ops.take_sampled_tokens(batch.token_ids, batch.token_src, prev_ids)
+            else:
+                batch = self.build_batch(items)
             fresh = [int(s) for s, p in zip(batch.host["slots"], batch.host["start_pos"]) if p == 0]
             if fresh and cache.state:
                 idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)

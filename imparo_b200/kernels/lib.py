@@ -97,6 +97,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gather_rows_f32", [P, P, P, I, I, S])
     _declare(lib, "imparo_argmax_rows", [P, P, P, P, I, I, I, S])
     _declare(lib, "imparo_sample_rows", [P, P, P, P, I, I, I, S])
+    _declare(lib, "imparo_take_sampled_tokens", [P, P, P, I, I, S])
 
 
 def _declare_host(lib):

@@ -729,6 +729,17 @@ def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y,
         _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], parts, part_stride, _ptr(status), _stream()), "gated_conv")
 
 
+def take_sampled_tokens(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
+    """token_ids[i] = prev[src[i]] where src[i] >= 0 (all int32): rows whose token is the id an
+    earlier step sampled take it from that step's output on the device."""
+    _cuda(token_ids, src, prev)
+    n = token_ids.numel()
+    _need(token_ids.dtype == torch.int32 and src.dtype == torch.int32 and prev.dtype == torch.int32 and src.numel() >= n,
+          "take_sampled_tokens: int32 ids, one source index per token")
+    _check(_lib.kernels().imparo_take_sampled_tokens(_ptr(token_ids), _ptr(src), _ptr(prev), n, prev.numel(), _stream()),
+           "take_sampled_tokens")
+
+
 _argmax_scratch = {}
 
 

@@ -76,10 +76,11 @@ class Sampler:
             ops.sample_rows(logits, None, None, out)
         else:
             h = self._host_in[self._turn]
+            hn = h.numpy()                      # the same pinned memory: element writes without tensor indexing
             for r in range(n):
                 t = float(temperatures[r])
-                h[0, r] = t
-                h[1, r] = uniform_for(seeds[r], steps[r]) if t > 0 else 0.0
+                hn[0, r] = t
+                hn[1, r] = uniform_for(seeds[r], steps[r]) if t > 0 else 0.0
             self._dev_in[:, :n].copy_(h[:, :n], non_blocking=True)
             ops.sample_rows(logits, self._dev_in[0, :n], self._dev_in[1, :n], out)
         host = self._host_outs[self._turn][:n]
