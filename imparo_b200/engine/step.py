@@ -34,7 +34,7 @@ class StepBatch:
     """The step's batch on the device.  All index arrays are int32."""
     __slots__ = ("n_tokens", "n_items", "token_ids", "positions", "item_of_token", "item_row_start",
                  "item_slot", "item_start_pos", "tables", "want_rows", "n_want", "max_tokens_per_item",
-                 "max_context", "decode_only", "host", "token_src")
+                 "max_context", "decode_only", "host", "token_src", "n_single", "fresh_slots")
 
 
 def _round_up(x: int, m: int) -> int:
@@ -80,8 +80,26 @@ class StepFunction:
             slot[1].synchronize()
         return slot[0]
 
-    def build_batch(self, items: Sequence[StepItem], token_src: Optional[Sequence[int]] = None) -> StepBatch:
+    def build_batch(self, items: Sequence[StepItem], token_src: Optional[Sequence[int]] = None,
+                    singles_first: bool = False) -> StepBatch:
+        """singles_first: requests that bring one token are put before those that bring more (the
+        order among each kind stays), so that a mixer may treat the decode rows and the prompt
+        portions of one step as two contiguous ranges (batch.n_single rows, then the rest).
+        Wanted rows keep the caller's order, whatever the order of the rows."""
         cache = self.cache
+        n_single = 0
+        if singles_first and any(len(it.tokens) == 1 for it in items) and any(len(it.tokens) > 1 for it in items):
+            order = sorted(range(len(items)), key=lambda i: len(items[i].tokens) != 1)       # stable
+            n_single = sum(1 for it in items if len(it.tokens) == 1)
+            if token_src is not None:
+                starts = np.concatenate([[0], np.cumsum([len(it.tokens) for it in items])])
+                token_src = [s for i in order for s in token_src[starts[i]:starts[i + 1]]]
+            caller_items, items = items, [items[i] for i in order]
+            place = [0] * len(order)                     # the caller's item j is item place[j] of the batch
+            for k, i in enumerate(order):
+                place[i] = k
+        else:
+            caller_items, place = items, list(range(len(items)))
         R = len(items)
         T = sum(len(it.tokens) for it in items)
         W = sum(len(it.want) for it in items)
@@ -92,7 +110,7 @@ class StepFunction:
             strides.append(_round_up(max(longest, 1), 32))
         # the last array (one source index per token, -1 = the id the host wrote) is there in every
         # step, so that the layout depends on the step's totals only
-        sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides] + [T]
+        sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides] + [T, R]
         offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
         host = self._host_buffer(int(offs[-1]))
         h = host.numpy()
@@ -101,7 +119,7 @@ class StepFunction:
         slot = h[offs[4]:offs[4] + R]
         start_pos = h[offs[5]:offs[5] + R]
         want = h[offs[6]:offs[6] + max(W, 1)]
-        t = w = 0
+        t = 0
         for i, it in enumerate(items):
             n = len(it.tokens)
             start = cache.cached(it.request)
@@ -111,13 +129,17 @@ class StepFunction:
             row_start[i] = t
             slot[i] = cache.slot(it.request)
             start_pos[i] = start
+            t += n
+        row_start[R] = T
+        w = 0
+        for j_item, it in enumerate(caller_items):       # wanted rows: in the caller's order
+            n = len(it.tokens)
+            base = int(row_start[place[j_item]])
             for j in it.want:
                 if not 0 <= j < n:
                     raise ValueError(f"request {it.request}: wanted place {j} is not among its {n} tokens")
-                want[w] = t + j
+                want[w] = base + j
                 w += 1
-            t += n
-        row_start[R] = T
         for g in range(ng):
             tab = h[offs[7 + g]:offs[7 + g] + R * strides[g]].reshape(R, strides[g])
             tab[:] = -1
@@ -128,6 +150,11 @@ class StepFunction:
             src[:] = -1
         else:
             src[:] = np.asarray(token_src, dtype=np.int32)
+        # state slots of requests that start in this step (they are zeroed before the step runs); the
+        # list is padded with its first entry, so that it travels with the description
+        fresh = [int(slot[i]) for i in range(R) if start_pos[i] == 0]
+        fresh_at = offs[8 + ng]
+        h[fresh_at:fresh_at + R] = (fresh + [fresh[0]] * (R - len(fresh))) if fresh else 0
         n_ints = int(offs[-1])
         self.last_h2d_bytes = n_ints * 4
         self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
@@ -144,11 +171,13 @@ class StepFunction:
         b.want_rows = d[offs[6]:offs[6] + max(W, 1)]
         b.tables = [d[offs[7 + g]:offs[7 + g] + R * strides[g]].view(R, strides[g]) for g in range(ng)]
         b.token_src = d[offs[7 + ng]:offs[7 + ng] + T]
+        b.n_single = n_single
+        b.fresh_slots = d[fresh_at:fresh_at + R] if fresh else None
         b.max_tokens_per_item = max(len(it.tokens) for it in items)
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
         b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),
-                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item), "h2d_bytes": n_ints * 4}
+                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single), "h2d_bytes": n_ints * 4}
         return b
 
     # -- decode-only steps replay a captured graph ------------------------------------------
@@ -265,13 +294,12 @@ class StepFunction:
                 prev_ids, token_src = device_tokens
                 if len(token_src) != sum(len(it.tokens) for it in items):
                     raise ValueError("device_tokens: one source index per token of the batch")
-                batch = self.build_batch(items, token_src)
+                batch = self.build_batch(items, token_src, singles_first=True)
                 ops.take_sampled_tokens(batch.token_ids, batch.token_src, prev_ids)
             else:
-                batch = self.build_batch(items)
-            fresh = [int(s) for s, p in zip(batch.host["slots"], batch.host["start_pos"]) if p == 0]
-            if fresh and cache.state:
-                idx = torch.tensor(fresh, dtype=torch.int64, device=self.device)
+                batch = self.build_batch(items, singles_first=True)
+            if batch.fresh_slots is not None and cache.state:
+                idx = batch.fresh_slots.long()          # on the device already: no copy that would wait for the stream
                 for t in cache.state.values():
                     t.index_fill_(0, idx, 0.0)
             if self.use_graphs:

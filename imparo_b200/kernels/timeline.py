@@ -115,14 +115,17 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--prefill", action="store_true", help="print the step of a whole prompt instead of a decode step "
                     "(library products are not stamped: their time shows in the share of the kernel before them)")
+    ap.add_argument("--mixed", type=int, default=0, help="print a step of one prompt portion of --prompt-len tokens beside "
+                    "this many decode rows, each with --context positions in the cache")
+    ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--json", action="store_true")
     args = ap.parse_args(argv)
     import numpy as np
     from ..engine import Engine, StepItem
     from . import ops
     if args.model:
-        engine = Engine(model=args.model, dtype="bfloat16", ctx=args.prompt_len + 64, parallel=args.batch,
-                        max_step_tokens=args.prompt_len)
+        engine = Engine(model=args.model, dtype="bfloat16", ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
+                        parallel=max(args.batch, args.mixed + 1), max_step_tokens=max(args.prompt_len, args.context) + args.mixed)
     else:
         if not args.config:
             ap.error("give a model folder (-m) or a configuration (--config)")
@@ -132,11 +135,31 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args.layers:
             cfg["layer_types"] = cfg["layer_types"][:args.layers]
             cfg["num_hidden_layers"] = args.layers
-        engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=args.prompt_len + 64, parallel=args.batch,
-                        max_step_tokens=args.prompt_len, random_init={"norm_jitter": 0.0})
+        engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
+                        parallel=max(args.batch, args.mixed + 1), max_step_tokens=max(args.prompt_len, args.context) + args.mixed,
+                        random_init={"norm_jitter": 0.0})
     tl = Timeline()
     rng = np.random.default_rng(0)
     V = engine.vocab_size
+    if args.mixed:
+        ids = list(range(args.mixed))
+        for r in ids:
+            engine.add_request(r)
+            engine.step([StepItem(r, rng.integers(0, V, args.context).tolist(), [])])
+        rows = None
+        for rep in range(3):                     # the third time the step's shape is replayed from its graph
+            engine.add_request(900 + rep)
+            before, n_before = tl.host_launches(), tl.records().shape[0]
+            engine.step([StepItem(r, [int(t)], [0]) for r, t in zip(ids, rng.integers(0, V, args.mixed))]
+                        + [StepItem(900 + rep, rng.integers(0, V, args.prompt_len).tolist(), [args.prompt_len - 1])])
+            rec = tl.records()[n_before:]
+            if tl.host_launches() > before:
+                names = tl.names(before, tl.host_launches())
+            engine.end_request(900 + rep)
+            rows = step_table(names[-rec.shape[0]:], rec)
+        tl.stop()
+        _print_table(rows, f"portion of {args.prompt_len} tokens beside {args.mixed} decode rows at {args.context} positions", args.json)
+        return 0
     if args.prefill:
         rows = None
         for rep in range(3):

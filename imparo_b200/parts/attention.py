@@ -82,7 +82,24 @@ class AttentionMixer(Part):
                                self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
         out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype)
         done = False
-        if batch.max_tokens_per_item >= 8:
+        n1 = getattr(batch, "n_single", 0)             # decode rows come first when the step also holds portions
+        if batch.max_tokens_per_item >= 8 and 0 < n1 < batch.n_items and nh // self.nkv <= 8:
+            # Portions beside decode rows: the prompt kernel walks a request's keys tile by tile in one
+            # CTA per 128 query rows, which for a single query token is one CTA crawling over the whole
+            # context.  So the portions (requests n1 onward) go to the prompt kernel and the decode rows
+            # (the first n1 tokens, one per request) to the split-key kernel, which cuts their keys
+            # over many CTAs.
+            done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start[n1:], batch.item_start_pos[n1:],
+                                         batch.n_items - n1, table[n1:], kv.page_size, kv.n_pages, self.window, self.scale,
+                                         out, nh, self.nkv, hd, rt.status)
+            if done:
+                chunk, n_splits = ops.split_plan(n1, self.nkv, table.shape[1] * kv.page_size)
+                part_acc = rt.workspace.get("attn_part_acc", (n1 * nh * n_splits * hd,), torch.float32)
+                part_ml = rt.workspace.get("attn_part_ml", (n1 * nh * n_splits * 2,), torch.float32)
+                ops.paged_attention_split(q[:n1], kv.k, kv.v, batch.positions[:n1], batch.item_of_token[:n1], table,
+                                          kv.page_size, kv.n_pages, self.window, self.scale, out[:n1], part_acc, part_ml,
+                                          chunk, n_splits, nh, self.nkv, hd, rt.status, fresh=1)
+        elif batch.max_tokens_per_item >= 8:
             # prompt portions: the tensor-core kernel (bfloat16, head size 64 or 128), tiles of one request each
             done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start, batch.item_start_pos, batch.n_items, table,
                                          kv.page_size, kv.n_pages, self.window, self.scale, out, nh, self.nkv, hd, rt.status)

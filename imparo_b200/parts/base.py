@@ -73,7 +73,12 @@ class Workspace:
         if buf is None or buf.numel() < n:
             if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"workspace buffer '{tag}' would grow during graph capture")
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            # small buffers grow by doubling: every move makes captured graphs stale, and a serving loop
+            # meets slightly larger shapes for a long while
+            grown = max(n, 1)
+            if buf is not None and grown * buf.element_size() <= (64 << 20):
+                grown = max(grown, 2 * buf.numel())
+            buf = torch.empty(grown, dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
         return buf[:n].view(*shape)
