@@ -695,3 +695,17 @@ def test_product_with_the_next_norm_behind_it(T, N, K, monkeypatch):
     assert ni2._done
     o.rmsnorm(stream, wn.to(DEV), eps, sep)
     assert (buf.float() - sep.float()).abs().max() <= 1.6e-2 * ref_norm.abs().max() + 0.1
+
+
+@pytest.mark.parametrize("n,n_prev", [(1, 1), (37, 8), (700, 64)])
+def test_take_sampled_tokens(n, n_prev):
+    """token_ids[i] = prev[src[i]] where src[i] >= 0; other rows keep what the host wrote."""
+    from imparo_b200.kernels import ops as o
+    rng = np.random.default_rng(n)
+    ids = rng.integers(0, 60000, n).astype(np.int32)
+    prev = rng.integers(0, 60000, n_prev).astype(np.int32)
+    src = np.where(rng.random(n) < 0.5, rng.integers(0, n_prev, n), -1).astype(np.int32)
+    d_ids = torch.from_numpy(ids).to(DEV)
+    o.take_sampled_tokens(d_ids, torch.from_numpy(src).to(DEV), torch.from_numpy(prev).to(DEV))
+    want = np.where(src >= 0, prev[np.clip(src, 0, None)], ids)
+    assert np.array_equal(d_ids.cpu().numpy(), want)

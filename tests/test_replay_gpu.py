@@ -205,3 +205,29 @@ def test_long_context_whole_against_portions():
     assert np.abs(a[0] - a[4]).max() > 0.1 * scale
     eng.end_request(1); eng.end_request(2)
     eng.cache.check()
+
+
+def test_rows_of_one_token_come_first_and_wanted_rows_keep_their_order():
+    """A step that holds portions and single tokens is laid out with the single tokens first; the
+    logits still come in the order of the entries and of want."""
+    from imparo_b200.engine import StepItem
+    from tests.gpu_helpers import plain_logits
+    name = "E"                                        # head size 64: the tensor-core kernels take this step
+    reqs = make_requests(name, [40, 9, 33, 12], seed=41)
+    all_live = [{"step": 0, "entries": [{"id": k, "tokens": v, "want": []} for k, v in reqs.items()], "end": []}]
+    eng = engine_for(name, "bfloat16", all_live)
+    ids = {k: i + 1 for i, k in enumerate(reqs)}
+    for k in reqs:
+        eng.add_request(ids[k])
+    eng.step([StepItem(ids[k], v[:8], []) for k, v in reqs.items()])
+    # r0: a portion, r1: its last token, r2: a portion, r3: one token (not its last)
+    items = [StepItem(ids["r0"], reqs["r0"][8:30], [0, 21]), StepItem(ids["r1"], reqs["r1"][8:9], [0]),
+             StepItem(ids["r2"], reqs["r2"][8:20], [5]), StepItem(ids["r3"], reqs["r3"][8:9], [0])]
+    batch = eng.step_fn.build_batch(items, singles_first=True)
+    assert batch.n_single == 2 and batch.item_row_start.cpu().tolist() == [0, 1, 2, 24, 36]
+    assert batch.want_rows.cpu().tolist()[:5] == [2, 23, 0, 29, 1]
+    got = eng.step(items).cpu().numpy()
+    ref = plain_logits(name, reqs)
+    want = np.stack([ref["r0"][8], ref["r0"][29], ref["r1"][8], ref["r2"][13], ref["r3"][8]])
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    assert np.abs(got - want).max() <= 2.5e-2 * scale
