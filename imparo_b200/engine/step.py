@@ -180,7 +180,7 @@ class StepFunction:
                   "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single), "h2d_bytes": n_ints * 4}
         return b
 
-    # -- decode-only steps replay a captured graph ------------------------------------------
+    # -- a step whose shape has come before replays its captured graph -----------------------
     def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
         x, picked = self.model.forward(batch, self._views, wanted=(batch.want_rows, batch.n_want))
         if not batch.n_want:
