@@ -37,8 +37,10 @@ def _need(cond: bool, msg: str) -> None:
 def _cuda(*ts) -> None:
     for t in ts:
         if t is not None:
-            _need(t.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
-            _need(t.is_contiguous(), "kernel arguments must be contiguous")
+            if not t.is_cuda:
+                raise KernelError("kernels run on CUDA tensors only (there is no CPU path)")
+            if not t.is_contiguous():
+                raise KernelError("kernel arguments must be contiguous")
 
 
 def _ptr(t: Optional[torch.Tensor]):

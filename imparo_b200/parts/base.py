@@ -62,9 +62,14 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}      # (tag, dtype, shape) -> view handed out before
         self.generation = 0      # bumped whenever a buffer moves: captured graphs of older generations are stale
 
     def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        seen = self._views.get((tag, dtype, shape))
+        if seen is not None:
+            return seen
         n = 1
         for s in shape:
             n *= int(s)
@@ -81,7 +86,11 @@ class Workspace:
             buf = torch.empty(grown, dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
-        return buf[:n].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if k[:2] != key}
+        view = buf[:n].view(*shape)
+        if len(self._views) < 4096:
+            self._views[(tag, dtype, shape)] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
