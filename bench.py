@@ -12,6 +12,14 @@ host token lists in, host token lists out, with the per-step host-to-device copy
 batch descriptor and device-to-host copy of the sampled ids inside the timed region.
 One JSON line is printed.  For --gpus N > 1 one line says that this engine is a
 one-GPU engine and the exit code is 2.
+
+`prefill` times one 2,048-token prompt per repetition (a new request each time, CUDA events
+around the step); from its third run on the step is replayed from the graph the engine
+captured for its shape, as every step whose shape repeats is.
+
+--workload continuous | long run the baseline's two other workloads (LFM2-700M sizes under
+continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 32-bit) and
+print one JSON line each; the default is the headline above.
 """
 import argparse
 import json
