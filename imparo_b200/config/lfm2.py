@@ -126,7 +126,7 @@ def parse_lfm2_config(values: dict) -> Lfm2Config:
         conv_L_cache=taps,
         conv_bias=r.boolean("conv_bias", default=False),
         block_ff_dim=r.integer("block_ff_dim", "intermediate_size", minimum=1),
-        block_auto_adjust_ff_dim=r.boolean("block_auto_adjust_ff_dim", default=False),
+        block_auto_adjust_ff_dim=_auto_adjust(r),
         block_ffn_dim_multiplier=r.number("block_ffn_dim_multiplier", default=None),
         block_multiple_of=r.integer("block_multiple_of", default=256, minimum=1),
         rope_theta=_rope_theta(r),
@@ -137,6 +137,18 @@ def parse_lfm2_config(values: dict) -> Lfm2Config:
         layer_schedule=schedule,
         eos_token_ids=tuple(eos or ()),
     )
+
+
+def _auto_adjust(r: KeyReader) -> bool:
+    """block_auto_adjust_ff_dim has no default here: the feed-forward width follows from it, writers
+    of config.json do not agree on what an absent key means, and a guess would show up only as
+    wrong-shape weights (or, with random weights, as another model).  The key must be there."""
+    v = r.raw("block_auto_adjust_ff_dim")
+    if v is None:
+        raise ConfigError("config.json: missing required key 'block_auto_adjust_ff_dim' (true: the feed-forward width is "
+                          "block_ff_dim * 2/3, times block_ffn_dim_multiplier, rounded up to block_multiple_of; "
+                          "false: block_ff_dim as it is)")
+    return r.boolean("block_auto_adjust_ff_dim")
 
 
 def _rope_theta(r: KeyReader) -> float:

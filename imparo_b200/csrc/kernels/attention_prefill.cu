@@ -560,7 +560,10 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
-    if (n_tok > 65535 || nkv > 65535 || chunk < 64 || n_splits < 1) return -2;
+    // at most 2048 splits (the ordered combine keeps one pair per split in shared memory), and the
+    // chunks must cover every position a table of this width can hold; refused before any launch
+    if (n_tok > 65535 || nkv > 65535 || chunk < 64 || n_splits < 1 || n_splits > 2048) return -2;
+    if ((long long)chunk * n_splits < (long long)max_blocks * page_size) return -2;
     dim3 grid(n_splits, nkv, n_tok);
     const size_t smem = (size_t)4 * pf::KEYS * hd * 2;          // the fold's 256 + 128 * hd bytes fit inside
     static bool configured = false;

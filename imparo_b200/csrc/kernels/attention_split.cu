@@ -100,7 +100,8 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
     // the row has more than 32 vectors), so one load instruction of the warp covers KPI keys.
     const int vecs = hd / VN;
     const int LPR = vecs < 32 ? vecs : 32;            // lanes per row
-    const int VPL = vecs / LPR;                       // vectors per lane (1, or 2 for float32 head 256)
+    const int VPL = (vecs + LPR - 1) / LPR;           // vectors per lane: 1, or 2 for float32 heads above 128 (the
+                                                      // second exists for lanes with lig + LPR < vecs only)
     const int KPI = 32 / LPR;                         // keys per instruction
     const int grp = lane / LPR, lig = lane % LPR;     // lane group = which key, lane in group = which vector
     const bool pv_lane = grp < KPI;
@@ -177,13 +178,13 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
                 jjs[u] = jj & 31;
                 const V* vp = reinterpret_cast<const V*>(v_cache + (size_t)(rj < 0 ? 0 : rj) * kvw + (size_t)kvh * hd);
                 vv[u][0] = vp[lig];
-                if (VPL > 1) vv[u][1] = vp[lig + LPR];
+                if (VPL > 1 && lig + LPR < vecs) vv[u][1] = vp[lig + LPR];
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 float v[ACC];
                 unpack(vv[u][0], v);
-                if (VPL > 1) unpack(vv[u][1], v + VN); else { for (int i = VN; i < ACC; ++i) v[i] = 0.f; }
+                if (VPL > 1 && lig + LPR < vecs) unpack(vv[u][1], v + VN); else { for (int i = VN; i < ACC; ++i) v[i] = 0.f; }
                 if (rjs[u] < 0) {             // whatever row 0 holds must not reach the sum (0 * inf)
 #pragma unroll
                     for (int i = 0; i < ACC; ++i) v[i] = 0.f;
@@ -207,7 +208,7 @@ attn_split_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_cache
             for (int u = 0; u < VPL; ++u)
 #pragma unroll
                 for (int i = 0; i < ACC; ++i)
-                    if (i < VN) my_acc[(size_t)g * hd + (lig + u * LPR) * VN + i] = acc[g][u * VN + i];
+                    if (i < VN && lig + u * LPR < vecs) my_acc[(size_t)g * hd + (lig + u * LPR) * VN + i] = acc[g][u * VN + i];
         }
     }
     __syncthreads();
@@ -336,7 +337,9 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
     if (n_tok <= 0) return 0;
     if (hd < 16 || hd > SPLIT_MAX_HEAD || hd % 16 != 0) return -3;
     if (nkv <= 0 || nh % nkv != 0) return -5;
-    if (n_tok > 65535 || nkv > 65535 || chunk < 32 || n_splits < 1) return -2;
+    if (n_tok > 65535 || nkv > 65535 || chunk < 32 || n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return -2;
+    // the chunks must cover every position a table of this width can hold, or keys would be dropped silently
+    if ((long long)chunk * n_splits < (long long)max_blocks * page_size) return -2;
     const int G = nh / nkv;
     int rc;
     if (dtype == IMPARO_DT_F32)
@@ -416,6 +419,10 @@ extern "C" int imparo_paged_attention_split_static(const void* q, const void* k_
                                                    int n_tok, int nh, int nkv, int hd, int chunk, int n_splits,
                                                    int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
+    // sizes first, so that the product below cannot wrap
+    if (hd < 16 || hd > SPLIT_MAX_HEAD || hd % 16 != 0) return -3;
+    if (nkv <= 0 || nh <= 0 || nh % nkv != 0) return -5;
+    if (n_tok > 65535 || nh > 65535 || n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return -2;
     const long long need = imparo_paged_attention_split_static_need(n_tok, nh, hd, n_splits);
     if (need <= 0 || need > (long long)IMPARO_STATIC_SCRATCH_FLOATS) return IMPARO_ERR_STATIC_SCRATCH_TOO_SMALL;
     float* base = nullptr;

@@ -29,6 +29,11 @@
 //     streams, or graph branches that may run concurrently — would overwrite each other's
 //     partials: run them one after the other.
 //   * Inputs and outputs are the caller's, exactly as for imparo_paged_attention_split.
+//   * chunk * n_splits must be at least max_blocks * page_size (every position the block table
+//     can hold lies in some chunk; fewer splits would drop keys), and n_splits at most 2048 (the
+//     combine kernel keeps one pair per split in shared memory).  Both are checked, with the
+//     head size, the head counts and n_tok <= 65535, before the scratch need is computed and
+//     before anything is launched; a call that breaks one returns -2 (-3, -5 for the heads).
 #pragma once
 #include <cuda_runtime.h>
 

@@ -64,7 +64,8 @@ class Engine:
         self.model = Model(self.arch.model_spec(self.config), self.rt)
         specs = self.model.weight_specs()
         if model is not None:
-            tensors = load_weights(model, specs, self.precision, self.device)
+            tensors = load_weights(model, specs, self.precision, self.device,
+                                   duplicates=dict(self.model.spec.duplicate_tensors))
         else:
             if config is None:
                 raise ValueError("give a model folder or a config dictionary")

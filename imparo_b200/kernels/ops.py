@@ -621,6 +621,9 @@ def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_s
         _ptr(status), _stream()), "paged_attention")
 
 
+MAX_SPLITS = 2048        # the ordered combine keeps one (max, sum) pair per key chunk in shared memory
+
+
 def split_plan(n_tok: int, nkv: int, upper_context: int):
     """(chunk, n_splits) for the split-key attention kernel: the largest chunk of 512, 256, 128
     or 64 keys that still gives about four CTAs per SM; when even the smallest does not (a step of
@@ -638,6 +641,8 @@ def split_plan(n_tok: int, nkv: int, upper_context: int):
             if n_tok * nkv * -(-upper_context // c) >= 64:
                 chunk = c
                 break
+    while -(-upper_context // chunk) > MAX_SPLITS:       # tables wider than 2048 * 512 positions: longer chunks
+        chunk *= 2
     return chunk, max(1, -(-upper_context // chunk))
 
 
@@ -663,6 +668,9 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     _need(part_acc.dtype == torch.float32 and part_acc.numel() >= T * nh * n_splits * hd
           and part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * n_splits * 2, "split scratch too small")
     _need(T <= 65535, "paged_attention_split: at most 65535 query tokens per launch")
+    _need(1 <= n_splits <= MAX_SPLITS, f"paged_attention_split: 1 to {MAX_SPLITS} key chunks per request, found {n_splits}")
+    _need(chunk * n_splits >= table.shape[1] * page_size,
+          "paged_attention_split: chunk * n_splits must cover every position the block table can hold")
     if use_mma:
         # bfloat16, head 64/128: the tensor-core version (the scalar one is bound by instruction issue)
         rc = _lib.kernels().imparo_attention_decode_mma(

@@ -45,7 +45,8 @@ def lfm2_model_spec(cfg: Lfm2Config) -> ModelSpec:
         final_norm=PartSpec("rmsnorm", {"width": H, "eps": cfg.norm_eps, "name": MODEL_PREFIX + "embedding_norm.weight"}),
         head=PartSpec("linear", {"vocab": cfg.vocab_size, "width": H,
                                  "name": embed_name if cfg.tie_embedding else "lm_head.weight"}),
-        max_positions=cfg.max_position_embeddings, eos_token_ids=cfg.eos_token_ids)
+        max_positions=cfg.max_position_embeddings, eos_token_ids=cfg.eos_token_ids,
+        duplicate_tensors=(("lm_head.weight", embed_name),) if cfg.tie_embedding else ())
 
 
 register_architecture(Architecture(name="Lfm2ForCausalLM", model_types=("lfm2",),

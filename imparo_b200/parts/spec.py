@@ -55,6 +55,9 @@ class ModelSpec:
     head: PartSpec
     max_positions: int
     eos_token_ids: Tuple[int, ...] = ()
+    # (stored name, name the model reads): tensors a file may carry as a copy of another one (a tied head
+    # written out beside the embedding table); the loader accepts them when they equal the original
+    duplicate_tensors: Tuple[Tuple[str, str], ...] = ()
 
     def __post_init__(self):
         n = len(self.layers)

@@ -65,10 +65,19 @@ def target_dtype(role: str, precision: str) -> torch.dtype:
     raise ValueError(f"unknown tensor role '{role}'")
 
 
-def load_weights(folder: str, specs: Iterable[WeightSpec], precision: str, device) -> Dict[str, torch.Tensor]:
-    """-> {spec name: device tensor}.  Raises WeightError listing every mismatch."""
+def load_weights(folder: str, specs: Iterable[WeightSpec], precision: str, device,
+                 duplicates: Dict[str, str] = None) -> Dict[str, torch.Tensor]:
+    """-> {spec name: device tensor}.  Raises WeightError listing every mismatch.
+
+    duplicates: {stored name: spec name} for tensors a file may carry although the model reads them
+    under another name (a tied head written out beside the embedding table).  Such a tensor is not
+    "unexpected" when it equals the one it duplicates; when it differs, it is reported as a wrong
+    tensor, since the model would silently ignore it."""
     path = os.path.join(folder, "model.safetensors")
     if not os.path.isfile(path):
+        if os.path.isfile(path + ".index.json"):
+            raise FileNotFoundError(f"{folder}: the checkpoint is sharded (model.safetensors.index.json); sharded checkpoints "
+                                    "are not read: merge the shards into one model.safetensors")
         raise FileNotFoundError(f"{folder}: no model.safetensors in this model folder")
     specs = list(specs)
     missing, wrong, bad = [], [], []
@@ -96,6 +105,14 @@ def load_weights(folder: str, specs: Iterable[WeightSpec], precision: str, devic
                 continue
             t = f.tensor(found)
             out[w.name] = t.to(device=device, dtype=target_dtype(w.role, precision)).contiguous()
+        for dup, name in (duplicates or {}).items():
+            found = next((a for a in _aliases(dup) if a in stored and a not in used), None)
+            orig = next((a for a in _aliases(name) if a in used), None)
+            if found is None or orig is None:
+                continue
+            used.add(found)
+            if f.info(found) != f.info(orig) or not torch.equal(f.tensor(found), f.tensor(orig)):
+                bad.append((dup, f.info(found)[0], f"the model reads {name} in its place and the two differ"))
         unexpected = sorted(stored - used)
     if missing or unexpected or wrong or bad:
         raise WeightError(path, missing, unexpected, wrong, bad)

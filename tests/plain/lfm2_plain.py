@@ -68,7 +68,7 @@ class PlainConfig:
         self.taps = int(d["conv_L_cache"])
         self.conv_bias = bool(d.get("conv_bias", False))
         ff = int(d["block_ff_dim"] if "block_ff_dim" in d else d["intermediate_size"])
-        if d.get("block_auto_adjust_ff_dim", False):
+        if d["block_auto_adjust_ff_dim"]:
             ff = int(2 * ff / 3)
             mult = d.get("block_ffn_dim_multiplier")
             if mult is not None:

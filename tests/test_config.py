@@ -60,6 +60,7 @@ def test_full_attn_idxs_alias_and_intermediate_size():
     ({"hidden_size": 66}, "multiple"),
     ({"layer_types": ["conv", "conv", "sliding_attention", "conv"]}, "sliding_window"),
     ({"conv_bias": "yes"}, "conv_bias"),
+    ({"block_auto_adjust_ff_dim": None}, "block_auto_adjust_ff_dim"),      # no default: the width follows from it
 ])
 def test_bad_config_names_the_key(change, needle):
     d = copy.deepcopy(TINY_A)

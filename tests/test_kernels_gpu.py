@@ -270,7 +270,9 @@ KINDS = [("general", None), ("split", None), ("split", 64), ("split", 512), ("sp
          ("split_mma", 512), ("split_mma_early", None), ("split_mma_early", 64), ("split_mma_early", 128)]
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256), (8, 1, 64)])
+# heads 144 and 192: in float32 a row has more vectors than a warp has lanes and not twice as many
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (3, 1, 48), (5, 5, 64), (8, 2, 128), (2, 1, 256), (8, 1, 64),
+                                       (2, 1, 192), (2, 1, 144), (4, 2, 240)])
 @pytest.mark.parametrize("page,window", [(1, None), (4, None), (16, 13), (64, None), (8, 40)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("kind,chunk", KINDS)
@@ -304,11 +306,25 @@ def test_paged_attention(nh, nkv, hd, page, window, dtype, kind, chunk):
                                         (63, None), (64, None), (127, None), (128, None)])
 @pytest.mark.parametrize("kind,chunk", KINDS)
 def test_one_far_key_stands_out(dtype, far, window, kind, chunk):
+    _far_key(dtype, far, window, kind, chunk, 4, 2, 64)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far,window", [(3, None), (512, None), (701, 200), (899, 200)])
+@pytest.mark.parametrize("kind,chunk", [("general", None), ("split", None), ("split", 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(2, 1, 192), (2, 1, 144), (3, 1, 208)])
+def test_one_far_key_stands_out_wide_heads(dtype, far, window, kind, chunk, nh, nkv, hd):
+    """Head sizes whose float32 rows have more 16-byte vectors than a warp has lanes, and not twice as many:
+    every value dimension must reach the output (the far key's value is compared over the whole head)."""
+    _far_key(dtype, far, window, kind, chunk, nh, nkv, hd)
+
+
+def _far_key(dtype, far, window, kind, chunk, nh, nkv, hd):
     """Among 900 keys one is scaled so that its score dominates: the output must be that
     key's value (or must NOT be, when a window has passed it).  Random weights would hide
     a kernel that drops a far key, a page edge or a window edge."""
     o = ops()
-    nh, nkv, hd, page = 4, 2, 64, 16
+    page = 16
     rng = np.random.default_rng(far)
     n = 900
     table, kc, vc, ks, vs, n_pages = make_paged(rng, [n], page, nkv, hd, dtype)
@@ -490,6 +506,28 @@ def test_kernels_refuse_sizes_they_do_not_take():
         o.gated_conv(z(1, 24), z(8, 17), None, z(1, 16, 8), zi(2), zi(1), zi(1), z(1, 8), 17, st)
     with pytest.raises(o.KernelError):
         o.rmsnorm(torch.zeros(2, 8), torch.zeros(8), 1e-5, torch.zeros(2, 8))      # CPU tensors: no CPU path
+    # split-key attention: more key chunks than the combine kernel holds, or chunks that do not cover the
+    # table, are refused by the launcher and by both entry points, before anything is launched
+    q, kv, tab = z(1, 16), z(2, 16, 16), zi(1, 4096)
+    with pytest.raises(o.KernelError, match="key chunks"):
+        o.paged_attention_split(q, kv, kv, zi(1), zi(1), tab, 16, 2, None, 1.0, z(1, 16), z(16 * 4096), z(2 * 4096), 32, 4096,
+                                1, 1, 16, st)
+    with pytest.raises(o.KernelError, match="cover"):
+        o.paged_attention_split(q, kv, kv, zi(1), zi(1), tab, 16, 2, None, 1.0, z(1, 16), z(16 * 8), z(2 * 8), 64, 8, 1, 1, 16, st)
+    k = o._lib.kernels()
+    stream = torch.cuda.current_stream().cuda_stream
+    p = lambda t: t.data_ptr()
+    assert k.imparo_paged_attention_split(p(q), p(kv), p(kv), 0, p(zi(1)), p(zi(1)), p(tab), 4096, 16, 2, 0, 1.0, p(z(1, 16)),
+                                          p(z(16 * 4096)), p(z(2 * 4096)), 1, 1, 1, 16, 32, 4096, p(st), stream) == -2
+    qb, kvb = z(1, 64, dt=torch.bfloat16), z(2, 16, 64, dt=torch.bfloat16)
+    assert k.imparo_attention_decode_mma(p(qb), p(kvb), p(kvb), p(zi(1)), p(zi(1)), p(tab), 4096, 16, 2, 0, 1.0,
+                                         p(z(1, 64, dt=torch.bfloat16)), p(z(64 * 4096)), p(z(2 * 4096)), 1, 1, 1, 64, 64, 4096, 0,
+                                         p(st), stream) == -2
+    torch.cuda.synchronize()
+    o.read_status(st)
+    # the plan never asks for more chunks than that: very wide tables get longer chunks
+    chunk, n = o.split_plan(1, 1, 3_000_000)
+    assert n <= o.MAX_SPLITS and chunk * n >= 3_000_000
 
 
 # ---------------------------------------------------------------------------------------

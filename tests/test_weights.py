@@ -99,3 +99,36 @@ def test_safetensors_round_trip(tmp_path):
     with SafetensorsFile(p) as f:
         for k, v in t.items():
             assert torch.equal(f.tensor(k), v)
+
+
+def test_a_tied_head_stored_beside_the_embedding_is_accepted_when_equal(tmp_path):
+    """TINY_A ties its head to the embedding table.  A file that also carries lm_head.weight loads when the
+    copy equals the table; when it differs the model would ignore it silently, so the load fails and says so."""
+    d = _folder(tmp_path, TINY_A)
+    path = os.path.join(d, "model.safetensors")
+    with SafetensorsFile(path) as f:
+        tensors = {n: f.tensor(n) for n in f.names()}
+    _, _, model = model_on_cpu(TINY_A)
+    dup = dict(model.spec.duplicate_tensors)
+    assert dup == {"lm_head.weight": "model.embed_tokens.weight"}
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(path, tensors)
+    out = load_weights(d, model.weight_specs(), "float32", "cpu", duplicates=dup)
+    assert "lm_head.weight" not in out
+    with pytest.raises(WeightError) as e:                       # without the declaration it stays unexpected
+        load_weights(d, model.weight_specs(), "float32", "cpu")
+    assert e.value.unexpected == ["lm_head.weight"]
+    tensors["lm_head.weight"] = tensors["lm_head.weight"] + 1
+    write_safetensors(path, tensors)
+    with pytest.raises(WeightError, match="the two differ"):
+        load_weights(d, model.weight_specs(), "float32", "cpu", duplicates=dup)
+
+
+def test_a_sharded_checkpoint_is_refused_by_name(tmp_path):
+    d = _folder(tmp_path, TINY_A)
+    os.remove(os.path.join(d, "model.safetensors"))
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        f.write("{}")
+    _, _, model = model_on_cpu(TINY_A)
+    with pytest.raises(FileNotFoundError, match="sharded"):
+        load_weights(d, model.weight_specs(), "float32", "cpu")

@@ -93,5 +93,16 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     rc = fn(z.data_ptr(), z.data_ptr(), z.data_ptr(), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, 16, 1, 0, 1.0,
             z.data_ptr(), 4096, 32, 8, 64, 256, 16, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == -30                                           # IMPARO_ERR_STATIC_SCRATCH_TOO_SMALL, nothing launched
+    # more key chunks than the combine kernel can hold, although the partials would fit the array: refused (-2)
+    args = lambda n_tok, nh, nkv, hd, chunk, n_splits, max_blocks: (
+        z.data_ptr(), z.data_ptr(), z.data_ptr(), 0, z.data_ptr(), z.data_ptr(), z.data_ptr(), max_blocks, 16, 1, 0, 1.0,
+        z.data_ptr(), n_tok, nh, nkv, hd, chunk, n_splits, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert need(1, 1, 16, 4096) <= 2 * 1024 * 1024
+    assert fn(*args(1, 1, 1, 16, 32, 4096, 1)) == -2
+    # chunks that do not cover the block table (keys would be dropped silently): refused (-2)
+    assert fn(*args(1, 1, 1, 16, 64, 2, 64)) == -2
+    # a head size or head counts the kernel does not take, checked before the scratch need is computed
+    assert fn(*args(1, 1, 1, 24, 64, 1, 1)) == -3
+    assert fn(*args(1, 3, 2, 16, 64, 1, 1)) == -5
     torch.cuda.synchronize()
     ops.read_status(status)
