@@ -23,10 +23,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// false when the wait ran out
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// false when the wait ran out (after `limit` polls)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");

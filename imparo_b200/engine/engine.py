@@ -110,10 +110,12 @@ class Engine:
 
     def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
         """items: StepItem(request, tokens, want).  Returns float32 logits [wanted, vocab]
-        on the device, or None."""
+        on the device, or None.  The result is the caller's own tensor: the step function writes
+        its logits into a buffer that the next step of the same shape overwrites (a workspace view,
+        or a captured graph's output), so what is handed out here is a copy of it."""
         self._check_tokens(items)
         out = self.step_fn(items)
-        return out
+        return None if out is None else out.clone()
 
     def check_device_status(self) -> None:
         ops.read_status(self.status)
@@ -160,13 +162,13 @@ class Engine:
         t_log = t0
         gen = {rid: 0 for rid in tokens}        # tokens sampled so far per request (values may still be on the device)
         dead = set()                            # ended by a stop token
-        zombies = set()                         # ended, but still part of the step in flight: aborted after it
         carry = None                            # (wanting entries, PendingSample): sampled, values not read yet
 
         def settle(c) -> None:
             """Read a step's sampled ids and book them.  The scheduler was already told that
-            these requests go on; one that hit a stop token is ended now (or after the step in
-            flight, if it is part of it)."""
+            these requests go on; one that hit a stop token is ended now.  This runs between
+            step_done and the next plan, so the request is in no planned step; if the step in
+            flight holds a row of it, that row is wasted work whose pages nobody reads."""
             entries, pending = c
             for e, tok in zip(entries, pending.result()):
                 r = e.request
@@ -175,7 +177,7 @@ class Engine:
                 if tok in stops:
                     dead.add(r)
                     if sched.abort(r) == -2:
-                        zombies.add(r)
+                        raise RuntimeError("a request ended by a stop token is part of a planned step")
                 else:
                     out[index[r]].append(tok)
                     tokens[r].append(tok)
@@ -196,19 +198,24 @@ class Engine:
                 continue
             idle = 0
             # Rows whose token is the id the step in flight is sampling take it from that step's output
-            # on the device; prompt portions bring tokens the host knows.  Only a row that needs a
-            # value which is neither makes the host read the pending ids first.
+            # on the device; prompt portions bring tokens the host knows.  Nothing else occurs: the
+            # pending ids are read right after the next step is issued, so the only values the host
+            # lacks when it plans are those of the step in flight, each wanted by a request whose next
+            # row is that one token; and a request preempted in a plan call is not admitted again in
+            # the same call, so its recomputation starts with every token on the host
+            # (tests/test_scheduler.py checks this over random runs).
             pending_at = {e.request: i for i, e in enumerate(carry[0])} if carry is not None else {}
             unknown = [e for e in plan if e.start + e.count > len(tokens[e.request])]
-            fed = carry is not None and all(e.count == 1 and e.start == len(tokens[e.request]) and e.request in pending_at
-                                            for e in unknown)
-            if carry is not None and not fed:
-                settle(carry)
-                carry = None
+            for e in unknown:
+                if not (e.count == 1 and e.start == len(tokens[e.request]) and e.request in pending_at):
+                    sched.step_done(False)
+                    raise RuntimeError(f"request {e.request}: the plan needs a token that is neither on the host "
+                                       "nor being sampled by the step in flight")
+            fed = carry is not None
             items, token_src = [], []
             for e in plan:
                 want = [e.count - 1] if e.want else []
-                if fed and e.start + e.count > len(tokens[e.request]):
+                if e.start + e.count > len(tokens[e.request]):
                     items.append(StepItem(e.request, [0], want))
                     token_src.append(pending_at[e.request])
                 else:
@@ -224,9 +231,6 @@ class Engine:
             if fed:
                 settle(carry)                   # while the step just launched runs
                 carry = None
-            for r in [z for z in zombies]:
-                if sched.abort(r) != -2:
-                    zombies.discard(r)
             wanting = [e for e in plan if e.want and e.request not in dead]
             all_wanting = [e for e in plan if e.want]
             if all_wanting:

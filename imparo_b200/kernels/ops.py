@@ -111,6 +111,15 @@ def read_status(status: torch.Tensor) -> None:
                           f"(kernel {s[1]}, index {s[2]}, value {s[3]})")
 
 
+def selftest_wait_limit(status: torch.Tensor, limit: int = 1000) -> int:
+    """Runs a kernel whose bounded wait cannot complete (csrc/kernels/selftest.cu).  Returns 2 when the kernel
+    gave up, recorded the wait-limit code in `status` and ran to its end; 1 if the wait completed (it cannot)."""
+    _cuda(status)
+    outcome = torch.zeros(1, dtype=torch.int32, device=status.device)
+    _check(_lib.kernels().imparo_selftest_wait_limit(_ptr(status), int(limit), _ptr(outcome), _stream()), "selftest_wait_limit")
+    return int(outcome.item())
+
+
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
     _cuda(table, ids, out, status)
     _pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void

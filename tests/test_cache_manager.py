@@ -143,3 +143,38 @@ def test_groups_are_formed_by_need():
     cm = CacheManager(specs, 4, 8, 2, device=None)
     assert cm.n_groups == 3
     assert cm.group_entries == [[0, 3], [2, 5], [6]]
+
+
+def test_block_tables_address_rows_as_the_reference_rule_does():
+    """tests/golden/kv_paging_golden.json holds what the reference's own physical_row
+    (imparo-cuda/native/kv_paging.cuh:25-30) gives for shuffled block tables at its page size of 64.  The
+    engine's rule, row = table[pos // page] * page + pos % page, with the table the cache manager hands to the
+    kernels, must give the same rows: requests are added and released so that the manager's table for one
+    request becomes each golden table."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kv_paging_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    assert len(cases) >= 3
+    for c in cases:
+        page, want_table = c["page"], c["table"]
+        n = len(want_table)
+        cm = CacheManager([(0, (PagedKV(1, 16),))], page, n, n + 1, device=None)
+        # one holder request per block, so that every block is taken; then the holders give their blocks back in
+        # the order the golden table names them while request 100 grows: the lowest free block is always the next one
+        for b in range(n):
+            cm.add(b)
+            cm.reserve(b, 1)
+            cm.commit(b, 1)
+            assert list(cm.table(b, 0)) == [b]
+        cm.add(100)
+        for b in want_table:
+            cm.release(b)
+            cm.reserve(100, page)
+            cm.commit(100, page)
+        table = [int(x) for x in cm.table(100, 0)]
+        assert table == want_table
+        for pos, row in zip(c["logical"], c["physical"]):
+            assert table[pos // page] * page + pos % page == row
+        cm.release(100)
+        cm.check()

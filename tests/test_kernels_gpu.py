@@ -747,3 +747,96 @@ def test_take_sampled_tokens(n, n_prev):
     o.take_sampled_tokens(d_ids, torch.from_numpy(src).to(DEV), torch.from_numpy(prev).to(DEV))
     want = np.where(src >= 0, prev[np.clip(src, 0, None)], ids)
     assert np.array_equal(d_ids.cpu().numpy(), want)
+
+
+# ---------------------------------------------------------------------------------------
+# failure paths that hang and fault nothing
+def test_a_bounded_wait_that_runs_out_reports_and_returns():
+    """Every device wait has a poll limit.  A kernel waits on a barrier nothing completes: it must give up,
+    record the wait-limit code in the status word and run to its end; the context stays usable."""
+    o = ops()
+    status = o.new_status(DEV)
+    assert o.selftest_wait_limit(status, limit=2000) == 2
+    with pytest.raises(o.KernelError, match="bounded device wait"):
+        o.read_status(status)
+    o.read_status(status)                                    # cleared by the read; later work runs
+    x = torch.ones(2, 8, device=DEV)
+    out = torch.empty(2, 8, device=DEV)
+    o.rmsnorm(x, torch.ones(8, device=DEV), 1e-5, out)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, torch.ones(2, 8, device=DEV), atol=1e-4)
+
+
+@pytest.mark.parametrize("bad_slot", [5, -1, 1 << 20])
+def test_gated_conv_reports_a_state_slot_out_of_range(bad_slot):
+    """A slot index outside the state arena is reported through the status word; the request's state and
+    output are not touched, the other requests' are computed."""
+    o = ops()
+    H, taps, n_slots, lens = 24, 3, 5, [1, 4, 1]
+    g = torch.Generator().manual_seed(1)
+    T = sum(lens)
+    bcx = torch.randn(T, 3 * H, generator=g).to(DEV)
+    w = torch.randn(H, taps, generator=g).to(DEV)
+    state = torch.randn(n_slots, taps - 1, H, generator=g).to(DEV)
+    before = state.clone()
+    row_start = torch.tensor([0, 1, 5, 6], dtype=torch.int32, device=DEV)
+    iot = torch.tensor([0, 1, 1, 1, 1, 2], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, bad_slot, 0], dtype=torch.int32, device=DEV)
+    y = torch.full((T, H), 7.0, device=DEV)
+    status = o.new_status(DEV)
+    o.gated_conv(bcx, w, None, state, row_start, iot, slots, y, taps, status)
+    with pytest.raises(o.KernelError, match="state slot"):
+        o.read_status(status)
+    assert torch.equal(state[[1, 3, 4]], before[[1, 3, 4]])          # untouched slots
+    assert not torch.equal(state[2], before[2]) and not torch.equal(state[0], before[0])
+    assert torch.equal(y[1:2], torch.full((1, H), 7.0, device=DEV))   # the bad request's first row was not written
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cache_rows_are_addressed_as_the_reference_addresses_them(dtype):
+    """tests/golden/kv_paging_golden.json: physical cache rows from the reference's own physical_row
+    (imparo-cuda/native/kv_paging.cuh:25-30) for shuffled block tables, page size 64.  The store kernel must put a
+    token's value row exactly there, and the attention kernels must find it there."""
+    o = ops()
+    with open(os.path.join(HERE, "golden", "kv_paging_golden.json")) as f:
+        cases = json.load(f)["cases"]
+    nh = nkv = 1
+    hd = 64
+    for c in cases:
+        page, table = c["page"], np.array([c["table"]], dtype=np.int32)
+        n_pages = table.shape[1]
+        seen, logical, physical = set(), [], []
+        for l, p in zip(c["logical"], c["physical"]):
+            if l not in seen:
+                seen.add(l); logical.append(l); physical.append(p)
+        T = len(logical)
+        qkv = torch.zeros(T, 3 * hd)
+        qkv[:, :2 * hd] = 1.0
+        for t in range(T):
+            qkv[t, 2 * hd:] = float(t + 1)                        # the value row names its token
+        kc = torch.zeros(n_pages, page, hd, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        q_out = torch.empty(T, hd, dtype=dtype, device=DEV)
+        status = o.new_status(DEV)
+        ones = torch.ones(hd, device=DEV)
+        o.qk_norm_rope_store(qkv.to(dtype).to(DEV), torch.tensor(logical, dtype=torch.int32, device=DEV),
+                             torch.zeros(T, dtype=torch.int32, device=DEV), ones, ones, None, 0, 1e-6, q_out, kc, vc,
+                             torch.from_numpy(table).to(DEV), page, n_pages, nh, nkv, hd, status)
+        o.read_status(status)
+        rows = vc.view(n_pages * page, hd).float().cpu()
+        want = torch.zeros(n_pages * page)
+        for t, p in enumerate(physical):
+            want[p] = t + 1
+        assert torch.equal(rows[:, 0], want) and torch.equal(rows[:, hd - 1], want)
+        # reading: a query at the last position of the table, every stored key scores alike except one that is
+        # scaled up; the output must be that token's value
+        star = T // 2
+        kc.view(n_pages * page, hd)[physical[star]] *= 30.0
+        pos = n_pages * page - 1
+        for kind in ("general", "split", "split_mma"):
+            out = torch.empty(1, hd, dtype=dtype, device=DEV)
+            run_attention(kind, torch.ones(1, hd, dtype=dtype, device=DEV), kc, vc, torch.tensor([pos], dtype=torch.int32, device=DEV),
+                          torch.zeros(1, dtype=torch.int32, device=DEV), torch.from_numpy(table).to(DEV), page, n_pages, None,
+                          1 / math.sqrt(hd), out, nh, nkv, hd, status)
+            o.read_status(status)
+            assert abs(float(out[0, 0]) - (star + 1)) < 0.05 * (star + 1), (kind, float(out[0, 0]), star + 1)

@@ -167,6 +167,86 @@ def test_full_width_layers_bfloat16_against_32_bit():
     assert np.abs(ref[0] - ref[-1]).max() > 0.2 * scale
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_full_width_layers_against_the_plain_implementation(dtype, tmp_path_factory):
+    """One conv layer and one attention layer at LFM2-1.2B width (hidden 2048, 32 heads in 8 groups, head 64,
+    ff 8192, vocabulary 65536) from a model folder, against the plain implementation in float64 on the same
+    folder: a mistake that the bfloat16 and the 32-bit path share at width (a descriptor, a table stride) cannot
+    pass here.  Three ways of cutting: the prompt whole and then single tokens; portions of 64 tokens (the
+    tensor-core product at its widest token tile); a stretch of single tokens from the start."""
+    import torch
+    from imparo_b200.engine import Engine, StepItem
+    from imparo_b200.weights import write_random_model
+    from tests.plain.lfm2_plain import PlainLfm2
+    cfg = {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 65536, "hidden_size": 2048,
+           "num_hidden_layers": 2, "layer_types": ["conv", "full_attention"], "num_attention_heads": 32,
+           "num_key_value_heads": 8, "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+           "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_embedding": True,
+           "max_position_embeddings": 4096}
+    d = _full_width_folder(cfg, tmp_path_factory)
+    rng = np.random.default_rng(17)
+    toks = rng.integers(0, 65536, 300 + 6).tolist()
+    want_prompt = [0, 63, 64, 150, 299]
+    ref = _full_width_reference(d, tuple(toks))
+    scale = float(np.abs(ref).max())
+    tol = (2.5e-2 if dtype == "bfloat16" else 2e-5) * scale
+    eng = Engine(d, dtype=dtype, ctx=512, parallel=3, page_size=16, max_step_tokens=512)
+
+    def check(got, places, what):
+        for row, p in zip(got, places):
+            err = float(np.abs(row - ref[p]).max())
+            assert err <= tol, f"{what}: position {p}: error {err:.3e} > {tol:.3e}"
+
+    # 1. the prompt whole, then its last six tokens one by one
+    eng.add_request(1)
+    check(eng.step([StepItem(1, toks[:300], want_prompt)]).cpu().numpy(), want_prompt, "whole")
+    for i in range(300, 306):
+        check(eng.step([StepItem(1, [toks[i]], [0])]).cpu().numpy(), [i], "single tokens after the prompt")
+    eng.end_request(1)
+    # 2. portions of 64 tokens
+    eng.add_request(2)
+    for a in range(0, 306, 64):
+        part = toks[a:a + 64]
+        places = [p for p in want_prompt + [305] if a <= p < a + len(part)]
+        out = eng.step([StepItem(2, part, [p - a for p in places])])
+        if places:
+            check(out.cpu().numpy(), places, "portions of 64")
+    eng.end_request(2)
+    # 3. single tokens from the start (the decode kernels at short contexts), beside a second request's portion
+    eng.add_request(3)
+    eng.add_request(4)
+    for i in range(40):
+        items = [StepItem(3, [toks[i]], [0])]
+        if i % 8 == 0:
+            items.append(StepItem(4, toks[i * 4:i * 4 + 32], [31]))
+        out = eng.step(items).cpu().numpy()
+        check(out[:1], [i], "single tokens from the start")
+        if i % 8 == 0:
+            check(out[1:], [i * 4 + 31], "a portion beside a single token")
+    eng.check_device_status()
+    eng.end_request(3); eng.end_request(4)
+    eng.cache.check()
+    del eng
+    torch.cuda.empty_cache()
+
+
+_FULL_WIDTH = {}
+
+
+def _full_width_folder(cfg, tmp_path_factory):
+    from imparo_b200.weights import write_random_model
+    if "dir" not in _FULL_WIDTH:
+        _FULL_WIDTH["dir"] = write_random_model(str(tmp_path_factory.mktemp("full_width")), cfg, seed=5, dtype="bfloat16")
+    return _FULL_WIDTH["dir"]
+
+
+def _full_width_reference(folder, toks):
+    from tests.plain.lfm2_plain import PlainLfm2
+    if "ref" not in _FULL_WIDTH:
+        _FULL_WIDTH["ref"] = PlainLfm2(folder, np.float64).logits(list(toks))
+    return _FULL_WIDTH["ref"]
+
+
 def test_long_context_whole_against_portions():
     """6,000 positions: hundreds of pages per request, table rows of several hundred blocks, key
     chunks and tiles far from position 0.  Whole prompt against 1,024-token portions and single

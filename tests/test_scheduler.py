@@ -169,3 +169,97 @@ def test_context_limit_ends_a_request():
     while s.has_work():
         run_step(s, s.plan()); n += 1
     assert n == 2 and cm.free_pages(0) == 64      # 10 -> 11 -> 12 known: stop
+
+
+def test_abort_in_the_middle_of_a_prompt_gives_everything_back():
+    """A request cancelled while its prompt is still entering in portions: slot and pages go back at once,
+    the others go on (the reference forgets a failed request and returns what it held:
+    imparo-server/src/sched.rs:857-883)."""
+    cm, s = make(pages=64, page=4, slots=3, budget=8)
+    a, b = s.submit(30, 4), s.submit(5, 4)
+    p = s.plan()
+    assert [(e.request, e.count) for e in p] == [(a, 8)]
+    run_step(s, p)
+    p = s.plan()                                     # a's second portion is planned (pages reserved)
+    assert (p[0].request, p[0].start, p[0].count) == (a, 8, 8)
+    assert s.abort(a) == -2                          # part of the planned step: not now
+    run_step(s, p)
+    assert cm.cached(a) == 16 and cm.free_pages(0) == 64 - 4 and cm.free_slots() == 2
+    assert s.abort(a) == 0                           # between steps: released
+    assert not cm.has(a) and cm.free_pages(0) == 64 and cm.free_slots() == 3
+    assert s.abort(a) == -1                          # unknown by now
+    p = s.plan()
+    assert [(e.request, e.start, e.count, e.want) for e in p] == [(b, 0, 5, True)]
+    while s.has_work():
+        run_step(s, s.plan())
+    assert cm.n_requests() == 0 and cm.free_pages(0) == 64 and cm.free_slots() == 3
+    cm.check()
+
+
+def test_abort_of_a_waiting_request():
+    cm, s = make(slots=1, budget=8)
+    a, b = s.submit(4, 2), s.submit(4, 2)
+    run_step(s, s.plan())
+    assert s.n_waiting == 1 and s.abort(b) == 0 and s.n_waiting == 0
+    while s.has_work():
+        run_step(s, s.plan())
+    assert cm.n_requests() == 0
+    cm.check()
+
+
+_PREEMPTIONS_SEEN = []
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_a_planned_row_never_needs_a_token_older_than_the_step_in_flight(seed):
+    """What Engine.generate's pipelined loop relies on.  It reads a step's sampled ids only after the NEXT step
+    has been issued.  So when it plans, the only values it lacks are those the step in flight is sampling,
+    and the plan must ask for such a value only as the single token of a one-token row of the very request
+    that wanted it; in particular a request that is preempted is never planned again before its
+    last token has reached the host.  Random lengths, budgets and pools small enough to force preemptions;
+    requests end by stop tokens (found one step late, as in the engine) and by length."""
+    import random
+    rng = random.Random(seed)
+    page, slots = rng.choice([2, 4]), rng.choice([2, 3, 5])
+    pages = rng.randint(14, 40)
+    cm, s = make(pages=pages, page=page, slots=slots, budget=rng.choice([4, 8, 16]), ctx=120)
+    host_known = {}                                  # request -> tokens whose values the host holds
+    for _ in range(rng.randint(4, 10)):
+        n = rng.randint(1, min(40, (pages - slots) * page))
+        host_known[s.submit(n, rng.randint(1, 12))] = n
+    in_flight = []                                   # requests whose sampled id is still on the device
+    dead = set()
+    steps = 0
+    while s.has_work() or in_flight:
+        p = s.plan() if s.has_work() else []
+        for r in s.take_failed():
+            host_known.pop(r, None)
+        if p:
+            for e in p:
+                need = e.start + e.count
+                if need > host_known[e.request]:
+                    assert e.count == 1 and e.start == host_known[e.request] and e.request in in_flight, \
+                        (seed, steps, e, host_known[e.request], in_flight)
+            s.step_done(True)
+        # the ids of the step before are read now, while the step just issued runs
+        for r in in_flight:
+            if r in dead:
+                continue
+            if rng.random() < 0.08:                  # it was a stop token
+                dead.add(r)
+                assert s.abort(r) in (0, -1)         # never -2: nothing is planned between step_done and plan
+            elif r in host_known:                    # (a request that failed alone meanwhile is gone)
+                host_known[r] += 1
+        in_flight = []
+        for e in p:
+            if e.want:
+                in_flight.append(e.request)
+                if e.request not in dead:
+                    s.on_token(e.request, False)     # optimistic, as the engine books it
+        steps += 1
+        assert steps < 5000
+    assert cm.n_requests() == 0 and cm.free_pages(0) == pages and cm.free_slots() == slots
+    cm.check()
+    _PREEMPTIONS_SEEN.append(s.n_preemptions)
+    if seed == 11:
+        assert sum(_PREEMPTIONS_SEEN) > 0            # the pools were small enough to matter
