@@ -206,40 +206,77 @@ def _preset(name):
 
 
 def workload_continuous(args):
-    """LFM2-700M sizes: requests with prompt lengths uniform in [64, 4096] through 32 slots, prompts
-    in portions under a 512-token step budget beside the running decode rows, temperature 0.7
-    (seeded), 128 new tokens each; with more requests than slots, slots and pages are used again."""
+    """LFM2-700M sizes: a continuous batch of requests (32 unless --requests says otherwise) with prompt lengths
+    uniform in [64, 4096] through 32 slots, prompts in portions under a 512-token step budget beside the running
+    decode rows, temperature 0.7 (seeded), 128 new tokens each; requests join and leave mid-run, and with more
+    requests than slots, slots and pages are used again.  Besides tokens per second: the step-time split (the
+    reference prints step / gpu / gap medians for its loop, imparo-server/src/sched.rs:572-649): per class of step
+    (decode rows only; portions beside decode rows; portions only) the device time between the events recorded after
+    consecutive steps, the host time between their launches, and, for steps of decode rows only, the bytes they have
+    to read (weights once, the cache of their rows) over that time against the measured HBM peak."""
     import numpy as np
+    import torch
     from imparo_b200.engine import Engine
     from imparo_b200.kernels import ops
     rng = np.random.default_rng(1)
     n, slots, new = args.requests, 32, 128
     engine = Engine(config=_preset("lfm2_700m"), seed=0, dtype="bfloat16", ctx=4096 + new, parallel=slots, page_size=PAGE,
                     max_step_tokens=512, random_init={"norm_jitter": 0.0})
+    pk = peaks()
+    weight_bytes, kv_per_token, prefill_flops, n_params = model_numbers(engine)
     V = engine.vocab_size
     lens = [int(x) for x in rng.integers(64, 4097, n)]
     prompts = [rng.integers(0, V, k).tolist() for k in lens]
     engine.generate(prompts[:4], max_tokens=8, temperature=0.7, seed=list(range(4)))       # warm-up: buffers, first graphs
-    shapes = {"steps": 0, "mixed": 0, "rows": 0}
+    steps = []                # per step: (class, event after it, host time, bytes of a decode-only step, tokens)
 
     def on_step(plan):
-        shapes["steps"] += 1
-        shapes["mixed"] += any(e.count > 1 for e in plan) and any(e.count == 1 for e in plan)
-        shapes["rows"] += len(plan)
-    before, replays = dict(ops.COUNTS), engine.step_fn.graph_replays
+        portions = any(e.count > 1 or e.start == 0 for e in plan)
+        rows = any(e.count == 1 and e.start > 0 for e in plan)
+        kind = "portions_beside_decode_rows" if portions and rows else ("portions_only" if portions else "decode_rows_only")
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        nbytes = weight_bytes + kv_per_token * sum(e.start + e.count for e in plan)
+        steps.append((kind, ev, time.perf_counter(), nbytes, sum(e.count for e in plan), len(plan)))
+    before, replays, captures = dict(ops.COUNTS), engine.step_fn.graph_replays, engine.step_fn.graph_captures
     with ClockSampler() as clocks:
         t0 = time.perf_counter()
         out = engine.generate(prompts, max_tokens=new, temperature=0.7, seed=list(range(n)), on_step=on_step, stop_token_ids=[])
+        torch.cuda.synchronize()
         dt = time.perf_counter() - t0
     assert all(len(o) == new for o in out)
     st = engine.stats()
+    split = {}
+    for kind in ("decode_rows_only", "portions_beside_decode_rows", "portions_only"):
+        dev, host, gbs, toks = [], [], [], []
+        for i in range(1, len(steps)):
+            if steps[i][0] != kind:
+                continue
+            d_ms = steps[i - 1][1].elapsed_time(steps[i][1])
+            dev.append(d_ms)
+            host.append((steps[i][2] - steps[i - 1][2]) * 1e3)
+            toks.append(steps[i][4])
+            if kind == "decode_rows_only" and d_ms > 0:
+                gbs.append(steps[i][3] / (d_ms * 1e-3) / 1e9)
+        if dev:
+            split[kind] = {"steps": len(dev), "device_ms_median": round(statistics.median(dev), 4),
+                           "host_ms_between_launches_median": round(statistics.median(host), 4),
+                           "tokens_per_step_mean": round(sum(toks) / len(toks), 1)}
+            if gbs:
+                split[kind]["roofline"] = {"bound": "hbm", "achieved": round(statistics.median(gbs), 1), "peak": pk["hbm_gbs"],
+                                           "unit": "GB/s", "frac": round(statistics.median(gbs) / pk["hbm_gbs"], 4),
+                                           "peaks": pk["source"]}
+    device_total = steps[0][1].elapsed_time(steps[-1][1]) * 1e-3 if len(steps) > 1 else 0.0
+    flops = sum(prefill_flops(k) for k in lens)
     print(json.dumps({
         "metric": "LFM2-700M continuous batching, prompt + generated tokens per second (wall clock, through Engine.generate)",
         "value": round((sum(lens) + n * new) / dt, 1), "unit": "tokens/s", "generated_per_s": round(n * new / dt, 1),
-        "seconds": round(dt, 3), "requests": n, "slots": slots, "prompt_tokens": sum(lens), "new_tokens": n * new,
-        "step_budget": 512, "steps": shapes["steps"], "steps_with_portions_beside_decode_rows": shapes["mixed"],
-        "mean_rows_per_step": round(shapes["rows"] / max(shapes["steps"], 1), 1),
-        "graph_replays": engine.step_fn.graph_replays - replays, "graph_captures": engine.step_fn.graph_captures,
+        "seconds": round(dt, 3), "device_seconds_first_to_last_step": round(device_total, 3),
+        "requests": n, "slots": slots, "prompt_tokens": sum(lens), "new_tokens": n * new,
+        "step_budget": 512, "steps": len(steps), "mean_rows_per_step": round(sum(s_[5] for s_ in steps) / max(len(steps), 1), 1),
+        "step_time_split": split,
+        "prompt_flops_over_time_frac_of_bf16_peak": round(flops / max(dt, 1e-9) / (pk["bf16_tflops"] * 1e12), 4),
+        "graph_replays": engine.step_fn.graph_replays - replays, "graph_captures": engine.step_fn.graph_captures - captures,
         "graph_resets": engine.step_fn.graph_resets, "preemptions": st["preemptions"], "failed": st["failed"],
         "own_kernel_launches": ops.COUNTS["own"] - before["own"], "library_gemms": ops.COUNTS["library"] - before["library"],
         "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "clocks": clocks.summary()}))
@@ -247,56 +284,107 @@ def workload_continuous(args):
 
 
 def workload_long(args):
-    """LFM2-350M sizes: 4 requests with 32,768-token prompts and 512 greedy tokens each, in bfloat16
-    and in 32-bit; in 32-bit also the logits at the prompt's last position, whole against portions
-    of 1,024 tokens."""
+    """LFM2-350M sizes: 4 requests with 32,768-token prompts and 512 greedy tokens each, in bfloat16 (all 16 layers:
+    throughput, with the prefill's flops over its time against the measured bfloat16 peak and the decode step's bytes
+    over its time against the measured HBM peak).  Then the 32-bit check: the logits at sampled positions of one
+    32,768-token prompt, through the engine whole and in portions of 1,024 tokens, against the plain implementation
+    (tests/plain, numpy, whole sequence, no cache).  The plain forward over 32,768 tokens is slow, so the check runs
+    on the first --long-check-layers layers of the configuration (4 by default: two convolution blocks and two
+    attention blocks, every width as configured); `config` names both numbers."""
+    import tempfile
     import numpy as np
     import torch
     from imparo_b200.engine import Engine, StepItem
+    from imparo_b200.weights import write_random_model
     cfg = _preset("lfm2_350m")
+    pk = peaks()
     rng = np.random.default_rng(2)
     P, new, B = 32768, 512, 4
     out = {"metric": "LFM2-350M long context: 4 x 32,768-token prompts + 512 greedy tokens", "unit": "tokens/s",
-           "data": "synthetic (random weights, uniform-random token ids)"}
-    prompts = None
-    for dtype in ("bfloat16", "float32"):
-        engine = Engine(config=cfg, seed=0, dtype=dtype, ctx=P + new, parallel=B, page_size=PAGE, max_step_tokens=P,
-                        random_init={"norm_jitter": 0.0})
-        if prompts is None:
-            prompts = [rng.integers(0, engine.vocab_size, P).tolist() for _ in range(B)]
-        n_new = new if dtype == "bfloat16" else 32          # the 32-bit path is for checks: a few decode steps suffice
-        stamps = []
-        torch.cuda.synchronize()
+           "data": "synthetic (random weights, uniform-random token ids)", "dtype": "bf16 (throughput), fp32 (check)"}
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=P + new, parallel=B, page_size=PAGE, max_step_tokens=P,
+                    random_init={"norm_jitter": 0.0})
+    weight_bytes, kv_per_token, prefill_flops, n_params = model_numbers(engine)
+    prompts = [rng.integers(0, engine.vocab_size, P).tolist() for _ in range(B)]
+    stamps = []
+
+    def on_step(plan):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        stamps.append((time.perf_counter(), sum(e.count for e in plan), ev))
+    torch.cuda.synchronize()
+    with ClockSampler() as clocks:
         t0 = time.perf_counter()
-        got = engine.generate(prompts, max_tokens=n_new, stop_token_ids=[],
-                              on_step=lambda plan: stamps.append((time.perf_counter(), sum(e.count for e in plan))))
+        got = engine.generate(prompts, max_tokens=new, stop_token_ids=[], on_step=on_step)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-        assert all(len(g) == n_new for g in got)
-        t_first_decode = next(t for t, c in stamps if c == B)       # the first step of decode rows only was issued
-        decode_steps = sum(1 for _, c in stamps if c == B)
-        key = "bf16" if dtype == "bfloat16" else "fp32"
-        out[key] = {"seconds": round(dt, 3), "prefill_tokens_per_s": round(B * P / (t_first_decode - t0), 1),
-                    "decode_tokens_per_s": round(B * (decode_steps - 1) / max(stamps[-1][0] - t_first_decode, 1e-9), 1),
-                    "new_tokens_each": n_new}
-        if dtype == "float32":
-            # the same prompt whole and in 1,024-token portions: logits at its last position
-            rows = []
-            for cut in (P, 1024):
-                engine.add_request(900 + cut)
-                at = 0
-                while at < P:
-                    k = min(cut, P - at)
-                    lg = engine.step([StepItem(900 + cut, prompts[0][at:at + k], [k - 1] if at + k == P else [])])
-                    at += k
-                rows.append(lg[0].double().cpu())
-                engine.end_request(900 + cut)
-            scale = float(rows[0].abs().max())
-            out[key]["whole_vs_1024_portions_max_abs_diff"] = float((rows[0] - rows[1]).abs().max())
-            out[key]["logit_scale"] = scale
-            out[key]["same_argmax"] = bool(int(rows[0].argmax()) == int(rows[1].argmax()))
-        del engine
-        torch.cuda.empty_cache()
+    assert all(len(g) == new for g in got)
+    first_decode = next(i for i, (_, c, _) in enumerate(stamps) if c == B)
+    prefill_s = stamps[first_decode][0] - t0
+    decode = [stamps[i - 1][2].elapsed_time(stamps[i][2]) for i in range(first_decode + 1, len(stamps)) if stamps[i][1] == B]
+    dec_ms = statistics.median(decode)
+    step_bytes = weight_bytes + B * (P + new / 2) * kv_per_token
+    out["value"] = round(B * P / prefill_s, 1)
+    out["bf16"] = {"seconds": round(dt, 3), "prefill_tokens_per_s": round(B * P / prefill_s, 1),
+                   "prefill": {"tokens": B * P, "ms": round(prefill_s * 1e3, 1),
+                               "frac": round(B * prefill_flops(P) / prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
+                   "decode_tokens_per_s": round(B * 1000.0 / dec_ms, 1), "decode_ms_per_step": round(dec_ms, 4),
+                   "roofline": {"bound": "hbm", "achieved": round(step_bytes / (dec_ms * 1e-3) / 1e9, 1), "peak": pk["hbm_gbs"],
+                                "unit": "GB/s", "frac": round(step_bytes / (dec_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                                "peaks": pk["source"], "bytes_per_step": int(step_bytes)},
+                   "new_tokens_each": new, "layers": cfg["num_hidden_layers"]}
+    del engine
+    torch.cuda.empty_cache()
+
+    # ---- the 32-bit check against the plain implementation ----
+    from tests.plain.lfm2_plain import PlainLfm2
+    n_layers = args.long_check_layers
+    small = dict(cfg)
+    # the configuration's first blocks up to and including its second attention block, cut to n_layers by keeping the
+    # last n_layers of them: two convolution and two attention blocks at the default of 4
+    types = list(cfg["layer_types"])
+    second_attn = [i for i, t_ in enumerate(types) if t_ != "conv"][1]
+    small["layer_types"] = types[max(0, second_attn + 1 - n_layers):second_attn + 1] if n_layers < len(types) else types
+    small["num_hidden_layers"] = len(small["layer_types"])
+    places = [0, 1023, 1024, 16384, P - 1]
+    toks = prompts[0]
+    with tempfile.TemporaryDirectory(prefix="imparo_b200_long_") as d:
+        write_random_model(d, small, seed=0, dtype="float32", norm_jitter=0.1)
+        t1 = time.perf_counter()
+        ref = PlainLfm2(d, np.float32).logits_at(toks, places, attend_block=256).astype(np.float64)
+        plain_s = time.perf_counter() - t1
+        engine = Engine(d, dtype="float32", ctx=P, parallel=1, page_size=PAGE, max_step_tokens=P)
+        rows = {}
+        for name, cut in (("whole", P), ("portions_of_1024", 1024)):
+            engine.add_request(900 + cut)
+            got_rows, at = [], 0
+            t2 = time.perf_counter()
+            while at < P:
+                k = min(cut, P - at)
+                want = [p_ - at for p_ in places if at <= p_ < at + k]
+                lg = engine.step([StepItem(900 + cut, toks[at:at + k], want)])
+                if want:
+                    got_rows.append(lg.double().cpu().numpy())
+                at += k
+            torch.cuda.synchronize()
+            rows[name] = (np.concatenate(got_rows), time.perf_counter() - t2)
+            engine.end_request(900 + cut)
+        engine.check_device_status()
+    scale = float(np.abs(ref).max())
+    out["fp32"] = {"layers": small["num_hidden_layers"], "layers_of_config": cfg["num_hidden_layers"],
+                   "layer_types": small["layer_types"], "positions": places, "logit_scale": round(scale, 4),
+                   "vs_plain_max_abs_diff": {k: float(np.abs(v[0] - ref).max()) for k, v in rows.items()},
+                   "vs_plain_max_abs_diff_over_scale": {k: float(np.abs(v[0] - ref).max() / scale) for k, v in rows.items()},
+                   "whole_vs_portions_max_abs_diff": float(np.abs(rows["whole"][0] - rows["portions_of_1024"][0]).max()),
+                   "same_argmax_as_plain": {k: bool((v[0].argmax(-1) == ref.argmax(-1)).all()) for k, v in rows.items()},
+                   "engine_seconds": {k: round(v[1], 2) for k, v in rows.items()}, "plain_seconds": round(plain_s, 1),
+                   "plain": "tests/plain/lfm2_plain.py, numpy float32, whole sequence, attention a block of 256 queries at a time"}
+    out["vs_plain_max_abs_diff"] = max(out["fp32"]["vs_plain_max_abs_diff"].values())
+    out["config"] = {"model": "LFM2-350M", "global_batch": B, "prompt_len": P, "new_tokens": new, "layers": cfg["num_hidden_layers"],
+                     "layers_of_config": cfg["num_hidden_layers"], "check_layers": small["num_hidden_layers"],
+                     "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                     "vocab": cfg["vocab_size"], "page_size": PAGE, "params": n_params}
+    out["clocks"] = clocks.summary()
     print(json.dumps(out))
     return 0
 
@@ -316,7 +404,8 @@ def main():
                     help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit")
-    ap.add_argument("--requests", type=int, default=64, help="continuous: requests in all")
+    ap.add_argument("--requests", type=int, default=32, help="continuous: requests in all (the baseline's workload has 32)")
+    ap.add_argument("--long-check-layers", type=int, default=4, help="long: layers of the 32-bit check against the plain implementation")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "zeraix/imparo is a Rust workspace (no setup.py or pyproject.toml: "

@@ -98,9 +98,27 @@ class CacheManager:
                 shape = (len(self.group_entries[g]), self.num_pages[g], self.page_size, key.width)
                 self.k_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
                 self.v_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
+            # every fixed-size state tensor is a stretch of ONE flat float32 arena, [slots, *shape] each, so that
+            # the slots of requests that start in a step are zeroed by one kernel of the step's own chain
+            # (state_segments: per tensor its offset in the arena and its floats per slot)
+            sizes = []
             for entry, lst in self._state_of_entry.items():
                 for j, spec in lst:
-                    self.state[(entry, j)] = torch.zeros((self.num_slots, *spec.shape), dtype=torch.float32, device=device)
+                    per_slot = 1
+                    for d in spec.shape:
+                        per_slot *= int(d)
+                    per_slot_padded = (per_slot + 3) // 4 * 4                 # 16-byte aligned stretches
+                    sizes.append(((entry, j), spec.shape, per_slot, per_slot_padded))
+            total = sum(self.num_slots * padded for _, _, _, padded in sizes)
+            self.state_arena = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
+            segs, off = [], 0
+            for key, shape, per_slot, padded in sizes:
+                n = self.num_slots * per_slot
+                self.state[key] = self.state_arena[off:off + n].view(self.num_slots, *shape)
+                segs.append((off, per_slot))
+                off += self.num_slots * padded
+            self.state_segments = torch.tensor(segs if segs else [(0, 0)], dtype=torch.int64, device=device)
+            self.n_state_segments = len(segs)
 
     def __del__(self):
         try:

@@ -26,8 +26,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--random", metavar="CONFIG.json", help="random weights for this config.json instead of a model folder")
     ap.add_argument("--write-random", metavar="DIR", help="with --random: write the model folder DIR and exit")
     ap.add_argument("--seed", type=int, default=0, help="seed of random weights and of temperature sampling")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
-    ap.add_argument("-c", "--ctx", type=int, default=4096, help="context length: most positions one request may reach")
+    ap.add_argument("--dtype", default=None, choices=["bfloat16", "float32", "bf16", "fp32"], help="default bfloat16")
+    ap.add_argument("-c", "--ctx", type=int, default=None, help="context length: most positions one request may reach (default 4096)")
+    ap.add_argument("--config-file", metavar="FILE.json", help="engine settings (ctx, parallel, page_size, switches, ...); a flag "
+                    "wins over an IMPARO_* variable, which wins over this file")
     ap.add_argument("-np", "--parallel", type=int, default=None, help="requests that decode at once")
     ap.add_argument("--decode", type=int, default=16, metavar="N", help="new tokens per request (the request's max_tokens)")
     ap.add_argument("--repeat", type=int, default=1, metavar="N", help="run the same requests N times (determinism check)")
@@ -35,9 +37,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("-t", "--tokens-file", metavar="FILE", help="token ids, whitespace-separated, one prompt per line")
     ap.add_argument("--prompt-len", type=int, help="uniform-random prompts of this length instead of given ids")
     ap.add_argument("--batch", type=int, default=1, help="with --prompt-len: how many prompts")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=None, help="positions per cache page (default 16)")
     ap.add_argument("--num-pages", type=int, default=None)
-    ap.add_argument("--max-step-tokens", type=int, default=2048, help="token budget of one step")
+    ap.add_argument("--max-step-tokens", type=int, default=None, help="token budget of one step (default 2048)")
     ap.add_argument("--probe-layer", type=int, default=None, metavar="I",
                     help="print rms, sum and first values of the stages of schedule entry I (for comparing engines; slow)")
     ap.add_argument("--json", action="store_true", help="print one JSON line with tokens and timings")
@@ -69,7 +71,8 @@ def main(argv=None) -> int:
     parallel = args.parallel or max(1, len(prompts) if prompts else args.batch)
     t0 = time.perf_counter()
     engine = Engine(args.model, config=config, seed=args.seed, dtype=args.dtype, ctx=args.ctx, parallel=parallel,
-                    page_size=args.page_size, num_pages=args.num_pages, max_step_tokens=args.max_step_tokens, probe_layer=args.probe_layer)
+                    page_size=args.page_size, num_pages=args.num_pages, max_step_tokens=args.max_step_tokens, probe_layer=args.probe_layer,
+                    config_file=args.config_file)
     load_s = time.perf_counter() - t0
     if not prompts:
         if not args.prompt_len:

@@ -51,9 +51,9 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
 
     float wreg[PER], sn[PAIRS], cs[PAIRS];
     if (is_q || is_k) {
-        const float* w = is_q ? q_w : k_w;
+        const float* w = is_q ? q_w : k_w;                  // null: this side has no per-head norm
 #pragma unroll
-        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; wreg[j] = d < hd ? w[d] : 0.f; }
+        for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; wreg[j] = d < hd ? (w ? w[d] : 1.f) : 0.f; }
         if (inv_freq) {
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) {
@@ -125,7 +125,7 @@ qk_norm_rope_store_kernel(const T* __restrict__ qkv, const int* __restrict__ pos
     }
     if (is_q || is_k) {
         ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        const float scale = (is_q ? q_w : k_w) ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
 #pragma unroll
         for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; if (d < hd) row[d] = val[j] * scale * wreg[j]; }
         __syncwarp();
@@ -172,8 +172,8 @@ qk_norm_rope_rows_kernel(const T* __restrict__ qkv, const int* __restrict__ posi
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         const int d = lane + 32 * j;
-        wq[j] = d < hd ? q_w[d] : 0.f;
-        wk[j] = (d < hd && nkv > 0) ? k_w[d] : 0.f;
+        wq[j] = d < hd ? (q_w ? q_w[d] : 1.f) : 0.f;         // null weights: no per-head norm on that side
+        wk[j] = (d < hd && nkv > 0) ? (k_w ? k_w[d] : 1.f) : 0.f;
         sn[j] = 0.f; cs[j] = 1.f;
         if (inv_freq && j < hj) sincosf((float)pos * inv_freq[d], &sn[j], &cs[j]);
     }
@@ -214,7 +214,7 @@ qk_norm_rope_rows_kernel(const T* __restrict__ qkv, const int* __restrict__ posi
 #pragma unroll
             for (int j = 0; j < PER; ++j) ss += val[j] * val[j];
             ss = warp_sum(ss);
-            const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+            const float scale = (is_q ? q_w : k_w) ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
 #pragma unroll
             for (int j = 0; j < PER; ++j) val[j] = val[j] * scale * (is_q ? wq[j] : wk[j]);
             if (inv_freq) {

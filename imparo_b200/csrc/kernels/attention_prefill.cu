@@ -550,7 +550,8 @@ extern "C" int imparo_attention_split_combine(const float* part_acc, const float
                                               int n_rows, int hd, int n_splits, cudaStream_t stream);
 
 // Single query tokens on tensor cores: bfloat16, head size 64 or 128, at most 8 query heads per
-// kv head; else -8.  Scratch as for imparo_paged_attention_split.
+// kv head; else -8.  Scratch as for imparo_paged_attention_split.  out == nullptr: the partials are
+// left in scratch for a consumer that combines them itself (imparo_gemm_tc_combine).
 extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
                                            const int* positions, const int* item_of_token,
                                            const int* table, int max_blocks, int page_size, int n_pages,
@@ -583,5 +584,6 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
                    (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
                    page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status);
     if (e != cudaSuccess) return (int)e;
+    if (out == nullptr) return 0;
     return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, stream);
 }

@@ -351,6 +351,7 @@ extern "C" int imparo_paged_attention_split(const void* q, const void* k_cache, 
                                            status, stream);
     else return -1;
     if (rc != 0) return rc;
+    if (out == nullptr) return 0;               // the partials stay in scratch for a consumer that combines them itself
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == IMPARO_DT_F32)
         launch(attn_split_combine_kernel<float>, dim3(n_tok * nh), dim3(threads), 0, stream, part_acc, part_ml, (float*)out, hd, n_splits);

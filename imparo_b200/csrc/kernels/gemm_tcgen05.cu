@@ -32,6 +32,13 @@ constexpr int BM = 128;            // rows of W per CTA (MMA M)
 constexpr int THREADS = 192;       // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
 enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU_BF16 = 3, PARTIAL_F32 = 4 };
+// Who makes the token operand.  PROD_NONE: it is a stored tensor, loaded by TMA beside the W tiles.  Otherwise
+// the four epilogue warps (idle during the main loop) compute it after the wait on the previous kernel and write
+// it, as bfloat16 in the MMA's swizzled K-major layout, into shared memory for all k-blocks of this CTA; the ring
+// then carries W tiles only, and the kernel that would have made the tensor is gone from the chain:
+//   PROD_NORM     the RMS norm of rows of the 32-bit stream
+//   PROD_COMBINE  the ordered combine of the split-key attention's partial results
+enum Producer { PROD_NONE = 0, PROD_NORM = 1, PROD_COMBINE = 3 };
 
 template <int EPI>
 __device__ __forceinline__ void store_out(void* out, size_t o, float v) {
@@ -60,25 +67,31 @@ struct Params {
     const float* after_w;        // [N]
     float after_eps;
     int* after_counter;          // zero before the launch, left zero
+    int kb_cap;                  // PROD != NONE: k-blocks of the resident token operand (the most one split owns)
+    // PROD_COMBINE: token operand [t, h * hd + d] = sum_s acc[t,h,s,d] f_s / sum_s l_s f_s, f_s = exp(m_s - max m)
+    const float* cb_acc;         // [T, heads, splits, hd]
+    const float* cb_ml;          // [T, heads, splits, 2]  (max, sum)
+    int cb_splits, cb_hd, cb_heads;
 };
 
-// shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
-// buffer of the SwiGLU epilogue.  Tiles are 1024-byte aligned (128-byte swizzle).
-// NORM: the input is the 32-bit residual stream and its RMS norm is computed here: the four
-// epilogue warps (idle during the main loop otherwise) normalise the CTA's token rows,
-// y = x * 1/sqrt(mean(x^2)+eps) * w (imparo-cpu/src/ops.rs:6-22), round to bfloat16 and write
-// them into shared memory in the MMA's swizzled K-major layout for ALL k-blocks of this CTA;
-// the ring then carries W tiles only.  One kernel less per product and no round trip of the
-// normed activations through global memory.
-template <int NT, int STAGES, int EPI, bool NORM>
-__global__ void __launch_bounds__(THREADS, 1)
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+    return make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                      *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+}
+template <int PROD> struct ThreadsOf { static constexpr int value = (PROD == PROD_COMBINE) ? 320 : THREADS; };
+
+template <int NT, int STAGES, int EPI, int PROD>
+__global__ void __launch_bounds__(ThreadsOf<PROD>::value, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = NORM ? A_BYTES : A_BYTES + B_BYTES;
+    constexpr bool NORM = PROD == PROD_NORM;
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = PROD != PROD_NONE ? A_BYTES : A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* bres = smem + STAGES * STAGE_BYTES;                               // NORM: [kblocks][NT][128 B]
-    uint8_t* aux = bres + (NORM ? (size_t)p.kblocks * B_BYTES : 0);
+    uint8_t* bres = smem + STAGES * STAGE_BYTES;                               // PROD: [kb_cap][NT][128 B]
+    uint8_t* aux = bres + (PROD != PROD_NONE ? (size_t)p.kb_cap * B_BYTES : 0);
     uint64_t* full = reinterpret_cast<uint64_t*>(aux);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_ready = empty + STAGES;
@@ -101,7 +114,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
-        mbar_init(b_ready, 128);
+        mbar_init(b_ready, (PROD == PROD_COMBINE) ? 256 : 128);
         flags[0] = 0;
         flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -122,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             auto load_w = [&](int i) {
                 const int s = i % STAGES;
                 uint8_t* a = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);          // NORM: the W tile only
+                mbar_expect_tx(&full[s], STAGE_BYTES);          // PROD: the W tile only
                 const int k0 = (kb_begin + i) * BK;
                 if (EPI == SWIGLU_BF16) {
                     tma_load_2d(a, &map_w, &full[s], k0, tile_n * 64);                       // 64 gate rows
@@ -132,14 +145,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 }
             };
             auto load_x = [&](int i) {
-                if (NORM) return;                                // the input rows are made in place by the epilogue warps
+                if (PROD != PROD_NONE) return;                   // the input rows are made in place by the epilogue warps
                 const int s = i % STAGES;
                 tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, &map_x, &full[s], (kb_begin + i) * BK, tile_t * NT);
             };
             const int early = n_kb < STAGES ? n_kb : STAGES;
             pdl_trigger();
             for (int i = 0; i < early; ++i) load_w(i);
-            if (!NORM) pdl_wait();
+            pdl_wait();                                          // (PROD: nothing below needs it; it orders this thread's stamps)
             for (int i = 0; i < early; ++i) load_x(i);
             for (int i = early; i < n_kb; ++i) {
                 const int s = i % STAGES;
@@ -155,10 +168,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         if (lane == 0) {
             const uint32_t idesc = instr_desc(BM, NT);
             bool ok = true;
-            if (NORM && !mbar_wait(b_ready, 0)) {
+            if (PROD != PROD_NONE && !mbar_wait(b_ready, 0)) {
                 report(p.status, IMPARO_ST_WAIT_LIMIT, 13, tile_n, split);
                 ok = false;
             }
+            if (PROD == PROD_COMBINE) timeline_mark(0);       // the token operand is made
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % STAGES;
@@ -169,7 +183,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                const uint32_t b_addr = NORM ? smem_u32(bres + (size_t)i * B_BYTES) : a_addr + A_BYTES;
+                const uint32_t b_addr = PROD != PROD_NONE ? smem_u32(bres + (size_t)i * B_BYTES) : a_addr + A_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     // 16 elements along K = 32 bytes inside the 128-byte swizzle atom
@@ -229,8 +243,109 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // generic-proxy writes -> visible to the MMA
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b_ready)) : "memory");
         }
+        if (PROD == PROD_COMBINE) {
+            // A thread per (live token row of the tile, 16-byte chunk = 8 consecutive k) of this CTA's k-range; eight
+            // warps (2..9) share the items.  The (max, sum) pairs of an item and the first accumulators are requested
+            // together, so that the usual case costs two round trips to memory.
+            const int pe = (int)threadIdx.x - 64;                               // 0 .. 255
+            const int k_lo = kb_begin * BK, k_hi = min(p.K, kb_end * BK);
+            const int chunks = n_kb * (BK / 8);
+            const int live = min(NT, p.T - tile_t * NT);
+            const int n_items = live * chunks;
+            for (int item = pe; item < NT * chunks; item += 256) {
+                const int r = item / chunks, cc = item - r * chunks;
+                const int k = k_lo + cc * 8;
+                const int t = tile_t * NT + r;
+                float yv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) yv[i] = 0.f;
+                if (item < n_items && k < k_hi) {                             // K is a multiple of 8: whole chunks only
+                    {
+                        const int hd = p.cb_hd, S = p.cb_splits;
+                        const int h = k / hd, d = k - h * hd;
+                        const size_t th = (size_t)t * p.cb_heads + h;
+                        const float2* ml = reinterpret_cast<const float2*>(p.cb_ml) + th * S;
+                        const float* acc_p = p.cb_acc + th * S * hd + d;
+                        float L = 0.f;
+                        if (S <= 16) {
+                            // the (max, sum) pairs and the first eight splits' accumulators are requested together
+                            float2 v[16];
+                            float4 a[8][2];
+#pragma unroll
+                            for (int u = 0; u < 16; ++u) v[u] = u < S ? __ldcg(ml + u) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                if (u < S) {
+                                    a[u][0] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)u * hd));
+                                    a[u][1] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)u * hd + 4));
+                                }
+                            }
+                            float M = -INFINITY;
+#pragma unroll
+                            for (int u = 0; u < 16; ++u) if (v[u].y > 0.f) M = fmaxf(M, v[u].x);
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                if (half == 1) {
+#pragma unroll
+                                    for (int u = 0; u < 8; ++u) {
+                                        if (8 + u < S) {
+                                            a[u][0] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)(8 + u) * hd));
+                                            a[u][1] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)(8 + u) * hd + 4));
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const int sidx = half * 8 + u;
+                                    float2 vv = v[0];
+#pragma unroll
+                                    for (int q = 1; q < 16; ++q) if (q == sidx) vv = v[q];
+                                    if (sidx < S && vv.y > 0.f) {
+                                        const float f = expf(vv.x - M);
+                                        yv[0] += a[u][0].x * f; yv[1] += a[u][0].y * f; yv[2] += a[u][0].z * f; yv[3] += a[u][0].w * f;
+                                        yv[4] += a[u][1].x * f; yv[5] += a[u][1].y * f; yv[6] += a[u][1].z * f; yv[7] += a[u][1].w * f;
+                                        L += vv.y * f;
+                                    }
+                                }
+                            }
+                        } else {
+                            float M = -INFINITY;
+                            for (int s0 = 0; s0 < S; ++s0) { const float2 v = __ldcg(ml + s0); if (v.y > 0.f) M = fmaxf(M, v.x); }
+                            for (int s0 = 0; s0 < S; s0 += 4) {
+                                float4 a[4], b[4];
+                                float2 v[4];
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    if (s0 + u < S) {
+                                        v[u] = __ldcg(ml + s0 + u);
+                                        a[u] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)(s0 + u) * hd));
+                                        b[u] = __ldcg(reinterpret_cast<const float4*>(acc_p + (size_t)(s0 + u) * hd + 4));
+                                    }
+                                }
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    if (s0 + u < S && v[u].y > 0.f) {
+                                        const float f = expf(v[u].x - M);
+                                        yv[0] += a[u].x * f; yv[1] += a[u].y * f; yv[2] += a[u].z * f; yv[3] += a[u].w * f;
+                                        yv[4] += b[u].x * f; yv[5] += b[u].y * f; yv[6] += b[u].z * f; yv[7] += b[u].w * f;
+                                        L += v[u].y * f;
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) yv[i] = L > 0.f ? yv[i] / L : 0.f;
+                    }
+                }
+                const int i = cc / (BK / 8), chunk = cc % (BK / 8);
+                *reinterpret_cast<uint4*>(bres + (size_t)i * B_BYTES + (size_t)r * 128 + ((chunk ^ (r & 7)) << 4)) = pack8(yv);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b_ready)) : "memory");
+            if (warp >= 6) goto done;                                           // warps 6..9 only help to make the operand
+        }
         bool ok = n_kb == 0 || mbar_wait(acc_ready, 0);
-        if (threadIdx.x == 64) timeline_mark(0);                // the accumulator is complete
+        if (threadIdx.x == 64 && PROD != PROD_COMBINE) timeline_mark(0);                // the accumulator is complete
         if (!ok && lane == 0) report(p.status, IMPARO_ST_WAIT_LIMIT, 12, tile_n, split);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -330,11 +445,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
             }
         }
     }
+done:
     if (clustered) {
         // every thread of every CTA of the cluster: partials are written / may be read
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6) {
             const int quad = warp & 3;
             const int row = quad * 32 + lane;
             const int n = tile_n * BM + row;
@@ -367,7 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
-    if (EPI == ADD_F32 && p.after_out != nullptr && warp >= 2) {
+    if (EPI == ADD_F32 && p.after_out != nullptr && warp >= 2 && warp < 6) {
         // The reference fuses the same pair, residual add then the next RMS norm
         // (imparo-backend/src/lib.rs:2609-2623 add_rms_norm).  Here the product's last CTA does it.
         __threadfence();
@@ -411,13 +527,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
 }
 
 // ---- host side ---------------------------------------------------------------------------
-template <int NT, int STAGES, int EPI, bool NORM = false>
+template <int NT, int STAGES, int EPI, int PROD = PROD_NONE>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (NORM ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
+    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (PROD != PROD_NONE ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
     static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
-    const size_t smem = fixed + (NORM ? (size_t)p.kblocks * NT * BK * 2 : 0);
-    if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller norms separately
-    auto kern = gemm_kernel<NT, STAGES, EPI, NORM>;
+    const size_t smem = fixed + (PROD != PROD_NONE ? (size_t)p.kb_cap * NT * BK * 2 : 0);
+    if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller makes the tensor with its own kernel
+    auto kern = gemm_kernel<NT, STAGES, EPI, PROD>;
     static size_t configured = 0;               // per instantiation: the largest size asked for so far
     cudaError_t e;
     if (smem > configured) {
@@ -429,7 +545,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(ThreadsOf<PROD>::value);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -449,7 +565,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 template <int NT, int STAGES, int EPI>
 static int max_clusters(int cluster) {
     constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
-    auto kern = gemm_kernel<NT, STAGES, EPI, false>;
+    auto kern = gemm_kernel<NT, STAGES, EPI, PROD_NONE>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, cluster);
@@ -638,18 +754,72 @@ extern "C" int imparo_gemm_tc_norm(const float* x32, int ldx32, const float* nor
     p.out = out; p.status = status;
     p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
     p.x32 = x32; p.norm_w = norm_w; p.norm_rows = norm_rows; p.eps = eps; p.ldx32 = ldx32;
+    p.kb_cap = (p.kblocks + splits - 1) / splits;          // floor((s+1)k/S) - floor(sk/S) <= ceil(k/S)
     const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
     dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
     if (nt == 16) {
         switch (epilogue) {
-            case STORE_BF16: return launch<16, 9, STORE_BF16, true>(mw, mw, p, grid, stream);
-            case STORE_F32: return launch<16, 9, STORE_F32, true>(mw, mw, p, grid, stream);
-            default: return launch<16, 9, SWIGLU_BF16, true>(mw, mw, p, grid, stream);
+            case STORE_BF16: return launch<16, 9, STORE_BF16, PROD_NORM>(mw, mw, p, grid, stream);
+            case STORE_F32: return launch<16, 9, STORE_F32, PROD_NORM>(mw, mw, p, grid, stream);
+            default: return launch<16, 9, SWIGLU_BF16, PROD_NORM>(mw, mw, p, grid, stream);
         }
     }
     switch (epilogue) {
-        case STORE_BF16: return launch<32, 5, STORE_BF16, true>(mw, mw, p, grid, stream);
-        case STORE_F32: return launch<32, 5, STORE_F32, true>(mw, mw, p, grid, stream);
-        default: return launch<32, 5, SWIGLU_BF16, true>(mw, mw, p, grid, stream);
+        case STORE_BF16: return launch<32, 5, STORE_BF16, PROD_NORM>(mw, mw, p, grid, stream);
+        case STORE_F32: return launch<32, 5, STORE_F32, PROD_NORM>(mw, mw, p, grid, stream);
+        default: return launch<32, 5, SWIGLU_BF16, PROD_NORM>(mw, mw, p, grid, stream);
     }
+}
+
+
+// ---- a product whose token operand the kernel makes itself: the attention's output product ----------------
+// It takes out (32-bit stream, [T, N]) and either adds into it (epilogue 2) or leaves split partials in
+// scratch (epilogue 4, scratch from imparo_gemm_tc_plan with that epilogue): the two forms the mixers' output
+// products use.  T at most 16.  Returns -25 when it does not take the case.
+static int launch_produced(int nt, int epilogue, const CUtensorMap& mw, const Params& p, dim3 grid, cudaStream_t stream) {
+#define IMPARO_PRODUCED(NT_, ST_) \
+    if (epilogue == PARTIAL_F32) return launch<NT_, ST_, PARTIAL_F32, PROD_COMBINE>(mw, mw, p, grid, stream); \
+    return launch<NT_, ST_, ADD_F32, PROD_COMBINE>(mw, mw, p, grid, stream)
+    // up to 16 tokens: with more, the eight producer warps walk several items each, one round trip after the other,
+    // and the kernels apart are faster
+    if (nt == 16) { IMPARO_PRODUCED(16, 6); }
+#undef IMPARO_PRODUCED
+    return -25;
+}
+
+static int produced_common(const void* w, float* out, int ldo, int T, int N, int K, int epilogue, float* scratch, int* status,
+                           Params& p, CUtensorMap& mw, int& nt, dim3& grid) {
+    if (K <= 0 || K % 8 != 0 || (((uintptr_t)w) & 15)) return -23;
+    if (epilogue != ADD_F32 && epilogue != PARTIAL_F32) return -22;
+    if (T > 16) return -25;
+    int splits, ncnt;
+    long long sfl;
+    imparo_gemm_tc_plan(T, N, K, epilogue, &nt, &splits, &sfl, &ncnt);
+    if (epilogue == PARTIAL_F32 && !scratch) return -24;
+    int rc = get_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BM, &mw);
+    if (rc) return rc;
+    p.out = out; p.scratch = scratch; p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
+    p.kb_cap = (p.kblocks + splits - 1) / splits;          // floor((s+1)k/S) - floor(sk/S) <= ceil(k/S)
+    grid = dim3((N + BM - 1) / BM, (T + nt - 1) / nt, splits);
+    return 0;
+}
+
+// out (+)= combine(partials) w^T: the ordered combine of the split-key attention (attention_split.cu) computed inside
+// the output product.  part_acc [T, heads, splits, hd], part_ml [T, heads, splits, 2]; K = heads * hd.
+extern "C" int imparo_gemm_tc_combine(const float* part_acc, const float* part_ml, int heads, int hd, int n_splits,
+                                      const void* w, float* out, int ldo, int T, int N, int K, int epilogue, float* scratch,
+                                      int* status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (heads <= 0 || hd % 8 != 0 || heads * hd != K || n_splits < 1) return -2;
+    if (n_splits > 64) return -25;
+    if ((((uintptr_t)part_acc) | ((uintptr_t)part_ml)) & 15) return -23;
+    Params p = {};
+    CUtensorMap mw;
+    int nt;
+    dim3 grid;
+    int rc = produced_common(w, out, ldo, T, N, K, epilogue, scratch, status, p, mw, nt, grid);
+    if (rc) return rc;
+    p.cb_acc = part_acc; p.cb_ml = part_ml; p.cb_splits = n_splits; p.cb_hd = hd; p.cb_heads = heads;
+    return launch_produced(nt, epilogue, mw, p, grid, stream);
 }

@@ -233,9 +233,43 @@ __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ b
     out[i] = from_f32<T>(to_f32(out[i]) + bias[i % width]);
 }
 
+// ---- zero the state slots of requests that start in this step --------------------------------
+// arena: every fixed-size state tensor of the model, [slots][floats per slot] each, one after the
+// other; segments: per tensor (offset in the arena, floats per slot).  slots: the fresh slots of
+// the step (a padded list: entries below 0 are skipped).  One block column per (tensor, slot).
+__global__ void zero_state_slots_kernel(float* __restrict__ arena, const long long* __restrict__ segments,
+                                        const int* __restrict__ slots, int n_slots_total, int* status) {
+    pdl_trigger();
+    const int seg = blockIdx.y, which = blockIdx.z;
+    const int slot = slots[which];
+    const long long off = segments[2 * seg], per = segments[2 * seg + 1];
+    pdl_wait();
+    if (slot < 0) return;
+    if (slot >= n_slots_total) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && seg == 0) report(status, IMPARO_ST_SLOT_RANGE, 6, which, slot);
+        return;
+    }
+    float* p = arena + off + (long long)slot * per;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) p[i] = 0.f;
+}
+
 }  // namespace imparo
 
 using namespace imparo;
+
+extern "C" int imparo_zero_state_slots(float* arena, const long long* segments, int n_segments, long long max_per_slot,
+                                       const int* slots, int n, int n_slots_total, int* status, cudaStream_t stream) {
+    if (n <= 0 || n_segments <= 0) return 0;
+    if (n > 65535 || n_segments > 65535) return -2;
+    const int threads = 256;
+    long long bx = (max_per_slot + threads * 4 - 1) / (threads * 4);
+    if (bx < 1) bx = 1;
+    if (bx > 64) bx = 64;
+    launch(zero_state_slots_kernel, dim3((unsigned)bx, n_segments, n), dim3(threads), 0, stream, arena, segments, slots,
+           n_slots_total, status);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
 
 // Programmatic dependent launch for every kernel of the engine: on by default.
 static int g_pdl = 1;

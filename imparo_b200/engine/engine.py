@@ -19,6 +19,7 @@ from typing import Dict, List, Optional, Sequence, Union
 import torch
 
 from ..cache import CacheFull, CacheManager
+from ..config.engine import EngineConfig
 from ..config.registry import load_config
 from ..kernels import lib as _lib
 from ..kernels import ops
@@ -35,32 +36,45 @@ _PRECISIONS = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32",
 
 class Engine:
     def __init__(self, model: Optional[str] = None, *, config: Optional[dict] = None, seed: int = 0,
-                 dtype: str = "bfloat16", device: Union[str, torch.device] = "cuda:0", ctx: int = 4096,
-                 parallel: int = 8, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_step_tokens: int = 2048, random_init: Optional[dict] = None,
-                 probe_layer: Optional[int] = None, probe=None):
+                 dtype: Optional[str] = None, device: Union[str, torch.device, None] = None, ctx: Optional[int] = None,
+                 parallel: Optional[int] = None, page_size: Optional[int] = None, num_pages: Optional[int] = None,
+                 max_step_tokens: Optional[int] = None, random_init: Optional[dict] = None,
+                 probe_layer: Optional[int] = None, probe=None, switches: Optional[dict] = None,
+                 config_file: Optional[str] = None, engine_config: Optional[EngineConfig] = None):
         """model: a folder with config.json and model.safetensors.  Or config (a config.json
         dictionary) with seed: random weights drawn on the device (random_init may give
-        matrix_std, conv_std, norm_jitter).  ctx: the most positions one request may reach.
-        parallel: the most requests live at once.  num_pages: pages in each pool (default:
-        enough for parallel requests of ctx positions).
-        probe_layer (or IMPARO_PROBE_LAYER in the environment): a schedule entry whose block shows its
-        stages (stream in, mixer norm, stream after the mixer, feed-forward norm, stream out) to
-        probe(name, tensor); the default probe prints rms, sum and the first five values of each to
-        stderr, as the reference's stage probes do (imparo-model/src/cpu_support.rs:26-46).  Probing
-        evaluates every stage on its own and switches graph replay off: for comparing engines, not for timing."""
-        if dtype not in _PRECISIONS:
+        matrix_std, conv_std, norm_jitter).
+
+        The engine's own settings are one typed EngineConfig (config/engine.py), resolved here once: a keyword
+        given to this constructor wins over the environment (IMPARO_CTX, IMPARO_PARALLEL, IMPARO_GEMM, ...), which
+        wins over the JSON file config_file (or the one IMPARO_CONFIG names), which wins over the defaults; or
+        pass a resolved engine_config.  dtype: "bfloat16" | "float32".  ctx: the most positions one request may
+        reach.  parallel: the most requests live at once.  num_pages: pages in each pool (default: enough for
+        parallel requests of ctx positions).  switches: kernel-path switches by name (KernelSwitches).
+        probe_layer: a schedule entry whose block shows its stages (stream in, mixer norm, stream after the mixer,
+        feed-forward norm, stream out) to probe(name, tensor); the default probe prints rms, sum and the first
+        five values of each to stderr, as the reference's stage probes do (imparo-model/src/cpu_support.rs:26-46).
+        Probing evaluates every stage on its own and switches graph replay off: for comparing engines, not for timing."""
+        if engine_config is None:
+            engine_config = EngineConfig.resolve(
+                flags={"dtype": dtype, "device": None if device is None else str(device), "ctx": ctx, "parallel": parallel,
+                       "page_size": page_size, "num_pages": num_pages, "max_step_tokens": max_step_tokens,
+                       "probe_layer": probe_layer, "switches": switches}, file=config_file)
+        self.engine_config = cfg = engine_config
+        if cfg.dtype not in _PRECISIONS:
             raise ValueError(f"dtype must be one of {sorted(_PRECISIONS)}")
-        self.precision = _PRECISIONS[dtype]
-        self.device = torch.device(device)
+        self.precision = _PRECISIONS[cfg.dtype]
+        self.device = torch.device(cfg.device)
         if self.device.type != "cuda" or not torch.cuda.is_available():
             raise RuntimeError("imparo_b200 runs on a CUDA device (sm_100a); there is no CPU path")
         _lib.kernels()      # build/load now: fail loudly if the extension is missing
         torch.cuda.set_device(self.device)
+        ctx, parallel, page_size, num_pages = cfg.ctx, cfg.parallel, cfg.page_size, cfg.num_pages
+        max_step_tokens, probe_layer = cfg.max_step_tokens, cfg.probe_layer
         self.arch, self.config = load_config(model if model is not None else config)
         self.status = ops.new_status(self.device)
         self.rt = Runtime(precision=self.precision, device=self.device, status=self.status,
-                          workspace=Workspace(self.device))
+                          workspace=Workspace(self.device), launch_state=ops.LaunchState(cfg.switches))
         self.model = Model(self.arch.model_spec(self.config), self.rt)
         specs = self.model.weight_specs()
         if model is not None:
@@ -82,9 +96,7 @@ class Engine:
         self.cache = CacheManager(self.model.cache_requirements(), self.page_size, int(num_pages), self.parallel,
                                   kv_dtype=self.rt.act_dtype, device=self.device)
         self.max_step_tokens = int(max_step_tokens)
-        self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel)
-        if probe_layer is None and os.environ.get("IMPARO_PROBE_LAYER", "") != "":
-            probe_layer = int(os.environ["IMPARO_PROBE_LAYER"])
+        self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel, use_graphs=cfg.use_graphs)
         if probe_layer is not None:
             if not 0 <= int(probe_layer) < len(self.model.schedule):
                 raise ValueError(f"probe_layer {probe_layer} is not one of the model's {len(self.model.schedule)} schedule entries")
@@ -137,6 +149,13 @@ class Engine:
         ids per prompt.  temperature 0 is greedy; seed keys the per-request random stream.
         A stop token ends its request and is not part of the output.  A request that cannot
         fit the cache even alone ends with what it has (see failed in stats())."""
+        previous = ops.use_state(self.rt.launch_state)       # the sampler's launches use this engine's scratch too
+        try:
+            return self._generate(prompts, max_tokens, temperature, seed, stop_token_ids, on_step)
+        finally:
+            ops.use_state(previous)
+
+    def _generate(self, prompts, max_tokens, temperature, seed, stop_token_ids, on_step):
         n = len(prompts)
         as_list = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n
         max_new, temps, seeds = as_list(max_tokens), as_list(temperature), as_list(seed)
@@ -158,7 +177,7 @@ class Engine:
             index[rid] = i
         failed: List[int] = []
         t0 = time.perf_counter()
-        log = os.environ.get("IMPARO_LOG", "") not in ("", "0")
+        log = self.engine_config.log
         t_log = t0
         gen = {rid: 0 for rid in tokens}        # tokens sampled so far per request (values may still be on the device)
         dead = set()                            # ended by a stop token

@@ -150,11 +150,11 @@ class StepFunction:
             src[:] = -1
         else:
             src[:] = np.asarray(token_src, dtype=np.int32)
-        # state slots of requests that start in this step (they are zeroed before the step runs); the
-        # list is padded with its first entry, so that it travels with the description
+        # state slots of requests that start in this step (they are zeroed before the step's first token runs);
+        # the list is padded with -1 (skipped by the kernel), so that it travels with the description
         fresh = [int(slot[i]) for i in range(R) if start_pos[i] == 0]
         fresh_at = offs[8 + ng]
-        h[fresh_at:fresh_at + R] = (fresh + [fresh[0]] * (R - len(fresh))) if fresh else 0
+        h[fresh_at:fresh_at + R] = (fresh + [-1] * (R - len(fresh))) if fresh else -1
         n_ints = int(offs[-1])
         self.last_h2d_bytes = n_ints * 4
         self._dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
@@ -177,11 +177,16 @@ class StepFunction:
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
         b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),
-                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single), "h2d_bytes": n_ints * 4}
+                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single, bool(fresh)), "h2d_bytes": n_ints * 4}
         return b
 
     # -- a step whose shape has come before replays its captured graph -----------------------
     def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        cache = self.cache
+        if batch.fresh_slots is not None and getattr(cache, "n_state_segments", 0):
+            # a fresh request's state starts at zero: one kernel over the flat state arena, first in the step's chain
+            ops.zero_state_slots(cache.state_arena, cache.state_segments, cache.n_state_segments, batch.fresh_slots,
+                                 cache.num_slots, self.rt.status)
         x, picked = self.model.forward(batch, self._views, wanted=(batch.want_rows, batch.n_want))
         if not batch.n_want:
             return None
@@ -197,7 +202,7 @@ class StepFunction:
         which a scheduler with a fixed token budget produces again and again.  Issued launch by
         launch from Python a step of the full-size model costs the host about 2.5 ms."""
         ws = self.rt.workspace
-        generation = (ws.generation, ops.TC_GENERATION)
+        generation = (ws.generation, ops.generation())
         key = batch.host["key"]
         entry = self._graphs.get(key)
         if entry is not None and entry[4] != generation:
@@ -230,7 +235,7 @@ class StepFunction:
             entry[3] = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
             ops.COUNTS.update(before)          # capture launched nothing
             self.graph_captures += 1
-            if entry[4] != (ws.generation, ops.TC_GENERATION):      # a buffer moved during the capture run
+            if entry[4] != (ws.generation, ops.generation()):      # a buffer moved during the capture run
                 self._graphs.clear()
                 self.graph_resets += 1
                 return self._forward(batch)
@@ -278,6 +283,14 @@ class StepFunction:
         whose tokens the host knows (the reference's pipelined decode does the same for its
         one-token step: imparo-model/src/lib.rs:2457-2537 queue_step / argmax_feed)."""
         self.check_items(items)
+        previous = ops.use_state(self.rt.launch_state) if self.rt.launch_state is not None else None
+        try:
+            return self._step(items, manage_cache, device_tokens)
+        finally:
+            if previous is not None:
+                ops.use_state(previous)
+
+    def _step(self, items, manage_cache, device_tokens):
         cache = self.cache
         if manage_cache:
             done = []
@@ -298,10 +311,6 @@ class StepFunction:
                 ops.take_sampled_tokens(batch.token_ids, batch.token_src, prev_ids)
             else:
                 batch = self.build_batch(items, singles_first=True)
-            if batch.fresh_slots is not None and cache.state:
-                idx = batch.fresh_slots.long()          # on the device already: no copy that would wait for the stream
-                for t in cache.state.values():
-                    t.index_fill_(0, idx, 0.0)
             if self.use_graphs:
                 logits = self._forward_graphed(batch)
             else:

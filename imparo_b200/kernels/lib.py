@@ -80,12 +80,15 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gemm_tc_add_norm", [P, I, I, P, P, I, I, I, I, P, c_float, P, P, P, S])
     _declare(lib, "imparo_gemm_tc_norm", [P, I, P, P, c_float, P, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_gemm_tc", [P, I, I, P, P, I, I, I, I, I, P, P, P, S])
+    _declare(lib, "imparo_gemm_tc_combine", [P, P, I, I, I, P, P, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_gemm_prefill", [P, I, I, P, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_qk_norm_rope_store",
              [P, I, P, P, P, P, P, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_paged_attention",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_paged_attention_split",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_attention_split_combine", [P, P, P, I, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma",
              [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
@@ -99,6 +102,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_sample_rows", [P, P, P, P, I, I, I, S])
     _declare(lib, "imparo_take_sampled_tokens", [P, P, P, I, I, S])
     _declare(lib, "imparo_selftest_wait_limit", [P, I, P, S])
+    _declare(lib, "imparo_zero_state_slots", [P, P, I, c_int64, P, I, I, P, S])
 
 
 def _declare_host(lib):

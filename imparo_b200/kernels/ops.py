@@ -59,21 +59,57 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-_environ_bytes = getattr(os.environ, "_data", None)      # the mapping behind os.environ (bytes keys on POSIX)
-if not isinstance(_environ_bytes, dict) or (_environ_bytes and not isinstance(next(iter(_environ_bytes)), bytes)):
-    _environ_bytes = None
-
-
-def _env(name: str, default: str = "") -> str:
-    """os.environ.get for the switches read on every launch, without its per-call encoding."""
-    if _environ_bytes is not None:
-        v = _environ_bytes.get(name.encode())
-        return default if v is None else v.decode()
-    return os.environ.get(name, default)
-
-
 # Launch counts since import: "own" = this engine's CUDA kernels, "library" = cuBLAS products.
 COUNTS = {"own": 0, "library": 0}
+
+
+class LaunchState:
+    """What the launchers remember between calls: which streams have split partials pending, which
+    norms a product may fill, and the scratch buffers behind them.  An engine owns one (its Runtime
+    holds it and the step function makes it current for the length of a step), so two engines in
+    one process neither share bookkeeping nor scratch; code that calls the launchers directly
+    works on the module's default state."""
+
+    def __init__(self, switches=None):
+        # which kernel paths are taken (config/engine.py KernelSwitches): resolved once, never read from the
+        # environment on the launch path
+        self.switches = switches if switches is not None else _default_switches()
+        self.deferrable = set()      # data_ptr of streams whose next accumulate-product may stay pending
+        self.pending = {}            # data_ptr -> (scratch, n_splits, rows, width)
+        self.partials = {}           # device index -> scratch of products into the stream
+        self.consumer_parts = {}     # device index -> scratch of products a consumer kernel folds
+        self.tc_scratch = {}         # device index -> (floats, counters) of the cluster-folded products
+        self.armed = {}              # data_ptr of a stream -> NormedInput the next accumulate-product should fill
+        self.filled = {}             # data_ptr -> NormedInput a product has filled (a later write to the stream voids it)
+        self.after_counter = {}
+        self.argmax_scratch = {}
+        self.status_fallback = {}
+        self.generation = 0          # bumped when a scratch buffer moves: captured graphs that used it are stale
+
+
+def _default_switches():
+    from ..config.engine import EngineConfig
+    return EngineConfig.resolve().switches
+
+
+_S = LaunchState()
+
+
+def switches():
+    """The kernel switches of the state that is current (an engine's, during its steps; else the module's own,
+    resolved from the environment and the optional configuration file when the module was imported)."""
+    return _S.switches
+
+
+def use_state(state: "LaunchState") -> "LaunchState":
+    """Makes `state` the one the launchers work on; returns the one it replaces."""
+    global _S
+    old, _S = _S, state
+    return old
+
+
+def generation() -> int:
+    return _S.generation
 
 
 def _check(rc: int, what: str, kind: str = "own") -> None:
@@ -122,7 +158,7 @@ def selftest_wait_limit(status: torch.Tensor, limit: int = 1000) -> int:
 
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
     _cuda(table, ids, out, status)
-    _pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void
+    _S.pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void
     n, width = out.shape
     _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
     _need(out.dtype == torch.float32 and table.shape[1] == width, "embedding output is float32 [tokens, width]")
@@ -134,29 +170,26 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
 # A decode-sized product into the stream is cut along K over many CTAs.  Instead of folding the
 # splits itself it may leave them in scratch ("pending"); the next reader of the stream — nearly
 # always the RMS norm — adds them in split order and goes on in the same kernel.
-_deferrable = set()      # data_ptr of streams whose next accumulate-product may stay pending
-_pending = {}            # data_ptr -> (scratch, n_splits, rows, width)
-_partials = {}           # device index -> scratch tensor
 
 
 def defer_adds() -> bool:
-    return _env("IMPARO_DEFER_ADDS", "1") == "1"
+    return _S.switches.defer_adds
 
 
 def allow_deferred_add(stream: torch.Tensor) -> None:
     """The caller promises that whatever reads `stream` next goes through ops.rmsnorm,
     ops.settle, ops.add_bias or another ops.linear(accumulate=True)."""
     if defer_adds():
-        _deferrable.add(stream.data_ptr())
+        _S.deferrable.add(stream.data_ptr())
 
 
 def disallow_deferred_add(stream: torch.Tensor) -> None:
-    _deferrable.discard(stream.data_ptr())
+    _S.deferrable.discard(stream.data_ptr())
 
 
 def settle(stream: torch.Tensor) -> None:
     """Fold pending partials into the stream (no-op when there are none)."""
-    p = _pending.pop(stream.data_ptr(), None)
+    p = _S.pending.pop(stream.data_ptr(), None)
     if p is not None:
         scratch, S, T, N = p
         _check(_lib.kernels().imparo_add_partials_rmsnorm(_ptr(stream), _ptr(scratch), S, T * N, None, 0.0, None, 0, T, N,
@@ -166,12 +199,12 @@ def settle(stream: torch.Tensor) -> None:
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
     _cuda(x, w, out, rows)
-    pend = _pending.get(x.data_ptr())
+    pend = _S.pending.get(x.data_ptr())
     if pend is not None:
         scratch, S, T, N = pend
         if rows is None and out.shape == (T, N) and x.shape[1] == N and w.numel() == N and w.dtype == torch.float32:
             # the stream's pending partials are added and the updated rows normed in one kernel
-            _pending.pop(x.data_ptr())
+            _S.pending.pop(x.data_ptr())
             _check(_lib.kernels().imparo_add_partials_rmsnorm(_ptr(x), _ptr(scratch), S, T * N, _ptr(w), float(eps), _ptr(out),
                                                               _code(out), T, N, _stream()), "add_partials_rmsnorm")
             return
@@ -216,15 +249,12 @@ def _gemm_lib_ready(device) -> None:
 
 # ---- tcgen05 product ---------------------------------------------------------------------
 EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2, 3, 4
-_tc_scratch = {}
 _tc_plans = {}
-_status_fallback = {}
 
 
 def gemm_backend() -> str:
-    """"tcgen05" (default) or "library" (cuBLAS), chosen by IMPARO_GEMM."""
-    v = _env("IMPARO_GEMM", "tcgen05").lower()
-    return "library" if v in ("library", "lib", "cublas") else "tcgen05"
+    """"tcgen05" (default) or "library" (cuBLAS): the switch `gemm`."""
+    return _S.switches.gemm
 
 
 def _tc_plan(T, N, K, epi):
@@ -244,7 +274,7 @@ def _tc_buffers(device, floats: int, counters: int):
     """Split-K scratch and tile counters, shared by all products of a device (they run one
     after the other on the stream).  Grown outside graph capture only."""
     key = torch.device(device).index or 0
-    buf = _tc_scratch.get(key)
+    buf = _S.tc_scratch.get(key)
     if buf is None or buf[0].numel() < floats or buf[1].numel() < counters:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("split-K scratch would grow during graph capture")
@@ -252,13 +282,11 @@ def _tc_buffers(device, floats: int, counters: int):
         old_c = buf[1].numel() if buf else 0
         buf = (torch.empty(max(floats, old_f, 1 << 20), dtype=torch.float32, device=device),
                torch.zeros(max(counters, old_c, 4096), dtype=torch.int32, device=device))
-        _tc_scratch[key] = buf
-        global TC_GENERATION
-        TC_GENERATION += 1
+        _S.tc_scratch[key] = buf
+        _S.generation += 1
     return buf
 
 
-TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that used it are stale
 
 
 # Above this many tokens the library product is faster than the hand-written kernel as it
@@ -267,12 +295,10 @@ TC_GENERATION = 0       # bumped when the scratch moves: captured graphs that us
 # batch 32: 1.058 / 1.107; batch 64: 1.381 / 1.421 (the own kernels stay in the chain of
 # programmatic dependent launches and prefetch their weights; a library product breaks it).  At
 # 2,048 tokens the library is ahead: down 66 / 50 us, gate+up 275 / 160 us per product.
-TC_MAX_TOKENS = 64
 
 
 def tc_max_tokens() -> int:
-    v = _env("IMPARO_TC_MAX_TOKENS")
-    return int(v) if v else TC_MAX_TOKENS
+    return _S.switches.tc_max_tokens
 
 
 def tc_usable(x: torch.Tensor, w: torch.Tensor, any_size: bool = False) -> bool:
@@ -306,13 +332,60 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
         scratch, cnt = _tc_buffers(x.device, floats, counters)
     if status is None:
         key = torch.device(x.device).index or 0
-        status = _status_fallback.get(key)
+        status = _S.status_fallback.get(key)
         if status is None:
-            status = _status_fallback[key] = new_status(x.device)
+            status = _S.status_fallback[key] = new_status(x.device)
     rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
     rows_alloc = max(T, min(rows_alloc, 1 << 30))
     _check(_lib.kernels().imparo_gemm_tc(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K, epilogue,
                                          _ptr(scratch), _ptr(cnt), _ptr(status), _stream()), "gemm_tc")
+
+
+# ---- tcgen05 product for prompt-sized batches (csrc/kernels/gemm_prefill.cu) ---------------------
+# From this many tokens on the persistent 128 x 256-tile kernel takes the product (below it, down to
+# TC_MAX_TOKENS, the library does): a tile holds 128 tokens, and its SwiGLU epilogue saves the
+# [T, 2F] intermediate only where the kernel also keeps up with the library on the product itself.
+
+
+def prefill_tc_min_tokens() -> int:
+    return _S.switches.prefill_tc_min_tokens
+
+
+def prefill_tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+    """Whether gemm_prefill takes out (+)= x w^T: bfloat16 operands with 16-byte rows, an output whose rows
+    are 16-byte aligned groups, enough tokens, and the own product not switched off."""
+    if gemm_backend() != "tcgen05" or _S.switches.prefill_gemm != "tcgen05":
+        return False
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] < prefill_tc_min_tokens():
+        return False
+    K = x.shape[1]
+    N = w.shape[0] // 2 if swiglu else w.shape[0]
+    group = 4 if out.dtype == torch.float32 else 8
+    return (K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and w.is_contiguous() and out.stride(1) == 1 and N % group == 0 and out.stride(0) % group == 0
+            and out.data_ptr() % 16 == 0 and out.dtype in (torch.float32, torch.bfloat16))
+
+
+def gemm_prefill(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: Optional[torch.Tensor] = None) -> None:
+    """The persistent tensor-core product for many tokens.  epilogue: EPI_STORE_BF16 | EPI_STORE_F32 |
+    EPI_ADD_F32 (out += x w^T) | EPI_SWIGLU (w = [gate rows; up rows], out = silu(x gate^T) * (x up^T))."""
+    _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    _need(epilogue in (EPI_STORE_BF16, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU), "gemm_prefill: unknown epilogue")
+    T, K = x.shape
+    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    _need(w.shape[1] == K and (epilogue != EPI_SWIGLU or w.shape[0] % 2 == 0), "gemm_prefill: weight shape")
+    _need(tuple(out.shape) == (T, N), f"gemm_prefill: out must be [{T}, {N}]")
+    want_dtype = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32
+    _need(out.dtype == want_dtype, f"gemm_prefill: this epilogue writes {want_dtype}")
+    if status is None:
+        key = torch.device(x.device).index or 0
+        status = _S.status_fallback.get(key)
+        if status is None:
+            status = _S.status_fallback[key] = new_status(x.device)
+    rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
+    rows_alloc = max(T, min(rows_alloc, 1 << 30))
+    _check(_lib.kernels().imparo_gemm_prefill(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K,
+                                              epilogue, _ptr(status), _stream()), "gemm_prefill")
 
 
 class NormedInput:
@@ -345,9 +418,6 @@ class NormedInput:
 
 
 # ---- residual add with the next norm behind it ----------------------------------------------
-_armed = {}          # data_ptr of a 32-bit stream -> NormedInput the next accumulate-product should fill
-_filled = {}         # data_ptr -> NormedInput a product has filled (a later write to the stream voids it)
-_after_counter = {}
 
 
 def fuse_add_norm() -> bool:
@@ -356,7 +426,7 @@ def fuse_add_norm() -> bool:
     1.04 ms without.  The product's last CTA has to wait for every other CTA's writes (fence,
     counter) and then norms all rows alone, which is a longer serial tail than the separate norm
     kernel, whose launch the programmatic dependent launch already overlaps."""
-    return _env("IMPARO_FUSE_ADD_NORM", "0") == "1"
+    return _S.switches.fuse_add_norm
 
 
 def arm_norm(stream: torch.Tensor, normed: "NormedInput") -> None:
@@ -364,15 +434,15 @@ def arm_norm(stream: torch.Tensor, normed: "NormedInput") -> None:
     the stream after the add) in its own kernel.  If it does not, `normed` stays unevaluated and
     whoever needs it runs the norm kernel; nothing is lost."""
     if isinstance(normed, NormedInput) and normed.rows is None and normed.x.data_ptr() == stream.data_ptr():
-        _armed[stream.data_ptr()] = normed
+        _S.armed[stream.data_ptr()] = normed
 
 
 def disarm_norm(stream: torch.Tensor) -> None:
-    _armed.pop(stream.data_ptr(), None)
+    _S.armed.pop(stream.data_ptr(), None)
 
 
 def _void_filled(stream: torch.Tensor) -> None:
-    ni = _filled.pop(stream.data_ptr(), None)
+    ni = _S.filled.pop(stream.data_ptr(), None)
     if ni is not None:
         ni._done = False
 
@@ -386,7 +456,7 @@ def fuse_norm() -> bool:
     measured on B200 the fused form is slower in the decode step (1.11 ms against 1.05 ms at
     batch 8): every CTA redoes the norm of all token rows, and the separate norm kernel already
     runs while the product prefetches its weights."""
-    return _env("IMPARO_FUSE_NORM", "0") == "1"
+    return _S.switches.fuse_norm
 
 
 def _try_fused_norm(x: "NormedInput", w: torch.Tensor, out: torch.Tensor, epilogue: int, status) -> bool:
@@ -399,9 +469,9 @@ def _try_fused_norm(x: "NormedInput", w: torch.Tensor, out: torch.Tensor, epilog
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     if status is None:
         key = torch.device(out.device).index or 0
-        status = _status_fallback.get(key)
+        status = _S.status_fallback.get(key)
         if status is None:
-            status = _status_fallback[key] = new_status(out.device)
+            status = _S.status_fallback[key] = new_status(out.device)
     rc = _lib.kernels().imparo_gemm_tc_norm(_ptr(x.x), x.x.stride(0), _ptr(x.weight), _ptr(x.rows), x.eps, _ptr(w), _ptr(out),
                                             out.stride(0), T, N, K, epilogue, _ptr(status), _stream())
     if rc == -25:
@@ -415,27 +485,28 @@ def _gemm_tc_add_norm(x, w, out, ni: "NormedInput", status) -> None:
     T, K = x.shape
     N = w.shape[0]
     key = torch.device(x.device).index or 0
-    cnt = _after_counter.get(key)
+    cnt = _S.after_counter.get(key)
     if cnt is None:
-        cnt = _after_counter[key] = torch.zeros(4, dtype=torch.int32, device=x.device)
+        cnt = _S.after_counter[key] = torch.zeros(4, dtype=torch.int32, device=x.device)
     if status is None:
-        status = _status_fallback.get(key)
+        status = _S.status_fallback.get(key)
         if status is None:
-            status = _status_fallback[key] = new_status(x.device)
+            status = _S.status_fallback[key] = new_status(x.device)
     rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
     rows_alloc = max(T, min(rows_alloc, 1 << 30))
     _check(_lib.kernels().imparo_gemm_tc_add_norm(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K,
                                                   _ptr(ni.weight), ni.eps, _ptr(ni._out), _ptr(cnt), _ptr(status), _stream()),
            "gemm_tc_add_norm")
     ni._done = True
-    _filled[out.data_ptr()] = ni
+    _S.filled[out.data_ptr()] = ni
 
 
 def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
                   tmp: Optional[torch.Tensor] = None) -> None:
     """out[T, F] = silu(x gate^T) * (x up^T) with w_gu = [gate; up] of shape [2F, K].
-    bfloat16 on the tensor-core kernel: one launch, the activation in the epilogue.
-    Otherwise: the product into tmp [T, 2F], then the activation kernel."""
+    bfloat16 on the tensor-core kernels (the weight streamer for few tokens, the persistent tile kernel for
+    many): one launch, the activation in the epilogue.  Otherwise: the product into tmp [T, 2F] (a tensor,
+    or a function that makes it, called only on this path), then the activation kernel."""
     if isinstance(x, NormedInput):
         if _try_fused_norm(x, w_gu, out, EPI_SWIGLU, status):
             return
@@ -443,6 +514,11 @@ def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[tor
     if x.dtype == torch.bfloat16 and gemm_backend() == "tcgen05" and tc_usable(x, w_gu):
         gemm_tc(x, w_gu, out, EPI_SWIGLU, status)
         return
+    if prefill_tc_usable(x, w_gu, out, swiglu=True):
+        gemm_prefill(x, w_gu, out, EPI_SWIGLU, status)
+        return
+    if callable(tmp):
+        tmp = tmp()
     _need(tmp is not None and tmp.shape == (x.shape[0], w_gu.shape[0]), "linear_swiglu: tmp [T, 2F] needed on this path")
     linear(x, w_gu, tmp)
     swiglu_act(tmp, out)
@@ -475,25 +551,24 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
         _need(not accumulate or out.dtype == torch.float32, "linear: accumulate needs a float32 output")
         if gemm_backend() == "tcgen05" and tc_usable(x, w):
             epi = EPI_ADD_F32 if accumulate else (EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16)
-            if accumulate and out.data_ptr() in _deferrable and out.is_contiguous():
+            if accumulate and out.data_ptr() in _S.deferrable and out.is_contiguous():
                 settle(out)                                       # one set of partials at a time
                 nt, splits, floats, _ = _tc_plan(M, N, K, EPI_PARTIAL)
                 if splits > 1:
                     key = torch.device(x.device).index or 0
-                    buf = _partials.get(key)
+                    buf = _S.partials.get(key)
                     if buf is None or buf.numel() < floats:
                         _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
-                        buf = _partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
-                        global TC_GENERATION
-                        TC_GENERATION += 1
+                        buf = _S.partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                        _S.generation += 1
                     _void_filled(out)
-                    _armed.pop(out.data_ptr(), None)
+                    _S.armed.pop(out.data_ptr(), None)
                     gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
-                    _pending[out.data_ptr()] = (buf, splits, M, N)
+                    _S.pending[out.data_ptr()] = (buf, splits, M, N)
                     return
             if accumulate:
                 settle(out)
-            ni = _armed.pop(out.data_ptr(), None) if accumulate else None
+            ni = _S.armed.pop(out.data_ptr(), None) if accumulate else None
             if ni is not None and fuse_add_norm() and not ni._done and tuple(ni.shape) == (M, N) and N % 4 == 0 \
                     and ni._out.is_contiguous() and ni.dtype == torch.bfloat16:
                 _void_filled(out)
@@ -505,8 +580,12 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
             return
         if accumulate:
             settle(out)
-            _armed.pop(out.data_ptr(), None)
+            _S.armed.pop(out.data_ptr(), None)
             _void_filled(out)
+        if _S.switches.prefill_linear and prefill_tc_usable(x, w, out):
+            gemm_prefill(x, w, out, EPI_ADD_F32 if accumulate else (EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16),
+                         status)
+            return
         _gemm_lib_ready(x.device)
         _check(_lib.kernels().imparo_gemm_bf16_nt(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), N,
                                                   int(accumulate), _stream()), "gemm_bf16_nt", "library")
@@ -546,13 +625,11 @@ class PartialProduct:
         return self._out
 
 
-_consumer_parts = {}
 
 
 def unfolded_products() -> bool:
-    """Whether linear_unfolded may leave split partials to its consumer (IMPARO_UNFOLDED=0 turns it off)."""
-    import os
-    return os.environ.get("IMPARO_UNFOLDED", "1") != "0"
+    """Whether linear_unfolded may leave split partials to its consumer (the switch `unfolded`)."""
+    return _S.switches.unfolded
 
 
 def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
@@ -569,16 +646,79 @@ def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torc
         nt, splits, floats, _ = _tc_plan(M, N, K, EPI_PARTIAL)
         if splits > 1:
             key = torch.device(x.device).index or 0
-            buf = _consumer_parts.get(key)
+            buf = _S.consumer_parts.get(key)
             if buf is None or buf.numel() < floats:
                 _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
-                buf = _consumer_parts[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
-                global TC_GENERATION
-                TC_GENERATION += 1
+                buf = _S.consumer_parts[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                _S.generation += 1
             gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
             return PartialProduct(buf, splits, (M, N), out)
     linear(x, w, out, status=status)
     return out
+
+
+# ---- the attention's output product with the combine of the split partials inside (decode rows) ----------
+def fuse_producers() -> bool:
+    """Whether the attention combine of decode rows runs inside the output product that follows it (the switch
+    `fuse_producers`; off: as a kernel of its own)."""
+    return _S.switches.fuse_producers
+
+
+def _into_stream(out: torch.Tensor, M: int, N: int, K: int):
+    """How a tensor-core product into the 32-bit stream `out` is issued: (EPI_PARTIAL, scratch, splits) when its add
+    may stay split partials for the next reader of the stream, else (EPI_ADD_F32, None, 1) with the stream made whole."""
+    if out.data_ptr() in _S.deferrable and out.is_contiguous():
+        settle(out)                                           # one set of partials at a time
+        nt, splits, floats, _ = _tc_plan(M, N, K, EPI_PARTIAL)
+        if splits > 1:
+            key = torch.device(out.device).index or 0
+            buf = _S.partials.get(key)
+            if buf is None or buf.numel() < floats:
+                _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                buf = _S.partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=out.device)
+                _S.generation += 1
+            return EPI_PARTIAL, buf, splits
+    settle(out)
+    return EPI_ADD_F32, None, 1
+
+
+def _produced_usable(T: int, w: torch.Tensor, out: torch.Tensor) -> bool:
+    K = w.shape[1]
+    return (fuse_producers() and gemm_backend() == "tcgen05" and T <= min(16, tc_max_tokens()) and w.dtype == torch.bfloat16
+            and w.is_contiguous() and w.data_ptr() % 16 == 0 and K % 8 == 0 and out.dtype == torch.float32
+            and out.dim() == 2 and out.stride(1) == 1 and out.shape[1] == w.shape[0])
+
+
+def _after_stream_product(out, epi, buf, splits, M, N) -> None:
+    _S.armed.pop(out.data_ptr(), None)
+    _void_filled(out)
+    if epi == EPI_PARTIAL:
+        _S.pending[out.data_ptr()] = (buf, splits, M, N)
+
+
+def linear_of_attention_partials(part_acc, part_ml, n_tok, nh, hd, n_splits, w_out, out, status) -> bool:
+    """out += combine(partials) w_out^T: the ordered combine of the split-key attention's partial results (as
+    paged_attention_split(out=None) leaves them) computed inside the output product.  Returns False, having launched
+    nothing, when the kernel does not take the case; the caller then combines with attention_split_combine."""
+    if not (_produced_usable(n_tok, w_out, out) and w_out.shape[1] == nh * hd and hd % 8 == 0 and n_splits <= 64):
+        return False
+    _cuda(part_acc, part_ml, w_out, out, status)
+    N, K = w_out.shape
+    epi, buf, splits = _into_stream(out, n_tok, N, K)
+    rc = _lib.kernels().imparo_gemm_tc_combine(_ptr(part_acc), _ptr(part_ml), nh, hd, n_splits, _ptr(w_out), _ptr(out),
+                                               out.stride(0), n_tok, N, K, epi, _ptr(buf), _ptr(status), _stream())
+    if rc == -25:
+        return False
+    _check(rc, "gemm_tc_combine")
+    _after_stream_product(out, epi, buf, splits, n_tok, N)
+    return True
+
+
+def attention_split_combine(part_acc, part_ml, out, n_rows, hd, n_splits) -> None:
+    """The ordered combine alone: out[row, :] from the partials of paged_attention_split(out=None)."""
+    _cuda(part_acc, part_ml, out)
+    _check(_lib.kernels().imparo_attention_split_combine(_ptr(part_acc), _ptr(part_ml), _ptr(out), _code(out), n_rows, hd,
+                                                         n_splits, _stream()), "attention_split_combine")
 
 
 def _parts_of(x):
@@ -592,7 +732,7 @@ def qk_norm_rope_store(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot,
                        k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, status) -> None:
     """qkv [T, (nh+2*nkv)*hd] (a tensor or a PartialProduct) -> q_out [T, nh*hd] normed and rotated;
     k (normed, rotated) and v written into their pages.  nkv == 0: q only (a layer that reads
-    another's cache)."""
+    another's cache).  q_w / k_w None: no per-head norm on that side (rotation only)."""
     src, parts, part_stride = _parts_of(qkv)
     _cuda(src, positions, item_of_token, q_w, k_w, inv_freq, q_out, k_cache, v_cache, table, status)
     T = q_out.shape[0]
@@ -600,9 +740,9 @@ def qk_norm_rope_store(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot,
     _need(qkv.dtype == q_out.dtype, "qk_norm_rope_store: q_out must have the activations' dtype")
     _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
           and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
-    _need(q_w.dtype == torch.float32 and q_w.numel() == hd, "q norm weight must be float32 [head]")
+    _need(q_w is None or (q_w.dtype == torch.float32 and q_w.numel() == hd), "q norm weight must be float32 [head]")
     if nkv:
-        _need(k_w.dtype == torch.float32 and k_w.numel() == hd, "k norm weight must be float32 [head]")
+        _need(k_w is None or (k_w.dtype == torch.float32 and k_w.numel() == hd), "k norm weight must be float32 [head]")
         _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype must match activations")
         _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * hd,
               "cache arena smaller than n_pages")
@@ -633,15 +773,28 @@ def paged_attention(q, k_cache, v_cache, positions, item_of_token, table, page_s
 MAX_SPLITS = 2048        # the ordered combine keeps one (max, sum) pair per key chunk in shared memory
 
 
-def split_plan(n_tok: int, nkv: int, upper_context: int):
+_sm_count = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the device (the current one by default), asked once."""
+    key = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    n = _sm_count.get(key)
+    if n is None:
+        n = _sm_count[key] = int(torch.cuda.get_device_properties(key).multi_processor_count)
+    return n
+
+
+def split_plan(n_tok: int, nkv: int, upper_context: int, sms: Optional[int] = None):
     """(chunk, n_splits) for the split-key attention kernel: the largest chunk of 512, 256, 128
     or 64 keys that still gives about four CTAs per SM; when even the smallest does not (a step of
     one or two tokens), the largest of 256, 128, 64 that gives 64 CTAs, since fewer and longer CTAs
     with fewer partials to combine then measured faster (batch 1: 0.735 ms per step with 256, 0.743
     with 64).  A function of the launch's shape only."""
     chunk = None
+    full = 4 * (sms if sms is not None else sm_count())
     for c in (512, 256, 128, 64):
-        if n_tok * nkv * -(-upper_context // c) >= 592:
+        if n_tok * nkv * -(-upper_context // c) >= full:
             chunk = c
             break
     if chunk is None:
@@ -661,6 +814,9 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
     combine).  Returns False, having launched nothing, when the group size is above 8.
 
+    out None: the partial results stay in part_acc / part_ml, uncombined, for a consumer that combines them itself
+    (linear_of_attention_partials).
+
     fresh: the most tokens one request brings to this step, when the caller knows that cache rows
     below `position + 1 - fresh` were written before the stream's last copy or foreign kernel (the
     engine's steps start with such a copy).  The tensor-core kernel then requests its first key
@@ -670,7 +826,8 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
     use_mma = mma and q.dtype == torch.bfloat16 and hd in (64, 128) and chunk >= 64
     T = q.shape[0]
-    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * hd) and out.dtype == q.dtype, "paged_attention_split: q/out shapes")
+    _need(q.shape == (T, nh * hd) and (out is None or (out.shape == (T, nh * hd) and out.dtype == q.dtype)),
+          "paged_attention_split: q/out shapes")
     _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
     _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
     _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
@@ -692,7 +849,8 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
             T, nh, nkv, hd, int(chunk), int(n_splits), _ptr(status), _stream())
     _check(rc, "paged_attention_split")
-    COUNTS["own"] += 1          # partial + combine
+    if out is not None:
+        COUNTS["own"] += 1      # partial + combine
     return True
 
 
@@ -719,8 +877,7 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
             _stream())
     if kernel == "auto":
-        import os
-        kernel = "mma" if os.environ.get("IMPARO_ATTN_PREFILL", "") == "mma" else "auto"
+        kernel = _S.switches.attn_prefill
     if kernel in ("auto", "tcgen05"):
         rc = _lib.kernels().imparo_attention_prefill_tc(*args)
         if rc != -8:
@@ -748,6 +905,18 @@ def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y,
         _ptr(item_slot), _ptr(y), T, width, taps, state.shape[0], parts, part_stride, _ptr(status), _stream()), "gated_conv")
 
 
+def zero_state_slots(arena: torch.Tensor, segments: torch.Tensor, n_segments: int, slots: torch.Tensor, n_slots_total: int,
+                     status: torch.Tensor) -> None:
+    """Zero, in every state tensor of the arena, the slots named in `slots` (int32 on the device; entries below 0
+    are skipped).  segments: int64 [n_segments, 2] on the device: (offset in the arena, floats per slot)."""
+    _cuda(arena, segments, slots, status)
+    _need(arena.dtype == torch.float32 and segments.dtype == torch.int64 and slots.dtype == torch.int32, "zero_state_slots: dtypes")
+    if n_segments == 0 or slots.numel() == 0:
+        return
+    _check(_lib.kernels().imparo_zero_state_slots(_ptr(arena), _ptr(segments), int(n_segments), int(arena.numel()), _ptr(slots),
+                                                  slots.numel(), int(n_slots_total), _ptr(status), _stream()), "zero_state_slots")
+
+
 def take_sampled_tokens(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
     """token_ids[i] = prev[src[i]] where src[i] >= 0 (all int32): rows whose token is the id an
     earlier step sampled take it from that step's output on the device."""
@@ -759,7 +928,6 @@ def take_sampled_tokens(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.
            "take_sampled_tokens")
 
 
-_argmax_scratch = {}
 
 
 def sample_rows(logits, temperature, uniform, out) -> None:
@@ -771,10 +939,10 @@ def sample_rows(logits, temperature, uniform, out) -> None:
     if temperature is None and vocab >= 4096 and n <= 65535:
         # greedy over a large vocabulary: 32 blocks per row, then one warp per row
         key = torch.device(logits.device).index or 0
-        buf = _argmax_scratch.get(key)
+        buf = _S.argmax_scratch.get(key)
         if buf is None or buf[0].numel() < n * 32:
             _need(not torch.cuda.is_current_stream_capturing(), "argmax scratch would grow during graph capture")
-            buf = _argmax_scratch[key] = (torch.empty(max(n, 256) * 32, dtype=torch.float32, device=logits.device),
+            buf = _S.argmax_scratch[key] = (torch.empty(max(n, 256) * 32, dtype=torch.float32, device=logits.device),
                                           torch.empty(max(n, 256) * 32, dtype=torch.int32, device=logits.device))
         _check(_lib.kernels().imparo_argmax_rows(_ptr(logits), _ptr(out), _ptr(buf[0]), _ptr(buf[1]), n, vocab,
                                                  logits.stride(0), _stream()), "argmax_rows")

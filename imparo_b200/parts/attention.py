@@ -19,14 +19,17 @@ from .spec import PagedKV, PartSpec, WeightSpec
 
 class AttentionMixer(Part):
     """params: hidden, n_heads, n_kv_heads, head_dim, eps, window (None or int), position
-    (PartSpec), qk_norm (bool, default True), names (optional dict of tensor names)."""
+    (PartSpec), qk_norm (bool, default True: per-head RMS norm of q and k with a weight each; False: none, and
+    no norm tensors are declared), bias (bool, default False: True declares optional q/k/v/out biases, used
+    when the file carries them), names (optional dict of tensor names)."""
     accepts_lazy_input = True
     adds_with_linear = True
 
 
     NAMES = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
              "o": "self_attn.out_proj.weight", "q_norm": "self_attn.q_layernorm.weight",
-             "k_norm": "self_attn.k_layernorm.weight"}
+             "k_norm": "self_attn.k_layernorm.weight", "q_bias": "self_attn.q_proj.bias", "k_bias": "self_attn.k_proj.bias",
+             "v_bias": "self_attn.v_proj.bias", "o_bias": "self_attn.out_proj.bias"}
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -37,6 +40,8 @@ class AttentionMixer(Part):
         self.hd = int(p["head_dim"])
         self.eps = float(p["eps"])
         self.window = int(p["window"]) if p.get("window") else None
+        self.qk_norm = bool(p.get("qk_norm", True))
+        self.bias = bool(p.get("bias", False))
         if self.nh % self.nkv:
             raise ValueError(f"attention: kv heads {self.nkv} must divide heads {self.nh}")
         if self.hd % 16 or not 16 <= self.hd <= 256:
@@ -45,22 +50,37 @@ class AttentionMixer(Part):
         self.scale = 1.0 / math.sqrt(self.hd)
         self.names = {k: prefix + v for k, v in {**self.NAMES, **p.get("names", {})}.items()}
         self.position = make_part("position", p.get("position", PartSpec("none")), prefix, rt)
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
 
     def weight_specs(self):
         n, H, hd = self.names, self.hidden, self.hd
-        return [WeightSpec(n["q"], ((self.nh * hd, H),)), WeightSpec(n["k"], ((self.nkv * hd, H),)),
-                WeightSpec(n["v"], ((self.nkv * hd, H),)), WeightSpec(n["o"], ((H, self.nh * hd),)),
-                WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
-                WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))] + self.position.weight_specs()
+        specs = [WeightSpec(n["q"], ((self.nh * hd, H),)), WeightSpec(n["k"], ((self.nkv * hd, H),)),
+                 WeightSpec(n["v"], ((self.nkv * hd, H),)), WeightSpec(n["o"], ((H, self.nh * hd),))]
+        if self.qk_norm:
+            specs += [WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
+                      WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))]
+        if self.bias:
+            specs += [WeightSpec(n["q_bias"], ((self.nh * hd,),), role="vector", init=("bias",), optional=True),
+                      WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",), optional=True),
+                      WeightSpec(n["v_bias"], ((self.nkv * hd,),), role="vector", init=("bias",), optional=True),
+                      WeightSpec(n["o_bias"], ((H,),), role="vector", init=("bias",), optional=True)]
+        return specs + self.position.weight_specs()
 
     def bind(self, tensors):
         n = self.names
         # one fused projection [q | k | v]: a layout choice, the arithmetic is unchanged
         self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         self.w_o = tensors[n["o"]]
-        self.q_norm = tensors[n["q_norm"]]
-        self.k_norm = tensors[n["k_norm"]]
+        self.q_norm = tensors[n["q_norm"]] if self.qk_norm else None
+        self.k_norm = tensors[n["k_norm"]] if self.qk_norm else None
+        if self.bias:
+            parts = [(tensors.get(n["q_bias"]), self.nh * self.hd), (tensors.get(n["k_bias"]), self.nkv * self.hd),
+                     (tensors.get(n["v_bias"]), self.nkv * self.hd)]
+            if any(t is not None for t, _ in parts):      # one vector [q | k | v], zeros where the file has none
+                ref = self.w_o
+                self.b_qkv = torch.cat([t.float() if t is not None else torch.zeros(w, dtype=torch.float32, device=ref.device)
+                                        for t, w in parts]).contiguous()
+            self.b_o = tensors.get(n["o_bias"])
         self.position.bind(tensors)
 
     def cache_specs(self):
@@ -73,7 +93,11 @@ class AttentionMixer(Part):
         nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only
         width = (nh + 2 * nkv) * hd
         qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype)
-        qkv = ops.linear_unfolded(x, self.w_qkv[:width], qkv, status=rt.status)    # the kernel below can add split partials
+        if self.b_qkv is None:
+            qkv = ops.linear_unfolded(x, self.w_qkv[:width], qkv, status=rt.status)    # the kernel below can add split partials
+        else:
+            ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+            ops.add_bias(qkv, self.b_qkv[:width])
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype)
         rot = self.position.rotary()
         table = batch.tables[kv.group]
@@ -108,6 +132,18 @@ class AttentionMixer(Part):
             chunk, n_splits = ops.split_plan(T, self.nkv, table.shape[1] * kv.page_size)
             part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32)
             part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32)
+            if batch.decode_only and rt.act_dtype == torch.bfloat16 and n_splits <= 64 and ops.fuse_producers():
+                # decode rows: the partial results stay as they are and the output product combines them while it
+                # makes its token operand; no combine kernel and no tensor between the two
+                ops.paged_attention_split(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size,
+                                          kv.n_pages, self.window, self.scale, None, part_acc, part_ml, chunk,
+                                          n_splits, nh, self.nkv, hd, rt.status, fresh=1)
+                if not ops.linear_of_attention_partials(part_acc, part_ml, T, nh, hd, n_splits, self.w_o, residual, rt.status):
+                    ops.attention_split_combine(part_acc, part_ml, out, T * nh, hd, n_splits)
+                    ops.linear(out, self.w_o, residual, accumulate=True, status=rt.status)
+                if self.b_o is not None:
+                    ops.add_bias(residual, self.b_o)
+                return
             done = ops.paged_attention_split(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size,
                                              kv.n_pages, self.window, self.scale, out, part_acc, part_ml, chunk,
                                              n_splits, nh, self.nkv, hd, rt.status, fresh=batch.max_tokens_per_item)
@@ -115,3 +151,5 @@ class AttentionMixer(Part):
             ops.paged_attention(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages,
                                 self.window, self.scale, out, nh, self.nkv, hd, rt.status)
         ops.linear(out, self.w_o, residual, accumulate=True, status=rt.status)
+        if self.b_o is not None:
+            ops.add_bias(residual, self.b_o)

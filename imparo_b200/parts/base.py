@@ -8,7 +8,7 @@ model it is in.  Kinds:
   "norm"         forward(x, out=None, rows=None)      -> normed activations
   "position"     tables / apply for queries and keys
   "block"        forward(x, batch, caches)            arranges norm, mixer, feed-forward
-  "embedding"    forward(token_ids, out)              -> the 32-bit residual stream
+  "embedding"    forward(batch)                       -> the 32-bit residual stream [tokens, width]
   "head"         forward(h)                           -> 32-bit logits
 
 x is the normed input in the activation dtype (bfloat16, or float32 in the 32-bit
@@ -43,6 +43,8 @@ class Runtime:
     probe_entry: Optional[int] = None
     probe: Optional[object] = None
     probe_now: bool = False                     # set by the model while the probed entry runs
+    # the launchers' bookkeeping and scratch of this engine (kernels/ops.py LaunchState); None: the module's default
+    launch_state: Optional[object] = None
 
     @property
     def act_dtype(self) -> torch.dtype:
@@ -127,6 +129,22 @@ class Part:
 
     def cache_specs(self) -> Tuple:
         return ()
+
+
+class Block(Part):
+    """Base of the "block" kind: how a layer's parts are arranged.  The model calls
+    forward(x, batch, caches, ready=None, next_norm=None, only_rows=None) and reads two declared facts:
+
+    first_norm: the norm part that reads the stream first in this block, or None.  The block before may
+        produce that norm's input while it finishes (it gets it as next_norm and returns what it made; the
+        model hands it on as `ready`).  A block that returns None from forward() simply made nothing.
+    picks_rows: True when forward(only_rows=(rows, n)) is implemented: as the model's last block it may then
+        run whatever follows its mixer on the n wanted rows only and return their stream [n, width]."""
+    first_norm = None
+    picks_rows = False
+
+    def forward(self, x, batch, caches, ready=None, next_norm=None, only_rows=None):
+        raise NotImplementedError
 
 
 _PARTS: Dict[Tuple[str, str], type] = {}

@@ -3,10 +3,10 @@ x += mixer(norm(x)); x += feed_forward(norm(x)), pre-norms only
 (imparo-model/src/lfm2/workflow_cpu.rs:8-18,172-319)."""
 from __future__ import annotations
 
-from .base import Part, make_part
+from .base import Block, make_part
 
 
-class PreNormResidualBlock(Part):
+class PreNormResidualBlock(Block):
     """params: layer (LayerSpec)."""
 
     def __init__(self, params, prefix, rt):
@@ -18,6 +18,7 @@ class PreNormResidualBlock(Part):
         self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt)
         self.parts = (self.mixer_norm, self.mixer, self.ff_norm, self.ff)
         self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.first_norm = self.mixer_norm
         self.picks_rows = True         # forward(only_rows=...) is implemented
 
     def weight_specs(self):

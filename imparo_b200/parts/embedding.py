@@ -29,9 +29,11 @@ class TokenEmbedding(Part):
     def bind(self, tensors):
         self.table = tensors[self.name]
 
-    def forward(self, token_ids: torch.Tensor, n_tokens: int) -> torch.Tensor:
-        out = self.rt.workspace.get("residual", (n_tokens, self.width), torch.float32)
-        ops.embed_gather(self.table, token_ids, out, self.rt.status)
+    def forward(self, batch) -> torch.Tensor:
+        """batch: the step's batch (token_ids, positions, item_of_token, ... on the device).  This part reads
+        the token ids only; an embedding that adds learned positions or segment rows reads the rest."""
+        out = self.rt.workspace.get("residual", (batch.n_tokens, self.width), torch.float32)
+        ops.embed_gather(self.table, batch.token_ids, out, self.rt.status)
         return out
 
 

@@ -38,10 +38,6 @@ class SwiGLU(Part):
     def forward(self, x, batch, residual):
         rt, T, F = self.rt, x.shape[0], self.ff
         h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype)
-        if T <= ops.tc_max_tokens() and x.dtype == torch.bfloat16 and ops.gemm_backend() == "tcgen05" \
-                and self.hidden % 8 == 0:
-            gu = None                                            # gate/up product with silu(gate)*up in its epilogue
-        else:
-            gu = rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype)
-        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=gu)
+        # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
+        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype))
         ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)

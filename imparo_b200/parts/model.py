@@ -69,24 +69,19 @@ class Model:
         they are fewer than the batch's tokens and the last entry is a block that can run its
         feed-forward on picked rows, the result is (stream of the picked rows [n, width] or None
         for n = 0, True); else (the whole stream, False)."""
-        x = self.embedding.forward(batch.token_ids, batch.n_tokens)
+        x = self.embedding.forward(batch)
         ready = None
         last = len(self.schedule) - 1
         for i, e in enumerate(self.schedule):
             layer = self.layers[e.layer]
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             self.rt.probe_now = self.rt.probe is not None and self.rt.probe_entry == i
-            if hasattr(layer, "mixer_norm"):
-                if i == last and wanted is not None and wanted[1] < batch.n_tokens and getattr(layer, "picks_rows", False):
-                    out = layer.forward(x, batch, cache_views(i), ready=ready, only_rows=wanted)
-                    self.rt.probe_now = False
-                    return out, True
-                # a block may hand the next block its (already computed) norm input
-                ready = layer.forward(x, batch, cache_views(i), ready=ready,
-                                      next_norm=getattr(nxt, "mixer_norm", None) if nxt is not None else None)
-            else:
-                layer.forward(x, batch, cache_views(i))
-                ready = None
+            if i == last and wanted is not None and wanted[1] < batch.n_tokens and layer.picks_rows:
+                out = layer.forward(x, batch, cache_views(i), ready=ready, only_rows=wanted)
+                self.rt.probe_now = False
+                return out, True
+            # a block may hand the next block its (already computed) norm input
+            ready = layer.forward(x, batch, cache_views(i), ready=ready, next_norm=nxt.first_norm if nxt is not None else None)
         self.rt.probe_now = False
         return (x, False) if wanted is not None else x
 

@@ -152,10 +152,41 @@ def attend(q, k, v, scale, window=None):
     return out
 
 
-def attention_mixer(cur, w, cfg, positions):
+def attend_blocked(q, k, v, scale, window=None, block=256):
+    """The same formula as attend() (imparo-model/src/cpu_support.rs:402-445: token t sees keys lo..=t, head h
+    reads kv head h // (heads / kv_heads), softmax of the scaled scores, times the values), evaluated for a
+    block of query tokens at a time so that long sequences finish: scores of a block against keys 0..end of the
+    block, positions a query must not see set to -inf before the softmax."""
+    T, nh, hd = q.shape
+    nkv = k.shape[1]
+    per_kv = nh // nkv
+    out = np.zeros_like(q)
+    neg = q.dtype.type(-np.inf)
+    for a in range(0, T, block):
+        b = min(T, a + block)
+        lo_blk = 0 if not window else max(0, a + 1 - int(window))
+        kpos = np.arange(lo_blk, b)[None, :]
+        qpos = np.arange(a, b)[:, None]
+        dead = kpos > qpos
+        if window:
+            dead = dead | (kpos < qpos + 1 - int(window))
+        for kvh in range(nkv):
+            kk = k[lo_blk:b, kvh, :]                                  # [keys, hd]
+            vv = v[lo_blk:b, kvh, :]
+            qq = q[a:b, kvh * per_kv:(kvh + 1) * per_kv, :]           # [block, per_kv, hd]
+            s = np.einsum("tgd,kd->tgk", qq, kk) * q.dtype.type(scale)
+            s = np.where(dead[:, None, :], neg, s)
+            s = s - s.max(axis=-1, keepdims=True)
+            e = np.exp(s)
+            p = e * (q.dtype.type(1.0) / e.sum(axis=-1, keepdims=True))
+            out[a:b, kvh * per_kv:(kvh + 1) * per_kv, :] = np.einsum("tgk,kd->tgd", p, vv)
+    return out
+
+
+def attention_mixer(cur, w, cfg, positions, attend_block=None):
     """imparo-model/src/lfm2/workflow_cpu.rs:203-250 — q/k/v projections, per-head
     norm and rotation of q and k, causal attention scaled by 1/sqrt(head_dim),
-    output projection."""
+    output projection.  attend_block: evaluate the attention a block of queries at a time (long sequences)."""
     T = cur.shape[0]
     hd = cfg.head_dim
     q = (cur @ w["q_proj"].T).reshape(T, cfg.n_heads, hd)
@@ -163,7 +194,10 @@ def attention_mixer(cur, w, cfg, positions):
     v = (cur @ w["v_proj"].T).reshape(T, cfg.n_kv, hd)
     q = head_norm_rope(q, w["q_layernorm"], cfg.eps, positions, hd, cfg.theta)
     k = head_norm_rope(k, w["k_layernorm"], cfg.eps, positions, hd, cfg.theta)
-    o = attend(q, k, v, 1.0 / math.sqrt(hd), window=w.get("window"))
+    if attend_block:
+        o = attend_blocked(q, k, v, 1.0 / math.sqrt(hd), window=w.get("window"), block=int(attend_block))
+    else:
+        o = attend(q, k, v, 1.0 / math.sqrt(hd), window=w.get("window"))
     return o.reshape(T, cfg.n_heads * hd) @ w["out_proj"].T
 
 
@@ -209,7 +243,7 @@ def swiglu(n, w):
     return (silu(n @ w["w1"].T) * (n @ w["w3"].T)) @ w["w2"].T
 
 
-def block(x, lw, cfg, positions, probe=None):
+def block(x, lw, cfg, positions, probe=None, attend_block=None):
     """imparo-model/src/lfm2/workflow_cpu.rs:172-319 — pre-norms only:
     x += mixer(rms(x, operator_norm)); x += ffn(rms(x, ffn_norm)).
     probe(name, array): shown the stages the reference's probe names
@@ -221,7 +255,7 @@ def block(x, lw, cfg, positions, probe=None):
     if lw["kind"] == "conv":
         mix = conv_mixer(cur, lw, cfg)
     else:
-        mix = attention_mixer(cur, lw, cfg, positions)
+        mix = attention_mixer(cur, lw, cfg, positions, attend_block)
     x = x + mix
     show("stream_mixer", x)
     h = rms_norm(x, lw["ffn_norm"], cfg.eps)
@@ -276,15 +310,22 @@ class PlainLfm2:
                     lw["window"] = int(cfg.window)
             self.layers.append(lw)
 
-    def hidden_states(self, tokens, probe_layer=None, probe=None):
+    def hidden_states(self, tokens, probe_layer=None, probe=None, attend_block=None):
         """imparo-model/src/cpu_support.rs:327-342 (rows of the table, no scale), then
         every block in order.  probe_layer / probe: see block()."""
         tokens = np.asarray(tokens, dtype=np.int64)
         positions = np.arange(len(tokens))
         x = self.embed[tokens].astype(self.dtype)
         for i, lw in enumerate(self.layers):
-            x = block(x, lw, self.cfg, positions, probe if i == probe_layer else None)
+            x = block(x, lw, self.cfg, positions, probe if i == probe_layer else None, attend_block)
         return x
+
+    def logits_at(self, tokens, places, attend_block=256):
+        """Logits at the given positions only, with the attention evaluated block by block: for sequences too
+        long for logits().  [len(places), vocab]."""
+        x = self.hidden_states(tokens, attend_block=attend_block)[np.asarray(places, dtype=np.int64)]
+        h = rms_norm(x, self.out_norm, self.cfg.eps)
+        return h @ self.head.T
 
     def logits(self, tokens):
         """imparo-model/src/cpu_support.rs:451-466 — final norm then the head, here at

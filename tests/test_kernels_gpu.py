@@ -654,8 +654,8 @@ def test_attention_prefill_far_key_and_refusals(kernel):
 def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
     """ops.linear / ops.linear_swiglu on a NormedInput: the RMS norm of the 32-bit rows is
     computed inside the tensor-core product.  Against float64, and against the unfused path."""
-    monkeypatch.setenv("IMPARO_FUSE_NORM", "1")
-    monkeypatch.setenv("IMPARO_TC_MAX_TOKENS", "64")        # the own product for every T of this test
+    monkeypatch.setattr(ops().switches(), "fuse_norm", True)
+    monkeypatch.setattr(ops().switches(), "tc_max_tokens", 64)        # the own product for every T of this test
     o = ops()
     g = torch.Generator().manual_seed(T * 7 + N)
     x = torch.randn(40, K, generator=g) * 2
@@ -697,8 +697,8 @@ def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
 def test_product_with_the_next_norm_behind_it(T, N, K, monkeypatch):
     """linear(..., accumulate=True) into an armed stream: out += x w^T and, in the same kernel,
     the RMS norm of the updated rows.  Against float64 and against the separate norm kernel."""
-    monkeypatch.setenv("IMPARO_FUSE_ADD_NORM", "1")
-    monkeypatch.setenv("IMPARO_TC_MAX_TOKENS", "64")
+    monkeypatch.setattr(ops().switches(), "fuse_add_norm", True)
+    monkeypatch.setattr(ops().switches(), "tc_max_tokens", 64)
     o = ops()
     g = torch.Generator().manual_seed(T + N + K)
     x = bf16_round(torch.randn(T, K, generator=g))
@@ -840,3 +840,58 @@ def test_cache_rows_are_addressed_as_the_reference_addresses_them(dtype):
                           1 / math.sqrt(hd), out, nh, nkv, hd, status)
             o.read_status(status)
             assert abs(float(out[0, 0]) - (star + 1)) < 0.05 * (star + 1), (kind, float(out[0, 0]), star + 1)
+
+
+# ---------------------------------------------------------------------------------------
+# the attention's output product that makes its own token operand (decode rows)
+@pytest.mark.parametrize("T,nh,nkv,hd,N,ctx", [(8, 32, 8, 64, 2048, 2100), (1, 4, 2, 64, 256, 300), (16, 6, 2, 128, 512, 700),
+                                                (3, 8, 8, 64, 384, 9000), (20, 4, 2, 64, 256, 150)])
+@pytest.mark.parametrize("deferred", [False, True])
+def test_output_product_with_the_attention_combine_inside(T, nh, nkv, hd, N, ctx, deferred):
+    """The split-key attention leaves its partial results (out=None) and linear_of_attention_partials combines them
+    inside the output product; against the combine kernel followed by linear."""
+    o = ops()
+    rng = np.random.default_rng(T + hd)
+    page = 16
+    lens = [int(x) for x in rng.integers(max(1, ctx // 3), ctx, T)]
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, lens, page, nkv, hd, torch.bfloat16)
+    q = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).bfloat16().to(DEV)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    items = torch.arange(T, dtype=torch.int32, device=DEV)
+    tab = torch.from_numpy(table).to(DEV)
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    w_o = torch.from_numpy((rng.standard_normal((N, nh * hd)) * 0.05).astype(np.float32)).bfloat16().to(DEV)
+    base = torch.from_numpy(rng.standard_normal((T, N)).astype(np.float32)).to(DEV)
+    chunk, n_splits = o.split_plan(T, nkv, tab.shape[1] * page)
+    status = o.new_status(DEV)
+    scale = 1 / math.sqrt(hd)
+    outs = []
+    for fused in (False, True):
+        part_acc = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
+        out = base.clone()
+        if fused:
+            assert o.paged_attention_split(q, kc, vc, positions, items, tab, page, n_pages, None, scale, None, part_acc, part_ml,
+                                           chunk, n_splits, nh, nkv, hd, status)
+            if deferred:
+                o.allow_deferred_add(out)
+            took = o.linear_of_attention_partials(part_acc, part_ml, T, nh, hd, n_splits, w_o, out, status)
+            o.disallow_deferred_add(out)
+            assert took == (T <= 16 and n_splits <= 64)
+            if not took:
+                return
+            o.settle(out)
+        else:
+            att = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+            assert o.paged_attention_split(q, kc, vc, positions, items, tab, page, n_pages, None, scale, att, part_acc, part_ml,
+                                           chunk, n_splits, nh, nkv, hd, status)
+            o.linear(att, w_o, out, accumulate=True, status=status)
+        outs.append(out)
+    torch.cuda.synchronize()
+    o.read_status(status)
+    s_ = float(outs[0].abs().max())
+    assert float((outs[0] - outs[1]).abs().max()) <= 2e-6 * s_
+    ref = np.stack([attention_reference(q[t].double().cpu().numpy(), ks[t].double().numpy(), vs[t].double().numpy(), lens[t] - 1,
+                                        nh, nkv, hd, scale, None) for t in range(T)])
+    want = base.double().cpu().numpy() + ref @ w_o.double().cpu().numpy().T
+    assert np.abs(outs[1].double().cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()

@@ -153,7 +153,7 @@ def test_norm_embedding_and_head_alone(precision):
     V, H = 333, 56
     emb, w = build("embedding", PartSpec("token_table", {"vocab": V, "width": H, "name": "E.weight"}), "", rt)
     ids = torch.tensor([5, 332, 0, 5], dtype=torch.int32, device=DEV)
-    x = emb.forward(ids, 4)
+    x = emb.forward(SimpleNamespace(token_ids=ids, n_tokens=4))          # an embedding part is given the step's batch
     assert np.array_equal(x.cpu().double().numpy(), w["E.weight"][[5, 332, 0, 5]])
     norm, wn = build("norm", PartSpec("rmsnorm", {"width": H, "eps": 1e-4, "name": "n.weight"}), "", rt, seed=3)
     y = norm.forward(x)
@@ -205,3 +205,68 @@ def test_block_alone(precision):
           "w2": w["B.feed_forward.w2.weight"], "w3": w["B.feed_forward.w3.weight"]}
     ref = P.block(x0.astype(np.float32).astype(np.float64), lw, SimpleNamespace(eps=1e-5), np.arange(10))
     assert np.abs(np.concatenate(outs) - ref).max() <= TOL[precision] * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("precision", ["float32", "bfloat16"])
+@pytest.mark.parametrize("qk_norm,bias", [(False, False), (True, True), (False, True)])
+def test_attention_mixer_without_head_norms_and_with_biases(precision, qk_norm, bias):
+    """The attention part's options: qk_norm=False declares no norm tensors and rotates q and k as they are;
+    bias=True adds q/k/v and output biases.  Against the plain functions put together the same way."""
+    from imparo_b200.parts.spec import PartSpec
+    rt = runtime(precision)
+    H, nh, nkv, hd = 88, 4, 2, 32
+    spec = PartSpec("attention", {"hidden": H, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "eps": 1e-5, "window": None,
+                                  "qk_norm": qk_norm, "bias": bias,
+                                  "position": PartSpec("rope_neox", {"head_dim": hd, "theta": 5000.0})})
+    part, w = build("mixer", spec, "L.", rt)
+    names = set(w)
+    assert ("L.self_attn.q_layernorm.weight" in names) == qk_norm and ("L.self_attn.q_proj.bias" in names) == bias
+    rng = np.random.default_rng(1)
+    xs = {1: rounded(rng.standard_normal((29, H)), precision), 2: rounded(rng.standard_normal((6, H)), precision)}
+    got = run_mixer(part, rt, xs, cuts=[4, 1, 1, 9, 30])
+    for r, xt in xs.items():
+        x = xt.double().numpy()
+        T = x.shape[0]
+        pos = np.arange(T)
+        q = x @ w["L.self_attn.q_proj.weight"].T
+        k = x @ w["L.self_attn.k_proj.weight"].T
+        v = x @ w["L.self_attn.v_proj.weight"].T
+        if bias:
+            q, k, v = q + w["L.self_attn.q_proj.bias"], k + w["L.self_attn.k_proj.bias"], v + w["L.self_attn.v_proj.bias"]
+        q, k, v = q.reshape(T, nh, hd), k.reshape(T, nkv, hd), v.reshape(T, nkv, hd)
+        if qk_norm:
+            q = P.rms_norm(q, w["L.self_attn.q_layernorm.weight"], 1e-5)
+            k = P.rms_norm(k, w["L.self_attn.k_layernorm.weight"], 1e-5)
+        q, k = P.rope_neox(q, pos, hd, 5000.0), P.rope_neox(k, pos, hd, 5000.0)
+        ref = P.attend(q, k, v, 1 / math.sqrt(hd)).reshape(T, nh * hd) @ w["L.self_attn.out_proj.weight"].T
+        if bias:
+            ref = ref + w["L.self_attn.out_proj.bias"]
+        assert np.abs(got[r] - ref).max() <= TOL[precision] * max(1.0, np.abs(ref).max()), (r, np.abs(got[r] - ref).max())
+
+
+def test_two_engines_in_one_process_do_not_share_launch_state():
+    """Two engines of different configurations stepped in turn: each keeps its own launcher bookkeeping and
+    scratch (pending split partials, captured graphs), and gives what it gives alone."""
+    from imparo_b200.engine import Engine, StepItem
+    from tests.gpu_helpers import make_requests, model_dir, plain_model
+    engines, toks, refs = {}, {}, {}
+    for name, page in (("E", 16), ("F", 64)):
+        engines[name] = Engine(model_dir(name), dtype="bfloat16", ctx=128, parallel=2, page_size=page)
+        toks[name] = make_requests(name, [40], seed=7)["r0"]
+        refs[name] = plain_model(name).logits(toks[name])
+        engines[name].add_request(1)
+    assert engines["E"].rt.launch_state is not engines["F"].rt.launch_state
+    at = {"E": 0, "F": 0}
+    for cut in (8, 1, 1, 1, 5, 1, 1, 1, 1, 20):
+        for name, eng in engines.items():
+            n = min(cut, 40 - at[name])
+            if n <= 0:
+                continue
+            got = eng.step([StepItem(1, toks[name][at[name]:at[name] + n], [n - 1])]).cpu().numpy()[0]
+            ref = refs[name][at[name] + n - 1]
+            assert np.abs(got - ref).max() <= 2.5e-2 * np.abs(refs[name]).max(), (name, at[name], n)
+            at[name] += n
+    for eng in engines.values():
+        eng.check_device_status()
+        eng.end_request(1)
+        assert eng.step_fn.graph_replays >= 1

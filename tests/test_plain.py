@@ -110,3 +110,24 @@ def test_whole_model_is_causal_and_prefix_stable(tmp_path):
         assert full.shape == (23, cfg["vocab_size"])
         assert np.allclose(m.logits(toks[:9]), full[:9], atol=1e-12)
         assert P.PlainConfig(cfg).ff == (192 if name == "a" else 512)
+
+
+def test_blocked_attention_is_the_same_formula():
+    """attend_blocked (a block of queries at a time, for long sequences) against attend (token by token), with and
+    without a window, block sizes that do and do not divide the length."""
+    rng = np.random.default_rng(3)
+    T, nh, nkv, hd = 45, 6, 2, 8
+    q, k, v = rng.standard_normal((T, nh, hd)), rng.standard_normal((T, nkv, hd)), rng.standard_normal((T, nkv, hd))
+    for window in (None, 7, 16):
+        ref = P.attend(q, k, v, 0.3, window)
+        for block in (1, 8, 16, 64):
+            assert np.allclose(P.attend_blocked(q, k, v, 0.3, window, block), ref, atol=1e-12), (window, block)
+
+
+def test_logits_at_places_equal_whole_logits(tmp_path):
+    from imparo_b200.weights import write_random_model
+    d = write_random_model(str(tmp_path / "b"), TINY_B, seed=4)
+    m = P.PlainLfm2(d, np.float64)
+    toks = np.random.default_rng(2).integers(0, TINY_B["vocab_size"], 37).tolist()
+    full = m.logits(toks)
+    assert np.allclose(m.logits_at(toks, [0, 5, 36], attend_block=8), full[[0, 5, 36]], atol=1e-10)

@@ -52,11 +52,35 @@ def register_toy():
 
     register_part("mixer", "toy_running_mean", RunningMeanMixer, replace=True)
 
+    class PositionalTable(Part):
+        """An embedding that reads more of the batch than the token ids: row of the token table plus a learned
+        row per absolute position (out = E[token] + P[position])."""
+        graph_safe = False      # it indexes with torch, which allocates: not for capture and replay
+
+        def __init__(self, params, prefix, rt):
+            super().__init__(params, prefix, rt)
+            self.vocab, self.width, self.n_pos = int(params["vocab"]), int(params["width"]), int(params["positions"])
+            self.names = (prefix + params["name"], prefix + "toy.positions.weight")
+            self.table = self.pos = None
+
+        def weight_specs(self):
+            return [WeightSpec(self.names[0], ((self.vocab, self.width),)), WeightSpec(self.names[1], ((self.n_pos, self.width),))]
+
+        def bind(self, tensors):
+            self.table, self.pos = tensors[self.names[0]], tensors[self.names[1]]
+
+        def forward(self, batch):
+            out = self.rt.workspace.get("residual", (batch.n_tokens, self.width), torch.float32)
+            out.copy_(self.table[batch.token_ids.long()].float() + self.pos[batch.positions.long()].float())
+            return out
+
+    register_part("embedding", "toy_positional_table", PositionalTable, replace=True)
+
     def parse(values):
         r = KeyReader(values)
         return {"vocab": r.integer("vocab_size"), "hidden": r.integer("hidden_size"), "layers": r.strings("layer_types"),
                 "heads": r.integer("num_attention_heads"), "ff": r.integer("ff"), "eps": r.number("norm_eps"),
-                "schedule": values.get("layer_schedule")}
+                "schedule": values.get("layer_schedule"), "embedding": values.get("embedding", "token_table")}
 
     def spec(c):
         H = c["hidden"]
@@ -73,7 +97,8 @@ def register_toy():
         sched = c["schedule"] or list(range(len(layers)))
         sched = tuple(ScheduleEntry(*e) if isinstance(e, (list, tuple)) else ScheduleEntry(e) for e in sched)
         return ModelSpec(architecture="ToyForCausalLM", vocab_size=c["vocab"], hidden_size=H,
-                         embedding=PartSpec("token_table", {"vocab": c["vocab"], "width": H, "name": "toy.embed.weight"}),
+                         embedding=PartSpec(c["embedding"], {"vocab": c["vocab"], "width": H, "name": "toy.embed.weight",
+                                                              "positions": 128}),
                          layers=tuple(layers), schedule=sched,
                          final_norm=PartSpec("rmsnorm", {"width": H, "eps": c["eps"], "name": "toy.norm.weight"}),
                          head=PartSpec("linear", {"vocab": c["vocab"], "width": H, "name": "toy.embed.weight"}),
@@ -123,6 +148,35 @@ def test_toy_mixer_is_registered_built_and_stepped(schedule):
             assert np.abs(other[k] - results[0][k]).max() <= 1e-5, k
     # and the state matters: the same token at another position gives other logits
     assert np.abs(results[0][("r0", 5)] - results[0][("r0", 6)]).max() > 1e-3
+
+
+def test_toy_embedding_that_reads_positions():
+    """An embedding part gets the step's batch, so one that adds learned absolute positions is a new part and
+    nothing else: registered here, built by the engine, stepped whole, in portions and mixed."""
+    from imparo_b200.engine import Engine, StepItem
+    register_toy()
+    cfg = dict(TOY, embedding="toy_positional_table", layer_types=["toy", "toy"])       # no mixer knows positions
+    rng = np.random.default_rng(3)
+    reqs = {f"r{i}": rng.integers(0, 97, n).tolist() for i, n in enumerate([30, 17])}
+    results = []
+    for build in (traces.whole, traces.portions, lambda r: traces.mixed(r, seed=4, tail=4, max_portion=7)):
+        steps = build(reqs)
+        eng = Engine(config=cfg, seed=9, dtype="float32", ctx=64, parallel=2, page_size=4, num_pages=8,
+                     random_init={"matrix_std": 0.1})
+        results.append(logits_by_position(steps, run_trace(eng, steps)))
+    for other in results[1:]:
+        for k in results[0]:
+            assert np.abs(other[k] - results[0][k]).max() <= 1e-5, k
+    # the part alone: rows of the two tables, added
+    emb = eng.model.embedding
+    eng.add_request(7)
+    eng.cache.reserve(7, 3)
+    batch = eng.step_fn.build_batch([StepItem(7, [5, 5, 9])])
+    x = emb.forward(batch).cpu()
+    eng.cache.rollback(7)
+    eng.end_request(7)
+    want = emb.table[[5, 5, 9]].float().cpu() + emb.pos[[0, 1, 2]].float().cpu()
+    assert torch.allclose(x, want, atol=1e-6) and not torch.allclose(x[0], x[1])
 
 
 # ---------------------------------------------------------------------------------------------

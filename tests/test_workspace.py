@@ -1,5 +1,5 @@
 """The activation scratch by tag (no GPU needed): stable addresses, growth, views handed out again,
-and the switches read from the environment on every launch."""
+(the engine's settings and switches: tests/test_engine_config.py)."""
 import os
 
 import torch
@@ -29,16 +29,3 @@ def test_small_buffers_grow_by_doubling():
     ws.get("s", (190,), torch.float32)                     # within the doubled size: no move
     assert ws.generation == g
     assert ws.bytes() == 200 * 4
-
-
-def test_switches_follow_the_environment(monkeypatch):
-    from imparo_b200.kernels import ops
-    monkeypatch.delenv("IMPARO_GEMM", raising=False)
-    monkeypatch.delenv("IMPARO_TC_MAX_TOKENS", raising=False)
-    assert ops.gemm_backend() == "tcgen05" and ops.tc_max_tokens() == ops.TC_MAX_TOKENS
-    monkeypatch.setenv("IMPARO_GEMM", "library")
-    monkeypatch.setenv("IMPARO_TC_MAX_TOKENS", "16")
-    assert ops.gemm_backend() == "library" and ops.tc_max_tokens() == 16
-    monkeypatch.delenv("IMPARO_GEMM")
-    assert ops.gemm_backend() == "tcgen05"
-    assert ops._env("IMPARO_NOT_SET", "fallback") == "fallback" and os.environ.get("IMPARO_NOT_SET") is None
