@@ -58,7 +58,7 @@ class KernelSwitches:
     fuse_norm: bool = False               # IMPARO_FUSE_NORM: RMS norm of the input inside the product
     fuse_add_norm: bool = False           # IMPARO_FUSE_ADD_NORM: the next norm computed by the product's last CTA
     fuse_producers: bool = True           # IMPARO_FUSE_PRODUCERS: the attention combine inside the output product (decode rows)
-    attn_prefill: str = "auto"            # IMPARO_ATTN_PREFILL: "auto" | "mma" | "tcgen05"
+    attn_prefill: str = "auto"            # IMPARO_ATTN_PREFILL: "auto" | "mma" | "tcgen05" | "tcgen05_one_tile"
 
     ENV_PREFIX = "IMPARO_"
 
@@ -67,8 +67,8 @@ class KernelSwitches:
         self.prefill_gemm = {"lib": "library", "cublas": "library"}.get(self.prefill_gemm.lower(), self.prefill_gemm.lower())
         if self.gemm not in ("tcgen05", "library") or self.prefill_gemm not in ("tcgen05", "library"):
             raise ConfigError("gemm and prefill_gemm must be 'tcgen05' or 'library'")
-        if self.attn_prefill not in ("auto", "mma", "tcgen05"):
-            raise ConfigError("attn_prefill must be 'auto', 'mma' or 'tcgen05'")
+        if self.attn_prefill not in ("auto", "mma", "tcgen05", "tcgen05_one_tile"):
+            raise ConfigError("attn_prefill must be 'auto', 'mma', 'tcgen05' or 'tcgen05_one_tile'")
         if self.tc_max_tokens < 0 or self.prefill_tc_min_tokens < 1:
             raise ConfigError("tc_max_tokens must be >= 0 and prefill_tc_min_tokens >= 1")
 

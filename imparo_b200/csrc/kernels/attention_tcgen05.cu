@@ -422,19 +422,427 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a
     return e == cudaSuccess ? 0 : (int)e;
 }
 
+
+// ---- two query tiles per CTA in turn (head size 64) ------------------------------------------------
+// The kernel above does the two products and the softmax of a step one after the other; the tensor cores wait while
+// the softmax runs.  Here a CTA owns TWO query tiles of 128 rows (consecutive tokens of one request, the same kv
+// head) and ONE stream of keys and values that both use:
+//
+//   warp 0      TMA: keys and values page by page into a ring of three stages
+//   warp 1      tcgen05.mma for both tiles: S_x = Q_x K^T into the tile's 128 score columns of tensor memory, and
+//               O_x += P_x V accumulated IN tensor memory; while one tile's softmax runs, the other tile's products do
+//   warps 2-9   softmax of tile A, warps 10-17 of tile B: two threads per row, one for each half of the step's keys
+//               and of the head's dims.  A thread's 64 scores of the step go to registers in one sweep (the score
+//               columns are free for the next step's product at once), the two threads of a row agree on the row's
+//               max through shared memory, P = exp2(s - max) goes to shared memory as bfloat16 in the MMA's layout.
+// The output stays in tensor memory across steps.  When a row's max grows, what has been accumulated must be scaled
+// down; that costs a round trip of the row's output through registers, so it is done only when the max has grown by
+// more than 8 (in log2 units: a factor of 256) in some row of the warp; otherwise the old max stays in use, the
+// exponentials are at most 256, and the final division by the row's sum (taken with the same max) gives the same
+// result.  Formulas and masks as above.
+constexpr int PP_THREADS = 576;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: softmax of tile A, 10-17: of tile B
+constexpr int PP_STAGES = 3;
+constexpr float PP_GROW = 8.0f;
+
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void keep32(uint32_t (&r)[32]) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]) :: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(PP_THREADS, 1)
+attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a) {
+    constexpr int HD = 64;
+    constexpr uint32_t Q_BYTES = REGION, P_BYTES = 2 * REGION, STAGE_BYTES = 2 * REGION;      // per tile; per stage K | V
+    constexpr uint32_t TMEM_COLS = 512;                      // scores of A, of B: 0..127, 128..255; outputs: 256.., 320..
+    extern __shared__ __align__(1024) uint8_t fa_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;                                     // [2][Q_BYTES]
+    uint8_t* p_s = q_s + 2 * Q_BYTES;                        // [2][P_BYTES]
+    uint8_t* kv_s = p_s + 2 * P_BYTES;                       // [stage][K | V]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + PP_STAGES * STAGE_BYTES);
+    uint64_t* kv_full = bars;                                // [PP_STAGES]
+    uint64_t* kv_empty = kv_full + PP_STAGES;                // [PP_STAGES]
+    uint64_t* q_ready = kv_empty + PP_STAGES;
+    uint64_t* s_ready = q_ready + 1;                         // [2]  the tile's scores of a step are complete
+    uint64_t* s_free = s_ready + 2;                          // [2]  ... and have been read into registers
+    uint64_t* p_ready = s_free + 2;                          // [2]  P of the step is in shared memory, the output scaled
+    uint64_t* o_done = p_ready + 2;                          // [2]  P V of the step is accumulated
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(bars) + 64;        // [tile][buffer][half][row]: what the two threads of a row exchange
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = a.nh / a.nkv;
+    const int TQ = ROWS / G;                                 // tokens per tile; a CTA takes two tiles
+    const int kvh = blockIdx.x;
+    int item = 0, pair = (int)gridDim.y - 1 - (int)blockIdx.y, n_item = 0, row0 = 0;
+    for (; item < a.n_items; ++item) {
+        row0 = a.item_row_start[item];
+        n_item = a.item_row_start[item + 1] - row0;
+        const int pairs = (n_item + 2 * TQ - 1) / (2 * TQ);
+        if (pair < pairs) break;
+        pair -= pairs;
+    }
+    if (item >= a.n_items) {                                 // the grid is an upper bound (uniform per CTA)
+        if (threadIdx.x == 0) pdl_wait();
+        return;
+    }
+    // tile x: tokens tok0[x] .. tok0[x] + n_tok[x] - 1 of the request
+    const int tokA = pair * 2 * TQ;
+    const int n_tokA = min(TQ, n_item - tokA), n_tokB = max(0, min(TQ, n_item - tokA - TQ));
+    const int start = a.item_start_pos[item];
+    const int posA0 = start + tokA, pos_lastA = posA0 + n_tokA - 1;
+    const int posB0 = posA0 + TQ, pos_lastB = posB0 + n_tokB - 1;
+    const int* tab = a.table + (size_t)item * a.max_blocks;
+    const int lo_min = (a.window > 0 && posA0 + 1 > a.window) ? posA0 + 1 - a.window : 0;
+    const int kb_first = lo_min / KEYS;
+    const int nA = pos_lastA / KEYS - kb_first + 1;
+    const int nB = n_tokB > 0 ? pos_lastB / KEYS - kb_first + 1 : 0;
+    const int n_steps = max(nA, nB);
+    const int pos_last = n_tokB > 0 ? pos_lastB : pos_lastA;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PP_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        mbar_init(q_ready, 512);
+        for (int x = 0; x < 2; ++x) { mbar_init(&s_ready[x], 1); mbar_init(&s_free[x], 256); mbar_init(&p_ready[x], 256); mbar_init(&o_done[x], 1); }
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();                                      // this step's keys were written by the kernel before
+            const int pages_per_step = KEYS / a.page_size;
+            const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
+            for (int i = 0; i < n_steps && !*gave_up; ++i) {
+                const int s = i % PP_STAGES;
+                if (i >= PP_STAGES && !mbar_wait(&kv_empty[s], ((i / PP_STAGES) - 1) & 1)) {
+                    report(a.status, IMPARO_ST_WAIT_LIMIT, 40, i, s);
+                    *gave_up = 1;
+                    break;
+                }
+                uint8_t* kdst = kv_s + s * STAGE_BYTES;
+                uint8_t* vdst = kdst + REGION;
+                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                const int blk0 = (kb_first + i) * pages_per_step;
+                for (int pg = 0; pg < pages_per_step; ++pg) {
+                    const int blk = min(max(blk0 + pg, first_blk), last_blk);       // (see the kernel above)
+                    int page = blk < a.max_blocks ? tab[blk] : -1;
+                    if (page < 0 || page >= a.n_pages) {
+                        report(a.status, IMPARO_ST_PAGE_RANGE, 41, item, page);
+                        page = 0;
+                    }
+                    const int y = page * a.page_size;
+                    const uint32_t off = (uint32_t)pg * a.page_size * 128;
+                    tma_load_2d(kdst + off, &map_k, &kv_full[s], kvh * HD, y);
+                    tma_load_2d(vdst + off, &map_v, &kv_full[s], kvh * HD, y);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = instr_desc_ab(ROWS, KEYS, false);
+            const uint32_t idesc_o = instr_desc_ab(ROWS, HD, true);
+            bool ok = mbar_wait(q_ready, 0);
+            if (!ok) { report(a.status, IMPARO_ST_WAIT_LIMIT, 42, 0, 0); *gave_up = 1; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            int kv_seen = -1;                                // steps whose keys and values have landed
+            auto need_kv = [&](int j) -> bool {
+                while (kv_seen < j) {
+                    const int i = kv_seen + 1;
+                    if (!mbar_wait(&kv_full[i % PP_STAGES], (i / PP_STAGES) & 1)) {
+                        report(a.status, IMPARO_ST_WAIT_LIMIT, 43, i, 0);
+                        *gave_up = 1;
+                        return false;
+                    }
+                    kv_seen = i;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                return true;
+            };
+            auto issue_s = [&](int x, int j) {               // S_x = Q_x K_j^T
+                const uint32_t qb = smem_u32(q_s + x * Q_BYTES), kb = smem_u32(kv_s + (j % PP_STAGES) * STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma(tmem_base + x * 128, smem_desc(qb + k * 32), smem_desc(kb + k * 32), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(&s_ready[x]);
+            };
+            auto issue_pv = [&](int x, int j) {              // O_x (+)= P_x V_j
+                const uint32_t vb = smem_u32(kv_s + (j % PP_STAGES) * STAGE_BYTES + REGION), pb = smem_u32(p_s + x * P_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < KEYS / UMMA_K; ++kk)
+                    umma(tmem_base + 256 + x * HD, smem_desc(pb + (kk >> 2) * REGION + (kk & 3) * 32),
+                         smem_desc_mn(vb + kk * (UMMA_K * 128), REGION), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&o_done[x]);
+            };
+            if (ok && need_kv(0)) {
+                if (nA > 0) issue_s(0, 0);
+                if (nB > 0) issue_s(1, 0);
+            } else {
+                ok = false;
+            }
+            // Tile B's positions lie behind tile A's, so B has every step A has (or B is empty): the last product
+            // that reads step j's keys and values is B's, or A's when there is no tile B.
+            const int last_x = nB > 0 ? 1 : 0;
+            for (int j = 0; j < n_steps && ok; ++j) {
+                for (int x = 0; x < 2 && ok; ++x) {
+                    const int n_x = x == 0 ? nA : nB;
+                    if (j < n_x) {
+                        if (!mbar_wait(&p_ready[x], j & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 44, j, x); *gave_up = 1; ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_pv(x, j);
+                    }
+                    if (x == last_x) umma_commit(&kv_empty[j % PP_STAGES]);      // the stage may be filled again
+                    if (j + 1 < n_x) {
+                        // the tile's next scores: while its softmax runs, the other tile's products follow
+                        if (!need_kv(j + 1)) { ok = false; break; }
+                        if (!mbar_wait(&s_free[x], j & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 45, j, x); *gave_up = 1; ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_s(x, j + 1);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- softmax: two threads per row of tile x, one for each half of the step's keys and of the head's dims ----
+        const int x = (warp - 2) >> 3;
+        const int half = ((warp - 2) >> 2) & 1;
+        const int r = (warp & 3) * 32 + lane;
+        const int n_x = x == 0 ? nA : nB;
+        const int n_rows = (x == 0 ? n_tokA : n_tokB) * G;
+        const bool valid = r < n_rows;
+        const int tok = r / G, head = kvh * G + r % G;
+        const int pos0 = x == 0 ? posA0 : posB0;
+        const int pos_r = pos0 + tok;
+        const int pos_last_x = x == 0 ? pos_lastA : pos_lastB;
+        const int lo_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
+        const int lo_last = (a.window > 0 && pos_last_x + 1 > a.window) ? pos_last_x + 1 - a.window : 0;
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t t_s = t_lane + x * 128 + half * 64, t_o = t_lane + 256 + x * HD + half * (HD / 2);
+        const size_t row_off = ((size_t)(row0 + tokA + x * TQ + (valid ? tok : 0)) * a.nh + head) * HD;
+        float* my_x = xch + ((x * 2 + 0) * 2 + half) * ROWS + r;              // [tile][buffer][half][row]
+        float* other_x = xch + ((x * 2 + 0) * 2 + (half ^ 1)) * ROWS + r;
+        pdl_wait();
+        {
+            // this thread's half of the row's queries -> shared memory, 16-byte chunks swizzled as the MMA reads them
+            const uint4* src = reinterpret_cast<const uint4*>(a.q + row_off);
+#pragma unroll
+            for (int cc = 0; cc < HD / 16; ++cc) {
+                const int c = half * (HD / 16) + cc;
+                const uint4 v = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(q_s + x * Q_BYTES + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(q_ready);
+        }
+        float m_used = -INFINITY, l_run = 0.f;
+        const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
+        bool ok = true;
+        uint8_t* prow = p_s + x * P_BYTES + half * REGION + r * 128;         // keys 0-63 and 64-127 are the two blocks of P
+        for (int j = 0; j < n_x; ++j) {
+            if (!mbar_wait(&s_ready[x], j & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 46, j, r); *gave_up = 1; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sv[2][32];                              // this thread's 64 scores of the step
+            tmem_ld32_nowait(t_s, sv[0]);
+            tmem_ld32_nowait(t_s + 32, sv[1]);
+            tmem_wait_ld();
+            keep32(sv[0]); keep32(sv[1]);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&s_free[x]);                         // the score columns may take the next step's product
+            const int key0 = (kb_first + j) * KEYS + half * 64;              // this thread's first key of the step
+            const int j_hi = valid ? min(63, pos_r - key0) : -1;             // the keys this row sees: [j_lo, j_hi]
+            const int j_lo = max(0, lo_r - key0);
+            const bool whole = (kb_first + j) * KEYS + KEYS - 1 <= pos0 && (kb_first + j) * KEYS >= lo_last;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (whole) {
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[q2][e]));
+            } else {
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int jj = q2 * 32 + e;
+                        if (jj >= j_lo && jj <= j_hi) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[q2][e]));
+                    }
+            }
+            // the row's max: the two threads of a row exchange theirs through shared memory (two buffers in turn: a
+            // buffer is written again only after the barrier of the step between, which both pass after reading it)
+            const int buf = (j & 1) * 2 * ROWS;
+            my_x[buf] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the barrier also carries the "a wait ran out somewhere" flag as a reduction, so that all 256 threads of
+            // the tile leave together (a flag another warp sets while some threads are past their own look at it
+            // would otherwise split them, and the next barrier would never fill)
+            int any_bad;
+            {
+                const int bad = *gave_up;
+                asm volatile("{\n.reg .pred p, q;\nsetp.ne.b32 q, %2, 0;\nbar.red.or.pred p, %1, 256, q;\nselp.b32 %0, 1, 0, p;\n}"
+                             : "=r"(any_bad) : "r"(1 + x), "r"(bad) : "memory");
+            }
+            if (any_bad) { ok = false; break; }
+            const float m_row = fmaxf(my_x[buf], other_x[buf]) * sl2;       // sl2 > 0: the max commutes with the scaling
+            // the max in use stays unless it would be exceeded by more than PP_GROW somewhere in the warp
+            float m_new, corr = 1.f;
+            if (j == 0) {
+                m_new = m_row;
+            } else {
+                const bool grow = m_row > m_used + PP_GROW;                  // (true for m_used = -inf and a finite m_row)
+                const bool rescale = __any_sync(0xffffffffu, grow);
+                m_new = grow ? m_row : m_used;
+                corr = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);   // 1 when the max stays
+                if (!mbar_wait(&o_done[x], (j - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 47, j, r); *gave_up = 1; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (rescale) {                                              // this thread's dims of the accumulated output, in place
+#pragma unroll 1
+                    for (int c = 0; c < HD / 2; c += 16) {
+                        float ov[16];
+                        tmem_ld16(t_o + c, ov);
+                        uint32_t ow[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) ow[e] = __float_as_uint(ov[e] * corr);
+                        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                                     ::"r"(t_o + c), "r"(ow[0]), "r"(ow[1]), "r"(ow[2]), "r"(ow[3]), "r"(ow[4]), "r"(ow[5]), "r"(ow[6]), "r"(ow[7]),
+                                       "r"(ow[8]), "r"(ow[9]), "r"(ow[10]), "r"(ow[11]), "r"(ow[12]), "r"(ow[13]), "r"(ow[14]), "r"(ow[15]) : "memory");
+                    }
+                    tmem_wait_st();
+                }
+            }
+            const float nbase = (m_new == -INFINITY) ? 0.f : -m_new;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (whole) {
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {         // 8 keys = one 16-byte chunk of P
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            const float p0 = ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e]), sl2, nbase));
+                            const float p1 = ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e + 1]), sl2, nbase));
+                            sum4[(e >> 1) & 3] += p0 + p1;
+                            w[e >> 1] = pack2(p0, p1);
+                        }
+                        *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+            } else {
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            const int jj = q2 * 32 + c8 * 8 + e;
+                            const float p0 = (jj >= j_lo && jj <= j_hi) ? ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e]), sl2, nbase)) : 0.f;
+                            const float p1 = (jj + 1 >= j_lo && jj + 1 <= j_hi) ? ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e + 1]), sl2, nbase)) : 0.f;
+                            sum4[(e >> 1) & 3] += p0 + p1;
+                            w[e >> 1] = pack2(p0, p1);
+                        }
+                        *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+            }
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            m_used = m_new;
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&p_ready[x]);
+        }
+        if (ok && n_x > 0) {
+            if (!mbar_wait(&o_done[x], (n_x - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 48, n_x, r); *gave_up = 1; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the row's sum: the two threads' shares, in the order (keys 0-63, keys 64-127)
+            const int buf = (n_x & 1) * 2 * ROWS;
+            my_x[buf] = l_run;
+            asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
+            const float l = half == 0 ? my_x[buf] + other_x[buf] : other_x[buf] + my_x[buf];
+            if (!*gave_up) {
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                uint32_t ov[32];
+                tmem_ld32_nowait(t_o, ov);
+                tmem_wait_ld();
+                keep32(ov);
+                if (valid) {
+                    uint4* dst = reinterpret_cast<uint4*>(a.out + row_off + half * (HD / 2));
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        dst[q] = make_uint4(pack2(__uint_as_float(ov[q * 8]) * inv, __uint_as_float(ov[q * 8 + 1]) * inv),
+                                            pack2(__uint_as_float(ov[q * 8 + 2]) * inv, __uint_as_float(ov[q * 8 + 3]) * inv),
+                                            pack2(__uint_as_float(ov[q * 8 + 4]) * inv, __uint_as_float(ov[q * 8 + 5]) * inv),
+                                            pack2(__uint_as_float(ov[q * 8 + 6]) * inv, __uint_as_float(ov[q * 8 + 7]) * inv));
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+static int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + 2 * REGION + 4 * REGION + (size_t)PP_STAGES * 2 * REGION + 256 + 2 * 2 * 2 * ROWS * 4;
+    static bool configured = false;
+    cudaError_t e;
+    if (!configured) {
+        e = cudaFuncSetAttribute(attn_prefill_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    e = launch(attn_prefill_pp_kernel, grid, dim3(PP_THREADS), smem, stream, mk, mv, a);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 }  // namespace fa
 }  // namespace imparo
 
 using namespace imparo;
 
 // bfloat16, head size 64 or 128, at most 8 query heads per kv head, pages of 16, 32, 64 or 128
-// positions; else -8 (the caller uses another kernel).  n_tok is the batch's token count, n_items
+// positions; else -8 (the caller uses another kernel).  two_tiles: at head size 64 the kernel that gives a CTA two
+// query tiles in turn (else, and at head size 128, one tile per CTA).  n_tok is the batch's token count, n_items
 // its requests.  The caches are [n_pages * page_size rows, nkv * hd] arenas.
 extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                            const int* item_row_start, const int* item_start_pos, int n_items,
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, int n_tok, int nh, int nkv, int hd,
-                                           int* status, cudaStream_t stream) {
+                                           int two_tiles, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     const int G = nh / nkv;
@@ -456,6 +864,11 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.item_row_start = item_row_start; a.item_start_pos = item_start_pos; a.table = table; a.status = status;
     a.n_items = n_items; a.max_blocks = max_blocks; a.page_size = page_size; a.n_pages = n_pages; a.window = window;
     a.nh = nh; a.nkv = nkv; a.scale = scale;
+    if (hd == 64 && two_tiles) {
+        // two tiles per CTA: half as many CTAs along y (an upper bound again)
+        const long long pairs = (n_tok + 2 * TQ - 1) / (2 * TQ) + n_items;
+        return fa::launch_pp(mk, mv, a, dim3(nkv, (unsigned)pairs), stream);
+    }
     dim3 grid(nkv, (unsigned)tiles);
     return hd == 64 ? fa::launch_tc<64>(mk, mv, a, grid, stream) : fa::launch_tc<128>(mk, mv, a, grid, stream);
 }

@@ -173,7 +173,12 @@ class StepFunction:
         b.token_src = d[offs[7 + ng]:offs[7 + ng] + T]
         b.n_single = n_single
         b.fresh_slots = d[fresh_at:fresh_at + R] if fresh else None
-        b.max_tokens_per_item = max(len(it.tokens) for it in items)
+        # The longest portion, rounded up to a power of two: launches may depend on it (which attention kernel takes
+        # the step; how far back a request's cache rows are surely older than this step), and as an upper bound it
+        # serves every step whose longest portion is no longer, so that steps of a continuous batch, whose longest
+        # portion is whatever the token budget left over, share captured graphs.
+        longest = max(len(it.tokens) for it in items)
+        b.max_tokens_per_item = 1 if longest <= 1 else 1 << (longest - 1).bit_length()
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
         b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),

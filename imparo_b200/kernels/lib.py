@@ -94,7 +94,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_attention_prefill",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill_tc",
-             [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
+             [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_fold_partials", [P, I, c_int64, P, I, c_int64, S])
     _declare(lib, "imparo_gather_rows_f32", [P, P, P, I, I, S])

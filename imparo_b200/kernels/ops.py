@@ -120,7 +120,10 @@ def _check(rc: int, what: str, kind: str = "own") -> None:
                -3: "head size must be a multiple of 16 between 16 and 256",
                -4: "rotated dimensions must be even and at most the head size",
                -5: "kv heads must divide heads", -6: "conv taps must be between 2 and 16",
-               -7: "temperature sampling needs uniform numbers"}
+               -7: "temperature sampling needs uniform numbers",
+               -23: "rows must be 16 bytes wide and 16-byte aligned (K and the row stride multiples of 8 elements; an output "
+                    "of 8 bfloat16 or 4 float32 per group)",
+               -22: "unknown epilogue", -24: "scratch missing", -25: "the kernel does not take this case"}
     if rc < 0:
         raise KernelError(f"{what}: refused: {reasons.get(rc, rc)}")
     if rc >= 1000:
@@ -860,7 +863,8 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     query heads per kv head).  Returns False, having launched nothing, for other shapes.
 
     kernel: "tcgen05" (TMA + tcgen05.mma with the scores in tensor memory; pages of 16, 32, 64 or
-    128 positions), "mma" (mma.sync, any page size), or "auto": the first where it takes the shape
+    128 positions; at head size 64 a CTA takes two query tiles in turn), "tcgen05_one_tile" (the same with one tile
+    per CTA at every head size), "mma" (mma.sync, any page size), or "auto": the first where it takes the shape
     (IMPARO_ATTN_PREFILL=mma in the environment makes "auto" skip it)."""
     if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
         return False
@@ -872,18 +876,18 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     _need(k_cache.numel() >= n_pages * page_size * nkv * hd, "cache arena smaller than n_pages")
     _need(table.dtype == torch.int32 and table.dim() == 2 and table.shape[0] >= n_items, "block table must be int32 [items, blocks]")
     _need(item_row_start.numel() >= n_items + 1 and item_start_pos.numel() >= n_items, "attention_prefill: item arrays")
-    _need(kernel in ("auto", "tcgen05", "mma"), "attention_prefill: kernel is auto, tcgen05 or mma")
+    _need(kernel in ("auto", "tcgen05", "tcgen05_one_tile", "mma"), "attention_prefill: kernel is auto, tcgen05, tcgen05_one_tile or mma")
     args = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
             _stream())
     if kernel == "auto":
         kernel = _S.switches.attn_prefill
-    if kernel in ("auto", "tcgen05"):
-        rc = _lib.kernels().imparo_attention_prefill_tc(*args)
+    if kernel in ("auto", "tcgen05", "tcgen05_one_tile"):
+        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], 0 if kernel == "tcgen05_one_tile" else 1, *args[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
             return True
-        if kernel == "tcgen05":
+        if kernel != "auto":
             return False
     _check(_lib.kernels().imparo_attention_prefill(*args), "attention_prefill")
     return True

@@ -174,12 +174,12 @@ def attend_blocked(q, k, v, scale, window=None, block=256):
             kk = k[lo_blk:b, kvh, :]                                  # [keys, hd]
             vv = v[lo_blk:b, kvh, :]
             qq = q[a:b, kvh * per_kv:(kvh + 1) * per_kv, :]           # [block, per_kv, hd]
-            s = np.einsum("tgd,kd->tgk", qq, kk) * q.dtype.type(scale)
-            s = np.where(dead[:, None, :], neg, s)
-            s = s - s.max(axis=-1, keepdims=True)
-            e = np.exp(s)
-            p = e * (q.dtype.type(1.0) / e.sum(axis=-1, keepdims=True))
-            out[a:b, kvh * per_kv:(kvh + 1) * per_kv, :] = np.einsum("tgk,kd->tgd", p, vv)
+            s = (qq.reshape(-1, hd) @ kk.T).reshape(b - a, per_kv, -1) * q.dtype.type(scale)     # one matrix product per block
+            s[np.broadcast_to(dead[:, None, :], s.shape)] = neg
+            s -= s.max(axis=-1, keepdims=True)
+            np.exp(s, out=s)
+            s *= q.dtype.type(1.0) / s.sum(axis=-1, keepdims=True)
+            out[a:b, kvh * per_kv:(kvh + 1) * per_kv, :] = (s.reshape(-1, s.shape[-1]) @ vv).reshape(b - a, per_kv, hd)
     return out
 
 

@@ -581,7 +581,7 @@ def test_temperature_sampling_is_the_inverse_cdf(V):
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (6, 2, 128), (3, 1, 64), (8, 1, 64), (2, 1, 128), (32, 8, 64), (4, 2, 64),
                                        (5, 1, 64), (6, 1, 128), (7, 1, 64)])
 @pytest.mark.parametrize("page,window", [(4, None), (16, None), (16, 50), (64, 7), (32, 200), (128, None)])
-@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05", "tcgen05_one_tile"])
 def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window, kernel):
     """Prompt portions of several requests in one launch: a long portion that starts in the
     middle of its request, a single token, a whole short prompt, a short tail, and one long enough
@@ -618,7 +618,7 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window, kernel):
             t += 1
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05", "tcgen05_one_tile"])
 def test_attention_prefill_far_key_and_refusals(kernel):
     o = ops()
     nh, nkv, hd, page, n = 8, 2, 64, 16, 900
@@ -895,3 +895,54 @@ def test_output_product_with_the_attention_combine_inside(T, nh, nkv, hd, N, ctx
                                         nh, nkv, hd, scale, None) for t in range(T)])
     want = base.double().cpu().numpy() + ref @ w_o.double().cpu().numpy().T
     assert np.abs(outs[1].double().cpu().numpy() - want).max() <= 2e-2 * np.abs(want).max()
+
+
+# ---------------------------------------------------------------------------------------
+# the persistent tile product for prompt-sized batches (gemm_prefill.cu)
+@pytest.mark.parametrize("T,N,K", [(128, 256, 64), (300, 520, 136), (129, 264, 72), (1000, 768, 1024), (2048, 2048, 2048), (257, 8, 8)])
+@pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "add_f32", "swiglu"])
+def test_prefill_product_against_float64(T, N, K, epi):
+    """Tokens, rows and depth that are no multiples of the tile (128 x 256 x 64), several tiles per CTA (the second
+    accumulator in tensor memory, the ring running on across tiles), every epilogue; against float64 on the same
+    bfloat16 inputs."""
+    o = ops()
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16()
+    rows = 2 * N if epi == "swiglu" else N
+    w = (torch.randn(rows, K, generator=g) * 0.1).bfloat16()
+    xd, wd = x.double(), w.double()
+    status = o.new_status(DEV)
+    if epi == "swiglu":
+        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        o.gemm_prefill(x.to(DEV), w.to(DEV), out, o.EPI_SWIGLU, status)
+        gate, up = xd @ wd[:N].T, xd @ wd[N:].T
+        ref = gate / (1 + torch.exp(-gate)) * up
+        tol = 1e-2
+    elif epi == "add_f32":
+        base = torch.randn(T, N, generator=g)
+        out = base.clone().to(DEV)
+        o.gemm_prefill(x.to(DEV), w.to(DEV), out, o.EPI_ADD_F32, status)
+        ref = base.double() + xd @ wd.T
+        tol = 1e-5                              # 32-bit accumulation over up to 2,048 products
+    else:
+        dt = torch.bfloat16 if epi == "store_bf16" else torch.float32
+        out = torch.full((T, N), float("nan"), dtype=dt, device=DEV)
+        o.gemm_prefill(x.to(DEV), w.to(DEV), out, o.EPI_STORE_BF16 if epi == "store_bf16" else o.EPI_STORE_F32, status)
+        ref = xd @ wd.T
+        tol = 1e-2 if epi == "store_bf16" else 1e-5
+    torch.cuda.synchronize()
+    o.read_status(status)
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= tol * max(1.0, float(ref.abs().max())), err
+
+
+def test_prefill_product_refuses_what_it_cannot_address():
+    o = ops()
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device=DEV)
+    with pytest.raises(o.KernelError, match="refused"):
+        o.gemm_prefill(z(256, 12), z(64, 12), z(256, 64), o.EPI_STORE_BF16)            # K no multiple of 8: rows not 16 bytes
+    with pytest.raises(o.KernelError, match="refused"):
+        o.gemm_prefill(z(256, 16), z(12, 16), z(256, 12), o.EPI_STORE_BF16)            # N no multiple of 8
+    assert not o.prefill_tc_usable(z(256, 12), z(64, 12), z(256, 64))
+    assert not o.prefill_tc_usable(z(100, 16), z(64, 16), z(100, 64))                 # too few tokens for this kernel
+    assert o.prefill_tc_usable(z(256, 16), z(64, 16), z(256, 64))
