@@ -19,7 +19,8 @@ captured for its shape, as every step whose shape repeats is.
 
 --workload continuous | long run the baseline's two other workloads (LFM2-700M sizes under
 continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 32-bit) and
-print one JSON line each; the default is the headline above.
+print one JSON line each; --workload sizes runs the headline's model at further prompt lengths
+and decode contexts; the default is the headline above.
 """
 import argparse
 import json
@@ -126,9 +127,10 @@ def model_numbers(engine):
     return weight_bytes, kv_per_token, prefill_flops, matrix_params + V * H
 
 
-def measure_decode(engine, batch, steps, warmup, rng, sampler=None):
+def measure_decode(engine, batch, steps, warmup, rng, sampler=None, prompt=None):
     """-> (ms per step, launches per step, h2d bytes per step, mean context) with `batch`
-    requests holding PROMPT tokens each."""
+    requests holding `prompt` (default PROMPT) tokens each."""
+    PROMPT = prompt or globals()["PROMPT"]
     import torch
     from imparo_b200.engine import StepItem
     from imparo_b200.kernels import ops
@@ -162,8 +164,9 @@ def measure_decode(engine, batch, steps, warmup, rng, sampler=None):
     return ms, launches, library, ctx
 
 
-def measure_prefill(engine, reps, warmup, rng):
+def measure_prefill(engine, reps, warmup, rng, prompt=None):
     import torch
+    PROMPT = prompt or globals()["PROMPT"]
     from imparo_b200.engine import StepItem
     V = engine.vocab_size
     times = []
@@ -198,6 +201,41 @@ def measure_e2e(engine, batch, steps, warmup, rng):
     assert all(len(o) == n_new for o in out) and len(stamps) > warmup + steps, (len(stamps), warmup + steps)
     dt = stamps[warmup + steps] - stamps[warmup]
     return batch * steps / dt, max(h2d[warmup:warmup + steps + 1])
+
+
+def workload_sizes(args):
+    """LFM2-1.2B layer sizes (all 16 layers, random bfloat16 weights) at further sizes than the headline: one prompt
+    of 512, 2,048, 8,192 and 32,768 tokens (tokens per second; flops over time against the measured bfloat16 peak), and
+    decode steps of 8 requests at contexts of 2,048, 16,384 and 32,768 tokens (tokens per second; bytes the step has
+    to read over its time against the measured HBM peak)."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    longest = 32768
+    engine = Engine(config=dict(LFM2_1_2B), seed=0, dtype="bfloat16", ctx=longest + 256, parallel=8, page_size=PAGE,
+                    max_step_tokens=longest, random_init={"norm_jitter": 0.0})
+    weight_bytes, kv_per_token, prefill_flops, n_params = model_numbers(engine)
+    out = {"metric": "LFM2-1.2B at further sizes: prefill of one prompt, decode at batch 8", "unit": "tokens/s", "dtype": "bf16",
+           "data": "synthetic (random weights, uniform-random token ids)", "prefill": {}, "decode_b8": {}}
+    with ClockSampler() as clocks:
+        for T in (512, 2048, 8192, 32768):
+            ms = measure_prefill(engine, reps=3 if T > 8192 else 5, warmup=3, rng=rng, prompt=T)
+            out["prefill"][str(T)] = {"value": round(T * 1000.0 / ms, 1), "ms": round(ms, 3),
+                                      "frac": round(prefill_flops(T) / (ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+        for ctx_len in (2048, 16384, 32768):
+            ms, _, _, ctx = measure_decode(engine, 8, 30, 5, rng, prompt=ctx_len)
+            nbytes = weight_bytes + 8 * ctx * kv_per_token
+            out["decode_b8"][str(ctx_len)] = {"value": round(8 * 1000.0 / ms, 1), "ms_per_step": round(ms, 4),
+                                              "roofline": {"bound": "hbm", "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                                                           "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                                           "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}}
+    out["peaks"] = pk["source"]
+    out["config"] = {"model": "LFM2-1.2B", "layers": 16, "layers_of_config": 16, "page_size": PAGE, "params": n_params}
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
 
 
 def _preset(name):
@@ -400,7 +438,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes"],
                     help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit")
@@ -423,6 +461,8 @@ def main():
         return workload_continuous(args)
     if args.workload == "long":
         return workload_long(args)
+    if args.workload == "sizes":
+        return workload_sizes(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

@@ -55,8 +55,6 @@ class KernelSwitches:
     prefill_linear: bool = False          # IMPARO_PREFILL_LINEAR: the tile product also for plain products (not only SwiGLU)
     unfolded: bool = True                 # IMPARO_UNFOLDED: in_proj / qkv leave split partials to their consumer
     defer_adds: bool = True               # IMPARO_DEFER_ADDS: products into the stream leave partials to the next norm
-    fuse_norm: bool = False               # IMPARO_FUSE_NORM: RMS norm of the input inside the product
-    fuse_add_norm: bool = False           # IMPARO_FUSE_ADD_NORM: the next norm computed by the product's last CTA
     fuse_producers: bool = True           # IMPARO_FUSE_PRODUCERS: the attention combine inside the output product (decode rows)
     attn_prefill: str = "auto"            # IMPARO_ATTN_PREFILL: "auto" | "mma" | "tcgen05" | "tcgen05_one_tile"
 

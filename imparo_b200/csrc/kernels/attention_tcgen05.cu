@@ -687,25 +687,25 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const int j_hi = valid ? min(63, pos_r - key0) : -1;             // the keys this row sees: [j_lo, j_hi]
             const int j_lo = max(0, lo_r - key0);
             const bool whole = (kb_first + j) * KEYS + KEYS - 1 <= pos0 && (kb_first + j) * KEYS >= lo_last;
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            float mx4[2] = {-INFINITY, -INFINITY};
             if (whole) {
 #pragma unroll
                 for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[q2][e]));
+                    for (int e = 0; e < 32; ++e) mx4[e & 1] = fmaxf(mx4[e & 1], __uint_as_float(sv[q2][e]));
             } else {
 #pragma unroll
                 for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
                         const int jj = q2 * 32 + e;
-                        if (jj >= j_lo && jj <= j_hi) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[q2][e]));
+                        if (jj >= j_lo && jj <= j_hi) mx4[e & 1] = fmaxf(mx4[e & 1], __uint_as_float(sv[q2][e]));
                     }
             }
             // the row's max: the two threads of a row exchange theirs through shared memory (two buffers in turn: a
             // buffer is written again only after the barrier of the step between, which both pass after reading it)
             const int buf = (j & 1) * 2 * ROWS;
-            my_x[buf] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            my_x[buf] = fmaxf(mx4[0], mx4[1]);
             // the barrier also carries the "a wait ran out somewhere" flag as a reduction, so that all 256 threads of
             // the tile leave together (a flag another warp sets while some threads are past their own look at it
             // would otherwise split them, and the next barrier would never fill)
@@ -744,7 +744,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
             }
             const float nbase = (m_new == -INFINITY) ? 0.f : -m_new;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            float sum4[2] = {0.f, 0.f};
             if (whole) {
 #pragma unroll
                 for (int q2 = 0; q2 < 2; ++q2)
@@ -755,7 +755,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         for (int e = 0; e < 8; e += 2) {
                             const float p0 = ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e]), sl2, nbase));
                             const float p1 = ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e + 1]), sl2, nbase));
-                            sum4[(e >> 1) & 3] += p0 + p1;
+                            sum4[(e >> 1) & 1] += p0 + p1;
                             w[e >> 1] = pack2(p0, p1);
                         }
                         *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -771,13 +771,13 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                             const int jj = q2 * 32 + c8 * 8 + e;
                             const float p0 = (jj >= j_lo && jj <= j_hi) ? ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e]), sl2, nbase)) : 0.f;
                             const float p1 = (jj + 1 >= j_lo && jj + 1 <= j_hi) ? ex2(fmaf(__uint_as_float(sv[q2][c8 * 8 + e + 1]), sl2, nbase)) : 0.f;
-                            sum4[(e >> 1) & 3] += p0 + p1;
+                            sum4[(e >> 1) & 1] += p0 + p1;
                             w[e >> 1] = pack2(p0, p1);
                         }
                         *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
             }
-            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            l_run = l_run * corr + (sum4[0] + sum4[1]);
             m_used = m_new;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -36,9 +36,8 @@ enum Epilogue { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU_BF16 = 3, PAR
 // the four epilogue warps (idle during the main loop) compute it after the wait on the previous kernel and write
 // it, as bfloat16 in the MMA's swizzled K-major layout, into shared memory for all k-blocks of this CTA; the ring
 // then carries W tiles only, and the kernel that would have made the tensor is gone from the chain:
-//   PROD_NORM     the RMS norm of rows of the 32-bit stream
 //   PROD_COMBINE  the ordered combine of the split-key attention's partial results
-enum Producer { PROD_NONE = 0, PROD_NORM = 1, PROD_COMBINE = 3 };
+enum Producer { PROD_NONE = 0, PROD_COMBINE = 3 };
 
 template <int EPI>
 __device__ __forceinline__ void store_out(void* out, size_t o, float v) {
@@ -54,19 +53,6 @@ struct Params {
     int* status;
     int T, N, K, ldo;        // N = rows of W (for SWIGLU: F, W has 2F rows)
     int splits, kblocks;     // kblocks = ceil(K / BK)
-    // fused RMS norm of the input (NORM kernels): X is the 32-bit stream, normalised here
-    const float* x32;        // [rows, ldx32]
-    const float* norm_w;     // [K]
-    const int* norm_rows;    // optional row gather (token t reads row norm_rows[t])
-    float eps;
-    int ldx32;
-    // ADD_F32 with the NEXT norm fused behind it: once every CTA of the launch has added its
-    // share into the 32-bit stream `out`, the CTA that finishes last writes
-    // after_out[t, :] = bfloat16(rms_norm(out[t, :], after_w, after_eps)) for every token.
-    __nv_bfloat16* after_out;    // [T, N] or nullptr
-    const float* after_w;        // [N]
-    float after_eps;
-    int* after_counter;          // zero before the launch, left zero
     int kb_cap;                  // PROD != NONE: k-blocks of the resident token operand (the most one split owns)
     // PROD_COMBINE: token operand [t, h * hd + d] = sum_s acc[t,h,s,d] f_s / sum_s l_s f_s, f_s = exp(m_s - max m)
     const float* cb_acc;         // [T, heads, splits, hd]
@@ -80,13 +66,16 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
     return make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
                       *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
 }
+// shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
+// buffer of the SwiGLU epilogue.  Tiles are 1024-byte aligned (128-byte swizzle).  With a producer
+// (PROD != PROD_NONE) the ring carries W tiles only and the token operand of all the CTA's k-blocks
+// follows the ring.
 template <int PROD> struct ThreadsOf { static constexpr int value = (PROD == PROD_COMBINE) ? 320 : THREADS; };
 
 template <int NT, int STAGES, int EPI, int PROD>
 __global__ void __launch_bounds__(ThreadsOf<PROD>::value, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    constexpr bool NORM = PROD == PROD_NORM;
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = PROD != PROD_NONE ? A_BYTES : A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -116,7 +105,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         mbar_init(acc_ready, 1);
         mbar_init(b_ready, (PROD == PROD_COMBINE) ? 256 : 128);
         flags[0] = 0;
-        flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -199,50 +187,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                       // row of the CTA's W tile
         pdl_wait();                                             // before any global write or residual read
-        if (NORM) {
-            // rows ew, ew+4, ... of the CTA's NT token rows; a warp per row, a lane per 16-byte
-            // chunk (8 elements) of the output, all loads 16 bytes wide
-            const int ew = warp - 2;
-            const int k_lo = kb_begin * BK, k_hi = min(p.K, kb_end * BK);
-            for (int r = ew; r < NT; r += 4) {
-                const int t = tile_t * NT + r;
-                uint8_t* dst_row = bres + (size_t)r * 128;
-                if (t < p.T) {
-                    const float* xr = p.x32 + (size_t)(p.norm_rows ? p.norm_rows[t] : t) * p.ldx32;
-                    float ss = 0.f;
-                    for (int k = lane * 4; k < p.K; k += 128) {
-                        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + k));
-                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    }
-                    ss = warp_sum(ss);
-                    const float scale = 1.0f / sqrtf(ss / (float)p.K + p.eps);
-                    for (int k = k_lo + lane * 8; k < kb_end * BK; k += 256) {
-                        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-                        if (k < k_hi) {                                       // K is a multiple of 8: whole chunks only
-                            const float4 x0 = __ldg(reinterpret_cast<const float4*>(xr + k));
-                            const float4 x1 = __ldg(reinterpret_cast<const float4*>(xr + k + 4));
-                            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
-                            const float4 w1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k + 4));
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(x0.x * scale * w0.x, x0.y * scale * w0.y);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(x0.z * scale * w0.z, x0.w * scale * w0.w);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(x1.x * scale * w1.x, x1.y * scale * w1.y);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(x1.z * scale * w1.z, x1.w * scale * w1.w);
-                            packed = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
-                                                *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
-                        }
-                        const int i = k / BK - kb_begin, chunk = (k % BK) >> 3;
-                        *reinterpret_cast<uint4*>(dst_row + (size_t)i * B_BYTES + ((chunk ^ (r & 7)) << 4)) = packed;
-                    }
-                } else {
-                    for (int k = k_lo + lane * 8; k < kb_end * BK; k += 256) {
-                        const int i = k / BK - kb_begin, chunk = (k % BK) >> 3;
-                        *reinterpret_cast<uint4*>(dst_row + (size_t)i * B_BYTES + (chunk << 4)) = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // generic-proxy writes -> visible to the MMA
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b_ready)) : "memory");
-        }
         if (PROD == PROD_COMBINE) {
             // A thread per (live token row of the tile, 16-byte chunk = 8 consecutive k) of this CTA's k-range; eight
             // warps (2..9) share the items.  The (max, sum) pairs of an item and the first accumulators are requested
@@ -483,41 +427,6 @@ done:
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
-    if (EPI == ADD_F32 && p.after_out != nullptr && warp >= 2 && warp < 6) {
-        // The reference fuses the same pair, residual add then the next RMS norm
-        // (imparo-backend/src/lib.rs:2609-2623 add_rms_norm).  Here the product's last CTA does it.
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-            const int total = gridDim.x * gridDim.y * gridDim.z;
-            const int prev = atomicAdd(p.after_counter, 1);
-            flags[1] = prev == total - 1;
-            if (prev == total - 1) *p.after_counter = 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (flags[1]) {
-            __threadfence();
-            const float* x = reinterpret_cast<const float*>(p.out);
-            for (int t = warp - 2; t < p.T; t += 4) {                 // a warp per token row
-                const float* xr = x + (size_t)t * p.ldo;
-                float ss = 0.f;
-                for (int k = lane * 4; k < p.N; k += 128) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                }
-                ss = warp_sum(ss);
-                const float scale = 1.0f / sqrtf(ss / (float)p.N + p.after_eps);
-                __nv_bfloat16* orow = p.after_out + (size_t)t * p.N;
-                for (int k = lane * 4; k < p.N; k += 128) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(xr + k));
-                    const float4 w = __ldg(reinterpret_cast<const float4*>(p.after_w + k));
-                    __nv_bfloat162 a = __floats2bfloat162_rn(v.x * scale * w.x, v.y * scale * w.y);
-                    __nv_bfloat162 b = __floats2bfloat162_rn(v.z * scale * w.z, v.w * scale * w.w);
-                    *reinterpret_cast<uint2*>(orow + k) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-                }
-            }
-        }
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0) timeline_mark(1);                     // this CTA's epilogue is done
@@ -701,74 +610,6 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
             return launch_nt<PARTIAL_F32>(nt, mw, mx, p, grid, stream);
     }
     return -22;
-}
-
-
-// out (32-bit stream) += X W^T, then after_out = bfloat16(rms_norm(out, after_w, after_eps)) by the
-// CTA that finishes last.  N must be a multiple of 4; counter: one int, zero (left zero).
-extern "C" int imparo_gemm_tc_add_norm(const void* x, int ldx, int x_rows_alloc, const void* w, float* out, int ldo,
-                                       int T, int N, int K, const float* after_w, float after_eps, void* after_out,
-                                       int* counter, int* status, cudaStream_t stream) {
-    if (T <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || N % 4 != 0 || ldo % 4 != 0) return -23;
-    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)after_out | (uintptr_t)after_w) & 15) return -23;
-    if (!after_w || !after_out || !counter) return -24;
-    int nt, splits, ncnt;
-    long long sfl;
-    imparo_gemm_tc_plan(T, N, K, ADD_F32, &nt, &splits, &sfl, &ncnt);
-    CUtensorMap mw, mx;
-    int rc = get_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BM, &mw);
-    if (rc) return rc;
-    rc = get_map(x, (uint64_t)(x_rows_alloc > T ? x_rows_alloc : T), (uint64_t)K, (uint64_t)ldx, (uint32_t)nt, &mx);
-    if (rc) return rc;
-    Params p = {};
-    p.out = out; p.status = status;
-    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
-    p.after_out = reinterpret_cast<__nv_bfloat16*>(after_out); p.after_w = after_w; p.after_eps = after_eps; p.after_counter = counter;
-    dim3 grid((N + BM - 1) / BM, (T + nt - 1) / nt, splits);
-    if (grid.y > 65535) return -2;
-    return launch_nt<ADD_F32>(nt, mw, mx, p, grid, stream);
-}
-
-// The same product with the RMS norm of its input fused in: X is the 32-bit stream x32[rows, ldx32]
-// (token t reads row norm_rows[t] when norm_rows is given), normalised with norm_w and eps inside
-// the kernel.  For T <= 32 tokens and K small enough that the CTA's normalised rows stay in shared
-// memory; returns -25 when that does not hold (the caller then norms with its own kernel).
-// epilogue: 0 store bf16, 1 store f32, 3 SwiGLU.
-extern "C" int imparo_gemm_tc_norm(const float* x32, int ldx32, const float* norm_w, const int* norm_rows, float eps,
-                                   const void* w, void* out, int ldo, int T, int N, int K, int epilogue,
-                                   int* status, cudaStream_t stream) {
-    if (T <= 0 || N <= 0) return 0;
-    if (T > 32) return -25;
-    if (K <= 0 || K % 8 != 0 || ldx32 % 4 != 0) return -23;
-    if ((((uintptr_t)w) & 15) || (((uintptr_t)x32) & 15)) return -23;
-    if (epilogue != STORE_BF16 && epilogue != STORE_F32 && epilogue != SWIGLU_BF16) return -22;
-    int nt, splits, ncnt;
-    long long sfl;
-    imparo_gemm_tc_plan(T, N, K, epilogue, &nt, &splits, &sfl, &ncnt);
-    const int w_rows = epilogue == SWIGLU_BF16 ? 2 * N : N;
-    CUtensorMap mw;
-    int rc = get_map(w, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, epilogue == SWIGLU_BF16 ? 64u : (uint32_t)BM, &mw);
-    if (rc) return rc;
-    Params p = {};
-    p.out = out; p.status = status;
-    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.splits = splits; p.kblocks = (K + BK - 1) / BK;
-    p.x32 = x32; p.norm_w = norm_w; p.norm_rows = norm_rows; p.eps = eps; p.ldx32 = ldx32;
-    p.kb_cap = (p.kblocks + splits - 1) / splits;          // floor((s+1)k/S) - floor(sk/S) <= ceil(k/S)
-    const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
-    dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
-    if (nt == 16) {
-        switch (epilogue) {
-            case STORE_BF16: return launch<16, 9, STORE_BF16, PROD_NORM>(mw, mw, p, grid, stream);
-            case STORE_F32: return launch<16, 9, STORE_F32, PROD_NORM>(mw, mw, p, grid, stream);
-            default: return launch<16, 9, SWIGLU_BF16, PROD_NORM>(mw, mw, p, grid, stream);
-        }
-    }
-    switch (epilogue) {
-        case STORE_BF16: return launch<32, 5, STORE_BF16, PROD_NORM>(mw, mw, p, grid, stream);
-        case STORE_F32: return launch<32, 5, STORE_F32, PROD_NORM>(mw, mw, p, grid, stream);
-        default: return launch<32, 5, SWIGLU_BF16, PROD_NORM>(mw, mw, p, grid, stream);
-    }
 }
 
 

@@ -77,8 +77,6 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gemm_bf16_nt", [P, P, P, I, I, I, I, I, I, I, S])
     _declare(lib, "imparo_gemm_tc_plan", [I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int)])
     _declare(lib, "imparo_gemm_tc_max_clusters", [I, I])
-    _declare(lib, "imparo_gemm_tc_add_norm", [P, I, I, P, P, I, I, I, I, P, c_float, P, P, P, S])
-    _declare(lib, "imparo_gemm_tc_norm", [P, I, P, P, c_float, P, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_gemm_tc", [P, I, I, P, P, I, I, I, I, I, P, P, P, S])
     _declare(lib, "imparo_gemm_tc_combine", [P, P, I, I, I, P, P, I, I, I, I, I, P, P, S])
     _declare(lib, "imparo_gemm_prefill", [P, I, I, P, P, I, I, I, I, I, P, S])

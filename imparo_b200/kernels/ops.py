@@ -64,8 +64,8 @@ COUNTS = {"own": 0, "library": 0}
 
 
 class LaunchState:
-    """What the launchers remember between calls: which streams have split partials pending, which
-    norms a product may fill, and the scratch buffers behind them.  An engine owns one (its Runtime
+    """What the launchers remember between calls: which streams have split partials pending and the
+    scratch buffers behind them.  An engine owns one (its Runtime
     holds it and the step function makes it current for the length of a step), so two engines in
     one process neither share bookkeeping nor scratch; code that calls the launchers directly
     works on the module's default state."""
@@ -79,9 +79,6 @@ class LaunchState:
         self.partials = {}           # device index -> scratch of products into the stream
         self.consumer_parts = {}     # device index -> scratch of products a consumer kernel folds
         self.tc_scratch = {}         # device index -> (floats, counters) of the cluster-folded products
-        self.armed = {}              # data_ptr of a stream -> NormedInput the next accumulate-product should fill
-        self.filled = {}             # data_ptr -> NormedInput a product has filled (a later write to the stream voids it)
-        self.after_counter = {}
         self.argmax_scratch = {}
         self.status_fallback = {}
         self.generation = 0          # bumped when a scratch buffer moves: captured graphs that used it are stale
@@ -180,8 +177,8 @@ def defer_adds() -> bool:
 
 
 def allow_deferred_add(stream: torch.Tensor) -> None:
-    """The caller promises that whatever reads `stream` next goes through ops.rmsnorm,
-    ops.settle, ops.add_bias or another ops.linear(accumulate=True)."""
+    """The caller promises that whatever reads `stream` next goes through ops.rmsnorm, ops.settle, ops.add_bias,
+    ops.gather_rows or another ops.linear(accumulate=True)."""
     if defer_adds():
         _S.deferrable.add(stream.data_ptr())
 
@@ -233,7 +230,6 @@ def swiglu_act(gu: torch.Tensor, out: torch.Tensor) -> None:
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     _cuda(out, bias)
     settle(out)
-    _void_filled(out)                # a norm computed before this write is stale
     n, width = out.shape
     _need(bias.dtype == torch.float32 and bias.numel() == width, "bias must be float32 [width]")
     _check(_lib.kernels().imparo_add_bias(_ptr(out), _code(out), _ptr(bias), n, width, _stream()), "add_bias")
@@ -391,129 +387,12 @@ def gemm_prefill(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
                                               epilogue, _ptr(status), _stream()), "gemm_prefill")
 
 
-class NormedInput:
-    """The RMS norm of rows of the 32-bit stream, not computed yet: a product that can fuse the
-    norm into its own kernel takes it as it is (gemm_tc_norm); anything else calls tensor(),
-    which runs the norm kernel once into the given buffer."""
-
-    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                 rows: Optional[torch.Tensor] = None):
-        self.x, self.weight, self.eps, self.rows, self._out = x, weight, float(eps), rows, out
-        self._done = False
-
-    @property
-    def shape(self):
-        return self._out.shape
-
-    @property
-    def dtype(self):
-        return self._out.dtype
-
-    @property
-    def device(self):
-        return self._out.device
-
-    def tensor(self) -> torch.Tensor:
-        if not self._done:
-            rmsnorm(self.x, self.weight, self.eps, self._out, self.rows)
-            self._done = True
-        return self._out
-
-
-# ---- residual add with the next norm behind it ----------------------------------------------
-
-
-def fuse_add_norm() -> bool:
-    """Whether an accumulate-product also computes the norm that follows it (IMPARO_FUSE_ADD_NORM=1).
-    Off by default: measured on B200 the decode step at batch 8 takes 1.38 ms with it against
-    1.04 ms without.  The product's last CTA has to wait for every other CTA's writes (fence,
-    counter) and then norms all rows alone, which is a longer serial tail than the separate norm
-    kernel, whose launch the programmatic dependent launch already overlaps."""
-    return _S.switches.fuse_add_norm
-
-
-def arm_norm(stream: torch.Tensor, normed: "NormedInput") -> None:
-    """The next linear(..., accumulate=True) into `stream` may compute `normed` (the RMS norm of
-    the stream after the add) in its own kernel.  If it does not, `normed` stays unevaluated and
-    whoever needs it runs the norm kernel; nothing is lost."""
-    if isinstance(normed, NormedInput) and normed.rows is None and normed.x.data_ptr() == stream.data_ptr():
-        _S.armed[stream.data_ptr()] = normed
-
-
-def disarm_norm(stream: torch.Tensor) -> None:
-    _S.armed.pop(stream.data_ptr(), None)
-
-
-def _void_filled(stream: torch.Tensor) -> None:
-    ni = _S.filled.pop(stream.data_ptr(), None)
-    if ni is not None:
-        ni._done = False
-
-
-def as_tensor(x) -> torch.Tensor:
-    return x.tensor() if isinstance(x, NormedInput) else x
-
-
-def fuse_norm() -> bool:
-    """Whether products fuse the RMS norm of their input (IMPARO_FUSE_NORM=1).  Off by default:
-    measured on B200 the fused form is slower in the decode step (1.11 ms against 1.05 ms at
-    batch 8): every CTA redoes the norm of all token rows, and the separate norm kernel already
-    runs while the product prefetches its weights."""
-    return _S.switches.fuse_norm
-
-
-def _try_fused_norm(x: "NormedInput", w: torch.Tensor, out: torch.Tensor, epilogue: int, status) -> bool:
-    """Run the product with the norm fused in when the kernel takes the case."""
-    if not fuse_norm() or x._done or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or gemm_backend() != "tcgen05":
-        return False
-    T, K = x.shape
-    if T > min(32, tc_max_tokens()) or K % 8 or not w.is_contiguous() or w.data_ptr() % 16 or x.x.stride(0) % 4:
-        return False
-    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
-    if status is None:
-        key = torch.device(out.device).index or 0
-        status = _S.status_fallback.get(key)
-        if status is None:
-            status = _S.status_fallback[key] = new_status(out.device)
-    rc = _lib.kernels().imparo_gemm_tc_norm(_ptr(x.x), x.x.stride(0), _ptr(x.weight), _ptr(x.rows), x.eps, _ptr(w), _ptr(out),
-                                            out.stride(0), T, N, K, epilogue, _ptr(status), _stream())
-    if rc == -25:
-        return False
-    _check(rc, "gemm_tc_norm")
-    return True
-
-
-def _gemm_tc_add_norm(x, w, out, ni: "NormedInput", status) -> None:
-    """out += x w^T on the tensor-core kernel, whose last CTA then writes ni (the RMS norm of out)."""
-    T, K = x.shape
-    N = w.shape[0]
-    key = torch.device(x.device).index or 0
-    cnt = _S.after_counter.get(key)
-    if cnt is None:
-        cnt = _S.after_counter[key] = torch.zeros(4, dtype=torch.int32, device=x.device)
-    if status is None:
-        status = _S.status_fallback.get(key)
-        if status is None:
-            status = _S.status_fallback[key] = new_status(x.device)
-    rows_alloc = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // x.stride(0) if x.stride(0) else T
-    rows_alloc = max(T, min(rows_alloc, 1 << 30))
-    _check(_lib.kernels().imparo_gemm_tc_add_norm(_ptr(x), x.stride(0), rows_alloc, _ptr(w), _ptr(out), out.stride(0), T, N, K,
-                                                  _ptr(ni.weight), ni.eps, _ptr(ni._out), _ptr(cnt), _ptr(status), _stream()),
-           "gemm_tc_add_norm")
-    ni._done = True
-    _S.filled[out.data_ptr()] = ni
-
-
 def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
                   tmp: Optional[torch.Tensor] = None) -> None:
     """out[T, F] = silu(x gate^T) * (x up^T) with w_gu = [gate; up] of shape [2F, K].
     bfloat16 on the tensor-core kernels (the weight streamer for few tokens, the persistent tile kernel for
     many): one launch, the activation in the epilogue.  Otherwise: the product into tmp [T, 2F] (a tensor,
     or a function that makes it, called only on this path), then the activation kernel."""
-    if isinstance(x, NormedInput):
-        if _try_fused_norm(x, w_gu, out, EPI_SWIGLU, status):
-            return
-        x = x.tensor()
     if x.dtype == torch.bfloat16 and gemm_backend() == "tcgen05" and tc_usable(x, w_gu):
         gemm_tc(x, w_gu, out, EPI_SWIGLU, status)
         return
@@ -530,13 +409,7 @@ def linear_swiglu(x, w_gu: torch.Tensor, out: torch.Tensor, status: Optional[tor
 def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
            status: Optional[torch.Tensor] = None) -> None:
     """out[M,N] (+)= x[M,K] @ w[N,K]^T.  float32 x/w -> the FFMA kernel (true 32-bit);
-    bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16.
-    x may be a NormedInput: its norm is then fused into the product where the kernel allows."""
-    if isinstance(x, NormedInput):
-        if not accumulate and out.is_contiguous() and out.dtype in (torch.bfloat16, torch.float32) and \
-                _try_fused_norm(x, w, out, EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16, status):
-            return
-        x = x.tensor()
+    bfloat16 x/w -> tensor cores with 32-bit accumulation, out float32 or bfloat16."""
     _need(x.is_cuda and w.is_cuda and out.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
     M, K = x.shape
     N = w.shape[0]
@@ -564,27 +437,15 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                         _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
                         buf = _S.partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
                         _S.generation += 1
-                    _void_filled(out)
-                    _S.armed.pop(out.data_ptr(), None)
                     gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
                     _S.pending[out.data_ptr()] = (buf, splits, M, N)
                     return
             if accumulate:
                 settle(out)
-            ni = _S.armed.pop(out.data_ptr(), None) if accumulate else None
-            if ni is not None and fuse_add_norm() and not ni._done and tuple(ni.shape) == (M, N) and N % 4 == 0 \
-                    and ni._out.is_contiguous() and ni.dtype == torch.bfloat16:
-                _void_filled(out)
-                _gemm_tc_add_norm(x, w, out, ni, status)
-                return
-            if accumulate:
-                _void_filled(out)
             gemm_tc(x, w, out, epi, status)
             return
         if accumulate:
             settle(out)
-            _S.armed.pop(out.data_ptr(), None)
-            _void_filled(out)
         if _S.switches.prefill_linear and prefill_tc_usable(x, w, out):
             gemm_prefill(x, w, out, EPI_ADD_F32 if accumulate else (EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16),
                          status)
@@ -640,8 +501,6 @@ def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torc
     Returns `out`, filled; or, when the tensor-core product is cut along K (few tokens), a
     PartialProduct: each split's CTAs store their tile and are done, with no fold across CTAs inside
     the product, and the consumer adds the splits while it reads."""
-    if isinstance(x, NormedInput):
-        x = x.tensor()
     if unfolded_products() and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous() \
             and gemm_backend() == "tcgen05" and tc_usable(x, w):
         M, K = x.shape
@@ -693,8 +552,6 @@ def _produced_usable(T: int, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def _after_stream_product(out, epi, buf, splits, M, N) -> None:
-    _S.armed.pop(out.data_ptr(), None)
-    _void_filled(out)
     if epi == EPI_PARTIAL:
         _S.pending[out.data_ptr()] = (buf, splits, M, N)
 

@@ -22,7 +22,6 @@ class AttentionMixer(Part):
     (PartSpec), qk_norm (bool, default True: per-head RMS norm of q and k with a weight each; False: none, and
     no norm tensors are declared), bias (bool, default False: True declares optional q/k/v/out biases, used
     when the file carries them), names (optional dict of tensor names)."""
-    accepts_lazy_input = True
     adds_with_linear = True
 
 

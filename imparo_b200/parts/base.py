@@ -7,7 +7,7 @@ model it is in.  Kinds:
   "feed_forward" forward(x, batch, residual)          adds its output into residual
   "norm"         forward(x, out=None, rows=None)      -> normed activations
   "position"     tables / apply for queries and keys
-  "block"        forward(x, batch, caches)            arranges norm, mixer, feed-forward
+  "block"        forward(x, batch, caches, only_rows) arranges norm, mixer, feed-forward
   "embedding"    forward(batch)                       -> the 32-bit residual stream [tokens, width]
   "head"         forward(h)                           -> 32-bit logits
 
@@ -106,13 +106,9 @@ class Part:
     # tables, slots) from the batch's DEVICE arrays, so a step of single tokens can be captured
     # once and replayed.  A part that reads batch.host in forward() must set this to False.
     graph_safe = True
-    # True when forward() hands its input x straight to ops.linear / ops.linear_swiglu and
-    # never touches it otherwise: the block may then pass the norm unevaluated
-    # (ops.NormedInput) so that the product fuses it.  Parts that read x as a tensor keep False.
-    accepts_lazy_input = False
     # True when the part's LAST write to the residual is ops.linear(..., residual, accumulate=True)
-    # (ops.add_bias after it is fine): the block may then ask that product to compute the next
-    # norm in its own kernel (ops.arm_norm).  A part that writes the residual any other way keeps False.
+    # (ops.add_bias after it is fine): that add may then stay split partials that the next norm folds in
+    # (ops.allow_deferred_add).  A part that writes the residual any other way keeps False.
     adds_with_linear = False
 
     def __init__(self, params: dict, prefix: str, rt: Runtime):
@@ -133,17 +129,13 @@ class Part:
 
 class Block(Part):
     """Base of the "block" kind: how a layer's parts are arranged.  The model calls
-    forward(x, batch, caches, ready=None, next_norm=None, only_rows=None) and reads two declared facts:
+    forward(x, batch, caches, only_rows=None) (x: the 32-bit stream, updated in place) and reads one declared fact:
 
-    first_norm: the norm part that reads the stream first in this block, or None.  The block before may
-        produce that norm's input while it finishes (it gets it as next_norm and returns what it made; the
-        model hands it on as `ready`).  A block that returns None from forward() simply made nothing.
     picks_rows: True when forward(only_rows=(rows, n)) is implemented: as the model's last block it may then
         run whatever follows its mixer on the n wanted rows only and return their stream [n, width]."""
-    first_norm = None
     picks_rows = False
 
-    def forward(self, x, batch, caches, ready=None, next_norm=None, only_rows=None):
+    def forward(self, x, batch, caches, only_rows=None):
         raise NotImplementedError
 
 

@@ -18,7 +18,6 @@ class PreNormResidualBlock(Block):
         self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt)
         self.parts = (self.mixer_norm, self.mixer, self.ff_norm, self.ff)
         self.graph_safe = all(p.graph_safe for p in self.parts)
-        self.first_norm = self.mixer_norm
         self.picks_rows = True         # forward(only_rows=...) is implemented
 
     def weight_specs(self):
@@ -31,11 +30,8 @@ class PreNormResidualBlock(Block):
     def cache_specs(self):
         return self.mixer.cache_specs()
 
-    def forward(self, x, batch, caches, ready=None, next_norm=None, only_rows=None):
+    def forward(self, x, batch, caches, only_rows=None):
         """x: the 32-bit residual stream [tokens, width], updated in place.
-        ready: this block's mixer-norm input when the block before already produced it.
-        next_norm: the norm part that reads x after this block (the next block's mixer norm);
-        returns its unevaluated/filled input for that block, or None.
         only_rows = (rows, n): the caller needs the block's output at these n rows only (the
         model's last block, whose output feeds nothing but the wanted logits; the reference skips
         the same work, imparo-model/src/lfm2/workflow_gpu.rs:990-992,1201-1203).  The mixer still
@@ -43,49 +39,32 @@ class PreNormResidualBlock(Block):
         and their stream [n, width] is returned instead (None when n is 0)."""
         from ..kernels import ops
         if self.rt.probe_now:
-            return self._forward_probed(x, batch, caches, ready, only_rows)
-        h = ready if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
-            self._normed(self.mixer_norm, self.mixer, x, "normed_mixer")
-        ff_in = None
-        if only_rows is None and self.mixer.adds_with_linear and self.ff.accepts_lazy_input and self._defers(self.ff_norm):
-            ff_in = self.ff_norm.lazy(x, tag="normed_ff")     # unevaluated: the mixer's output product may fill it
-            ops.arm_norm(x, ff_in)
+            return self._forward_probed(x, batch, caches, only_rows)
+        h = self.mixer_norm.forward(x, tag="normed_mixer")
         self._run(self.mixer, x, lambda: self.mixer.forward(h, batch, caches, x))
         if only_rows is not None:
-            ops.disarm_norm(x)
             rows, n = only_rows
             if n == 0:
                 ops.settle(x)
                 return None
             xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype)
             ops.gather_rows(x, rows, xs)
-            picked_in = self._normed(self.ff_norm, self.ff, xs, "normed_ff")
+            picked_in = self.ff_norm.forward(xs, tag="normed_ff")
             self._run(self.ff, xs, lambda: self.ff.forward(picked_in, batch, xs))
             return xs
-        if ff_in is not None:
-            ops.disarm_norm(x)
-        else:
-            ff_in = self._normed(self.ff_norm, self.ff, x, "normed_ff")
-        nxt = None
-        if next_norm is not None and self.ff.adds_with_linear and self._defers(next_norm):
-            nxt = next_norm.lazy(x, tag="normed_mixer")
-            nxt.owner = next_norm
-            ops.arm_norm(x, nxt)                             # the feed-forward's output product may fill it
+        ff_in = self.ff_norm.forward(x, tag="normed_ff")
         self._run(self.ff, x, lambda: self.ff.forward(ff_in, batch, x))
-        if nxt is not None:
-            ops.disarm_norm(x)
-        return nxt
+        return None
 
-    def _forward_probed(self, x, batch, caches, ready, only_rows):
+    def _forward_probed(self, x, batch, caches, only_rows):
         """The same block with every stage evaluated and shown to the runtime's probe: the stream
         going in, the mixer's normed input, the stream after the mixer, the feed-forward's normed
-        input, the stream going out.  Nothing is deferred or fused here."""
+        input, the stream going out.  Nothing is deferred here."""
         from ..kernels import ops
         probe = self.rt.probe
         ops.settle(x)
         probe("stream_in", x)
-        h = ops.as_tensor(ready) if ready is not None and getattr(ready, "owner", None) is self.mixer_norm else \
-            self.mixer_norm.forward(x, tag="normed_mixer")
+        h = self.mixer_norm.forward(x, tag="normed_mixer")
         probe("mixer_norm", h)
         ops.settle(x)
         self.mixer.forward(h, batch, caches, x)
@@ -120,13 +99,3 @@ class PreNormResidualBlock(Block):
         else:
             ops.settle(x)
             call()
-
-    @staticmethod
-    def _defers(norm) -> bool:
-        return hasattr(norm, "lazy") and getattr(norm, "can_defer", lambda: False)()
-
-    @staticmethod
-    def _normed(norm, consumer, x, tag):
-        if consumer.accepts_lazy_input and hasattr(norm, "lazy"):
-            return norm.lazy(x, tag=tag)
-        return norm.forward(x, tag=tag)

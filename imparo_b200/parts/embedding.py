@@ -39,8 +39,6 @@ class TokenEmbedding(Part):
 
 class LinearHead(Part):
     """params: vocab, width, name (the table's own tensor, or the embedding's when tied)."""
-    accepts_lazy_input = True
-
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)

@@ -12,7 +12,6 @@ from .spec import WeightSpec
 
 class SwiGLU(Part):
     """params: hidden, ff, names (optional)."""
-    accepts_lazy_input = True
     adds_with_linear = True
 
 

@@ -70,18 +70,15 @@ class Model:
         feed-forward on picked rows, the result is (stream of the picked rows [n, width] or None
         for n = 0, True); else (the whole stream, False)."""
         x = self.embedding.forward(batch)
-        ready = None
         last = len(self.schedule) - 1
         for i, e in enumerate(self.schedule):
             layer = self.layers[e.layer]
-            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             self.rt.probe_now = self.rt.probe is not None and self.rt.probe_entry == i
             if i == last and wanted is not None and wanted[1] < batch.n_tokens and layer.picks_rows:
-                out = layer.forward(x, batch, cache_views(i), ready=ready, only_rows=wanted)
+                out = layer.forward(x, batch, cache_views(i), only_rows=wanted)
                 self.rt.probe_now = False
                 return out, True
-            # a block may hand the next block its (already computed) norm input
-            ready = layer.forward(x, batch, cache_views(i), ready=ready, next_norm=nxt.first_norm if nxt is not None else None)
+            layer.forward(x, batch, cache_views(i))
         self.rt.probe_now = False
         return (x, False) if wanted is not None else x
 
@@ -94,8 +91,5 @@ class Model:
     def logits(self, x: torch.Tensor, rows: Optional[torch.Tensor], n_rows: int) -> torch.Tensor:
         """Final norm and head at the wanted rows only: [n_rows, vocab] in 32-bit.  rows None: x
         holds exactly the wanted rows."""
-        if getattr(self.head, "accepts_lazy_input", False) and hasattr(self.final_norm, "lazy"):
-            h = self.final_norm.lazy(x, rows=rows, n_rows=n_rows, tag="final_normed")
-        else:
-            h = self.final_norm.forward(x, rows=rows, n_rows=n_rows, tag="final_normed")
+        h = self.final_norm.forward(x, rows=rows, n_rows=n_rows, tag="final_normed")
         return self.head.forward(h)

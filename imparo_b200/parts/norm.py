@@ -35,17 +35,3 @@ class RMSNorm(Part):
         out = self.rt.workspace.get(tag, (n, self.width), self.rt.act_dtype)
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
-
-    def can_defer(self) -> bool:
-        """Whether lazy() returns an unevaluated norm (bfloat16 path) rather than computing it."""
-        return self.rt.act_dtype == torch.bfloat16
-
-    def lazy(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
-             tag: str = "normed"):
-        """The norm as an ops.NormedInput: a product that can fuse it does, anything else gets
-        the tensor by calling .tensor().  In the 32-bit path this is forward()."""
-        if self.rt.act_dtype != torch.bfloat16:
-            return self.forward(x, rows=rows, n_rows=n_rows, tag=tag)
-        n = x.shape[0] if rows is None else int(n_rows if n_rows is not None else rows.numel())
-        out = self.rt.workspace.get(tag, (n, self.width), self.rt.act_dtype)
-        return ops.NormedInput(x, self.weight, self.eps, out, rows)

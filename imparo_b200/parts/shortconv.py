@@ -12,7 +12,6 @@ from .spec import SlotState, WeightSpec
 
 class ShortConvMixer(Part):
     """params: hidden, taps, bias (bool), names (optional)."""
-    accepts_lazy_input = True
     adds_with_linear = True
 
 

@@ -12,14 +12,14 @@ def test_defaults():
     assert (c.dtype, c.ctx, c.parallel, c.page_size, c.num_pages, c.max_step_tokens, c.log) == \
         ("bfloat16", 4096, 8, 16, None, 2048, False)
     s = c.switches
-    assert (s.gemm, s.tc_max_tokens, s.unfolded, s.defer_adds, s.fuse_norm, s.fuse_add_norm, s.attn_prefill) == \
-        ("tcgen05", 64, True, True, False, False, "auto")
+    assert (s.gemm, s.tc_max_tokens, s.unfolded, s.defer_adds, s.fuse_producers, s.attn_prefill) == \
+        ("tcgen05", 64, True, True, True, "auto")
 
 
 def test_flag_over_environment_over_file_over_default(tmp_path):
     f = tmp_path / "engine.json"
     f.write_text(json.dumps({"ctx": 1000, "parallel": 3, "page_size": 32, "log": True,
-                             "switches": {"gemm": "library", "tc_max_tokens": 8}, "fuse_norm": True}))
+                             "switches": {"gemm": "library", "tc_max_tokens": 8}, "fuse_producers": False}))
     env = {"IMPARO_CTX": "2000", "IMPARO_PARALLEL": "5", "IMPARO_TC_MAX_TOKENS": "16", "IMPARO_DEFER_ADDS": "0"}
     c = EngineConfig.resolve(flags={"ctx": 3000, "dtype": None, "switches": {"attn_prefill": "mma"}}, env=env, file=str(f))
     assert c.ctx == 3000                 # flag over environment and file
@@ -33,7 +33,7 @@ def test_flag_over_environment_over_file_over_default(tmp_path):
     assert s.tc_max_tokens == 16         # environment over file
     assert s.defer_adds is False         # environment
     assert s.gemm == "library"           # file (nested)
-    assert s.fuse_norm is True           # file (flat)
+    assert s.fuse_producers is False     # file (flat)
     assert s.unfolded is True            # default
     # the file may also be named by the environment
     c2 = EngineConfig.resolve(env={"IMPARO_CONFIG": str(f)})

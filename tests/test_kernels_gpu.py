@@ -648,93 +648,6 @@ def test_attention_prefill_far_key_and_refusals(kernel):
     assert not o.attention_prefill(zf, zf, zf, None, None, 1, None, 4, 1, None, 1.0, zf, 1, 1, 64, None)
 
 
-@pytest.mark.parametrize("T,N,K,epi", [(1, 2048, 2048, "bf16"), (8, 6144, 2048, "bf16"), (8, 3072, 2048, "bf16"), (8, 8192, 2048, "swiglu"),
-                                       (16, 512, 192, "swiglu"), (5, 331, 144, "f32"), (32, 1000, 264, "bf16"), (17, 640, 2048, "f32"),
-                                       (3, 65536, 2048, "f32")])
-def test_product_with_the_norm_fused_in(T, N, K, epi, monkeypatch):
-    """ops.linear / ops.linear_swiglu on a NormedInput: the RMS norm of the 32-bit rows is
-    computed inside the tensor-core product.  Against float64, and against the unfused path."""
-    monkeypatch.setattr(ops().switches(), "fuse_norm", True)
-    monkeypatch.setattr(ops().switches(), "tc_max_tokens", 64)        # the own product for every T of this test
-    o = ops()
-    g = torch.Generator().manual_seed(T * 7 + N)
-    x = torch.randn(40, K, generator=g) * 2
-    wn = 1 + 0.1 * torch.randn(K, generator=g)
-    rows = torch.randperm(40, generator=g)[:T].to(torch.int32)
-    w = bf16_round(torch.randn(2 * N if epi == "swiglu" else N, K, generator=g) * 0.05)
-    eps = 1e-5
-    xs = x[rows.long()].double()
-    normed = (xs * (1.0 / torch.sqrt((xs ** 2).mean(-1, keepdim=True) + eps)) * wn.double()).float()
-    normed = bf16_round(normed).double()                    # what the tensor cores are fed
-    ref = normed @ w.double().T
-    if epi == "swiglu":
-        gate, up = ref[:, :N], ref[:, N:]
-        ref = gate / (1 + torch.exp(-gate)) * up
-    out_dtype = torch.float32 if epi == "f32" else torch.bfloat16
-    results = []
-    for fused in (True, False):
-        buf = torch.empty(T, K, dtype=torch.bfloat16, device=DEV)
-        ni = o.NormedInput(x.to(DEV), wn.to(DEV), eps, buf, rows.to(DEV))
-        if not fused:
-            ni.tensor()                                     # evaluated: the product can no longer fuse it
-        out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
-        status = o.new_status(DEV)
-        if epi == "swiglu":
-            o.linear_swiglu(ni, w.to(torch.bfloat16).to(DEV), out, status)
-        else:
-            o.linear(ni, w.to(torch.bfloat16).to(DEV), out, status=status)
-        o.read_status(status)
-        assert ni._done == (not fused)
-        results.append(out.float().cpu().double())
-    tol = 2e-5 if epi == "f32" else 8e-3
-    for r in results:
-        assert (r - ref).abs().max() <= tol * max(1.0, ref.abs().max())
-    # same rounding of the normed rows in both paths: the two results agree far inside bf16 noise
-    assert (results[0] - results[1]).abs().max() <= 1e-2 * max(1.0, ref.abs().max())
-
-
-@pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (8, 2048, 8192), (8, 192, 512), (20, 144, 200), (32, 2048, 2048)])
-def test_product_with_the_next_norm_behind_it(T, N, K, monkeypatch):
-    """linear(..., accumulate=True) into an armed stream: out += x w^T and, in the same kernel,
-    the RMS norm of the updated rows.  Against float64 and against the separate norm kernel."""
-    monkeypatch.setattr(ops().switches(), "fuse_add_norm", True)
-    monkeypatch.setattr(ops().switches(), "tc_max_tokens", 64)
-    o = ops()
-    g = torch.Generator().manual_seed(T + N + K)
-    x = bf16_round(torch.randn(T, K, generator=g))
-    w = bf16_round(torch.randn(N, K, generator=g) * 0.05)
-    base = torch.randn(T, N, generator=g)
-    wn = 1 + 0.1 * torch.randn(N, generator=g)
-    eps = 1e-6
-    stream = base.to(DEV).clone()
-    buf = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ni = o.NormedInput(stream, wn.to(DEV), eps, buf)
-    o.arm_norm(stream, ni)
-    status = o.new_status(DEV)
-    o.linear(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), stream, accumulate=True, status=status)
-    o.read_status(status)
-    assert ni._done                                             # filled by the product's own kernel
-    ref_stream = base.double() + x.double() @ w.double().T
-    assert (stream.cpu().double() - ref_stream).abs().max() <= 1e-5 * max(1.0, ref_stream.abs().max())
-    s64 = stream.cpu().double()
-    ref_norm = s64 * (1.0 / torch.sqrt((s64 ** 2).mean(-1, keepdim=True) + eps)) * wn.double()
-    assert (buf.float().cpu().double() - ref_norm).abs().max() <= 8e-3 * ref_norm.abs().max()
-    sep = torch.empty_like(buf)
-    o.rmsnorm(stream, wn.to(DEV), eps, sep)
-    assert (buf.float() - sep.float()).abs().max() <= 1.6e-2 * ref_norm.abs().max()
-    # a later write to the stream voids the filled norm
-    o.add_bias(stream, torch.ones(N, device=DEV))
-    assert not ni._done
-    # a second product into the same stream: the counter was left clean
-    ni2 = o.NormedInput(stream, wn.to(DEV), eps, buf)
-    o.arm_norm(stream, ni2)
-    o.linear(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV), stream, accumulate=True, status=status)
-    o.read_status(status)
-    assert ni2._done
-    o.rmsnorm(stream, wn.to(DEV), eps, sep)
-    assert (buf.float() - sep.float()).abs().max() <= 1.6e-2 * ref_norm.abs().max() + 0.1
-
-
 @pytest.mark.parametrize("n,n_prev", [(1, 1), (37, 8), (700, 64)])
 def test_take_sampled_tokens(n, n_prev):
     """token_ids[i] = prev[src[i]] where src[i] >= 0; other rows keep what the host wrote."""
