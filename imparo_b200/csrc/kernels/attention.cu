@@ -238,6 +238,108 @@ qk_norm_rope_rows_kernel(const T* __restrict__ qkv, const int* __restrict__ posi
     }
 }
 
+// bfloat16, many tokens, a head fully rotated (n_rot == head size) or not at all, head size 32 * V: a lane owns V
+// consecutive dims of a head (one load of 2 V bytes), so the lower half of a head lies in lanes 0-15 and the pair
+// (i, i + head/2) of the rotation in lanes l and l ^ 16: one shuffle per value.  A block owns one token, its eight warps
+// share the token's heads, FOUR heads at a time per warp with all their loads in flight together; sines and cosines
+// of the position once per warp.  The kernel above keeps one head in flight per warp and is bound by that.
+template <int V>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_rows_vec_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                             const int* __restrict__ item_of_token,
+                             const float* __restrict__ q_w, const float* __restrict__ k_w,
+                             const float* __restrict__ inv_freq, float eps,
+                             __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                             __nv_bfloat16* __restrict__ v_cache,
+                             const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                             int nh, int nkv, int* status) {
+    constexpr int HD = 32 * V, NW = 8, BATCH = 4;
+    struct alignas(2 * V) Vec { __nv_bfloat16 e[V]; };
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total = nh + 2 * nkv;
+    const int pos = positions[t];
+    // the position's sines and cosines: computed once per block (the first threads, one frequency each) and shared;
+    // eight warps computing them each would spend nearly half of the kernel's instructions on them
+    __shared__ float sn_s[HD / 2], cs_s[HD / 2];
+    if (inv_freq && threadIdx.x < HD / 2) sincosf((float)pos * inv_freq[threadIdx.x], &sn_s[threadIdx.x], &cs_s[threadIdx.x]);
+    float wq[V], wk[V], sn[V], cs[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+        const int d = V * lane + e;
+        wq[e] = q_w ? q_w[d] : 1.f;                          // null weights: no per-head norm on that side
+        wk[e] = (k_w && nkv > 0) ? k_w[d] : 1.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+        const int d = V * lane + e;
+        sn[e] = inv_freq ? sn_s[d % (HD / 2)] : 0.f;
+        cs[e] = inv_freq ? cs_s[d % (HD / 2)] : 1.f;
+    }
+    size_t cache_row = 0;
+    int page = 0;
+    if (nkv > 0) {
+        const int blk = pos / page_size;
+        page = blk < max_blocks ? table[(size_t)item_of_token[t] * max_blocks + blk] : -1;
+        if (page >= 0 && page < n_pages) cache_row = (size_t)page * page_size + (pos % page_size);
+    }
+    pdl_wait();
+    if (nkv > 0 && (page < 0 || page >= n_pages) && threadIdx.x == 0)
+        report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);     // the token's keys and values are skipped below, its queries written
+    const __nv_bfloat16* src = qkv + (size_t)t * total * HD + V * lane;
+    const bool upper = lane >= 16;
+    for (int h0 = warp * BATCH; h0 < total; h0 += NW * BATCH) {
+        Vec in[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u)
+            if (h0 + u < total) in[u] = *reinterpret_cast<const Vec*>(src + (size_t)(h0 + u) * HD);
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            const int hh = h0 + u;
+            if (hh >= total) break;
+            const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+            float val[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) val[e] = __bfloat162float(in[u].e[e]);
+            if (is_q || is_k) {
+                const float* wn = is_q ? q_w : k_w;
+                float scale = 1.f;
+                if (wn) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int e = 0; e < V; ++e) ss += val[e] * val[e];
+                    ss = warp_sum(ss);
+                    scale = 1.0f / sqrtf(ss / (float)HD + eps);
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) val[e] = val[e] * scale * (is_q ? wq[e] : wk[e]);
+                if (inv_freq) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) {
+                        const float other = __shfl_xor_sync(0xffffffffu, val[e], 16);
+                        // lower half: x0 cos - x1 sin with x1 = other; upper half: x0 sin + x1 cos with x0 = other
+                        val[e] = upper ? other * sn[e] + val[e] * cs[e] : val[e] * cs[e] - other * sn[e];
+                    }
+                }
+            }
+            __nv_bfloat16* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)t * nh + hh) * HD;
+            } else {
+                if (page < 0 || page >= n_pages) continue;
+                const int kvh = is_k ? hh - nh : hh - nh - nkv;
+                dst = (is_k ? k_cache : v_cache) + cache_row * ((size_t)nkv * HD) + (size_t)kvh * HD;
+            }
+            Vec o;
+#pragma unroll
+            for (int e = 0; e < V; ++e) o.e[e] = __float2bfloat16_rn(val[e]);
+            *reinterpret_cast<Vec*>(dst + V * lane) = o;
+        }
+    }
+}
+
 // ---- general paged attention ---------------------------------------------------------
 template <typename T> struct Vec;
 template <> struct Vec<float> { using type = float4; static constexpr int N = 4; };
@@ -357,6 +459,18 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
     if (parts < 0 || (parts > 0 && part_stride < (long long)n_tok * (nh + 2 * nkv) * hd)) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + WARPS - 1) / WARPS);
     const float* part = parts > 0 ? (const float*)qkv : nullptr;
+    if (n_tok >= 256 && parts == 0 && dtype == IMPARO_DT_BF16 && (hd == 64 || hd == 128 || hd == 256) &&
+        (inv_freq == nullptr || n_rot == hd) &&
+        (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
+        // a prompt portion in bfloat16 with whole-head rotation: vector loads, four heads in flight per warp
+#define IMPARO_QKV(V_) launch(qk_norm_rope_rows_vec_kernel<V_>, dim3(n_tok), dim3(256), 0, stream, (const __nv_bfloat16*)qkv, positions, \
+            item_of_token, q_w, k_w, inv_freq, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, \
+            max_blocks, page_size, n_pages, nh, nkv, status)
+        if (hd == 64) IMPARO_QKV(2); else if (hd == 128) IMPARO_QKV(4); else IMPARO_QKV(8);
+#undef IMPARO_QKV
+        IMPARO_CHECK_LAUNCH();
+        return 0;
+    }
     if (n_tok >= 256 && parts == 0 && hd % 32 == 0 && hd <= 128 && (inv_freq == nullptr || (n_rot >= 64 && n_rot % 64 == 0))) {
         // a prompt portion: the register-only kernel, one block per token
 #define IMPARO_QKR(T_, PER_) launch(qk_norm_rope_rows_kernel<T_, PER_>, dim3(n_tok), dim3(WARPS * 32), 0, stream, (const T_*)qkv, \

@@ -86,6 +86,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 // x / (1 + exp(-x))
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+// The same for results that are rounded to bfloat16 at once: the exponential and the division by their
+// approximate instructions (a few units in the last place of 32-bit, far below the rounding that follows).
+__device__ __forceinline__ float silu_bf16(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 }  // namespace imparo
 

@@ -225,7 +225,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 for (int e = 0; e < 4; ++e) {
                                     const float g0 = __uint_as_float(gr[j + 2 * e]), g1 = __uint_as_float(gr[j + 2 * e + 1]);
                                     const float u0 = __uint_as_float(ur[j + 2 * e]), u1 = __uint_as_float(ur[j + 2 * e + 1]);
-                                    w[e] = pack_bf16(silu(g0) * u0, silu(g1) * u1);
+                                    w[e] = pack_bf16(silu_bf16(g0) * u0, silu_bf16(g1) * u1);
                                 }
                                 *reinterpret_cast<uint4*>(out + f) = make_uint4(w[0], w[1], w[2], w[3]);
                             }

@@ -321,7 +321,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                         for (int j = 0; j < 16; j += 2) {
                             const int t = t0 + c + 16 * u + j + parity;
                             if (t < p.T)
-                                out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu(ex[ff * 17 + j + parity]) * ex[(64 + ff) * 17 + j + parity]);
+                                out[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_bf16(ex[ff * 17 + j + parity]) * ex[(64 + ff) * 17 + j + parity]);
                         }
                     }
                 }

@@ -72,6 +72,38 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
+// Many rows (a prompt portion) of a width that is a multiple of 128 up to 3,072 (the row must fit the registers): a warp per row, the row in
+// registers (every load of the row in flight at once), sums by shuffles: one pass and no block-wide barrier.  The
+// block-per-row kernel above spends its time in three barriers and a second pass over the row.
+template <typename TOut, int NV>       // NV float4 per lane: width = 128 * NV
+__global__ void __launch_bounds__(128)
+rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                    TOut* __restrict__ out, int n_rows) {
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    constexpr int width = 128 * NV;
+    float4 g[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) g[i] = __ldg(reinterpret_cast<const float4*>(w) + lane + 32 * i);
+    pdl_wait();
+    if (r >= n_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = xr[lane + 32 * i];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TOut* o = out + (size_t)r * width;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        store4<TOut>(o + 4 * (lane + 32 * i), v[i].x * scale * g[i].x, v[i].y * scale * g[i].y, v[i].z * scale * g[i].z,
+                     v[i].w * scale * g[i].w);
+}
+
 // ---- stream += split partials, then RMS norm ----------------------------------------------
 // A product that was cut along K leaves its partial results part[s][row][:] (s = 0..S-1) instead
 // of adding them into the 32-bit stream itself.  This kernel adds them in split order (the same
@@ -335,6 +367,23 @@ extern "C" int imparo_embed_gather(const void* table, int table_dtype, const int
 extern "C" int imparo_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out,
                               int out_dtype, int n_rows, int width, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (out_dtype != IMPARO_DT_F32 && out_dtype != IMPARO_DT_BF16) return -1;
+    if (n_rows >= 256 && width % 128 == 0 && width <= 3072 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+        // a prompt portion: a warp per row
+        const dim3 grid((n_rows + 3) / 4), block(128);
+#define IMPARO_RN(T_, NV_) launch(rmsnorm_rows_kernel<T_, NV_>, grid, block, 0, stream, x, rows, w, eps, (T_*)out, n_rows)
+#define IMPARO_RNV(T_) do { switch (width / 128) { \
+            case 1: IMPARO_RN(T_, 1); break; case 2: IMPARO_RN(T_, 2); break; case 3: IMPARO_RN(T_, 3); break; case 4: IMPARO_RN(T_, 4); break; \
+            case 5: IMPARO_RN(T_, 5); break; case 6: IMPARO_RN(T_, 6); break; case 7: IMPARO_RN(T_, 7); break; case 8: IMPARO_RN(T_, 8); break; \
+            case 12: IMPARO_RN(T_, 12); break; case 16: IMPARO_RN(T_, 16); break; case 24: IMPARO_RN(T_, 24); break; \
+            default: goto general; } } while (0)
+        if (out_dtype == IMPARO_DT_F32) IMPARO_RNV(float); else IMPARO_RNV(__nv_bfloat16);
+#undef IMPARO_RNV
+#undef IMPARO_RN
+        IMPARO_CHECK_LAUNCH();
+        return 0;
+    }
+general:
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (out_dtype == IMPARO_DT_F32)
         launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, w, eps, (float*)out, width);
