@@ -53,7 +53,10 @@ class CacheManager:
     def __init__(self, requirements: Sequence[Tuple[int, Tuple]], page_size: int, num_pages: int, num_slots: int,
                  kv_dtype: torch.dtype = torch.bfloat16, device=None, num_pages_by_group: Optional[Dict] = None):
         """requirements: (schedule entry, cache specs) for every entry that owns a cache.
-        device None: bookkeeping only (no arenas), for host-side use and tests."""
+        device None: bookkeeping only (no arenas), for host-side use and tests.
+
+        Every arena holds one page and one state slot more than the bookkeeping hands out (spare_page(group),
+        spare_slot): rows of a step that belong to no request (the step function's padding rows) write there."""
         self.page_size = int(page_size)
         self.num_slots = int(num_slots)
         self.device = device
@@ -95,7 +98,7 @@ class CacheManager:
         self.state: Dict[Tuple[int, int], torch.Tensor] = {}
         if device is not None:
             for g, key in enumerate(self.group_keys):
-                shape = (len(self.group_entries[g]), self.num_pages[g], self.page_size, key.width)
+                shape = (len(self.group_entries[g]), self.num_pages[g] + 1, self.page_size, key.width)
                 self.k_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
                 self.v_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
             # every fixed-size state tensor is a stretch of ONE flat float32 arena, [slots, *shape] each, so that
@@ -109,14 +112,15 @@ class CacheManager:
                         per_slot *= int(d)
                     per_slot_padded = (per_slot + 3) // 4 * 4                 # 16-byte aligned stretches
                     sizes.append(((entry, j), spec.shape, per_slot, per_slot_padded))
-            total = sum(self.num_slots * padded for _, _, _, padded in sizes)
+            slots = self.arena_slots
+            total = sum(slots * padded for _, _, _, padded in sizes)
             self.state_arena = torch.zeros(max(total, 1), dtype=torch.float32, device=device)
             segs, off = [], 0
             for key, shape, per_slot, padded in sizes:
-                n = self.num_slots * per_slot
-                self.state[key] = self.state_arena[off:off + n].view(self.num_slots, *shape)
+                n = slots * per_slot
+                self.state[key] = self.state_arena[off:off + n].view(slots, *shape)
                 segs.append((off, per_slot))
-                off += self.num_slots * padded
+                off += slots * padded
             self.state_segments = torch.tensor(segs if segs else [(0, 0)], dtype=torch.int64, device=device)
             self.n_state_segments = len(segs)
 
@@ -136,6 +140,18 @@ class CacheManager:
     @property
     def n_groups(self) -> int:
         return len(self.group_keys)
+
+    @property
+    def arena_slots(self) -> int:
+        """State slots in the device arenas: those the bookkeeping hands out, and the spare one."""
+        return self.num_slots + 1
+
+    @property
+    def spare_slot(self) -> int:
+        return self.num_slots
+
+    def spare_page(self, group: int) -> int:
+        return self.num_pages[group]
 
     def add(self, req: int) -> int:
         """A request enters: it takes the lowest free state slot, whose state is zeroed."""
@@ -234,7 +250,7 @@ class CacheManager:
             if isinstance(spec, PagedKV):
                 g, idx = self._paged_of_entry[src]
                 out.append(PagedKVView(k=self.k_arena[g][idx], v=self.v_arena[g][idx], group=g, page_size=self.page_size,
-                                       n_pages=self.num_pages[g], window=spec.window, writes=owner is None))
+                                       n_pages=self.num_pages[g] + 1, window=spec.window, writes=owner is None))
             else:
                 if owner is not None:
                     raise CacheError("a fixed-size state cannot be read through cache_from")

@@ -45,6 +45,8 @@ void* imparo_sched_create(void* cm, int max_step_tokens, int max_running, int ma
     return new Scheduler(static_cast<CacheManager*>(cm), max_step_tokens, max_running, max_context);
 }
 void imparo_sched_destroy(void* s) { delete static_cast<Scheduler*>(s); }
+void imparo_sched_count_padded_rows(void* s, int on) { static_cast<Scheduler*>(s)->count_padded_rows(on != 0); }
+int imparo_padded_rows(int n) { return imparo::padded_rows(n); }
 int64_t imparo_sched_submit(void* s, int prompt_len, int max_new) { return static_cast<Scheduler*>(s)->submit(prompt_len, max_new); }
 int imparo_sched_plan(void* s, int64_t* ids, int* start, int* count, int* want, int cap) {
     const auto& p = static_cast<Scheduler*>(s)->plan();

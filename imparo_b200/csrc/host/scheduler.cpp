@@ -72,6 +72,10 @@ const std::vector<PlanEntry>& Scheduler::plan() {
             --budget;
         }
         if (again) continue;
+        if (count_padded_rows_) {
+            const int rows = (int)plan_.size();
+            budget = std::max(0, budget - (padded_rows(rows) - rows));
+        }
 
         // 2. the next portion of every prompt in flight
         auto fit = [&](int64_t id, int want, int spare) {

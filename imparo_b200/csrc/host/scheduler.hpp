@@ -32,9 +32,24 @@ struct PlanEntry {
     int want;       // 1: logits of the portion's last token are needed (a token will be sampled)
 };
 
+// How many one-token rows a step runs when n requests bring one token each: up to 8 the next power of two,
+// above that the next multiple of 8.  The step function fills the difference with rows that belong to no
+// request (they write to the cache's spare page and slot), so that the steps of a continuous batch, whose
+// number of decoding requests changes by one every few steps, fall into few shapes and replay captured graphs.
+inline int padded_rows(int n) {
+    if (n <= 1) return n < 0 ? 0 : n;
+    if (n <= 8) { int p = 1; while (p < n) p <<= 1; return p; }
+    return (n + 7) / 8 * 8;
+}
+
 class Scheduler {
 public:
     Scheduler(CacheManager* cm, int max_step_tokens, int max_running, int max_context);
+
+    // true: the token budget counts the rows the step function will add beside the one-token requests
+    // (padded_rows), so that a step with prompt portions holds exactly max_step_tokens rows whenever prompts
+    // are left, whatever the number of decoding requests.
+    void count_padded_rows(bool on) { count_padded_rows_ = on; }
 
     int64_t submit(int prompt_len, int max_new_tokens);
     // Decide the next step.  Entries: decode tokens first (admission order), then prompt
@@ -78,6 +93,7 @@ private:
     std::vector<PlanEntry> plan_;
     std::vector<int64_t> preempted_, failed_;
     int64_t n_preemptions_ = 0, n_steps_ = 0;
+    bool count_padded_rows_ = false;
 };
 
 }  // namespace imparo

@@ -453,7 +453,10 @@ extern "C" int imparo_add_partials_rmsnorm(float* x, const float* part, int n_sp
                                            const float* w, float eps, void* out, int out_dtype, int n_rows, int width,
                                            cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    // a thread per four columns where the row fits a block (the kernel's one-pass form): 1,536 columns take 384
+    // threads, not 256 and a second trip
+    int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if ((width & 3) == 0 && width > threads * 4 && width <= 4096) threads = (width / 4 + 31) / 32 * 32;
     if (out == nullptr || out_dtype == IMPARO_DT_F32)
         launch(add_partials_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, part, n_splits, (size_t)split_stride,
                w, eps, (float*)out, width);

@@ -147,6 +147,180 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
     if (lane == 0) out[r] = m.i == 0x7fffffff ? 0 : m.i;
 }
 
+
+// ---- temperature sampling over a large vocabulary, in two stages ------------------------------------
+// The one-block-per-row kernel above walks a 65,536-entry row three times with 16 to 64 blocks on the
+// whole GPU (114 us measured).  Here SAMPLE_PARTS blocks per row each take a contiguous stretch: its
+// greedy pick, its max m_j and s_j = sum exp((v - m_j)/T).  The second stage (a block per row) scales the
+// parts to the row's max M (f_j = exp((m_j - M)/T)), walks them in vocabulary order to the part that holds
+// target = u * sum_j f_j s_j, and repeats that part's sums to find the entry.  Both stages compute a part's
+// sums by the same function (a thread owns a contiguous chunk, chunks are scanned in thread order), so the
+// second stage meets exactly the numbers the first one added up.
+constexpr int SAMPLE_PARTS = 32;
+constexpr int SAMPLE_PART_THREADS = 256;
+
+struct PartSum { float incl, excl, total; };
+
+// Inclusive / exclusive prefix of one value per thread in thread order, and the block's total.
+__device__ __forceinline__ PartSum block_scan(float own, float* scratch /* 33 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float incl = own;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        float t = lane < nw ? scratch[lane] : 0.f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t += up;
+        }
+        scratch[lane] = t;                       // inclusive over warps
+        if (lane == 31) scratch[32] = t;
+    }
+    __syncthreads();
+    const float before = warp > 0 ? scratch[warp - 1] : 0.f;
+    PartSum r;
+    r.incl = before + incl;
+    r.excl = r.incl - own;
+    r.total = scratch[((blockDim.x + 31) >> 5) - 1];
+    return r;
+}
+
+// The stretch of part j and the chunk of this thread inside it.
+__device__ __forceinline__ void part_chunk(int vocab, int part, int& lo, int& hi, int& clo, int& chi) {
+    const int per = (vocab + SAMPLE_PARTS - 1) / SAMPLE_PARTS;
+    lo = min(vocab, part * per);
+    hi = min(vocab, lo + per);
+    const int chunk = (per + SAMPLE_PART_THREADS - 1) / SAMPLE_PART_THREADS;
+    clo = min(hi, lo + (int)threadIdx.x * chunk);
+    chi = min(hi, clo + chunk);
+}
+
+__device__ __forceinline__ float chunk_exp_sum(const float* __restrict__ row, int clo, int chi, float m, float invT) {
+    float s = 0.f;
+    for (int i = clo; i < chi; ++i) {
+        const float v = row[i];
+        if (v == v) s += expf((v - m) * invT);
+    }
+    return s;
+}
+
+__global__ void __launch_bounds__(SAMPLE_PART_THREADS)
+sample_partial_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                      float* __restrict__ part_max, float* __restrict__ part_sum, int* __restrict__ part_idx,
+                      int vocab, int ld) {
+    __shared__ MaxIdx mscratch[33];
+    __shared__ float fscratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.y, part = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    int lo, hi, clo, chi;
+    part_chunk(vocab, part, lo, hi, clo, chi);
+    MaxIdx m{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > m.v || (v == m.v && i < m.i)) { m.v = v; m.i = i; }
+    }
+    m = block_argmax(m, mscratch);
+    const float T = temperature[r];
+    float total = 0.f;
+    if (T > 0.f && m.i != 0x7fffffff && m.v > -INFINITY)          // block-uniform: every thread holds the same m
+        total = block_scan(chunk_exp_sum(row, clo, chi, m.v, 1.0f / T), fscratch).total;
+    if (threadIdx.x == 0) {
+        part_max[r * SAMPLE_PARTS + part] = m.v;
+        part_idx[r * SAMPLE_PARTS + part] = m.i;
+        part_sum[r * SAMPLE_PARTS + part] = total;
+    }
+}
+
+__global__ void __launch_bounds__(SAMPLE_PART_THREADS)
+sample_final_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                    const float* __restrict__ uniform, const float* __restrict__ part_max,
+                    const float* __restrict__ part_sum, const int* __restrict__ part_idx,
+                    int* __restrict__ out, int vocab, int ld) {
+    __shared__ float fscratch[33];
+    __shared__ float s_run, s_f, s_target, s_m;
+    __shared__ int s_owner, s_best, s_first;
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float T = temperature[r];
+    if (threadIdx.x == 0) {
+        // the row's greedy pick (larger value, then smaller index) and max
+        MaxIdx best{-INFINITY, 0x7fffffff};
+        for (int j = 0; j < SAMPLE_PARTS; ++j)
+            best = better(best, MaxIdx{part_max[r * SAMPLE_PARTS + j], part_idx[r * SAMPLE_PARTS + j]});
+        s_best = best.i;
+        s_owner = -1;
+        s_first = 0x7fffffff;
+        if (T > 0.f && best.i != 0x7fffffff) {
+            const float invT = 1.0f / T;
+            float f[SAMPLE_PARTS], total = 0.f;
+            for (int j = 0; j < SAMPLE_PARTS; ++j) {
+                const float sj = part_sum[r * SAMPLE_PARTS + j];
+                f[j] = sj > 0.f ? expf((part_max[r * SAMPLE_PARTS + j] - best.v) * invT) : 0.f;
+                total += f[j] * sj;
+            }
+            const float target = uniform[r] * total;
+            // the first part whose sum carries the running sum past the target; if rounding leaves the target
+            // beyond every sum, the last part with any weight
+            float run = 0.f, before_owner = 0.f;
+            int owner = -1;
+            for (int j = 0; j < SAMPLE_PARTS; ++j) {
+                const float pj = f[j] * part_sum[r * SAMPLE_PARTS + j];
+                if (pj > 0.f) {
+                    owner = j;
+                    before_owner = run;
+                    if (run + pj > target) break;
+                }
+                run += pj;
+            }
+            run = before_owner;
+            s_owner = owner;
+            s_run = run;
+            s_f = owner >= 0 ? f[owner] : 0.f;
+            s_target = target;
+            s_m = owner >= 0 ? part_max[r * SAMPLE_PARTS + owner] : 0.f;
+        }
+    }
+    __syncthreads();
+    const int owner = s_owner;
+    if (owner < 0) {                                              // greedy row, or nothing to sample from
+        if (threadIdx.x == 0) out[r] = s_best == 0x7fffffff ? 0 : s_best;
+        return;
+    }
+    const float run = s_run, f = s_f, target = s_target, m = s_m, invT = 1.0f / T;
+    int lo, hi, clo, chi;
+    part_chunk(vocab, owner, lo, hi, clo, chi);
+    const float own = chunk_exp_sum(row, clo, chi, m, invT);
+    const PartSum ps = block_scan(own, fscratch);
+    if (own > 0.f && run + f * ps.incl > target) atomicMin(&s_first, (int)threadIdx.x);
+    __syncthreads();
+    if ((int)threadIdx.x == s_first) {
+        float acc = ps.incl - own;
+        int chosen = -1, last = -1;
+        for (int i = clo; i < chi; ++i) {
+            const float v = row[i];
+            if (v == v) {
+                acc += expf((v - m) * invT);
+                last = i;
+                if (run + f * acc > target) { chosen = i; break; }
+            }
+        }
+        out[r] = chosen >= 0 ? chosen : last;
+    }
+    if (s_first == 0x7fffffff && threadIdx.x == 0) out[r] = s_best;   // rounding left the target beyond the last sum
+}
+
 }  // namespace imparo
 
 // part_val / part_idx: scratch of n_rows * 32 entries each.
@@ -189,6 +363,23 @@ extern "C" int imparo_sample_rows(const float* logits, const float* temperature,
     if (n_rows <= 0) return 0;
     if (temperature && !uniform) return -7;
     launch(imparo::sample_rows_kernel, dim3(n_rows), dim3(imparo::SAMPLE_THREADS), 0, stream, logits, temperature, uniform, out, vocab, ld);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// Temperature (and greedy) rows over a large vocabulary in two stages.  part_f: 2 * n_rows * 32 floats,
+// part_idx: n_rows * 32 ints of scratch.
+extern "C" int imparo_sample_rows_parts(const float* logits, const float* temperature, const float* uniform, int* out,
+                                        float* part_f, int* part_idx, int n_rows, int vocab, int ld, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!temperature || !uniform) return -7;
+    if (n_rows > 65535) return -2;
+    float* part_max = part_f;
+    float* part_sum = part_f + (size_t)n_rows * imparo::SAMPLE_PARTS;
+    launch(imparo::sample_partial_kernel, dim3(imparo::SAMPLE_PARTS, n_rows), dim3(imparo::SAMPLE_PART_THREADS), 0, stream,
+           logits, temperature, part_max, part_sum, part_idx, vocab, ld);
+    launch(imparo::sample_final_kernel, dim3(n_rows), dim3(imparo::SAMPLE_PART_THREADS), 0, stream, logits, temperature,
+           uniform, (const float*)part_max, (const float*)part_sum, (const int*)part_idx, out, vocab, ld);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

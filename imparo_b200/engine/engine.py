@@ -96,7 +96,8 @@ class Engine:
         self.cache = CacheManager(self.model.cache_requirements(), self.page_size, int(num_pages), self.parallel,
                                   kv_dtype=self.rt.act_dtype, device=self.device)
         self.max_step_tokens = int(max_step_tokens)
-        self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel, use_graphs=cfg.use_graphs)
+        self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel, use_graphs=cfg.use_graphs,
+                                    pad_rows=cfg.pad_rows)
         if probe_layer is not None:
             if not 0 <= int(probe_layer) < len(self.model.schedule):
                 raise ValueError(f"probe_layer {probe_layer} is not one of the model's {len(self.model.schedule)} schedule entries")
@@ -160,7 +161,7 @@ class Engine:
         as_list = lambda v: list(v) if isinstance(v, (list, tuple)) else [v] * n
         max_new, temps, seeds = as_list(max_tokens), as_list(temperature), as_list(seed)
         stops = set(self.model.spec.eos_token_ids if stop_token_ids is None else stop_token_ids)
-        sched = Scheduler(self.cache, self.max_step_tokens, self.parallel, self.ctx)
+        sched = Scheduler(self.cache, self.max_step_tokens, self.parallel, self.ctx, count_padded_rows=self.step_fn.pad_rows)
         tokens: Dict[int, List[int]] = {}
         index: Dict[int, int] = {}
         out: List[List[int]] = [[] for _ in range(n)]

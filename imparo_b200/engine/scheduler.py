@@ -18,11 +18,22 @@ class PlanEntry:
     want: bool
 
 
+def padded_rows(n: int) -> int:
+    """How many one-token rows a step runs when n requests bring one token each (the rule lives in
+    csrc/host/scheduler.hpp: up to 8 the next power of two, above that the next multiple of 8)."""
+    return _lib.host().imparo_padded_rows(int(n))
+
+
 class Scheduler:
-    def __init__(self, cache: CacheManager, max_step_tokens: int, max_running: int, max_context: int):
+    def __init__(self, cache: CacheManager, max_step_tokens: int, max_running: int, max_context: int,
+                 count_padded_rows: bool = False):
+        """count_padded_rows: the step function this scheduler feeds fills the one-token rows up to padded_rows();
+        the token budget then counts those rows too."""
         self.cache = cache
         self._h = _lib.host()
         self._s = self._h.imparo_sched_create(cache.handle, int(max_step_tokens), int(max_running), int(max_context))
+        if count_padded_rows:
+            self._h.imparo_sched_count_padded_rows(self._s, 1)
         self.max_step_tokens = int(max_step_tokens)
         cap = self._cap = max(16, int(max_running) + 8)
         self._ids = (ctypes.c_int64 * cap)()

@@ -19,6 +19,7 @@ import torch
 from ..cache import CacheFull, CacheManager
 from ..kernels import ops
 from ..parts.model import Model
+from .scheduler import padded_rows
 
 
 @dataclass
@@ -41,9 +42,21 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+def _table_width(longest: int) -> int:
+    """The block tables' width for a step whose longest table has `longest` pages: a multiple of 32 pages up
+    to 256, then four widths per doubling (multiples of 64 up to 512, of 128 up to 1,024, ...).  The width is
+    part of the step's shape and the split-key attention plans its key chunks from it, so it follows the
+    longest request closely (at most a quarter more) without taking a new value every few steps."""
+    longest = max(int(longest), 1)
+    step = max(32, (1 << (longest.bit_length() - 1)) // 4)
+    return _round_up(longest, step)
+
+
 class StepFunction:
     def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_items: int,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, pad_rows: bool = False):
+        """pad_rows: fill the one-token rows of a step up to padded_rows() with rows of no request (build_batch)."""
+        self.pad_rows = bool(pad_rows)
         self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", False)
         self.last_h2d_bytes = 0
         self._graphs = {}        # key -> [times seen, graph, logits, (own, library) launches, generation], in order of use
@@ -85,14 +98,23 @@ class StepFunction:
         """singles_first: requests that bring one token are put before those that bring more (the
         order among each kind stays), so that a mixer may treat the decode rows and the prompt
         portions of one step as two contiguous ranges (batch.n_single rows, then the rest).
-        Wanted rows keep the caller's order, whatever the order of the rows."""
+        Wanted rows keep the caller's order, whatever the order of the rows.
+
+        With pad_rows the one-token rows are filled up to padded_rows(their number) with rows that belong to no
+        request: token 0 at position 0 of the cache's spare page and slot, logits wanted (their rows come after
+        every real wanted row; host["n_want_real"] says how many are real).  A row reads only its own token,
+        cache and state, so the real rows' results do not change; the step's shape does: it no longer follows
+        every change of the number of decoding requests."""
         cache = self.cache
         n_single = 0
-        if singles_first and any(len(it.tokens) == 1 for it in items) and any(len(it.tokens) > 1 for it in items):
-            order = sorted(range(len(items)), key=lambda i: len(items[i].tokens) != 1)       # stable
-            n_single = sum(1 for it in items if len(it.tokens) == 1)
+        lens = [len(it.tokens) for it in items]
+        n_ones = sum(1 for n in lens if n == 1)
+        mixed = 0 < n_ones < len(items)
+        if singles_first and mixed:
+            order = sorted(range(len(items)), key=lambda i: lens[i] != 1)       # stable
+            n_single = n_ones
             if token_src is not None:
-                starts = np.concatenate([[0], np.cumsum([len(it.tokens) for it in items])])
+                starts = np.concatenate([[0], np.cumsum(lens)])
                 token_src = [s for i in order for s in token_src[starts[i]:starts[i + 1]]]
             caller_items, items = items, [items[i] for i in order]
             place = [0] * len(order)                     # the caller's item j is item place[j] of the batch
@@ -100,14 +122,26 @@ class StepFunction:
                 place[i] = k
         else:
             caller_items, place = items, list(range(len(items)))
+        # padding rows go right after the one-token rows, which must then be the first rows of the batch
+        pad = 0
+        if self.pad_rows and n_ones and (n_single == n_ones or n_ones == len(items)):
+            pad = padded_rows(n_ones) - n_ones
+        if pad:
+            items = list(items[:n_ones]) + [None] * pad + list(items[n_ones:])
+            place = [k if k < n_ones else k + pad for k in place]
+            if token_src is not None:
+                token_src = list(token_src[:n_ones]) + [-1] * pad + list(token_src[n_ones:])
+            if n_single:
+                n_single += pad
         R = len(items)
-        T = sum(len(it.tokens) for it in items)
-        W = sum(len(it.want) for it in items)
+        T = sum(lens) + pad
+        W_real = sum(len(it.want) for it in caller_items)
+        W = W_real + pad
         ng = cache.n_groups
         strides = []
         for g in range(ng):
-            longest = max(cache.table_len(it.request, g) for it in items)
-            strides.append(_round_up(max(longest, 1), 32))
+            longest = max(cache.table_len(it.request, g) for it in caller_items)
+            strides.append(_table_width(longest))
         # the last array (one source index per token, -1 = the id the host wrote) is there in every
         # step, so that the layout depends on the step's totals only
         sizes = [T, T, T, R + 1, R, R, max(W, 1)] + [R * s for s in strides] + [T, R]
@@ -121,6 +155,11 @@ class StepFunction:
         want = h[offs[6]:offs[6] + max(W, 1)]
         t = 0
         for i, it in enumerate(items):
+            if it is None:                               # a padding row
+                tok[t], pos[t], iot[t] = 0, 0, i
+                row_start[i], slot[i], start_pos[i] = t, cache.spare_slot, 0
+                t += 1
+                continue
             n = len(it.tokens)
             start = cache.cached(it.request)
             tok[t:t + n] = np.asarray(it.tokens, dtype=np.int64)
@@ -140,11 +179,17 @@ class StepFunction:
                     raise ValueError(f"request {it.request}: wanted place {j} is not among its {n} tokens")
                 want[w] = base + j
                 w += 1
+        for i in range(n_ones, n_ones + pad):            # then the padding rows
+            want[w] = int(row_start[i])
+            w += 1
         for g in range(ng):
             tab = h[offs[7 + g]:offs[7 + g] + R * strides[g]].reshape(R, strides[g])
             tab[:] = -1
             for i, it in enumerate(items):
-                cache.fill_table(it.request, g, tab[i])
+                if it is None:
+                    tab[i, 0] = cache.spare_page(g)
+                else:
+                    cache.fill_table(it.request, g, tab[i])
         src = h[offs[7 + ng]:offs[7 + ng] + T]
         if token_src is None:
             src[:] = -1
@@ -152,7 +197,7 @@ class StepFunction:
             src[:] = np.asarray(token_src, dtype=np.int32)
         # state slots of requests that start in this step (they are zeroed before the step's first token runs);
         # the list is padded with -1 (skipped by the kernel), so that it travels with the description
-        fresh = [int(slot[i]) for i in range(R) if start_pos[i] == 0]
+        fresh = [int(slot[i]) for i in range(R) if start_pos[i] == 0 and items[i] is not None]
         fresh_at = offs[8 + ng]
         h[fresh_at:fresh_at + R] = (fresh + [-1] * (R - len(fresh))) if fresh else -1
         n_ints = int(offs[-1])
@@ -177,12 +222,13 @@ class StepFunction:
         # the step; how far back a request's cache rows are surely older than this step), and as an upper bound it
         # serves every step whose longest portion is no longer, so that steps of a continuous batch, whose longest
         # portion is whatever the token budget left over, share captured graphs.
-        longest = max(len(it.tokens) for it in items)
+        longest = max(lens)
         b.max_tokens_per_item = 1 if longest <= 1 else 1 << (longest - 1).bit_length()
         b.max_context = int(max(start_pos[i] + (row_start[i + 1] - row_start[i]) for i in range(R)))
         b.decode_only = b.max_tokens_per_item == 1
         b.host = {"start_pos": start_pos[:R].copy(), "slots": slot[:R].copy(), "row_start": row_start[:R + 1].copy(),
-                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single, bool(fresh)), "h2d_bytes": n_ints * 4}
+                  "key": (T, R, W, tuple(strides), b.max_tokens_per_item, n_single, bool(fresh)), "h2d_bytes": n_ints * 4,
+                  "n_want_real": W_real, "padding_rows": pad}
         return b
 
     # -- a step whose shape has come before replays its captured graph -----------------------
@@ -191,7 +237,7 @@ class StepFunction:
         if batch.fresh_slots is not None and getattr(cache, "n_state_segments", 0):
             # a fresh request's state starts at zero: one kernel over the flat state arena, first in the step's chain
             ops.zero_state_slots(cache.state_arena, cache.state_segments, cache.n_state_segments, batch.fresh_slots,
-                                 cache.num_slots, self.rt.status)
+                                 cache.arena_slots, self.rt.status)
         x, picked = self.model.forward(batch, self._views, wanted=(batch.want_rows, batch.n_want))
         if not batch.n_want:
             return None
@@ -320,6 +366,9 @@ class StepFunction:
                 logits = self._forward_graphed(batch)
             else:
                 logits = self._forward(batch)
+            if logits is not None and batch.host["padding_rows"]:
+                n_real = batch.host["n_want_real"]
+                logits = logits[:n_real] if n_real else None
         except Exception:
             if manage_cache:
                 for it in items:

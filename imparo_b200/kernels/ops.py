@@ -80,6 +80,7 @@ class LaunchState:
         self.consumer_parts = {}     # device index -> scratch of products a consumer kernel folds
         self.tc_scratch = {}         # device index -> (floats, counters) of the cluster-folded products
         self.argmax_scratch = {}
+        self.sample_scratch = {}
         self.status_fallback = {}
         self.generation = 0          # bumped when a scratch buffer moves: captured graphs that used it are stale
 
@@ -170,6 +171,14 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
 # A decode-sized product into the stream is cut along K over many CTAs.  Instead of folding the
 # splits itself it may leave them in scratch ("pending"); the next reader of the stream — nearly
 # always the RMS norm — adds them in split order and goes on in the same kernel.
+
+
+def _grown(floats: int, old) -> int:
+    """Size of a scratch buffer that must hold `floats`: at least 4 MB, and twice the old size while that stays
+    under 256 MB, because every move of a scratch buffer makes the captured graphs that used it stale and a
+    serving loop meets slightly larger steps for a long while."""
+    had = old.numel() if old is not None else 0
+    return max(floats, 1 << 20, 2 * had if had <= (32 << 20) else 0)
 
 
 def defer_adds() -> bool:
@@ -435,7 +444,7 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                     buf = _S.partials.get(key)
                     if buf is None or buf.numel() < floats:
                         _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
-                        buf = _S.partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                        buf = _S.partials[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=x.device)
                         _S.generation += 1
                     gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
                     _S.pending[out.data_ptr()] = (buf, splits, M, N)
@@ -511,7 +520,7 @@ def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torc
             buf = _S.consumer_parts.get(key)
             if buf is None or buf.numel() < floats:
                 _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
-                buf = _S.consumer_parts[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=x.device)
+                buf = _S.consumer_parts[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=x.device)
                 _S.generation += 1
             gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
             return PartialProduct(buf, splits, (M, N), out)
@@ -537,7 +546,7 @@ def _into_stream(out: torch.Tensor, M: int, N: int, K: int):
             buf = _S.partials.get(key)
             if buf is None or buf.numel() < floats:
                 _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
-                buf = _S.partials[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=out.device)
+                buf = _S.partials[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=out.device)
                 _S.generation += 1
             return EPI_PARTIAL, buf, splits
     settle(out)
@@ -812,5 +821,18 @@ def sample_rows(logits, temperature, uniform, out) -> None:
     if temperature is not None:
         _need(temperature.dtype == torch.float32 and uniform is not None and uniform.dtype == torch.float32
               and temperature.numel() >= n and uniform.numel() >= n, "sample_rows: temperature/uniform float32 per row")
+        if vocab >= 4096 and n <= 65535:
+            # a large vocabulary: 32 blocks per row take a stretch each, then a block per row picks
+            key = torch.device(logits.device).index or 0
+            buf = _S.sample_scratch.get(key)
+            if buf is None or buf[1].numel() < n * 32:
+                _need(not torch.cuda.is_current_stream_capturing(), "sampling scratch would grow during graph capture")
+                buf = _S.sample_scratch[key] = (torch.empty(max(n, 256) * 64, dtype=torch.float32, device=logits.device),
+                                                torch.empty(max(n, 256) * 32, dtype=torch.int32, device=logits.device))
+            _check(_lib.kernels().imparo_sample_rows_parts(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out),
+                                                           _ptr(buf[0]), _ptr(buf[1]), n, vocab, logits.stride(0), _stream()),
+                   "sample_rows_parts")
+            COUNTS["own"] += 1
+            return
     _check(_lib.kernels().imparo_sample_rows(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, vocab,
                                              logits.stride(0), _stream()), "sample_rows")

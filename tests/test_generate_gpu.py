@@ -220,3 +220,44 @@ def test_logits_of_two_steps_of_the_same_shape_can_both_be_kept(dtype):
     for i, t in enumerate(kept):
         assert np.abs(t.cpu().numpy()[0] - ref[8 + i]).max() <= TOL[dtype] * scale, i
     assert len({t.data_ptr() for t in kept}) == 4
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
+def test_padding_rows_change_the_shape_not_the_results(dtype, tol):
+    """Three decoding requests beside a prompt portion: with padding the step runs four one-token rows (the
+    fourth belongs to no request and writes to the spare page and slot); the real rows' logits are those of the
+    step without padding and of the plain implementation, and nothing of the pool is taken."""
+    from imparo_b200.engine import Engine, StepItem
+    reqs = make_requests("B", [9, 14, 6, 30], seed=21)
+    prompts = list(reqs.values())
+    plain = plain_model("B")
+    want = np.stack([plain.logits(prompts[3][:20])[19]] + [plain.logits(prompts[r])[-1] for r in range(3)])
+    nxt = [int(np.argmax(want[i + 1])) for i in range(3)]
+    outs = []
+    for pad in (False, True):
+        eng = Engine(model_dir("B"), dtype=dtype, ctx=64, parallel=4, page_size=4, num_pages=40, switches={})
+        eng.step_fn.pad_rows = pad
+        for r in range(4):
+            eng.add_request(r)
+        for r in range(3):                                   # three prompts but their last token, each alone
+            eng.step([StepItem(r, prompts[r][:-1], [])])
+        free = eng.cache.free_pages(0)
+        items = [StepItem(3, prompts[3][:20], [19])] + [StepItem(r, prompts[r][-1:], [0]) for r in range(3)]
+        logits = eng.step(items)
+        key = eng.step_fn._graphs and list(eng.step_fn._graphs)[-1]
+        assert key[1] == (5 if pad else 4) and key[0] == (24 if pad else 23)
+        assert logits.shape[0] == 4
+        outs.append(logits.float().cpu())
+        # decode-only step of three rows: padded to four as well
+        l2 = eng.step([StepItem(r, [nxt[r]], [0]) for r in range(3)])
+        assert l2.shape[0] == 3
+        outs.append(l2.float().cpu())
+        eng.check_device_status()
+        eng.cache.check()
+        for r in range(4):
+            eng.end_request(r)
+        assert eng.cache.free_pages(0) == 40 and eng.cache.free_slots() == 4 and free < 40
+    scale = float(np.abs(want).max())
+    for got in (outs[0], outs[2]):
+        assert np.abs(got.numpy() - want).max() <= tol * scale
+    assert np.abs(outs[1].numpy() - outs[3].numpy()).max() <= tol * scale

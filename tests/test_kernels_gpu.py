@@ -544,7 +544,26 @@ def test_greedy_pick_smallest_index_and_nan():
     assert out.tolist() == [123, 77, 0, V - 1]
 
 
-@pytest.mark.parametrize("V", [331, 65536])
+def test_temperature_sampling_skips_nan_and_empty_stretches():
+    """Large vocabulary (the two-stage kernels): whole stretches of -inf or NaN carry no weight, a row of NaN gives 0,
+    a row with one finite entry gives that entry whatever the uniform number."""
+    o = ops()
+    V = 70001
+    logits = torch.full((5, V), float("-inf"))
+    logits[0, 40000] = 1.0; logits[0, 40001] = 1.0                      # two equal entries: u picks between them
+    logits[1, :] = float("nan"); logits[1, 69000] = -3.0
+    logits[2, :] = float("nan")
+    logits[3, :] = float("nan"); logits[3, 5] = 0.0; logits[3, V - 1] = 0.0
+    logits[4, 123] = 2.0                                                # greedy row among sampled ones
+    temps = torch.tensor([0.7, 1.0, 1.0, 2.0, 0.0])
+    for us, want in (([0.25, 0.5, 0.5, 0.25, 0.9], [40000, 69000, 0, 5, 123]),
+                     ([0.75, 0.0, 0.99, 0.75, 0.1], [40001, 69000, 0, V - 1, 123])):
+        out = torch.empty(5, dtype=torch.int32, device=DEV)
+        o.sample_rows(logits.to(DEV), temps.to(DEV), torch.tensor(us).to(DEV), out)
+        assert out.tolist() == want
+
+
+@pytest.mark.parametrize("V", [331, 65536, 70001])
 def test_temperature_sampling_is_the_inverse_cdf(V):
     o = ops()
     rng = np.random.default_rng(V)

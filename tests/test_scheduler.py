@@ -263,3 +263,37 @@ def test_a_planned_row_never_needs_a_token_older_than_the_step_in_flight(seed):
     _PREEMPTIONS_SEEN.append(s.n_preemptions)
     if seed == 11:
         assert sum(_PREEMPTIONS_SEEN) > 0            # the pools were small enough to matter
+
+
+def test_padded_rows_rule_and_budget():
+    """The step function fills the one-token rows up to 1, 2, 4, 8, 16, 24, ... rows; a scheduler told so counts
+    those rows in its token budget, so a step with prompt portions holds exactly the budget while prompts are left."""
+    from imparo_b200.engine.scheduler import padded_rows
+    assert [padded_rows(n) for n in (0, 1, 2, 3, 4, 5, 8, 9, 16, 17, 31, 33)] == [0, 1, 2, 4, 4, 8, 8, 16, 16, 24, 32, 40]
+    cm = CacheManager([(0, (PagedKV(1, 8, None),))], page_size=4, num_pages=4000, num_slots=12)
+    budget = 64
+    s = Scheduler(cm, budget, 12, 1000, count_padded_rows=True)
+    plain = Scheduler(CacheManager([(0, (PagedKV(1, 8, None),))], page_size=4, num_pages=4000, num_slots=12), budget, 12, 1000)
+    for sched in (s, plain):
+        for n in (5, 9, 30, 200, 7, 300, 11, 250, 400):
+            sched.submit(n, 40)
+    seen = set()
+    for _ in range(60):
+        plan = s.plan()
+        if not plan:
+            break
+        ones = sum(1 for e in plan if e.count == 1)
+        total = sum(e.count for e in plan)
+        padded = total + padded_rows(ones) - ones
+        assert padded <= budget
+        if s.n_waiting > 0 or any(e.count > 1 and not e.want for e in plan):
+            assert padded == budget, (ones, total)          # prompts are left: the step is full to the row
+        seen.add(ones)
+        s.step_done(True)
+        for e in plan:
+            if e.want:
+                s.on_token(e.request, False)
+    assert len(seen) > 3
+    # without the option the budget counts real tokens only
+    p = plain.plan()
+    assert sum(e.count for e in p) == budget
