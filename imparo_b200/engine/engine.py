@@ -28,7 +28,7 @@ from ..parts.model import Model
 from ..sampling import Sampler
 from ..weights.loader import load_weights, target_dtype
 from ..weights.random_init import draw_random_tensors
-from .scheduler import Scheduler
+from .scheduler import Scheduler, padded_rows
 from .step import StepFunction, StepItem
 
 _PRECISIONS = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32", "f32": "float32"}
@@ -104,7 +104,11 @@ class Engine:
             self.rt.probe_entry = int(probe_layer)
             self.rt.probe = probe if probe is not None else self._print_probe
             self.step_fn.use_graphs = False
-        self.sampler = Sampler(self.device, max_rows=max(self.parallel, 8))
+        # what the largest step holds, for buffers that are then made once (a moved buffer voids the captured graphs)
+        rows = padded_rows(self.parallel) + 2 if cfg.pad_rows else self.parallel + 2
+        self.rt.workspace.expect(tokens=min(self.max_step_tokens + rows, 8192), rows=min(rows, 512), context=self.ctx)
+        self.step_fn.reserve(min(self.max_step_tokens + rows, 8192), min(rows, 512), -(-self.ctx // self.page_size))
+        self.sampler = Sampler(self.device, max_rows=max(rows, 8))
         self.vocab_size = self.model.spec.vocab_size
         self._stats = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0, "preemptions": 0, "seconds": 0.0}
 

@@ -93,6 +93,14 @@ class StepFunction:
             slot[1].synchronize()
         return slot[0]
 
+    def reserve(self, tokens: int, rows: int, pages_per_request: int) -> None:
+        """Make the descriptor buffers for the largest step now (they move, and captured graphs with them, whenever
+        a step needs more than they hold)."""
+        ng = self.cache.n_groups
+        n = 4 * (tokens + 4) + 5 * (rows + 4) + ng * rows * _table_width(pages_per_request) + 64
+        if self._cap < n <= (4 << 20):           # beyond 16 MB per buffer: on demand
+            self._host_buffer(n)
+
     def build_batch(self, items: Sequence[StepItem], token_src: Optional[Sequence[int]] = None,
                     singles_first: bool = False) -> StepBatch:
         """singles_first: requests that bring one token are put before those that bring more (the

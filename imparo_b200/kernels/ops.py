@@ -291,7 +291,7 @@ def _tc_buffers(device, floats: int, counters: int):
         buf = (torch.empty(max(floats, old_f, 1 << 20), dtype=torch.float32, device=device),
                torch.zeros(max(counters, old_c, 4096), dtype=torch.int32, device=device))
         _S.tc_scratch[key] = buf
-        _S.generation += 1
+        _S.generation += 1 if old_f else 0          # a buffer that did not exist is in no captured graph
     return buf
 
 
@@ -444,8 +444,8 @@ def linear(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                     buf = _S.partials.get(key)
                     if buf is None or buf.numel() < floats:
                         _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                        _S.generation += 0 if buf is None else 1      # a buffer that did not exist is in no captured graph
                         buf = _S.partials[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=x.device)
-                        _S.generation += 1
                     gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
                     _S.pending[out.data_ptr()] = (buf, splits, M, N)
                     return
@@ -520,8 +520,8 @@ def linear_unfolded(x, w: torch.Tensor, out: torch.Tensor, status: Optional[torc
             buf = _S.consumer_parts.get(key)
             if buf is None or buf.numel() < floats:
                 _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                _S.generation += 0 if buf is None else 1
                 buf = _S.consumer_parts[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=x.device)
-                _S.generation += 1
             gemm_tc(x, w, out, EPI_PARTIAL, status, scratch=buf)
             return PartialProduct(buf, splits, (M, N), out)
     linear(x, w, out, status=status)
@@ -546,8 +546,8 @@ def _into_stream(out: torch.Tensor, M: int, N: int, K: int):
             buf = _S.partials.get(key)
             if buf is None or buf.numel() < floats:
                 _need(not torch.cuda.is_current_stream_capturing(), "partials scratch would grow during graph capture")
+                _S.generation += 0 if buf is None else 1
                 buf = _S.partials[key] = torch.empty(_grown(floats, buf), dtype=torch.float32, device=out.device)
-                _S.generation += 1
             return EPI_PARTIAL, buf, splits
     settle(out)
     return EPI_ADD_F32, None, 1

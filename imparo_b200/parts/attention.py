@@ -85,25 +85,37 @@ class AttentionMixer(Part):
     def cache_specs(self):
         return (PagedKV(self.nkv, self.hd, self.window),)
 
+    def _partials_room(self, upper_context: int) -> int:
+        """Partial results (per head) that the split-key attention of this engine's largest step of one-token rows
+        leaves at the longest context the engine allows (or this table width, if longer): with few rows the plan fills about eight CTAs per SM with short chunks, with
+        many it cuts 512 keys per chunk.  The scratch is made for that at once, so it does not move (and void the
+        captured graphs) each time a few more requests decode."""
+        most = self.rt.workspace.most
+        rows = most.get("rows", 0)
+        if not rows:
+            return 0
+        context = max(int(upper_context), min(most.get("context", 0), 1 << 17))
+        return (8 * ops.sm_count() + rows * self.nkv * (1 + -(-context // 512))) * (self.nh // self.nkv)
+
     def forward(self, x, batch, caches, residual):
         kv = caches[0]
         rt, T = self.rt, x.shape[0]
         nh, hd = self.nh, self.hd
         nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only
         width = (nh + 2 * nkv) * hd
-        qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype)
+        qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
         if self.b_qkv is None:
             qkv = ops.linear_unfolded(x, self.w_qkv[:width], qkv, status=rt.status)    # the kernel below can add split partials
         else:
             ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
             ops.add_bias(qkv, self.b_qkv[:width])
-        q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype)
+        q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype, first="tokens")
         rot = self.position.rotary()
         table = batch.tables[kv.group]
         inv_freq, n_rot = rot if rot is not None else (None, 0)
         ops.qk_norm_rope_store(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq, n_rot,
                                self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
-        out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype)
+        out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype, first="tokens")
         done = False
         n1 = getattr(batch, "n_single", 0)             # decode rows come first when the step also holds portions
         if batch.max_tokens_per_item >= 8 and 0 < n1 < batch.n_items and nh // self.nkv <= 8:
@@ -117,8 +129,9 @@ class AttentionMixer(Part):
                                          out, nh, self.nkv, hd, rt.status)
             if done:
                 chunk, n_splits = ops.split_plan(n1, self.nkv, table.shape[1] * kv.page_size)
-                part_acc = rt.workspace.get("attn_part_acc", (n1 * nh * n_splits * hd,), torch.float32)
-                part_ml = rt.workspace.get("attn_part_ml", (n1 * nh * n_splits * 2,), torch.float32)
+                room = self._partials_room(table.shape[1] * kv.page_size)
+                part_acc = rt.workspace.get("attn_part_acc", (n1 * nh * n_splits * hd,), torch.float32, reserve=room * hd)
+                part_ml = rt.workspace.get("attn_part_ml", (n1 * nh * n_splits * 2,), torch.float32, reserve=room * 2)
                 ops.paged_attention_split(q[:n1], kv.k, kv.v, batch.positions[:n1], batch.item_of_token[:n1], table,
                                           kv.page_size, kv.n_pages, self.window, self.scale, out[:n1], part_acc, part_ml,
                                           chunk, n_splits, nh, self.nkv, hd, rt.status, fresh=1)
@@ -129,8 +142,9 @@ class AttentionMixer(Part):
         if not done and nh // self.nkv <= 8 and T <= 65535:
             # keys cut into chunks; the cut depends on the launch's shape (tokens, table width) only
             chunk, n_splits = ops.split_plan(T, self.nkv, table.shape[1] * kv.page_size)
-            part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32)
-            part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32)
+            room = self._partials_room(table.shape[1] * kv.page_size)
+            part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32, reserve=room * hd)
+            part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32, reserve=room * 2)
             if batch.decode_only and rt.act_dtype == torch.bfloat16 and n_splits <= 64 and ops.fuse_producers():
                 # decode rows: the partial results stay as they are and the output product combines them while it
                 # makes its token operand; no combine kernel and no tensor between the two

@@ -66,8 +66,20 @@ class Workspace:
         self._bufs: Dict[str, torch.Tensor] = {}
         self._views: Dict[tuple, torch.Tensor] = {}      # (tag, dtype, shape) -> view handed out before
         self.generation = 0      # bumped whenever a buffer moves: captured graphs of older generations are stale
+        # the most tokens and the most wanted (or one-token) rows a step of this engine holds, when known: a buffer
+        # whose first dimension is one of them is made for the most at once instead of growing step by step
+        self.most = {"tokens": 0, "rows": 0, "context": 0}
 
-    def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+    def expect(self, tokens: int = 0, rows: int = 0, context: int = 0) -> None:
+        """tokens / rows: the most a step holds; context: the most positions a request reaches."""
+        self.most["tokens"] = max(self.most["tokens"], int(tokens))
+        self.most["rows"] = max(self.most["rows"], int(rows))
+        self.most["context"] = max(self.most["context"], int(context))
+
+    def get(self, tag: str, shape: Sequence[int], dtype: torch.dtype, first: Optional[str] = None,
+            reserve: int = 0) -> torch.Tensor:
+        """first: what the first dimension counts ("tokens" | "rows"), if it is one of the step's totals;
+        reserve: elements to make room for at least (for buffers whose size follows no single dimension)."""
         shape = tuple(shape)
         seen = self._views.get((tag, dtype, shape))
         if seen is not None:
@@ -80,14 +92,18 @@ class Workspace:
         if buf is None or buf.numel() < n:
             if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"workspace buffer '{tag}' would grow during graph capture")
+            grown = max(n, 1, int(reserve))
+            if first is not None and shape and shape[0] <= self.most.get(first, 0):
+                grown = max(grown, n // max(int(shape[0]), 1) * self.most[first])
             # small buffers grow by doubling: every move makes captured graphs stale, and a serving loop
             # meets slightly larger shapes for a long while
-            grown = max(n, 1)
             if buf is not None and grown * buf.element_size() <= (64 << 20):
                 grown = max(grown, 2 * buf.numel())
+            moved = buf is not None
             buf = torch.empty(grown, dtype=dtype, device=self.device)
             self._bufs[key] = buf
-            self.generation += 1
+            if moved:                 # a buffer that did not exist is in no captured graph
+                self.generation += 1
             self._views = {k: v for k, v in self._views.items() if k[:2] != key}
         view = buf[:n].view(*shape)
         if len(self._views) < 4096:

@@ -47,7 +47,7 @@ class PreNormResidualBlock(Block):
             if n == 0:
                 ops.settle(x)
                 return None
-            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype)
+            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype, first="rows")
             ops.gather_rows(x, rows, xs)
             picked_in = self.ff_norm.forward(xs, tag="normed_ff")
             self._run(self.ff, xs, lambda: self.ff.forward(picked_in, batch, xs))
@@ -74,7 +74,7 @@ class PreNormResidualBlock(Block):
             rows, n = only_rows
             if n == 0:
                 return None
-            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype)
+            xs = self.rt.workspace.get("stream_picked", (n, x.shape[1]), x.dtype, first="rows")
             ops.gather_rows(x, rows, xs)
             x = xs
         ff_in = self.ff_norm.forward(x, tag="normed_ff")

@@ -32,7 +32,7 @@ class TokenEmbedding(Part):
     def forward(self, batch) -> torch.Tensor:
         """batch: the step's batch (token_ids, positions, item_of_token, ... on the device).  This part reads
         the token ids only; an embedding that adds learned positions or segment rows reads the rest."""
-        out = self.rt.workspace.get("residual", (batch.n_tokens, self.width), torch.float32)
+        out = self.rt.workspace.get("residual", (batch.n_tokens, self.width), torch.float32, first="tokens")
         ops.embed_gather(self.table, batch.token_ids, out, self.rt.status)
         return out
 
@@ -54,6 +54,6 @@ class LinearHead(Part):
         self.table = tensors[self.name]
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32)
+        logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32, first="rows")
         ops.linear(h, self.table, logits, status=self.rt.status)
         return logits

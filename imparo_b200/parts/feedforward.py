@@ -36,7 +36,7 @@ class SwiGLU(Part):
 
     def forward(self, x, batch, residual):
         rt, T, F = self.rt, x.shape[0], self.ff
-        h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype)
+        h = rt.workspace.get("ffn_h", (T, F), rt.act_dtype, first="tokens")
         # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
-        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype))
+        ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
         ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)

@@ -32,6 +32,6 @@ class RMSNorm(Part):
         """x: 32-bit [tokens, width].  rows (int32, device) picks input rows; n_rows is how
         many of them.  Returns activations in the path's dtype."""
         n = x.shape[0] if rows is None else int(n_rows if n_rows is not None else rows.numel())
-        out = self.rt.workspace.get(tag, (n, self.width), self.rt.act_dtype)
+        out = self.rt.workspace.get(tag, (n, self.width), self.rt.act_dtype, first="tokens" if rows is None else "rows")
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out

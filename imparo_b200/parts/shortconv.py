@@ -54,13 +54,13 @@ class ShortConvMixer(Part):
     def forward(self, x, batch, caches, residual):
         st = caches[0]
         rt, T, H = self.rt, x.shape[0], self.hidden
-        bcx = rt.workspace.get("conv_bcx", (T, 3 * H), rt.act_dtype)
+        bcx = rt.workspace.get("conv_bcx", (T, 3 * H), rt.act_dtype, first="tokens")
         if self.b_in is None:
             bcx = ops.linear_unfolded(x, self.w_in, bcx, status=rt.status)     # the conv kernel can add split partials itself
         else:
             ops.linear(x, self.w_in, bcx, status=rt.status)
             ops.add_bias(bcx, self.b_in)
-        y = rt.workspace.get("conv_y", (T, H), rt.act_dtype)
+        y = rt.workspace.get("conv_y", (T, H), rt.act_dtype, first="tokens")
         ops.gated_conv(bcx, self.w_conv, self.b_conv, st.state, batch.item_row_start, batch.item_of_token,
                        batch.item_slot, y, self.taps, rt.status)
         ops.linear(y, self.w_out, residual, accumulate=True, status=rt.status)
