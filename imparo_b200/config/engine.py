@@ -56,6 +56,7 @@ class KernelSwitches:
     unfolded: bool = True                 # IMPARO_UNFOLDED: in_proj / qkv leave split partials to their consumer
     defer_adds: bool = True               # IMPARO_DEFER_ADDS: products into the stream leave partials to the next norm
     fuse_producers: bool = True           # IMPARO_FUSE_PRODUCERS: the attention combine inside the output product (decode rows)
+    decode_from_qkv: bool = True          # IMPARO_DECODE_FROM_QKV: decode rows' q/k norm, rotation and cache write inside the attention kernel
     attn_prefill: str = "auto"            # IMPARO_ATTN_PREFILL: "auto" | "mma" | "tcgen05" | "tcgen05_one_tile"
 
     ENV_PREFIX = "IMPARO_"

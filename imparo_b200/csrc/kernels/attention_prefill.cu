@@ -279,15 +279,38 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 // previous kernel.  The general-purpose version of this kernel (any head size, 32-bit) is
 // attention_split.cu; this one exists because the scalar version is bound by instruction issue,
 // not by memory.
-template <int HD>
+// FROM_QKV: the kernel takes the qkv product's split partials instead of finished queries, for steps in which
+// every request brings one token.  Each CTA sums, norms and rotates the queries of its kv head's group itself
+// (every chunk's CTA repeats that: G heads of HD values), and the CTA whose chunk holds the token's own position
+// also makes the new key and value row, writes it into its page for later steps and, after a CTA-wide barrier,
+// reads it back with the rest of its tile.  This is the q/k kernel's arithmetic (attention.cu: sum in split
+// order, round to bfloat16, RMS norm over the head, rotation of pairs (i, i + n_rot/2)) without its launch.
+struct QkvSource {
+    const float* part;          // [parts][tokens][(nh + 2 nkv) * HD]
+    int parts;
+    size_t part_stride;
+    const float* q_w;           // per-head norm weights, or null: no norm on that side
+    const float* k_w;
+    const float* inv_freq;      // [n_rot / 2], or null: no rotation
+    int n_rot;
+    float eps;
+    __nv_bfloat16* k_out;       // the caches, writable
+    __nv_bfloat16* v_out;
+};
+
+template <int HD, bool FROM_QKV>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
                        const int* __restrict__ item_of_token, const int* __restrict__ table, int max_blocks,
                        int page_size, int n_pages, int window, float scale, float* __restrict__ part_acc,
-                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int fresh, int* status) {
+                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int fresh, int* status,
+                       QkvSource src) {
     constexpr int CH = HD / 8, KT = HD / 16, NT_O = HD / 8;
+    constexpr int PER = HD / 32, PAIRS = PER / 2;                  // a head's values per lane; rotation pairs per lane
     extern __shared__ __align__(128) uint8_t pf_smem[];
+    __shared__ __align__(16) __nv_bfloat16 q_made[FROM_QKV ? 8 * HD : 8];     // the group's queries, made here
+    __shared__ float head_row[FROM_QKV ? 4 : 1][FROM_QKV ? HD : 1];         // a warp's head between norm and rotation
     // shared memory: two buffers of 64 keys and 64 values (32 KB at head size 64, so that four
     // CTAs fit beside a resident product CTA); after the key loop the same bytes hold the warps'
     // partial results for the fold
@@ -357,6 +380,17 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             if (kb <= kb_last && min(end, (kb + 1) * KEYS) <= old_end) { load_kv(kb, u); requested = kb; } else break;
         }
     }
+    // FROM_QKV: the rotation's sines and cosines and the norm weights do not depend on the previous kernel either
+    float sn[PAIRS > 0 ? PAIRS : 1], cs[PAIRS > 0 ? PAIRS : 1];
+    const int half = FROM_QKV ? src.n_rot >> 1 : 0;
+    if (FROM_QKV) {
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            const int i = lane + 32 * j;
+            sn[j] = 0.f; cs[j] = 1.f;
+            if (src.inv_freq && i < half) sincosf((float)pos * src.inv_freq[i], &sn[j], &cs[j]);
+        }
+    }
     pdl_wait();
     if (begin >= end) {
         if (tid < G) {
@@ -366,11 +400,88 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         return;
     }
 
+    if (FROM_QKV) {
+        // Work items: the group's G query heads; in the CTA whose chunk holds the token's position also the new key
+        // (item G) and value (item G + 1).  Warp w takes items w, w + 4, ...; a lane holds the values lane + 32 j.
+        const bool owner = pos >= begin && pos < end;
+        const int total_w = (nh + 2 * nkv) * HD;
+        __nv_bfloat16* kdst = nullptr;
+        __nv_bfloat16* vdst = nullptr;
+        if (owner) {
+            const int blk = page_shift >= 0 ? pos >> page_shift : pos / page_size;
+            const int within = page_shift >= 0 ? pos & (page_size - 1) : pos % page_size;
+            const int page = blk < max_blocks ? tab[blk] : -1;
+            if (page < 0 || page >= n_pages) {
+                if (tid == 0) report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);
+            } else {
+                const size_t r = ((size_t)page * page_size + within) * kvw + (size_t)kvh * HD;
+                kdst = src.k_out + r;
+                vdst = src.v_out + r;
+            }
+        }
+        const int n_work = G + (owner ? 2 : 0);
+        for (int it = warp; it < n_work; it += 4) {
+            const bool is_q = it < G, is_k = it == G;
+            const int col0 = is_q ? (h0 + it) * HD : (is_k ? (nh + kvh) * HD : (nh + nkv + kvh) * HD);
+            const float* ps = src.part + (size_t)t * total_w + col0;
+            float val[PER];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int d = lane + 32 * j;
+                float acc = 0.f;
+                for (int s0 = 0; s0 < src.parts; s0 += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = s0 + u < src.parts ? __ldcg(ps + (size_t)(s0 + u) * src.part_stride + d) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) if (s0 + u < src.parts) acc += v[u];
+                }
+                val[j] = __bfloat162float(__float2bfloat16(acc));             // rounded as the stored product would be
+                ss += val[j] * val[j];
+            }
+            if (is_q || is_k) {
+                const float* w = is_q ? src.q_w : src.k_w;
+                ss = warp_sum(ss);
+                const float nscale = w ? 1.0f / sqrtf(ss / (float)HD + src.eps) : 1.0f;
+                float* row = head_row[warp];
+#pragma unroll
+                for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; row[d] = val[j] * nscale * (w ? w[d] : 1.f); }
+                __syncwarp();
+                if (src.inv_freq) {
+#pragma unroll
+                    for (int j = 0; j < PAIRS; ++j) {
+                        const int i = lane + 32 * j;
+                        if (i < half) {
+                            const float x0 = row[i], x1 = row[i + half];
+                            row[i] = x0 * cs[j] - x1 * sn[j];
+                            row[i + half] = x0 * sn[j] + x1 * cs[j];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (is_q) {
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; q_made[it * HD + d] = __float2bfloat16(row[d]); }
+                } else if (kdst) {
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; kdst[d] = __float2bfloat16(row[d]); }
+                }
+                __syncwarp();                                                  // the row buffer serves the warp's next item
+            } else if (vdst) {
+#pragma unroll
+                for (int j = 0; j < PER; ++j) { const int d = lane + 32 * j; vdst[d] = __float2bfloat16(val[j]); }
+            }
+        }
+        __syncthreads();            // the queries are complete; the new key and value row is visible to this CTA's loads
+    }
+
     // the queries go straight to registers in the MMA's A layout: row g of the 16-row tile is head
     // h0 + g (rows from G up are padding)
     uint32_t qf[KT][4];
     {
-        const __nv_bfloat16* qrow = q + ((size_t)t * nh + h0 + (g < G ? g : 0)) * HD + 2 * tg;
+        const __nv_bfloat16* qrow = FROM_QKV ? q_made + (g < G ? g : 0) * HD + 2 * tg
+                                             : q + ((size_t)t * nh + h0 + (g < G ? g : 0)) * HD + 2 * tg;
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt) {
             qf[kt][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16) : 0u;
@@ -552,12 +663,12 @@ extern "C" int imparo_attention_split_combine(const float* part_acc, const float
 // Single query tokens on tensor cores: bfloat16, head size 64 or 128, at most 8 query heads per
 // kv head; else -8.  Scratch as for imparo_paged_attention_split.  out == nullptr: the partials are
 // left in scratch for a consumer that combines them itself (imparo_gemm_tc_combine).
-extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
-                                           const int* positions, const int* item_of_token,
-                                           const int* table, int max_blocks, int page_size, int n_pages,
-                                           int window, float scale, void* out, float* part_acc, float* part_ml,
-                                           int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
-                                           int* status, cudaStream_t stream) {
+static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const void* k_cache, const void* v_cache,
+                             const int* positions, const int* item_of_token,
+                             const int* table, int max_blocks, int page_size, int n_pages,
+                             int window, float scale, void* out, float* part_acc, float* part_ml,
+                             int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
+                             int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
@@ -570,20 +681,53 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
     static bool configured = false;
     cudaError_t e;
     if (!configured) {
-        e = cudaFuncSetAttribute(pf::attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(pf::attn_decode_mma_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  4 * pf::KEYS * 128 * 2);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(pf::attn_decode_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     4 * pf::KEYS * 128 * 2);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    if (hd == 64)
-        e = launch(pf::attn_decode_mma_kernel<64>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
-                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
-                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status);
-    else
-        e = launch(pf::attn_decode_mma_kernel<128>, grid, dim3(pf::THREADS), smem, stream, (const __nv_bfloat16*)q,
-                   (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, max_blocks,
-                   page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status);
+    const bool from_qkv = qkv_src != nullptr;
+    const pf::QkvSource none{};
+    const pf::QkvSource& src = from_qkv ? *qkv_src : none;
+#define IMPARO_DECODE(HD_, F_) launch(pf::attn_decode_mma_kernel<HD_, F_>, grid, dim3(pf::THREADS), smem, stream, \
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, \
+        max_blocks, page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status, src)
+    if (hd == 64) e = from_qkv ? IMPARO_DECODE(64, true) : IMPARO_DECODE(64, false);
+    else e = from_qkv ? IMPARO_DECODE(128, true) : IMPARO_DECODE(128, false);
+#undef IMPARO_DECODE
     if (e != cudaSuccess) return (int)e;
     if (out == nullptr) return 0;
     return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, stream);
+}
+
+extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* positions, const int* item_of_token,
+                                           const int* table, int max_blocks, int page_size, int n_pages,
+                                           int window, float scale, void* out, float* part_acc, float* part_ml,
+                                           int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
+                                           int* status, cudaStream_t stream) {
+    return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
+                             scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, status, stream);
+}
+
+// The same for a step in which every request brings ONE token, straight from the qkv product's split partials
+// (part [parts][n_tok][(nh + 2 nkv) * hd], split s at part + s * part_stride): the queries are made inside the kernel
+// and the new key and value rows are written into their pages by it.  q_w / k_w null: no per-head norm on that side;
+// inv_freq null: no rotation.  n_rot even, at most hd.
+extern "C" int imparo_attention_decode_mma_qkv(const float* part, int parts, long long part_stride, const float* q_w,
+                                               const float* k_w, const float* inv_freq, int n_rot, float eps,
+                                               void* k_cache, void* v_cache, const int* positions, const int* item_of_token,
+                                               const int* table, int max_blocks, int page_size, int n_pages, int window,
+                                               float scale, void* out, float* part_acc, float* part_ml, int n_tok, int nh,
+                                               int nkv, int hd, int chunk, int n_splits, int* status, cudaStream_t stream) {
+    if (part == nullptr || parts < 1) return -24;
+    if (n_rot < 0 || (n_rot & 1) || n_rot > hd) return -4;
+    pf::QkvSource src{part, parts, (size_t)part_stride, q_w, k_w, inv_freq, inv_freq ? n_rot : 0, eps,
+                      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
+    // fresh = 1: a request's only new row is the one this kernel writes; older rows are safe to request early
+    return decode_mma_launch(nullptr, &src, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages,
+                             window, scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, 1, status, stream);
 }

@@ -723,6 +723,45 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     return True
 
 
+def attention_decode_from_qkv(qkv, positions, item_of_token, q_w, k_w, inv_freq, n_rot, eps, k_cache, v_cache, table,
+                              page_size, n_pages, window, scale, out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd,
+                              status) -> bool:
+    """The split-key attention of a step in which every request brings ONE token, straight from the qkv product's
+    split partials: the kernel makes its queries itself (sum in split order, per-head norm, rotation) and writes the
+    new key and value rows into their pages, so no q/k kernel runs before it.  Returns False, having launched
+    nothing, unless qkv is a PartialProduct in bfloat16 with head size 64 or 128 and at most 8 query heads per kv
+    head.  out None: the partial results stay uncombined (linear_of_attention_partials)."""
+    if not isinstance(qkv, PartialProduct) or qkv.dtype != torch.bfloat16 or hd not in (64, 128) or nkv < 1 \
+            or nh % nkv or nh // nkv > 8 or chunk < 64:
+        return False
+    T = qkv.shape[0]
+    _cuda(qkv.parts, positions, item_of_token, q_w, k_w, inv_freq, k_cache, v_cache, table, out, part_acc, part_ml, status)
+    _need(tuple(qkv.shape) == (T, (nh + 2 * nkv) * hd), "attention_decode_from_qkv: the product's width is (heads + 2 kv heads) * head size")
+    _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
+          and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
+    _need(q_w is None or (q_w.dtype == torch.float32 and q_w.numel() == hd), "q norm weight must be float32 [head]")
+    _need(k_w is None or (k_w.dtype == torch.float32 and k_w.numel() == hd), "k norm weight must be float32 [head]")
+    _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= n_rot // 2 and n_rot % 2 == 0
+                               and n_rot <= hd), "inv_freq must be float32 [n_rot/2], n_rot even and at most the head size")
+    _need(k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16, "cache dtype must match activations")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * hd,
+          "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _need(out is None or (out.shape == (T, nh * hd) and out.dtype == torch.bfloat16), "attention_decode_from_qkv: out shape")
+    _need(part_acc.dtype == torch.float32 and part_acc.numel() >= T * nh * n_splits * hd
+          and part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * n_splits * 2, "split scratch too small")
+    _need(T <= 65535 and 1 <= n_splits <= MAX_SPLITS, f"at most 65535 tokens and {MAX_SPLITS} key chunks")
+    _need(chunk * n_splits >= table.shape[1] * page_size, "chunk * n_splits must cover every position the block table can hold")
+    _check(_lib.kernels().imparo_attention_decode_mma_qkv(
+        _ptr(qkv.parts), qkv.splits, qkv.stride, _ptr(q_w), _ptr(k_w), _ptr(inv_freq), int(n_rot), float(eps),
+        _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table), table.shape[1], page_size, n_pages,
+        int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml), T, nh, nkv, hd, int(chunk), int(n_splits),
+        _ptr(status), _stream()), "attention_decode_from_qkv")
+    if out is not None:
+        COUNTS["own"] += 1      # partial + combine
+    return True
+
+
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
                       scale, out, nh, nkv, hd, status, kernel: str = "auto") -> bool:
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8

@@ -113,9 +113,29 @@ class AttentionMixer(Part):
         rot = self.position.rotary()
         table = batch.tables[kv.group]
         inv_freq, n_rot = rot if rot is not None else (None, 0)
+        out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype, first="tokens")
+        if batch.decode_only and kv.writes and ops.switches().decode_from_qkv and T <= 65535 and isinstance(qkv, ops.PartialProduct):
+            # Every request brings one token: the split-key kernel makes its queries from the product's partials
+            # itself and writes the new key and value rows, so the q/k kernel does not run (bfloat16, head 64 / 128).
+            chunk, n_splits = ops.split_plan(T, self.nkv, table.shape[1] * kv.page_size)
+            room = self._partials_room(table.shape[1] * kv.page_size)
+            part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32, reserve=room * hd)
+            part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32, reserve=room * 2)
+            in_product = n_splits <= 64 and ops.fuse_producers()          # the output product combines the partials while it makes its operand
+            if ops.attention_decode_from_qkv(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq,
+                                             n_rot, self.eps, kv.k, kv.v, table, kv.page_size, kv.n_pages, self.window,
+                                             self.scale, None if in_product else out, part_acc, part_ml, chunk, n_splits,
+                                             nh, self.nkv, hd, rt.status):
+                if not in_product or not ops.linear_of_attention_partials(part_acc, part_ml, T, nh, hd, n_splits, self.w_o,
+                                                                          residual, rt.status):
+                    if in_product:
+                        ops.attention_split_combine(part_acc, part_ml, out, T * nh, hd, n_splits)
+                    ops.linear(out, self.w_o, residual, accumulate=True, status=rt.status)
+                if self.b_o is not None:
+                    ops.add_bias(residual, self.b_o)
+                return
         ops.qk_norm_rope_store(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq, n_rot,
                                self.eps, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, rt.status)
-        out = rt.workspace.get("attn_out", (T, nh * hd), rt.act_dtype, first="tokens")
         done = False
         n1 = getattr(batch, "n_single", 0)             # decode rows come first when the step also holds portions
         if batch.max_tokens_per_item >= 8 and 0 < n1 < batch.n_items and nh // self.nkv <= 8:

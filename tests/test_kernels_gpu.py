@@ -878,3 +878,74 @@ def test_prefill_product_refuses_what_it_cannot_address():
     assert not o.prefill_tc_usable(z(256, 12), z(64, 12), z(256, 64))
     assert not o.prefill_tc_usable(z(100, 16), z(64, 16), z(100, 64))                 # too few tokens for this kernel
     assert o.prefill_tc_usable(z(256, 16), z(64, 16), z(256, 64))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,n_rot", [(8, 2, 64, 64), (6, 6, 64, 32), (16, 2, 128, 128), (3, 1, 64, 64), (8, 2, 128, 0)])
+@pytest.mark.parametrize("page,window,qk_norm", [(16, None, True), (4, 37, True), (64, None, False)])
+def test_decode_attention_from_the_qkv_partials(nh, nkv, hd, n_rot, page, window, qk_norm):
+    """Decode rows straight from the qkv product's split partials: the kernel makes its queries and the new key and
+    value rows itself.  It must leave the same cache rows and the same outputs as the q/k kernel followed by the
+    split-key attention (the same arithmetic in the same order), and both must agree with the float64 reference.
+    Requests stand at a page's first and last row, at position 0, inside and beyond a window."""
+    o = ops()
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(nh * 7 + hd + page)
+    pos = [0, page - 1, page, 5 * page + 3, 130, 259]                 # each request's new position = tokens it holds
+    lens = [p + 1 for p in pos]
+    T = len(pos)
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, lens, page, nkv, hd, dtype)
+    width = (nh + 2 * nkv) * hd
+    splits = 3
+    parts = torch.from_numpy(rng.standard_normal((splits, T, width)).astype(np.float32) * 0.6).to(DEV)
+    q_w = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).to(DEV) if qk_norm else None
+    k_w = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).to(DEV) if qk_norm else None
+    inv = (1e4 ** (-np.arange(n_rot // 2) * 2.0 / max(n_rot, 1))).astype(np.float32)
+    inv_freq = torch.from_numpy(inv).to(DEV) if n_rot else None
+    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    items = torch.arange(T, dtype=torch.int32, device=DEV)
+    tab = torch.from_numpy(table).to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    st = o.new_status(DEV)
+    chunk, n_splits = o.split_plan(T, nkv, table.shape[1] * page)
+    results = []
+    for fused in (False, True):
+        kcd, vcd = kc.clone().to(DEV), vc.clone().to(DEV)
+        qkv = o.PartialProduct(parts.reshape(-1), splits, (T, width), torch.empty(T, width, dtype=dtype, device=DEV))
+        out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        pa = torch.empty(T * nh * n_splits * hd, device=DEV)
+        pm = torch.empty(T * nh * n_splits * 2, device=DEV)
+        if fused:
+            assert o.attention_decode_from_qkv(qkv, positions, items, q_w, k_w, inv_freq, n_rot, 1e-5, kcd, vcd, tab, page,
+                                               n_pages, window, scale, out, pa, pm, chunk, n_splits, nh, nkv, hd, st)
+        else:
+            q = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+            o.qk_norm_rope_store(qkv, positions, items, q_w, k_w, inv_freq, n_rot, 1e-5, q, kcd, vcd, tab, page, n_pages,
+                                 nh, nkv, hd, st)
+            assert o.paged_attention_split(q, kcd, vcd, positions, items, tab, page, n_pages, window, scale, out, pa, pm,
+                                           chunk, n_splits, nh, nkv, hd, st, fresh=1)
+        torch.cuda.synchronize()
+        o.read_status(st)
+        results.append((out.float().cpu(), kcd.float().cpu(), vcd.float().cpu()))
+    (out_a, k_a, v_a), (out_b, k_b, v_b) = results
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)            # the same rows in the same pages, nothing else touched
+    assert torch.equal(out_a, out_b)
+    # and against float64: sum of the partials rounded to bfloat16, norm, rotation, attention over the request's rows
+    x = parts.sum(0).to(dtype).float().cpu().numpy().astype(np.float64)
+    for t in range(T):
+        def head(col0, w):
+            v = x[t, col0:col0 + hd].copy()
+            if w is not None:
+                v = v / np.sqrt((v * v).mean() + 1e-5) * w.cpu().numpy().astype(np.float64)
+            if n_rot:
+                ang = float(pos[t]) * inv.astype(np.float64)
+                a, b = v[:n_rot // 2].copy(), v[n_rot // 2:n_rot].copy()
+                v[:n_rot // 2] = a * np.cos(ang) - b * np.sin(ang)
+                v[n_rot // 2:n_rot] = a * np.sin(ang) + b * np.cos(ang)
+            return v
+        qq = np.concatenate([head(h * hd, q_w) for h in range(nh)])
+        kk = ks[t].numpy().astype(np.float64).copy()
+        vv = vs[t].numpy().astype(np.float64).copy()
+        kk[pos[t]] = np.concatenate([head((nh + g) * hd, k_w) for g in range(nkv)])
+        vv[pos[t]] = x[t, (nh + nkv) * hd:]
+        want = attention_reference(qq, kk, vv, pos[t], nh, nkv, hd, scale, window)
+        assert np.abs(out_b[t].numpy() - want).max() < 4e-2 * max(1.0, np.abs(want).max())
