@@ -54,6 +54,7 @@ struct Params {
     int T, N, K, ldo;        // N = rows of W (for SWIGLU: F, W has 2F rows)
     int splits, kblocks;     // kblocks = ceil(K / BK)
     int kb_cap;                  // PROD != NONE: k-blocks of the resident token operand (the most one split owns)
+    int tma_out;                 // PARTIAL_F32: the partial tile leaves through shared memory and one TMA store (map_o)
     // PROD_COMBINE: token operand [t, h * hd + d] = sum_s acc[t,h,s,d] f_s / sum_s l_s f_s, f_s = exp(m_s - max m)
     const float* cb_acc;         // [T, heads, splits, hd]
     const float* cb_ml;          // [T, heads, splits, 2]  (max, sum)
@@ -74,7 +75,8 @@ template <int PROD> struct ThreadsOf { static constexpr int value = (PROD == PRO
 
 template <int NT, int STAGES, int EPI, int PROD>
 __global__ void __launch_bounds__(ThreadsOf<PROD>::value, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+            const __grid_constant__ CUtensorMap map_o, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = NT * BK * 2, STAGE_BYTES = PROD != PROD_NONE ? A_BYTES : A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
@@ -333,6 +335,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
                 // this split's partial tile -> scratch[split][token][n]; whoever reads the stream next
                 // adds the splits in order (rows.cu: add_partials_rmsnorm)
                 float* part = p.scratch + (size_t)split * p.T * p.N;
+                if (p.tma_out) {
+                    // Through shared memory (the stage ring is idle now) as [token][row] and out with ONE store of
+                    // the TMA engine: a thread's 16 to 64 strided 32-bit stores took the load/store unit 0.4 to 2.4 us
+                    // at the very end of the kernel, where the next kernel waits for it.  Rows and tokens beyond the
+                    // tensor are clipped by the engine.
+                    float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+                    for (int c = 0; c < NT; c += 16 * CH) {
+                        float v[CH][16];
+                        tmem_ld_chunks<CH>(taddr + c, v);
+#pragma unroll
+                        for (int u = 0; u < CH; ++u)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) stage[(c + 16 * u + j) * BM + row] = v[u][j];
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64) {
+                        tma_store_3d(&map_o, stage, tile_n * BM, t0, split);
+                        tma_store_wait_read();
+                    }
+                } else
 #pragma unroll 1
                 for (int c = 0; c < NT; c += 16 * CH) {
                     float v[CH][16];
@@ -437,7 +461,7 @@ done:
 
 // ---- host side ---------------------------------------------------------------------------
 template <int NT, int STAGES, int EPI, int PROD = PROD_NONE>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Params& p, dim3 grid, cudaStream_t stream) {
     constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (PROD != PROD_NONE ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
     static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
     const size_t smem = fixed + (PROD != PROD_NONE ? (size_t)p.kb_cap * NT * BK * 2 : 0);
@@ -466,7 +490,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = imparo_pdl_enabled() ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, kern, mw, mx, p);
+    e = cudaLaunchKernelEx(&cfg, kern, mw, mx, mo, p);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -497,14 +521,14 @@ constexpr int deep_stages_for(int nt) { return nt <= 32 ? 5 : nt <= 64 ? 4 : nt 
 constexpr int stages_for(int nt) { return nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 
 template <int EPI>
-static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Params& p, dim3 grid, cudaStream_t stream) {
     const bool deep = (long long)grid.x * grid.y * grid.z <= 148;
     switch (nt) {
-        case 16: return deep ? launch<16, deep_stages_for(16), EPI>(mw, mx, p, grid, stream) : launch<16, stages_for(16), EPI>(mw, mx, p, grid, stream);
-        case 32: return deep ? launch<32, deep_stages_for(32), EPI>(mw, mx, p, grid, stream) : launch<32, stages_for(32), EPI>(mw, mx, p, grid, stream);
-        case 64: return deep ? launch<64, deep_stages_for(64), EPI>(mw, mx, p, grid, stream) : launch<64, stages_for(64), EPI>(mw, mx, p, grid, stream);
-        case 128: return deep ? launch<128, deep_stages_for(128), EPI>(mw, mx, p, grid, stream) : launch<128, stages_for(128), EPI>(mw, mx, p, grid, stream);
-        case 256: return launch<256, stages_for(256), EPI>(mw, mx, p, grid, stream);
+        case 16: return deep ? launch<16, deep_stages_for(16), EPI>(mw, mx, mo, p, grid, stream) : launch<16, stages_for(16), EPI>(mw, mx, mo, p, grid, stream);
+        case 32: return deep ? launch<32, deep_stages_for(32), EPI>(mw, mx, mo, p, grid, stream) : launch<32, stages_for(32), EPI>(mw, mx, mo, p, grid, stream);
+        case 64: return deep ? launch<64, deep_stages_for(64), EPI>(mw, mx, mo, p, grid, stream) : launch<64, stages_for(64), EPI>(mw, mx, mo, p, grid, stream);
+        case 128: return deep ? launch<128, deep_stages_for(128), EPI>(mw, mx, mo, p, grid, stream) : launch<128, stages_for(128), EPI>(mw, mx, mo, p, grid, stream);
+        case 256: return launch<256, stages_for(256), EPI>(mw, mx, mo, p, grid, stream);
     }
     return -22;
 }
@@ -576,6 +600,17 @@ extern "C" int imparo_gemm_tc_plan(int T, int N, int K, int epilogue, int* token
     return 0;
 }
 
+// The split partials leave by a TMA store where the rows are 16 bytes wide and aligned (N a multiple of 4) and the
+// token tile is at most 64 (the staged tile must fit the idle stage ring); else by plain stores.
+static int partials_map(float* scratch, int T, int N, int splits, int nt, Params& p, CUtensorMap& mo) {
+    p.tma_out = 0;
+    if (N % 4 != 0 || (((uintptr_t)scratch) & 15) || nt > 64) return 0;
+    int rc = get_map_partials(scratch, (uint64_t)N, (uint64_t)T, (uint64_t)splits, (uint32_t)nt, &mo);
+    if (rc) return rc;
+    p.tma_out = 1;
+    return 0;
+}
+
 // x: [T, K] bfloat16 with row stride ldx (elements), inside a buffer of x_rows_alloc rows.
 // w: [N, K] bfloat16 dense (SwiGLU: [2N, K], gate rows then up rows).  out: [T, ldo].
 // scratch / counters: from imparo_gemm_tc_plan; counters must be zero (they are left zero).
@@ -600,14 +635,17 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
     const int row_tiles = epilogue == SWIGLU_BF16 ? (N + 63) / 64 : (N + BM - 1) / BM;
     dim3 grid(row_tiles, (T + nt - 1) / nt, splits);
     if (grid.y > 65535) return -2;
+    CUtensorMap mo = mw;                                                    // unused unless the partials leave by TMA
     switch (epilogue) {
-        case STORE_BF16: return launch_nt<STORE_BF16>(nt, mw, mx, p, grid, stream);
-        case STORE_F32: return launch_nt<STORE_F32>(nt, mw, mx, p, grid, stream);
-        case ADD_F32: return launch_nt<ADD_F32>(nt, mw, mx, p, grid, stream);
-        case SWIGLU_BF16: return launch_nt<SWIGLU_BF16>(nt, mw, mx, p, grid, stream);
+        case STORE_BF16: return launch_nt<STORE_BF16>(nt, mw, mx, mo, p, grid, stream);
+        case STORE_F32: return launch_nt<STORE_F32>(nt, mw, mx, mo, p, grid, stream);
+        case ADD_F32: return launch_nt<ADD_F32>(nt, mw, mx, mo, p, grid, stream);
+        case SWIGLU_BF16: return launch_nt<SWIGLU_BF16>(nt, mw, mx, mo, p, grid, stream);
         case PARTIAL_F32:
             if (!scratch) return -24;
-            return launch_nt<PARTIAL_F32>(nt, mw, mx, p, grid, stream);
+            rc = partials_map(scratch, T, N, splits, nt, p, mo);
+            if (rc) return rc;
+            return launch_nt<PARTIAL_F32>(nt, mw, mx, mo, p, grid, stream);
     }
     return -22;
 }
@@ -617,10 +655,10 @@ extern "C" int imparo_gemm_tc(const void* x, int ldx, int x_rows_alloc, const vo
 // It takes out (32-bit stream, [T, N]) and either adds into it (epilogue 2) or leaves split partials in
 // scratch (epilogue 4, scratch from imparo_gemm_tc_plan with that epilogue): the two forms the mixers' output
 // products use.  T at most 16.  Returns -25 when it does not take the case.
-static int launch_produced(int nt, int epilogue, const CUtensorMap& mw, const Params& p, dim3 grid, cudaStream_t stream) {
+static int launch_produced(int nt, int epilogue, const CUtensorMap& mw, const CUtensorMap& mo, const Params& p, dim3 grid, cudaStream_t stream) {
 #define IMPARO_PRODUCED(NT_, ST_) \
-    if (epilogue == PARTIAL_F32) return launch<NT_, ST_, PARTIAL_F32, PROD_COMBINE>(mw, mw, p, grid, stream); \
-    return launch<NT_, ST_, ADD_F32, PROD_COMBINE>(mw, mw, p, grid, stream)
+    if (epilogue == PARTIAL_F32) return launch<NT_, ST_, PARTIAL_F32, PROD_COMBINE>(mw, mw, mo, p, grid, stream); \
+    return launch<NT_, ST_, ADD_F32, PROD_COMBINE>(mw, mw, mo, p, grid, stream)
     // up to 16 tokens: with more, the eight producer warps walk several items each, one round trip after the other,
     // and the kernels apart are faster
     if (nt == 16) { IMPARO_PRODUCED(16, 6); }
@@ -662,5 +700,10 @@ extern "C" int imparo_gemm_tc_combine(const float* part_acc, const float* part_m
     int rc = produced_common(w, out, ldo, T, N, K, epilogue, scratch, status, p, mw, nt, grid);
     if (rc) return rc;
     p.cb_acc = part_acc; p.cb_ml = part_ml; p.cb_splits = n_splits; p.cb_hd = hd; p.cb_heads = heads;
-    return launch_produced(nt, epilogue, mw, p, grid, stream);
+    CUtensorMap mo = mw;
+    if (epilogue == PARTIAL_F32) {
+        rc = partials_map(scratch, T, N, p.splits, nt, p, mo);
+        if (rc) return rc;
+    }
+    return launch_produced(nt, epilogue, mw, mo, p, grid, stream);
 }

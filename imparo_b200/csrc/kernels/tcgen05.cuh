@@ -39,6 +39,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// A tile of shared memory ([z][y][x], dense) written to a 3-D tensor by the TMA engine.  Elements outside the
+// tensor are not written (tiles that hang over the last row or column need no masks).  The calling thread must
+// wait with tma_store_wait_read() before the shared memory is reused or the CTA exits; the writes themselves are
+// complete, like any other of the kernel's, when the grid is.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups
 // are 1024 bytes apart (SBO); the leading-dimension offset is unused for this layout.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -139,6 +150,34 @@ static inline int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_
     return 0;
 }
 
+// A 3-D map over split partials [splits][T][N] in 32-bit, no swizzle, for stores of boxes [1][box_t][128] (x = the
+// row of W, the innermost dimension).  N must be a multiple of 4 (16-byte rows) and ptr 16-byte aligned.
+static inline int get_map_partials(const void* ptr, uint64_t N, uint64_t T, uint64_t splits, uint32_t box_t, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -20;
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    const MapKey key{ptr, T, N, splits, box_t | 0x80000000u};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+    if (g_maps.size() > 4096) g_maps.clear();
+    CUtensorMap m;
+    const cuuint64_t dims[3] = {N, T, splits};
+    const cuuint64_t strides[2] = {N * 4, T * N * 4};
+    const cuuint32_t box[3] = {128, box_t, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -21;
+    g_maps.emplace(key, m);
+    *out = m;
+    return 0;
+}
 
 }  // namespace tc
 }  // namespace imparo

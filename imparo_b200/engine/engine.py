@@ -10,7 +10,6 @@ once), the request fields max_tokens and temperature (imparo-server/src/main.rs:
 """
 from __future__ import annotations
 
-import os
 import sys
 
 import time
@@ -18,7 +17,7 @@ from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 
-from ..cache import CacheFull, CacheManager
+from ..cache import CacheManager
 from ..config.engine import EngineConfig
 from ..config.registry import load_config
 from ..kernels import lib as _lib

@@ -10,8 +10,8 @@ state (lib.rs:1141-1145); the cache advances only after the step succeeded
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -295,8 +295,6 @@ def _tc_buffers(device, floats: int, counters: int):
     return buf
 
 
-
-
 # Above this many tokens the library product is faster than the hand-written kernel as it
 # stands (one token tile per CTA, no overlap of epilogue and main loop).  Measured on B200, whole
 # decode steps of LFM2-1.2B shapes in their CUDA graph, ms per step (own kernel / library product):
@@ -496,8 +494,6 @@ class PartialProduct:
                                                        _code(self._out), self.stride, _stream()), "fold_partials")
             self._done = True
         return self._out
-
-
 
 
 def unfolded_products() -> bool:
@@ -835,8 +831,6 @@ def take_sampled_tokens(token_ids: torch.Tensor, src: torch.Tensor, prev: torch.
           "take_sampled_tokens: int32 ids, one source index per token")
     _check(_lib.kernels().imparo_take_sampled_tokens(_ptr(token_ids), _ptr(src), _ptr(prev), n, prev.numel(), _stream()),
            "take_sampled_tokens")
-
-
 
 
 def sample_rows(logits, temperature, uniform, out) -> None:
