@@ -82,6 +82,7 @@ class EngineConfig:
     num_pages: Optional[int] = None       # --num-pages / IMPARO_NUM_PAGES: pages per pool (default: parallel * ctx worth)
     max_step_tokens: int = 2048           # --max-step-tokens / IMPARO_MAX_STEP_TOKENS (the reference's IMPARO_BATCH)
     use_graphs: bool = True               # IMPARO_USE_GRAPHS: replay captured steps
+    capture_first: bool = True            # IMPARO_CAPTURE_FIRST: capture a step's graph the first time its shape comes
     pad_rows: bool = True                 # IMPARO_PAD_ROWS: one-token rows of a step filled up to 1, 2, 4, 8, 16, 24, ... rows
     probe_layer: Optional[int] = None     # --probe-layer / IMPARO_PROBE_LAYER
     log: bool = False                     # IMPARO_LOG: one line per generation step on stderr

@@ -39,7 +39,8 @@ class Engine:
                  parallel: Optional[int] = None, page_size: Optional[int] = None, num_pages: Optional[int] = None,
                  max_step_tokens: Optional[int] = None, random_init: Optional[dict] = None,
                  probe_layer: Optional[int] = None, probe=None, switches: Optional[dict] = None,
-                 config_file: Optional[str] = None, engine_config: Optional[EngineConfig] = None):
+                 config_file: Optional[str] = None, engine_config: Optional[EngineConfig] = None,
+                 use_graphs: Optional[bool] = None, pad_rows: Optional[bool] = None, capture_first: Optional[bool] = None):
         """model: a folder with config.json and model.safetensors.  Or config (a config.json
         dictionary) with seed: random weights drawn on the device (random_init may give
         matrix_std, conv_std, norm_jitter).
@@ -50,6 +51,8 @@ class Engine:
         pass a resolved engine_config.  dtype: "bfloat16" | "float32".  ctx: the most positions one request may
         reach.  parallel: the most requests live at once.  num_pages: pages in each pool (default: enough for
         parallel requests of ctx positions).  switches: kernel-path switches by name (KernelSwitches).
+        use_graphs: replay captured steps; capture_first: capture a shape the first time it comes; pad_rows: fill
+        the one-token rows of a step up to few sizes (StepFunction).
         probe_layer: a schedule entry whose block shows its stages (stream in, mixer norm, stream after the mixer,
         feed-forward norm, stream out) to probe(name, tensor); the default probe prints rms, sum and the first
         five values of each to stderr, as the reference's stage probes do (imparo-model/src/cpu_support.rs:26-46).
@@ -58,7 +61,8 @@ class Engine:
             engine_config = EngineConfig.resolve(
                 flags={"dtype": dtype, "device": None if device is None else str(device), "ctx": ctx, "parallel": parallel,
                        "page_size": page_size, "num_pages": num_pages, "max_step_tokens": max_step_tokens,
-                       "probe_layer": probe_layer, "switches": switches}, file=config_file)
+                       "probe_layer": probe_layer, "switches": switches, "use_graphs": use_graphs, "pad_rows": pad_rows,
+                       "capture_first": capture_first}, file=config_file)
         self.engine_config = cfg = engine_config
         if cfg.dtype not in _PRECISIONS:
             raise ValueError(f"dtype must be one of {sorted(_PRECISIONS)}")
@@ -96,7 +100,7 @@ class Engine:
                                   kv_dtype=self.rt.act_dtype, device=self.device)
         self.max_step_tokens = int(max_step_tokens)
         self.step_fn = StepFunction(self.model, self.cache, self.max_step_tokens, self.parallel, use_graphs=cfg.use_graphs,
-                                    pad_rows=cfg.pad_rows)
+                                    pad_rows=cfg.pad_rows, capture_first=cfg.capture_first)
         if probe_layer is not None:
             if not 0 <= int(probe_layer) < len(self.model.schedule):
                 raise ValueError(f"probe_layer {probe_layer} is not one of the model's {len(self.model.schedule)} schedule entries")
@@ -106,6 +110,11 @@ class Engine:
         # what the largest step holds, for buffers that are then made once (a moved buffer voids the captured graphs)
         rows = padded_rows(self.parallel) + 2 if cfg.pad_rows else self.parallel + 2
         self.rt.workspace.expect(tokens=min(self.max_step_tokens + rows, 8192), rows=min(rows, 512), context=self.ctx)
+        previous = ops.use_state(self.rt.launch_state)
+        try:
+            ops.prepare(self.device, rows=rows)         # nothing is left to be made at a first use, i.e. under capture
+        finally:
+            ops.use_state(previous)
         self.step_fn.reserve(min(self.max_step_tokens + rows, 8192), min(rows, 512), -(-self.ctx // self.page_size))
         self.sampler = Sampler(self.device, max_rows=max(rows, 8))
         self.vocab_size = self.model.spec.vocab_size

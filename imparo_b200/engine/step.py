@@ -54,9 +54,13 @@ def _table_width(longest: int) -> int:
 
 class StepFunction:
     def __init__(self, model: Model, cache: CacheManager, max_step_tokens: int, max_items: int,
-                 use_graphs: bool = True, pad_rows: bool = False):
-        """pad_rows: fill the one-token rows of a step up to padded_rows() with rows of no request (build_batch)."""
+                 use_graphs: bool = True, pad_rows: bool = False, capture_first: bool = False):
+        """pad_rows: fill the one-token rows of a step up to padded_rows() with rows of no request (build_batch).
+        capture_first: capture a step's graph the first time its shape comes (_forward_graphed)."""
         self.pad_rows = bool(pad_rows)
+        self.capture_first = bool(capture_first)
+        self.capture_failures = 0
+        self.last_capture_error = None      # why the last dropped recording was dropped
         self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", False)
         self.last_h2d_bytes = 0
         self._graphs = {}        # key -> [times seen, graph, logits, (own, library) launches, generation], in order of use
@@ -255,11 +259,16 @@ class StepFunction:
         """A step has the same launches whenever (tokens, requests, wanted rows, table widths,
         the longest portion) repeat; which request brings how many tokens, every position, table
         and wanted row is index data that the kernels read from the descriptor buffer, whose
-        address is fixed.  The second time such a step comes it is captured, from then on
-        replayed: steps of single tokens (the reference captures its one-token step the same way,
+        address is fixed.  Such a step is captured once, from then on replayed: steps of single
+        tokens (the reference captures its one-token step the same way,
         imparo-cuda/native/imparo_cuda.cu:7509-7660) and also portions of prompts beside them,
         which a scheduler with a fixed token budget produces again and again.  Issued launch by
-        launch from Python a step of the full-size model costs the host about 2.5 ms."""
+        launch from Python a step of the full-size model costs the host about 2.5 ms.
+
+        capture_first: a new shape is captured the first time it comes (buffers are made for the
+        engine's largest step beforehand, so nothing has to grow under capture); when something does
+        have to grow, or a launch cannot be captured, the capture is dropped, the step runs launch by
+        launch (which sizes what was missing) and the shape is captured the next time."""
         ws = self.rt.workspace
         generation = (ws.generation, ops.generation())
         key = batch.host["key"]
@@ -271,39 +280,67 @@ class StepFunction:
         if entry is None:
             if len(self._graphs) >= self.max_graphs:
                 self._graphs.pop(next(iter(self._graphs)))          # the shape used longest ago
-            self._graphs[key] = [1, None, None, None, generation]
-            return self._forward(batch)
-        self._graphs[key] = self._graphs.pop(key)                   # most recently used: to the end
-        if entry[1] is None:
-            before = dict(ops.COUNTS)
-            g = torch.cuda.CUDAGraph()
-            # Captured on a stream of its own, without torch.cuda.graph(): that helper first waits
-            # for the device and empties the allocators' caches, which a serving loop that meets a
-            # new shape every few steps cannot afford.  Nothing is allocated under capture (the
-            # first, uncaptured run of the shape sized every buffer).
-            if self._capture_stream is None:
-                self._capture_stream = torch.cuda.Stream(device=self.device)
-            self._capture_stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(self._capture_stream):
-                g.capture_begin()
-                try:
-                    logits = self._forward(batch)
-                finally:
-                    g.capture_end()
-            entry[1], entry[2] = g, logits
-            entry[3] = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
-            ops.COUNTS.update(before)          # capture launched nothing
-            self.graph_captures += 1
-            if entry[4] != (ws.generation, ops.generation()):      # a buffer moved during the capture run
-                self._graphs.clear()
-                self.graph_resets += 1
+            entry = self._graphs[key] = [1, None, None, None, generation]
+            if not self.capture_first or not self._capture(entry, batch, tolerant=True):
                 return self._forward(batch)
+        else:
+            self._graphs[key] = self._graphs.pop(key)               # most recently used: to the end
+            if entry[1] is None:
+                self._capture(entry, batch, tolerant=False)
+                if entry[4] != (ws.generation, ops.generation()):      # a buffer moved during the capture run
+                    self._graphs.clear()
+                    self.graph_resets += 1
+                    return self._forward(batch)
         entry[0] += 1
         entry[1].replay()
         ops.COUNTS["own"] += entry[3][0]
         ops.COUNTS["library"] += entry[3][1]
         self.graph_replays += 1
         return entry[2]
+
+    def _capture(self, entry, batch: StepBatch, tolerant: bool) -> bool:
+        """Record the step's launches into entry's graph.  tolerant: a failure while recording (a buffer that
+        would have to grow, a launch that cannot be captured) drops the recording and returns False instead of
+        raising; the entry stays without a graph."""
+        before = dict(ops.COUNTS)
+        g = torch.cuda.CUDAGraph()
+        # Captured on a stream of its own, without torch.cuda.graph(): that helper first waits
+        # for the device and empties the allocators' caches, which a serving loop that meets a
+        # new shape every few steps cannot afford.  Nothing is allocated under capture.
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+        self._capture_stream.wait_stream(torch.cuda.current_stream())
+        logits, failed = None, None
+        with torch.cuda.stream(self._capture_stream):
+            # "relaxed": calls that the stricter modes refuse while a stream is being captured (an occupancy query in a
+            # launcher's plan; the destruction of another engine's graphs when Python collects them at this moment)
+            # neither fail nor void this recording; none of them touches the capturing stream
+            g.capture_begin(capture_error_mode="relaxed")
+            try:
+                logits = self._forward(batch)
+            except Exception as e:                                   # noqa: BLE001 - re-raised unless tolerant
+                failed = e
+            finally:
+                try:
+                    g.capture_end()
+                except Exception as e:                               # noqa: BLE001
+                    failed = failed or e
+        launched = (ops.COUNTS["own"] - before["own"], ops.COUNTS["library"] - before["library"])
+        ops.COUNTS.update(before)          # capture launched nothing
+        if failed is not None:
+            self.capture_failures += 1
+            self.last_capture_error = repr(failed)
+            try:
+                torch.cuda.cudart().cudaGetLastError()       # a refused call under capture leaves its code behind
+            except Exception:                                # noqa: BLE001
+                pass
+            if tolerant:
+                return False
+            raise failed
+        entry[1], entry[2] = g, logits
+        entry[3] = launched
+        self.graph_captures += 1
+        return True
 
     # -- one step ---------------------------------------------------------------------------
     def check_items(self, items: Sequence[StepItem]) -> None:

@@ -100,6 +100,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gather_rows_f32", [P, P, P, I, I, S])
     _declare(lib, "imparo_argmax_rows", [P, P, P, P, I, I, I, S])
     _declare(lib, "imparo_sample_rows", [P, P, P, P, I, I, I, S])
+    _declare(lib, "imparo_gemm_tc_configure", [])
     _declare(lib, "imparo_sample_rows_parts", [P, P, P, P, P, P, I, I, I, S])
     _declare(lib, "imparo_take_sampled_tokens", [P, P, P, I, I, S])
     _declare(lib, "imparo_selftest_wait_limit", [P, I, P, S])

@@ -110,6 +110,14 @@ def generation() -> int:
     return _S.generation
 
 
+def _cuda_error_text(rc: int) -> str:
+    try:
+        rt = torch.cuda.cudart()
+        return rt.cudaGetErrorString(rt.cudaError(rc))
+    except Exception:                    # noqa: BLE001 - the text is a courtesy
+        return ""
+
+
 def _check(rc: int, what: str, kind: str = "own") -> None:
     if rc == 0:
         COUNTS[kind] += 1
@@ -126,7 +134,7 @@ def _check(rc: int, what: str, kind: str = "own") -> None:
         raise KernelError(f"{what}: refused: {reasons.get(rc, rc)}")
     if rc >= 1000:
         raise KernelError(f"{what}: cuBLAS status {rc - 1000}")
-    raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.cudart().cudaGetErrorString(rc) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+    raise KernelError(f"{what}: CUDA error {rc} ({_cuda_error_text(rc)})")
 
 
 # --------------------------------------------------------------------------------------
@@ -179,6 +187,36 @@ def _grown(floats: int, old) -> int:
     serving loop meets slightly larger steps for a long while."""
     had = old.numel() if old is not None else 0
     return max(floats, 1 << 20, 2 * had if had <= (32 << 20) else 0)
+
+
+def prepare(device, rows: int = 8) -> None:
+    """Make, for the launch state that is current, what the launchers would otherwise make at their first use: the
+    library product's handle and workspace, the split partials' scratch and the samplers' scratch for `rows` rows.
+    A step recorded into a graph must not allocate, so an engine calls this before its first step."""
+    device = torch.device(device)
+    key = device.index or 0
+    _gemm_lib_ready(device)
+    global _tc_configured
+    if not _tc_configured:
+        # shared-memory attributes and the cluster plan's occupancy table (a query the runtime refuses under capture)
+        with torch.cuda.device(device):
+            _check(_lib.kernels().imparo_gemm_tc_configure(), "gemm_tc_configure")
+        COUNTS["own"] -= 1           # nothing was launched
+        _tc_configured = True
+    if key not in _S.partials:
+        _S.partials[key] = torch.empty(_grown(0, None), dtype=torch.float32, device=device)
+    if key not in _S.consumer_parts:
+        _S.consumer_parts[key] = torch.empty(_grown(0, None), dtype=torch.float32, device=device)
+    if key not in _S.tc_scratch:
+        _S.tc_scratch[key] = (torch.empty(1 << 20, dtype=torch.float32, device=device),
+                              torch.zeros(4096, dtype=torch.int32, device=device))
+    n = max(int(rows), 256)
+    if key not in _S.argmax_scratch:
+        _S.argmax_scratch[key] = (torch.empty(n * 32, dtype=torch.float32, device=device),
+                                  torch.empty(n * 32, dtype=torch.int32, device=device))
+    if key not in _S.sample_scratch:
+        _S.sample_scratch[key] = (torch.empty(n * 64, dtype=torch.float32, device=device),
+                                  torch.empty(n * 32, dtype=torch.int32, device=device))
 
 
 def defer_adds() -> bool:
@@ -245,11 +283,13 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
 
 
 _gemm_ws = {}
+_tc_configured = False
 
 
 def _gemm_lib_ready(device) -> None:
-    key = device.index or 0
+    key = torch.device(device).index or 0
     if key not in _gemm_ws:
+        _need(not torch.cuda.is_current_stream_capturing(), "the library product's first use would allocate during graph capture")
         ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
         _check(_lib.kernels().imparo_gemm_lib_init(_ptr(ws), ws.numel()), "gemm_lib_init")
         _gemm_ws[key] = ws

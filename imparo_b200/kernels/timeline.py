@@ -124,7 +124,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     from ..engine import Engine, StepItem
     from . import ops
     if args.model:
-        engine = Engine(model=args.model, dtype="bfloat16", ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
+        engine = Engine(model=args.model, dtype="bfloat16", capture_first=False, ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
                         parallel=max(args.batch, args.mixed + 1), max_step_tokens=max(args.prompt_len, args.context) + args.mixed)
     else:
         if not args.config:
@@ -135,7 +135,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args.layers:
             cfg["layer_types"] = cfg["layer_types"][:args.layers]
             cfg["num_hidden_layers"] = args.layers
-        engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
+        engine = Engine(config=cfg, seed=0, dtype="bfloat16", capture_first=False, ctx=max(args.prompt_len, args.context if args.mixed else 0) + 64,
                         parallel=max(args.batch, args.mixed + 1), max_step_tokens=max(args.prompt_len, args.context) + args.mixed,
                         random_init={"norm_jitter": 0.0})
     tl = Timeline()

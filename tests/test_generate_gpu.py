@@ -261,3 +261,40 @@ def test_padding_rows_change_the_shape_not_the_results(dtype, tol):
     for got in (outs[0], outs[2]):
         assert np.abs(got.numpy() - want).max() <= tol * scale
     assert np.abs(outs[1].numpy() - outs[3].numpy()).max() <= tol * scale
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2.5e-2)])
+def test_a_new_shape_is_captured_at_first_sight_or_falls_back(dtype, tol):
+    """With buffers made for the largest step a new shape is captured the first time it comes and replayed from then
+    on.  When a buffer does have to grow under capture the recording is dropped, the step runs launch by launch, and
+    the shape is captured the next time.  The logits are those of the plain implementation either way."""
+    from imparo_b200.engine import Engine, StepItem
+    prompt = make_requests("B", [24], seed=5)["r0"]
+    want = plain_model("B").logits(prompt)
+    scale = float(np.abs(want).max())
+    for reserve in (True, False):
+        eng = Engine(model_dir("B"), dtype=dtype, ctx=64, parallel=2, page_size=4, num_pages=40, capture_first=True)
+        sf = eng.step_fn
+        if not sf.use_graphs:
+            pytest.skip("this model's steps are not captured")
+        if not reserve:
+            eng.rt.workspace.most = {"tokens": 0, "rows": 0, "context": 0}      # as if nothing were known beforehand
+        eng.add_request(1)
+        # the engine's very first step also makes the launchers' scratch, which cannot happen under capture: its
+        # recording may be dropped; from then on only a buffer that is too small can do that
+        got = [eng.step([StepItem(1, prompt[:12], [11])])[0].float().cpu().numpy()]
+        first_failures = sf.capture_failures
+        got.append(eng.step([StepItem(1, prompt[12:20], [7])])[0].float().cpu().numpy())      # a new shape
+        if reserve:
+            assert sf.capture_failures == first_failures, sf.last_capture_error
+            assert sf.graph_captures >= 1 and sf.graph_replays >= 1
+        for i in range(20, 24):                                                 # four steps of one more shape
+            got.append(eng.step([StepItem(1, [prompt[i]], [0])])[0].float().cpu().numpy())
+        if reserve:
+            assert sf.capture_failures == first_failures, sf.last_capture_error
+        assert sf.graph_replays >= 3
+        eng.check_device_status()
+        for g, pos in zip(got, (11, 19, 20, 21, 22, 23)):
+            assert np.abs(g - want[pos]).max() <= tol * scale
+        eng.end_request(1)
+        eng.cache.check()
