@@ -428,19 +428,28 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a
 // the softmax runs.  Here a CTA owns TWO query tiles of 128 rows (consecutive tokens of one request, the same kv
 // head) and ONE stream of keys and values that both use:
 //
-//   warp 0      TMA: keys and values page by page into a ring of three stages
-//   warp 1      tcgen05.mma for both tiles: S_x = Q_x K^T into the tile's 128 score columns of tensor memory, and
-//               O_x += P_x V accumulated IN tensor memory; while one tile's softmax runs, the other tile's products do
+//   warp 0      TMA: keys and values page by page into rings of three buffers each (lane p fetches page p of a step;
+//               keys and values have barriers of their own, since a step's keys are read long before its values)
+//   warp 1, 18  tcgen05.mma, one issuing thread per tile: S_x = Q_x K^T into the tile's 128 score columns of tensor
+//               memory, issued for the NEXT step as soon as the softmax has read the current scores, and
+//               O_x += P_x V accumulated IN tensor memory, issued when the step's probabilities are written
 //   warps 2-9   softmax of tile A, warps 10-17 of tile B: two threads per row, one for each half of the step's keys
 //               and of the head's dims.  A thread's 64 scores of the step go to registers in one sweep (the score
 //               columns are free for the next step's product at once), the two threads of a row agree on the row's
 //               max through shared memory, P = exp2(s - max) goes to shared memory as bfloat16 in the MMA's layout.
+// The two tiles take turns at the exponential pass (a barrier each way): the exp2 units are what both softmaxes need
+// at full rate, and with the passes apart one tile's products, loads and max run under the other tile's pass.
+// What the device's clock showed while this was shaped (stamps per phase in one CTA, a temporary build): one thread
+// issuing for both tiles was busy the whole step (an instruction of this size keeps its thread 70-120 cycles, 24 per
+// step of both tiles), one thread walking a step's pages paid eight dependent table reads in a row, and two exp passes
+// at once took 2,500 cycles each where one alone takes 1,400.
 // The output stays in tensor memory across steps.  When a row's max grows, what has been accumulated must be scaled
 // down; that costs a round trip of the row's output through registers, so it is done only when the max has grown by
 // more than 8 (in log2 units: a factor of 256) in some row of the warp; otherwise the old max stays in use, the
 // exponentials are at most 256, and the final division by the row's sum (taken with the same max) gives the same
 // result.  Formulas and masks as above.
-constexpr int PP_THREADS = 576;     // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: softmax of tile A, 10-17: of tile B
+constexpr int PP_THREADS = 608;     // warp 0: TMA, warp 1: tile A's products + tensor memory, warps 2-9: softmax of tile A, 10-17: of tile B, 18: tile B's products
+constexpr int PP_MMA_B_WARP = 18;
 constexpr int PP_STAGES = 3;
 constexpr float PP_GROW = 8.0f;
 
@@ -476,6 +485,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 __global__ void __launch_bounds__(PP_THREADS, 1)
 attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a) {
+
     constexpr int HD = 64;
     constexpr uint32_t Q_BYTES = REGION, P_BYTES = 2 * REGION, STAGE_BYTES = 2 * REGION;      // per tile; per stage K | V
     constexpr uint32_t TMEM_COLS = 512;                      // scores of A, of B: 0..127, 128..255; outputs: 256.., 320..
@@ -485,16 +495,25 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint8_t* p_s = q_s + 2 * Q_BYTES;                        // [2][P_BYTES]
     uint8_t* kv_s = p_s + 2 * P_BYTES;                       // [stage][K | V]
     uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + PP_STAGES * STAGE_BYTES);
-    uint64_t* kv_full = bars;                                // [PP_STAGES]
-    uint64_t* kv_empty = kv_full + PP_STAGES;                // [PP_STAGES]
-    uint64_t* q_ready = kv_empty + PP_STAGES;
+    // Keys and values of a step have barriers of their own: a step's keys are read last by the score products, which
+    // are issued a whole softmax before the step's P V products, so their buffer is free that much earlier
+    uint64_t* k_full = bars;                                 // [PP_STAGES]
+    uint64_t* k_empty = k_full + PP_STAGES;                  // [PP_STAGES]
+    uint64_t* q_ready = k_empty + PP_STAGES;
     uint64_t* s_ready = q_ready + 1;                         // [2]  the tile's scores of a step are complete
     uint64_t* s_free = s_ready + 2;                          // [2]  ... and have been read into registers
     uint64_t* p_ready = s_free + 2;                          // [2]  P of the step is in shared memory, the output scaled
     uint64_t* o_done = p_ready + 2;                          // [2]  P V of the step is accumulated
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+    uint64_t* v_full = o_done + 2;                           // [PP_STAGES]
+    uint64_t* v_empty = v_full + PP_STAGES;                  // [PP_STAGES]
+    // The two tiles take turns at the exponential: the SM's exp2 units are the one resource both softmaxes need at
+    // full rate, and when both tiles' passes coincide each takes twice as long while the units idle for the rest of
+    // the step.  turn[x] completes when the OTHER tile has finished a pass and tile x may start its next one.
+    uint64_t* turn = v_empty + PP_STAGES;                    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(bars) + 64;        // [tile][buffer][half][row]: what the two threads of a row exchange
+    static_assert((4 * PP_STAGES + 11) * 8 + 8 <= 256, "barriers overlap the exchange buffer");
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -528,8 +547,13 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int pos_last = n_tokB > 0 ? pos_lastB : pos_lastA;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PP_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < PP_STAGES; ++s) {
+            // a buffer is free when every tile that exists has read it
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], nB > 0 ? 2 : 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], nB > 0 ? 2 : 1);
+        }
         mbar_init(q_ready, 512);
+        mbar_init(&turn[0], 256); mbar_init(&turn[1], 256);
         for (int x = 0; x < 2; ++x) { mbar_init(&s_ready[x], 1); mbar_init(&s_free[x], 256); mbar_init(&p_ready[x], 256); mbar_init(&o_done[x], 1); }
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -544,97 +568,131 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            pdl_wait();                                      // this step's keys were written by the kernel before
-            const int pages_per_step = KEYS / a.page_size;
-            const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
-            for (int i = 0; i < n_steps && !*gave_up; ++i) {
-                const int s = i % PP_STAGES;
-                if (i >= PP_STAGES && !mbar_wait(&kv_empty[s], ((i / PP_STAGES) - 1) & 1)) {
-                    report(a.status, IMPARO_ST_WAIT_LIMIT, 40, i, s);
-                    *gave_up = 1;
-                    break;
+        // The whole warp fetches: lane 0 looks at the barriers and sets the byte count, then lane p looks up page p of
+        // the step in the block table and issues that page's copy.  (One thread walking the pages paid a dependent
+        // table read per page, eight in a row for pages of 16: about as long as a whole step of the softmax.)
+        pdl_wait();                                          // this step's keys were written by the kernel before
+        const int pages_per_step = KEYS / a.page_size;
+        const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
+        auto load = [&](int i, bool values) {                // warp-uniform call
+            const int s = i % PP_STAGES;
+            uint8_t* dst = kv_s + s * STAGE_BYTES + (values ? REGION : 0);
+            uint64_t* bar = values ? &v_full[s] : &k_full[s];
+            if (lane == 0) mbar_expect_tx(bar, REGION);
+            __syncwarp();
+            const int blk0 = (kb_first + i) * pages_per_step;
+            for (int pg = lane; pg < pages_per_step; pg += 32) {
+                const int blk = min(max(blk0 + pg, first_blk), last_blk);       // (see the kernel above)
+                int page = blk < a.max_blocks ? tab[blk] : -1;
+                if (page < 0 || page >= a.n_pages) {
+                    report(a.status, IMPARO_ST_PAGE_RANGE, 41, item, page);
+                    page = 0;
                 }
-                uint8_t* kdst = kv_s + s * STAGE_BYTES;
-                uint8_t* vdst = kdst + REGION;
-                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
-                const int blk0 = (kb_first + i) * pages_per_step;
-                for (int pg = 0; pg < pages_per_step; ++pg) {
-                    const int blk = min(max(blk0 + pg, first_blk), last_blk);       // (see the kernel above)
-                    int page = blk < a.max_blocks ? tab[blk] : -1;
-                    if (page < 0 || page >= a.n_pages) {
-                        report(a.status, IMPARO_ST_PAGE_RANGE, 41, item, page);
-                        page = 0;
-                    }
-                    const int y = page * a.page_size;
-                    const uint32_t off = (uint32_t)pg * a.page_size * 128;
-                    tma_load_2d(kdst + off, &map_k, &kv_full[s], kvh * HD, y);
-                    tma_load_2d(vdst + off, &map_v, &kv_full[s], kvh * HD, y);
+                tma_load_2d(dst + (uint32_t)pg * a.page_size * 128, values ? &map_v : &map_k, bar, kvh * HD, page * a.page_size);
+            }
+        };
+        // keys and values are fetched as their buffers come free, whichever first
+        int k_next = 0, v_next = 0;
+        uint32_t idle = 0;
+        while (k_next < n_steps || v_next < n_steps) {
+            int what = 0;                                    // bit 0: the next keys' buffer is free, bit 1: the next values', bit 2: stop
+            if (lane == 0) {
+                if (k_next < n_steps && (k_next < PP_STAGES || mbar_test(&k_empty[k_next % PP_STAGES], ((k_next / PP_STAGES) - 1) & 1))) what |= 1;
+                if (v_next < n_steps && (v_next < PP_STAGES || mbar_test(&v_empty[v_next % PP_STAGES], ((v_next / PP_STAGES) - 1) & 1))) what |= 2;
+                if (*gave_up) what = 4;
+                if (what == 0 && ++idle > WAIT_LIMIT / 16) {
+                    report(a.status, IMPARO_ST_WAIT_LIMIT, 40, k_next, v_next);
+                    *gave_up = 1;
+                    what = 4;
                 }
             }
+            what = __shfl_sync(0xffffffffu, what, 0);
+            if (what & 4) break;
+            if (what & 1) load(k_next++, false);
+            if (what & 2) load(v_next++, true);
+            if (what != 0) idle = 0; else __nanosleep(200);      // (not urgent: a buffer is free a period or more before it is needed)
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
+    } else if (warp == 1 || warp == PP_MMA_B_WARP) {
+        // One issuing thread per tile (warp 1: tile A, the last warp: tile B).  A tensor-core instruction of this size
+        // (128 x 128 x 16 for the scores, 128 x 64 x 16 for P V) keeps its issuing thread for 70 to 90 cycles, 24 of them
+        // per step of both tiles: one thread serving both tiles was busy the whole step and every product came late.
+        // A tile's thread issues the tile's NEXT scores as soon as the softmax has read the current ones (s_free), a
+        // whole softmax before they are needed, and the tile's P V product when its probabilities are written
+        // (p_ready); the waits block (a thread that polls takes issue slots from the softmax warps of its scheduler).
+        // A step's keys are free when both tiles' score products are issued, its values when both P V products are:
+        // each thread commits to those barriers after its own product (they count the tiles).
+        const int x = warp == 1 ? 0 : 1;
+        const int n_x = x == 0 ? nA : nB;
+        if (lane == 0 && (n_x > 0 || x == 0)) {
             const uint32_t idesc_s = instr_desc_ab(ROWS, KEYS, false);
             const uint32_t idesc_o = instr_desc_ab(ROWS, HD, true);
             bool ok = mbar_wait(q_ready, 0);
-            if (!ok) { report(a.status, IMPARO_ST_WAIT_LIMIT, 42, 0, 0); *gave_up = 1; }
+            if (!ok) { report(a.status, IMPARO_ST_WAIT_LIMIT, 42, x, 0); *gave_up = 1; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            int kv_seen = -1;                                // steps whose keys and values have landed
-            auto need_kv = [&](int j) -> bool {
-                while (kv_seen < j) {
-                    const int i = kv_seen + 1;
-                    if (!mbar_wait(&kv_full[i % PP_STAGES], (i / PP_STAGES) & 1)) {
-                        report(a.status, IMPARO_ST_WAIT_LIMIT, 43, i, 0);
-                        *gave_up = 1;
-                        return false;
-                    }
-                    kv_seen = i;
+            int k_seen = -1, v_seen = -1;                    // steps whose keys / values have landed
+            auto wait_or_give_up = [&](uint64_t* bar, uint32_t parity, int code, int j) -> bool {
+                if (mbar_wait(bar, parity)) { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); return true; }
+                report(a.status, IMPARO_ST_WAIT_LIMIT, code, j, x);
+                *gave_up = 1;
+                return false;
+            };
+            auto need_keys = [&](int j) -> bool {
+                while (k_seen < j) {
+                    const int i = k_seen + 1;
+                    if (!wait_or_give_up(&k_full[i % PP_STAGES], (i / PP_STAGES) & 1, 43, i)) return false;
+                    k_seen = i;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 return true;
             };
-            auto issue_s = [&](int x, int j) {               // S_x = Q_x K_j^T
-                const uint32_t qb = smem_u32(q_s + x * Q_BYTES), kb = smem_u32(kv_s + (j % PP_STAGES) * STAGE_BYTES);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma(tmem_base + x * 128, smem_desc(qb + k * 32), smem_desc(kb + k * 32), idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(&s_ready[x]);
-            };
-            auto issue_pv = [&](int x, int j) {              // O_x (+)= P_x V_j
-                const uint32_t vb = smem_u32(kv_s + (j % PP_STAGES) * STAGE_BYTES + REGION), pb = smem_u32(p_s + x * P_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < KEYS / UMMA_K; ++kk)
-                    umma(tmem_base + 256 + x * HD, smem_desc(pb + (kk >> 2) * REGION + (kk & 3) * 32),
-                         smem_desc_mn(vb + kk * (UMMA_K * 128), REGION), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&o_done[x]);
-            };
-            if (ok && need_kv(0)) {
-                if (nA > 0) issue_s(0, 0);
-                if (nB > 0) issue_s(1, 0);
-            } else {
-                ok = false;
-            }
-            // Tile B's positions lie behind tile A's, so B has every step A has (or B is empty): the last product
-            // that reads step j's keys and values is B's, or A's when there is no tile B.
-            const int last_x = nB > 0 ? 1 : 0;
-            for (int j = 0; j < n_steps && ok; ++j) {
-                for (int x = 0; x < 2 && ok; ++x) {
-                    const int n_x = x == 0 ? nA : nB;
-                    if (j < n_x) {
-                        if (!mbar_wait(&p_ready[x], j & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 44, j, x); *gave_up = 1; ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_pv(x, j);
-                    }
-                    if (x == last_x) umma_commit(&kv_empty[j % PP_STAGES]);      // the stage may be filled again
-                    if (j + 1 < n_x) {
-                        // the tile's next scores: while its softmax runs, the other tile's products follow
-                        if (!need_kv(j + 1)) { ok = false; break; }
-                        if (!mbar_wait(&s_free[x], j & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 45, j, x); *gave_up = 1; ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_s(x, j + 1);
-                    }
+            auto need_values = [&](int j) -> bool {
+                while (v_seen < j) {
+                    const int i = v_seen + 1;
+                    if (!wait_or_give_up(&v_full[i % PP_STAGES], (i / PP_STAGES) & 1, 49, i)) return false;
+                    v_seen = i;
                 }
+                return true;
+            };
+            // The descriptors of the buffers are made once; an operand at a byte offset inside a buffer is its
+            // descriptor plus offset / 16 (the address field is the low 14 bits and never carries: shared memory is
+            // smaller than that), with offsets the compiler knows.
+            const uint64_t qd = smem_desc(smem_u32(q_s + x * Q_BYTES)), dk0 = smem_desc(smem_u32(kv_s));
+            const uint64_t pd = smem_desc(smem_u32(p_s + x * P_BYTES)), dv0 = smem_desc_mn(smem_u32(kv_s + REGION), REGION);
+            const uint32_t t_s = tmem_base + x * 128, t_o = tmem_base + 256 + x * HD;
+            auto issue_s = [&](int j) {                      // S_x = Q_x K_j^T
+                const uint64_t kd = dk0 + (uint64_t)(((j % PP_STAGES) * STAGE_BYTES) >> 4);
+                umma(t_s, qd, kd, idesc_s, 0u);
+#pragma unroll
+                for (int k = 1; k < BK / UMMA_K; ++k) umma(t_s, qd + (uint64_t)((k * 32) >> 4), kd + (uint64_t)((k * 32) >> 4), idesc_s, 1u);
+                umma_commit(&s_ready[x]);
+                umma_commit(&k_empty[j % PP_STAGES]);        // this tile has read the step's keys when the product has run
+            };
+            auto issue_pv = [&](int j) {                     // O_x (+)= P_x V_j
+                const uint64_t vd = dv0 + (uint64_t)(((j % PP_STAGES) * STAGE_BYTES) >> 4);
+                umma(t_o, pd, vd, idesc_o, j > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 1; kk < KEYS / UMMA_K; ++kk)
+                    umma(t_o, pd + (uint64_t)(((kk >> 2) * REGION + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * (UMMA_K * 128)) >> 4), idesc_o, 1u);
+                umma_commit(&o_done[x]);
+                umma_commit(&v_empty[j % PP_STAGES]);
+            };
+            if (ok && n_x > 0 && need_keys(0)) issue_s(0); else ok = ok && n_x == 0;
+            for (int j = 0; j < n_x && ok; ++j) {
+                if (j + 1 < n_x) {
+                    ok = wait_or_give_up(&s_free[x], j & 1, 45, j) && need_keys(j + 1);
+                    if (!ok) break;
+                    issue_s(j + 1);
+                }
+                ok = wait_or_give_up(&p_ready[x], j & 1, 44, j) && need_values(j);
+                if (!ok) break;
+                issue_pv(j);
+            }
+            // Tile B may have one step more than tile A (its positions lie behind A's); A's thread then gives that
+            // step's keys and values free on its own behalf, having no product that reads them.
+            // (Only once that step's keys and values have landed: their buffers' earlier contents are then surely
+            // given free by both tiles, so this thread's two arrivals on a barrier cannot fall into one phase.)
+            if (ok && x == 0 && nB > nA && need_keys(nA) && need_values(nA)) {
+                umma_commit(&k_empty[nA % PP_STAGES]);
+                umma_commit(&v_empty[nA % PP_STAGES]);
             }
         }
     } else {
@@ -743,11 +801,14 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     tmem_wait_st();
                 }
             }
+            if (nB > 0 && (x == 1 || j > 0)) {
+                // tile A's pass of step j goes before tile B's, B's before A's of step j + 1
+                if (!mbar_wait(&turn[x], (x == 0 ? j - 1 : j) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 50, j, r); *gave_up = 1; }
+            }
             const float nbase = (m_new == -INFINITY) ? 0.f : -m_new;
             float sum4[2] = {0.f, 0.f};
-            if (whole) {
-#pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2)
+            auto exp_half = [&](const int q2) {             // keys 32 q2 .. 32 q2 + 31 of this thread's 64
+                if (whole) {
 #pragma unroll
                     for (int c8 = 0; c8 < 4; ++c8) {         // 8 keys = one 16-byte chunk of P
                         uint32_t w[4];
@@ -760,9 +821,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         }
                         *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-            } else {
-#pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2)
+                } else {
 #pragma unroll
                     for (int c8 = 0; c8 < 4; ++c8) {
                         uint32_t w[4];
@@ -776,13 +835,20 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         }
                         *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-            }
+                }
+            };
+            exp_half(0);
+            // the other tile may begin its pass when this one is half way through its own: one tile's pass alone keeps
+            // the exp2 units at about 70%, two whole passes at once take twice as long each
+            if (nB > 0) mbar_arrive(&turn[x ^ 1]);
+            exp_half(1);
             l_run = l_run * corr + (sum4[0] + sum4[1]);
             m_used = m_new;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&p_ready[x]);
         }
+        if (x == 0 && nB > nA) mbar_arrive(&turn[1]);        // tile B's one step more has no pass of A's to wait for
         if (ok && n_x > 0) {
             if (!mbar_wait(&o_done[x], (n_x - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 48, n_x, r); *gave_up = 1; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
