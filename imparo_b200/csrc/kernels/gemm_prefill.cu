@@ -152,6 +152,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc(TM, TN);
+            const uint64_t desc_a0 = smem_desc(smem_u32(smem)), desc_b0 = smem_desc(smem_u32(smem) + A_BYTES);
             int g = 0, it = 0;
             bool ok = true;
             for (int idx = blockIdx.x; idx < n_tiles_total && ok; idx += gridDim.x, ++it) {
@@ -170,12 +171,14 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + A_BYTES;
+                    // the stage's two descriptors are the ring's first ones plus the stage's offset / 16 (the address
+                    // field is the low 14 bits and never carries), a slice of 16 along K is 32 bytes further: the
+                    // issuing thread spends its cycles on the products, not on their operands' descriptors
+                    const uint64_t da = desc_a0 + (uint64_t)((s * STAGE_BYTES) >> 4), db = desc_b0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+                    umma(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma(d_tmem, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(b_addr + k * UMMA_K * 2), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 1; k < BK / UMMA_K; ++k)
+                        umma(d_tmem, da + (uint64_t)((k * UMMA_K * 2) >> 4), db + (uint64_t)((k * UMMA_K * 2) >> 4), idesc, 1u);
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[b]);
