@@ -340,6 +340,126 @@ qk_norm_rope_rows_vec_kernel(const __nv_bfloat16* __restrict__ qkv, const int* _
     }
 }
 
+// The same for heads of 64 or 128 with a WARP per token: a lane owns 8 consecutive dims of a head (16-byte loads and
+// stores), HD / 8 lanes make a head, so one load instruction of the warp fetches 4 (or 2) heads, and all of a token's heads
+// are in flight before the first is used.  The kernel above gives a token a block of eight warps: its chain of
+// dependent reads (position, table, the values) is paid per block with four to eight blocks on an SM, 20 us for 2,048
+// tokens of 48 heads; here 64 tokens are in flight per SM.  Rotation pairs (i, i + HD/2) lie HD/16 lanes apart.
+template <int HD>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_token_warp_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                               const int* __restrict__ item_of_token,
+                               const float* __restrict__ q_w, const float* __restrict__ k_w,
+                               const float* __restrict__ inv_freq, float eps,
+                               __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                               __nv_bfloat16* __restrict__ v_cache,
+                               const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                               int n_tok, int nh, int nkv, int* status) {
+    constexpr int LPH = HD / 8, HPL = 32 / LPH, CHUNK = 8, NF = HD / 64;      // lanes per head, heads per load, loads in flight, frequencies per lane
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= n_tok) return;
+    const int total = nh + 2 * nkv;
+    const int sub = lane % LPH, hsel = lane / LPH;           // which 8 dims of the head, which head of the load
+    const int pos = positions[t];
+    int page = 0;
+    size_t cache_row = 0;
+    if (nkv > 0) {
+        const int blk = pos / page_size;
+        page = blk < max_blocks ? table[(size_t)item_of_token[t] * max_blocks + blk] : -1;
+        if (page >= 0 && page < n_pages) cache_row = (size_t)page * page_size + (pos % page_size);
+    }
+    float wq[8], wk[8], sn[8], cs[8];
+    {
+        const float4* q4 = reinterpret_cast<const float4*>(q_w ? q_w + 8 * sub : nullptr);
+        const float4* k4 = reinterpret_cast<const float4*>((k_w && nkv > 0) ? k_w + 8 * sub : nullptr);
+        const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 a = q4 ? q4[0] : one, b = q4 ? q4[1] : one, c = k4 ? k4[0] : one, d = k4 ? k4[1] : one;
+        wq[0] = a.x; wq[1] = a.y; wq[2] = a.z; wq[3] = a.w; wq[4] = b.x; wq[5] = b.y; wq[6] = b.z; wq[7] = b.w;
+        wk[0] = c.x; wk[1] = c.y; wk[2] = c.z; wk[3] = c.w; wk[4] = d.x; wk[5] = d.y; wk[6] = d.z; wk[7] = d.w;
+    }
+    // the position's HD / 2 sines and cosines: NF per lane, then each lane fetches those of its 8 dims
+    {
+        float s_own[NF], c_own[NF];
+#pragma unroll
+        for (int f = 0; f < NF; ++f) {
+            s_own[f] = 0.f; c_own[f] = 1.f;
+            if (inv_freq) sincosf((float)pos * inv_freq[lane + 32 * f], &s_own[f], &c_own[f]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int i = (8 * sub + e) % (HD / 2);          // the pair's index
+            float sv = __shfl_sync(0xffffffffu, s_own[0], i & 31), cv = __shfl_sync(0xffffffffu, c_own[0], i & 31);
+            if (NF > 1) {
+                const float s1 = __shfl_sync(0xffffffffu, s_own[NF - 1], i & 31), c1 = __shfl_sync(0xffffffffu, c_own[NF - 1], i & 31);
+                if (i >= 32) { sv = s1; cv = c1; }
+            }
+            sn[e] = sv; cs[e] = cv;
+        }
+    }
+    pdl_wait();
+    if (nkv > 0 && (page < 0 || page >= n_pages) && lane == 0)
+        report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);     // the token's keys and values are skipped below, its queries written
+    const __nv_bfloat16* src = qkv + (size_t)t * total * HD + 8 * sub;
+    const bool upper = sub >= LPH / 2;
+    const int n_loads = (total + HPL - 1) / HPL;
+    for (int g0 = 0; g0 < n_loads; g0 += CHUNK) {
+        uint4 in[CHUNK];
+#pragma unroll
+        for (int u = 0; u < CHUNK; ++u) {
+            const int hh = (g0 + u) * HPL + hsel;
+            if (g0 + u < n_loads && hh < total) in[u] = *reinterpret_cast<const uint4*>(src + (size_t)hh * HD);
+        }
+#pragma unroll
+        for (int u = 0; u < CHUNK; ++u) {
+            const int hh = (g0 + u) * HPL + hsel;
+            const bool live = g0 + u < n_loads && hh < total;          // (the shuffles below are executed by every lane)
+            if (g0 + u >= n_loads) break;
+            const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+            float val[8];
+            {
+                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&in[u]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = live ? __bfloat1622float2(p2[e]) : make_float2(0.f, 0.f);
+                    val[2 * e] = f.x; val[2 * e + 1] = f.y;
+                }
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += val[e] * val[e];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const bool normed = (is_q && q_w) || (is_k && k_w);
+            const float scale = normed ? 1.0f / sqrtf(ss / (float)HD + eps) : 1.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float v = val[e];
+                if (is_q || is_k) v = v * scale * (is_q ? wq[e] : wk[e]);
+                const float other = __shfl_xor_sync(0xffffffffu, v, LPH / 2);
+                if ((is_q || is_k) && inv_freq)
+                    v = upper ? other * sn[e] + v * cs[e] : v * cs[e] - other * sn[e];
+                val[e] = v;
+            }
+            if (!live) continue;
+            __nv_bfloat16* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)t * nh + hh) * HD;
+            } else {
+                if (page < 0 || page >= n_pages) continue;
+                const int kvh = is_k ? hh - nh : hh - nh - nkv;
+                dst = (is_k ? k_cache : v_cache) + cache_row * ((size_t)nkv * HD) + (size_t)kvh * HD;
+            }
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(val[2 * e], val[2 * e + 1]);
+            *reinterpret_cast<uint4*>(dst + 8 * sub) = o;
+        }
+    }
+}
+
 // ---- general paged attention ---------------------------------------------------------
 template <typename T> struct Vec;
 template <> struct Vec<float> { using type = float4; static constexpr int N = 4; };
@@ -466,7 +586,13 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
 #define IMPARO_QKV(V_) launch(qk_norm_rope_rows_vec_kernel<V_>, dim3(n_tok), dim3(256), 0, stream, (const __nv_bfloat16*)qkv, positions, \
             item_of_token, q_w, k_w, inv_freq, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, \
             max_blocks, page_size, n_pages, nh, nkv, status)
-        if (hd == 64) IMPARO_QKV(2); else if (hd == 128) IMPARO_QKV(4); else IMPARO_QKV(8);
+#define IMPARO_QKW(HD_) launch(qk_norm_rope_token_warp_kernel<HD_>, dim3((n_tok + 3) / 4), dim3(128), 0, stream, (const __nv_bfloat16*)qkv, \
+            positions, item_of_token, q_w, k_w, inv_freq, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, \
+            max_blocks, page_size, n_pages, n_tok, nh, nkv, status)
+        const bool w_ok = (((uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0;                  // the norm weights are read 16 bytes at a time
+        if (hd == 64 && w_ok) IMPARO_QKW(64); else if (hd == 128 && w_ok) IMPARO_QKW(128);
+        else if (hd == 64) IMPARO_QKV(2); else if (hd == 128) IMPARO_QKV(4); else IMPARO_QKV(8);
+#undef IMPARO_QKW
 #undef IMPARO_QKV
         IMPARO_CHECK_LAUNCH();
         return 0;

@@ -949,3 +949,49 @@ def test_decode_attention_from_the_qkv_partials(nh, nkv, hd, n_rot, page, window
         vv[pos[t]] = x[t, (nh + nkv) * hd:]
         want = attention_reference(qq, kk, vv, pos[t], nh, nkv, hd, scale, window)
         assert np.abs(out_b[t].numpy() - want).max() < 4e-2 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(5, 2, 64), (3, 1, 128), (32, 8, 64)])
+@pytest.mark.parametrize("normed,rotated", [(False, True), (True, False), (False, False)])
+def test_qk_kernel_of_prompt_portions_without_norm_or_rotation(nh, nkv, hd, normed, rotated):
+    """The warp-per-token kernel (bfloat16, 256 tokens or more, heads of 64 / 128) with null norm weights (no per-head
+    norm on that side) and with no rotation: what is left is a copy of the values into q and the pages."""
+    o = ops()
+    rng = np.random.default_rng(nh + hd)
+    page, T, eps = 16, 300, 1e-5
+    n_pages = T // page + 2
+    positions = np.arange(T, dtype=np.int32)
+    items = np.zeros(T, dtype=np.int32)
+    table = np.arange(n_pages, dtype=np.int32)[None, :].copy()
+    qkv = torch.from_numpy(rng.standard_normal((T, (nh + 2 * nkv) * hd)).astype(np.float32)).bfloat16()
+    qw = torch.from_numpy(1 + 0.1 * rng.standard_normal(hd).astype(np.float32)) if normed else None
+    kw = torch.from_numpy(1 + 0.1 * rng.standard_normal(hd).astype(np.float32)) if normed else None
+    inv = (1e4 ** (-2.0 * np.arange(hd // 2) / hd)).astype(np.float32)
+    q_out = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(n_pages, page, nkv * hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    st = o.new_status(DEV)
+    o.qk_norm_rope_store(qkv.to(DEV), torch.from_numpy(positions).to(DEV), torch.from_numpy(items).to(DEV),
+                         None if qw is None else qw.to(DEV), None if kw is None else kw.to(DEV),
+                         torch.from_numpy(inv).to(DEV) if rotated else None, hd if rotated else 0, eps, q_out, kc, vc,
+                         torch.from_numpy(table).to(DEV), page, n_pages, nh, nkv, hd, st)
+    o.read_status(st)
+    x = qkv.double().numpy()
+
+    def ref(rows, w, pos):
+        if w is not None:
+            rows = rows / np.sqrt((rows * rows).mean(-1, keepdims=True) + eps) * w.double().numpy()
+        if rotated:
+            ang = (np.float64(pos) * inv.astype(np.float64))
+            half = hd // 2
+            out = rows.copy()
+            out[:, :half] = rows[:, :half] * np.cos(ang) - rows[:, half:] * np.sin(ang)
+            out[:, half:] = rows[:, :half] * np.sin(ang) + rows[:, half:] * np.cos(ang)
+            rows = out
+        return rows.reshape(-1)
+    for t in (0, 1, 15, 16, 255, 299):
+        qr = ref(x[t, :nh * hd].reshape(nh, hd), qw, t)
+        kr = ref(x[t, nh * hd:(nh + nkv) * hd].reshape(nkv, hd), kw, t)
+        assert np.abs(q_out[t].float().cpu().numpy() - qr).max() <= 1e-2 * np.abs(qr).max()
+        assert np.abs(kc[t // page, t % page].float().cpu().numpy() - kr).max() <= 1e-2 * np.abs(kr).max()
+        assert np.abs(vc[t // page, t % page].float().cpu().numpy() - x[t, (nh + nkv) * hd:]).max() <= 1e-7
