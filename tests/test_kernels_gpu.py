@@ -151,7 +151,8 @@ def conv_reference(bcx, w, bias, state):
 @pytest.mark.parametrize("bias", [False, True])
 @pytest.mark.parametrize("H,lens", [(72, [1, 9, 2, 1, 5]),          # shorter than taps-1, equal, longer
                                     (72, [40, 1, 3, 57, 6]),        # enough tokens for the 16-byte kernel
-                                    (76, [33, 2, 70, 1, 1])])       # a width it does not take
+                                    (76, [33, 2, 70, 1, 1]),        # a width it does not take
+                                    (72, [131, 1, 2, 97, 66])])     # a few hundred tokens, portions of every length
 def test_gated_conv_ragged_batch(taps, dtype, bias, H, lens):
     o = ops()
     n_slots = 5
@@ -995,3 +996,4 @@ def test_qk_kernel_of_prompt_portions_without_norm_or_rotation(nh, nkv, hd, norm
         assert np.abs(q_out[t].float().cpu().numpy() - qr).max() <= 1e-2 * np.abs(qr).max()
         assert np.abs(kc[t // page, t % page].float().cpu().numpy() - kr).max() <= 1e-2 * np.abs(kr).max()
         assert np.abs(vc[t // page, t % page].float().cpu().numpy() - x[t, (nh + nkv) * hd:]).max() <= 1e-7
+
