@@ -164,38 +164,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- keys and values, page by page ----
-            pdl_wait();                                      // this step's keys were written by the kernel before
-            const int pages_per_step = KEYS / a.page_size;
-            const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
-            for (int i = 0; i < n_steps; ++i) {
-                const int s = i % STAGES;
+        // ---- keys and values, page by page: lane 0 waits for the stage and sets the byte count, lane p then looks up
+        // page p of the step in the block table and issues that page's copies (one thread walking the pages pays a
+        // dependent table read per page) ----
+        pdl_wait();                                          // this step's keys were written by the kernel before
+        const int pages_per_step = KEYS / a.page_size;
+        const int first_blk = lo_min / a.page_size, last_blk = pos_last / a.page_size;
+        for (int i = 0; i < n_steps; ++i) {
+            const int s = i % STAGES;
+            int ok = 1;
+            if (lane == 0) {
                 if (i >= STAGES && !mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1)) {
                     report(a.status, IMPARO_ST_WAIT_LIMIT, 20, i, s);
-                    break;
+                    ok = 0;
+                } else {
+                    mbar_expect_tx(&kv_full[s], STAGE_BYTES);
                 }
-                uint8_t* kdst = kv_s + s * STAGE_BYTES;
-                uint8_t* vdst = kdst + K_BYTES;
-                mbar_expect_tx(&kv_full[s], STAGE_BYTES);
-                const int blk0 = (kb_first + i) * pages_per_step;
-                for (int pg = 0; pg < pages_per_step; ++pg) {
-                    // blocks before every row's window or past the request's last position hold nothing
-                    // this tile may use (a window's old pages may be gone): a mapped page stands in
-                    // for them (their keys are masked, their values finite)
-                    const int blk = min(max(blk0 + pg, first_blk), last_blk);
-                    int page = blk < a.max_blocks ? tab[blk] : -1;
-                    if (page < 0 || page >= a.n_pages) {
-                        report(a.status, IMPARO_ST_PAGE_RANGE, 21, item, page);
-                        page = 0;
-                    }
-                    const int y = page * a.page_size;
-                    const uint32_t off = (uint32_t)pg * a.page_size * 128;
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);            // (also orders the byte count before the copies)
+            if (!ok) break;
+            uint8_t* kdst = kv_s + s * STAGE_BYTES;
+            uint8_t* vdst = kdst + K_BYTES;
+            const int blk0 = (kb_first + i) * pages_per_step;
+            for (int pg = lane; pg < pages_per_step; pg += 32) {
+                // blocks before every row's window or past the request's last position hold nothing
+                // this tile may use (a window's old pages may be gone): a mapped page stands in
+                // for them (their keys are masked, their values finite)
+                const int blk = min(max(blk0 + pg, first_blk), last_blk);
+                int page = blk < a.max_blocks ? tab[blk] : -1;
+                if (page < 0 || page >= a.n_pages) {
+                    report(a.status, IMPARO_ST_PAGE_RANGE, 21, item, page);
+                    page = 0;
+                }
+                const int y = page * a.page_size;
+                const uint32_t off = (uint32_t)pg * a.page_size * 128;
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        tma_load_2d(kdst + nb * REGION + off, &map_k, &kv_full[s], kvh * HD + nb * 64, y);
-                        tma_load_2d(vdst + nb * REGION + off, &map_v, &kv_full[s], kvh * HD + nb * 64, y);
-                    }
+                for (int nb = 0; nb < NB; ++nb) {
+                    tma_load_2d(kdst + nb * REGION + off, &map_k, &kv_full[s], kvh * HD + nb * 64, y);
+                    tma_load_2d(vdst + nb * REGION + off, &map_v, &kv_full[s], kvh * HD + nb * 64, y);
                 }
             }
         }

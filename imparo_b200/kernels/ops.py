@@ -824,7 +824,11 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     if kernel == "auto":
         kernel = _S.switches.attn_prefill
     if kernel in ("auto", "tcgen05", "tcgen05_one_tile"):
-        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], 0 if kernel == "tcgen05_one_tile" else 1, *args[-2:])
+        # two tiles per CTA pay once a request has a thousand keys or so to walk (measured: 4 x 512 tokens 41.8 us with
+        # one tile, 45.6 with two; 2,048 tokens 71 against 63.5): "auto" decides by the width of the block table, which is
+        # part of the step's shape
+        two_tiles = kernel == "tcgen05" or (kernel == "auto" and table.shape[1] * page_size >= 1024)
+        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], 1 if two_tiles else 0, *args[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
             return True
