@@ -516,10 +516,11 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // full rate, and when both tiles' passes coincide each takes twice as long while the units idle for the rest of
     // the step.  turn[x] completes when the OTHER tile has finished a pass and tile x may start its next one.
     uint64_t* turn = v_empty + PP_STAGES;                    // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
+    uint64_t* p_half = turn + 2;                             // [2]  every thread's first 32 probabilities of the step are written
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_half + 2);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(bars) + 64;        // [tile][buffer][half][row]: what the two threads of a row exchange
-    static_assert((4 * PP_STAGES + 11) * 8 + 8 <= 256, "barriers overlap the exchange buffer");
+    static_assert((4 * PP_STAGES + 13) * 8 + 8 <= 256, "barriers overlap the exchange buffer");
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -560,6 +561,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         mbar_init(q_ready, 512);
         mbar_init(&turn[0], 256); mbar_init(&turn[1], 256);
+        mbar_init(&p_half[0], 256); mbar_init(&p_half[1], 256);
         for (int x = 0; x < 2; ++x) { mbar_init(&s_ready[x], 1); mbar_init(&s_free[x], 256); mbar_init(&p_ready[x], 256); mbar_init(&o_done[x], 1); }
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -672,14 +674,22 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 umma_commit(&s_ready[x]);
                 umma_commit(&k_empty[j % PP_STAGES]);        // this tile has read the step's keys when the product has run
             };
-            auto issue_pv = [&](int j) {                     // O_x (+)= P_x V_j
+            // O_x (+)= P_x V_j in two halves: a softmax thread writes the probabilities of its first 32 keys, then of its
+            // second 32 (the two threads of a row own keys 0-63 and 64-127), so keys 0-31 and 64-95 are there first.  Their
+            // share of the product is issued then, under the softmax's second half, and the product is done sooner after
+            // the step's end.
+            auto issue_pv_half = [&](int j, const int h) {
                 const uint64_t vd = dv0 + (uint64_t)(((j % PP_STAGES) * STAGE_BYTES) >> 4);
-                umma(t_o, pd, vd, idesc_o, j > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 1; kk < KEYS / UMMA_K; ++kk)
-                    umma(t_o, pd + (uint64_t)(((kk >> 2) * REGION + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * (UMMA_K * 128)) >> 4), idesc_o, 1u);
-                umma_commit(&o_done[x]);
-                umma_commit(&v_empty[j % PP_STAGES]);
+                for (int u = 0; u < 4; ++u) {
+                    const int kk = (u >> 1) * 4 + 2 * h + (u & 1);           // 16 keys each: 0, 1, 4, 5 then 2, 3, 6, 7
+                    umma(t_o, pd + (uint64_t)(((kk >> 2) * REGION + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * (UMMA_K * 128)) >> 4), idesc_o,
+                         (kk > 0 || j > 0) ? 1u : 0u);
+                }
+                if (h == 1) {
+                    umma_commit(&o_done[x]);
+                    umma_commit(&v_empty[j % PP_STAGES]);
+                }
             };
             if (ok && n_x > 0 && need_keys(0)) issue_s(0); else ok = ok && n_x == 0;
             for (int j = 0; j < n_x && ok; ++j) {
@@ -688,9 +698,12 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     if (!ok) break;
                     issue_s(j + 1);
                 }
-                ok = wait_or_give_up(&p_ready[x], j & 1, 44, j) && need_values(j);
+                ok = wait_or_give_up(&p_half[x], j & 1, 51, j) && need_values(j);
                 if (!ok) break;
-                issue_pv(j);
+                issue_pv_half(j, 0);
+                ok = wait_or_give_up(&p_ready[x], j & 1, 44, j);
+                if (!ok) break;
+                issue_pv_half(j, 1);
             }
             // Tile B may have one step more than tile A (its positions lie behind A's); A's thread then gives that
             // step's keys and values free on its own behalf, having no product that reads them.
@@ -844,6 +857,10 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
             };
             exp_half(0);
+            // each thread's first 32 keys' probabilities are in shared memory (and the output is scaled): their share of P V may run
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&p_half[x]);
             // the other tile may begin its pass when this one is half way through its own: one tile's pass alone keeps
             // the exp2 units at about 70%, two whole passes at once take twice as long each
             if (nB > 0) mbar_arrive(&turn[x ^ 1]);
