@@ -122,7 +122,9 @@ class AttentionMixer(Part):
             part_acc = rt.workspace.get("attn_part_acc", (T * nh * n_splits * hd,), torch.float32, reserve=room * hd)
             part_ml = rt.workspace.get("attn_part_ml", (T * nh * n_splits * 2,), torch.float32, reserve=room * 2)
             in_product = n_splits <= 64 and ops.fuse_producers()          # the output product combines the partials while it makes its operand
-            if ops.attention_decode_from_qkv(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq,
+            # every key chunk's CTA makes the group's queries again: worth the q/k kernel it saves up to 16 chunks or so
+            # (batch 8: 0.846 against 0.851 ms per step at 2,560 positions, equal at 16 k, 1.44-1.52 against 1.34-1.36 at 32 k)
+            if n_splits <= 16 and ops.attention_decode_from_qkv(qkv, batch.positions, batch.item_of_token, self.q_norm, self.k_norm, inv_freq,
                                              n_rot, self.eps, kv.k, kv.v, table, kv.page_size, kv.n_pages, self.window,
                                              self.scale, None if in_product else out, part_acc, part_ml, chunk, n_splits,
                                              nh, self.nkv, hd, rt.status):
