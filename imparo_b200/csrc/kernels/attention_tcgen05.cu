@@ -871,7 +871,14 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(&p_ready[x]);
         }
-        if (x == 0 && nB > nA) mbar_arrive(&turn[1]);        // tile B's one step more has no pass of A's to wait for
+        if (x == 0 && nB > nA) {
+            // Tile B's one step more has no pass of A's to wait for: A gives it its turn.  But only once B has taken the
+            // turn before (B's arrival of step nA - 1, the one a step nA of A's would wait for): two arrivals of A's in a
+            // row could otherwise complete two phases before B has looked at the first, and a wait by parity cannot tell
+            // "two on" from "not yet".
+            if (!mbar_wait(&turn[0], (nA - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 50, nA, r); *gave_up = 1; }
+            mbar_arrive(&turn[1]);
+        }
         if (ok && n_x > 0) {
             if (!mbar_wait(&o_done[x], (n_x - 1) & 1)) { report(a.status, IMPARO_ST_WAIT_LIMIT, 48, n_x, r); *gave_up = 1; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
