@@ -57,6 +57,7 @@ class KernelSwitches:
     defer_adds: bool = True               # IMPARO_DEFER_ADDS: products into the stream leave partials to the next norm
     fuse_producers: bool = True           # IMPARO_FUSE_PRODUCERS: the attention combine inside the output product (decode rows)
     decode_from_qkv: bool = True          # IMPARO_DECODE_FROM_QKV: decode rows' q/k norm, rotation and cache write inside the attention kernel
+    attn_side_by_side: bool = True        # IMPARO_ATTN_SIDE_BY_SIDE: a step's prompt-portion attention and decode-row attention run at the same time
     attn_prefill: str = "auto"            # IMPARO_ATTN_PREFILL: "auto" | "mma" | "tcgen05" | "tcgen05_one_tile"
 
     ENV_PREFIX = "IMPARO_"

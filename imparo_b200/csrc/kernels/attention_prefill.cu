@@ -304,16 +304,17 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
                        const int* __restrict__ item_of_token, const int* __restrict__ table, int max_blocks,
                        int page_size, int n_pages, int window, float scale, float* __restrict__ part_acc,
-                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int fresh, int* status,
-                       QkvSource src) {
+                       float* __restrict__ part_ml, int nh, int nkv, int chunk, int n_splits, int fresh, int overlap_prev,
+                       int* status, QkvSource src) {
     constexpr int CH = HD / 8, KT = HD / 16, NT_O = HD / 8;
     constexpr int PER = HD / 32, PAIRS = PER / 2;                  // a head's values per lane; rotation pairs per lane
     extern __shared__ __align__(128) uint8_t pf_smem[];
     __shared__ __align__(16) __nv_bfloat16 q_made[FROM_QKV ? 8 * HD : 8];     // the group's queries, made here
     __shared__ float head_row[FROM_QKV ? 4 : 1][FROM_QKV ? HD : 1];         // a warp's head between norm and rotation
     // shared memory: two buffers of 64 keys and 64 values (32 KB at head size 64, so that four
-    // CTAs fit beside a resident product CTA); after the key loop the same bytes hold the warps'
-    // partial results for the fold
+    // CTAs fit beside a resident product CTA; with three buffers, two of them in flight, fewer CTAs
+    // fit an SM and every decode step measured slower); after the key loop the same bytes hold the
+    // warps' partial results for the fold
     constexpr int TILE_BYTES = KEYS * HD * 2;
     auto k_s = [&](int buf) { return pf_smem + buf * TILE_BYTES; };          // computed, not an indexed array:
     auto v_s = [&](int buf) { return pf_smem + (2 + buf) * TILE_BYTES; };    // that would live in local memory
@@ -391,12 +392,15 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             if (src.inv_freq && i < half) sincosf((float)pos * src.inv_freq[i], &sn[j], &cs[j]);
         }
     }
-    pdl_wait();
+    // overlap_prev: the kernel before this one works on other rows (the step's prompt portions) and let this one start
+    // only after its own wait: what this kernel reads is complete, and it runs beside that kernel instead of after it
+    if (overlap_prev) pdl_no_wait(); else pdl_wait();
     if (begin >= end) {
         if (tid < G) {
             part_ml[(part_base + (size_t)tid * n_splits) * 2] = -INFINITY;
             part_ml[(part_base + (size_t)tid * n_splits) * 2 + 1] = 0.f;
         }
+        if (overlap_prev && tid == 0) pdl_wait_at_end();
         return;
     }
 
@@ -613,6 +617,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         // the combine kernel works in natural-log units
         if (d == 0) { part_ml[pb * 2] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; part_ml[pb * 2 + 1] = L; }
     }
+    if (overlap_prev && tid == 0) pdl_wait_at_end();          // this kernel completes after the one it ran beside
 }
 
 }  // namespace pf
@@ -667,7 +672,7 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
                              const int* positions, const int* item_of_token,
                              const int* table, int max_blocks, int page_size, int n_pages,
                              int window, float scale, void* out, float* part_acc, float* part_ml,
-                             int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
+                             int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh, int overlap_prev,
                              int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
@@ -694,7 +699,7 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
     const pf::QkvSource& src = from_qkv ? *qkv_src : none;
 #define IMPARO_DECODE(HD_, F_) launch(pf::attn_decode_mma_kernel<HD_, F_>, grid, dim3(pf::THREADS), smem, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, \
-        max_blocks, page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, status, src)
+        max_blocks, page_size, n_pages, window, scale, part_acc, part_ml, nh, nkv, chunk, n_splits, fresh, overlap_prev, status, src)
     if (hd == 64) e = from_qkv ? IMPARO_DECODE(64, true) : IMPARO_DECODE(64, false);
     else e = from_qkv ? IMPARO_DECODE(128, true) : IMPARO_DECODE(128, false);
 #undef IMPARO_DECODE
@@ -708,9 +713,10 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, float* part_acc, float* part_ml,
                                            int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
-                                           int* status, cudaStream_t stream) {
+                                           int overlap_prev, int* status, cudaStream_t stream) {
     return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
-                             scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, status, stream);
+                             scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, overlap_prev ? 1 : 0,
+                             status, stream);
 }
 
 // The same for a step in which every request brings ONE token, straight from the qkv product's split partials
@@ -729,5 +735,5 @@ extern "C" int imparo_attention_decode_mma_qkv(const float* part, int parts, lon
                       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
     // fresh = 1: a request's only new row is the one this kernel writes; older rows are safe to request early
     return decode_mma_launch(nullptr, &src, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages,
-                             window, scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, 1, status, stream);
+                             window, scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, 1, 0, status, stream);
 }

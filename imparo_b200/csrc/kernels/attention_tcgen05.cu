@@ -85,6 +85,7 @@ struct Args {
     int* status;
     int n_items, max_blocks, page_size, n_pages, window, nh, nkv;
     float scale;
+    int late_trigger;        // the next kernel runs beside this one and must find all before this one complete (common.cuh)
 };
 
 template <int HD>
@@ -114,7 +115,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 4);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);     // a softmax thread's wait ran out
 
-    pdl_trigger();
+    if (a.late_trigger) { timeline_begin(); pdl_wait(); pdl_trigger_late(); } else pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nh / a.nkv;
     const int TQ = ROWS / G;                                 // tokens per tile
@@ -522,7 +523,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float* xch = reinterpret_cast<float*>(bars) + 64;        // [tile][buffer][half][row]: what the two threads of a row exchange
     static_assert((4 * PP_STAGES + 13) * 8 + 8 <= 256, "barriers overlap the exchange buffer");
 
-    pdl_trigger();
+    if (a.late_trigger) { timeline_begin(); pdl_wait(); pdl_trigger_late(); } else pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = a.nh / a.nkv;
     const int TQ = ROWS / G;                                 // tokens per tile; a CTA takes two tiles
@@ -931,14 +932,16 @@ static int launch_pp(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a
 using namespace imparo;
 
 // bfloat16, head size 64 or 128, at most 8 query heads per kv head, pages of 16, 32, 64 or 128
-// positions; else -8 (the caller uses another kernel).  two_tiles: at head size 64 the kernel that gives a CTA two
-// query tiles in turn (else, and at head size 128, one tile per CTA).  n_tok is the batch's token count, n_items
-// its requests.  The caches are [n_pages * page_size rows, nkv * hd] arenas.
+// positions; else -8 (the caller uses another kernel).  mode bit 0: at head size 64 the kernel that gives a CTA two
+// query tiles in turn (else, and at head size 128, one tile per CTA); bit 1: the kernel lets its dependents come only
+// after its own wait, for a next kernel that runs beside it (imparo_attention_decode_mma with overlap_prev).
+// n_tok is the batch's token count, n_items its requests.  The caches are [n_pages * page_size rows, nkv * hd] arenas.
 extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                            const int* item_row_start, const int* item_start_pos, int n_items,
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, int n_tok, int nh, int nkv, int hd,
-                                           int two_tiles, int* status, cudaStream_t stream) {
+                                           int mode, int* status, cudaStream_t stream) {
+    const int two_tiles = mode & 1;
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     const int G = nh / nkv;
@@ -960,6 +963,7 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.item_row_start = item_row_start; a.item_start_pos = item_start_pos; a.table = table; a.status = status;
     a.n_items = n_items; a.max_blocks = max_blocks; a.page_size = page_size; a.n_pages = n_pages; a.window = window;
     a.nh = nh; a.nkv = nkv; a.scale = scale;
+    a.late_trigger = (mode >> 1) & 1;
     if (hd == 64 && two_tiles) {
         // two tiles per CTA: half as many CTAs along y (an upper bound again)
         const long long pairs = (n_tok + 2 * TQ - 1) / (2 * TQ) + n_items;

@@ -109,6 +109,13 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // A kernel that wants the SMs to itself for a while triggers late: timeline_begin() where it
 // starts, pdl_trigger_late() where the dependents may come.
 __device__ __forceinline__ void pdl_trigger_late() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Two kernels of the chain that touch different rows may run side by side (the prompt portions' attention and the decode
+// rows' of one step).  The first then lets its dependents come only after its own wait (timeline_begin(), pdl_wait(),
+// pdl_trigger_late()), so that the second, which starts with pdl_no_wait(), finds everything before the first complete;
+// and the second ends with pdl_wait_at_end() in one thread of every CTA: it completes only after the first, and the
+// chain behind it stays ordered.
+__device__ __forceinline__ void pdl_no_wait() {}
+__device__ __forceinline__ void pdl_wait_at_end() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void timeline_begin() {}
 __device__ __forceinline__ void timeline_mark(int) {}
 #else
@@ -156,6 +163,8 @@ __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (timeline_thread()) timeline_stamp(1);
 }
+__device__ __forceinline__ void pdl_no_wait() { if (timeline_thread()) timeline_stamp(1); }
+__device__ __forceinline__ void pdl_wait_at_end() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // which = 0 or 1; call it from ONE thread of the launch's blocks; only block (0,0,0) records
 __device__ __forceinline__ void timeline_mark(int which) {
     if (g_timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) timeline_stamp(2 + which);

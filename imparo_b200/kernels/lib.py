@@ -88,7 +88,7 @@ def _declare_kernels(lib):
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_split_combine", [P, P, P, I, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma",
-             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, P, S])
+             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_decode_mma_qkv",
              [P, I, c_int64, P, P, P, I, c_float, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",

@@ -715,7 +715,7 @@ def split_plan(n_tok: int, nkv: int, upper_context: int, sms: Optional[int] = No
 
 def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
                           out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True,
-                          fresh: int = 0) -> bool:
+                          fresh: int = 0, overlap_prev: bool = False) -> bool:
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
     combine).  Returns False, having launched nothing, when the group size is above 8.
 
@@ -725,7 +725,11 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     fresh: the most tokens one request brings to this step, when the caller knows that cache rows
     below `position + 1 - fresh` were written before the stream's last copy or foreign kernel (the
     engine's steps start with such a copy).  The tensor-core kernel then requests its first key
-    tiles while the kernels before it still run.  0: nothing is assumed."""
+    tiles while the kernels before it still run.  0: nothing is assumed.
+
+    overlap_prev: the kernel launched just before this one was attention_prefill with dependents_after_wait and
+    returned 2, and it neither writes what this launch reads nor reads what it writes: the tensor-core kernel then
+    runs beside it instead of after it (and completes after it)."""
     if nh // nkv > 8:
         return False
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
@@ -747,7 +751,7 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
         rc = _lib.kernels().imparo_attention_decode_mma(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table),
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
-            T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), _ptr(status), _stream())
+            T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), int(bool(overlap_prev)), _ptr(status), _stream())
     else:
         rc = _lib.kernels().imparo_paged_attention_split(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
@@ -799,9 +803,12 @@ def attention_decode_from_qkv(qkv, positions, item_of_token, q_w, k_w, inv_freq,
 
 
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
-                      scale, out, nh, nkv, hd, status, kernel: str = "auto") -> bool:
+                      scale, out, nh, nkv, hd, status, kernel: str = "auto", dependents_after_wait: bool = False):
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
     query heads per kv head).  Returns False, having launched nothing, for other shapes.
+
+    dependents_after_wait: the caller's next kernel works on other rows and may run beside this one
+    (paged_attention_split with overlap_prev).  Where the kernel that ran honours it the result is 2 instead of True.
 
     kernel: "tcgen05" (TMA + tcgen05.mma with the scores in tensor memory; pages of 16, 32, 64 or
     128 positions; at head size 64 a CTA takes two query tiles in turn), "tcgen05_one_tile" (the same with one tile
@@ -828,10 +835,11 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
         # one tile, 45.6 with two; 2,048 tokens 71 against 63.5): "auto" decides by the width of the block table, which is
         # part of the step's shape
         two_tiles = kernel == "tcgen05" or (kernel == "auto" and table.shape[1] * page_size >= 1024)
-        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], 1 if two_tiles else 0, *args[-2:])
+        late = bool(dependents_after_wait)      # without programmatic launches the two kernels simply run in stream order
+        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], (1 if two_tiles else 0) | (2 if late else 0), *args[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
-            return True
+            return 2 if late else True
         if kernel != "auto":
             return False
     _check(_lib.kernels().imparo_attention_prefill(*args), "attention_prefill")

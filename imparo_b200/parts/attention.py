@@ -148,7 +148,7 @@ class AttentionMixer(Part):
             # over many CTAs.
             done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start[n1:], batch.item_start_pos[n1:],
                                          batch.n_items - n1, table[n1:], kv.page_size, kv.n_pages, self.window, self.scale,
-                                         out, nh, self.nkv, hd, rt.status)
+                                         out, nh, self.nkv, hd, rt.status, dependents_after_wait=ops.switches().attn_side_by_side)
             if done:
                 chunk, n_splits = ops.split_plan(n1, self.nkv, table.shape[1] * kv.page_size)
                 room = self._partials_room(table.shape[1] * kv.page_size)
@@ -156,7 +156,7 @@ class AttentionMixer(Part):
                 part_ml = rt.workspace.get("attn_part_ml", (n1 * nh * n_splits * 2,), torch.float32, reserve=room * 2)
                 ops.paged_attention_split(q[:n1], kv.k, kv.v, batch.positions[:n1], batch.item_of_token[:n1], table,
                                           kv.page_size, kv.n_pages, self.window, self.scale, out[:n1], part_acc, part_ml,
-                                          chunk, n_splits, nh, self.nkv, hd, rt.status, fresh=1)
+                                          chunk, n_splits, nh, self.nkv, hd, rt.status, fresh=1, overlap_prev=done == 2)
         elif batch.max_tokens_per_item >= 8:
             # prompt portions: the tensor-core kernel (bfloat16, head size 64 or 128), tiles of one request each
             done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start, batch.item_start_pos, batch.n_items, table,

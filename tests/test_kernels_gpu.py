@@ -638,6 +638,60 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window, kernel):
             t += 1
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (6, 2, 64), (4, 2, 128)])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_one_tile"])
+def test_portion_attention_and_decode_row_attention_side_by_side(nh, nkv, hd, kernel):
+    """A step's prompt portions go to the prompt kernel and its decode rows to the split-key kernel, which may run
+    beside it: the first lets its dependents come after its own wait, the second does not wait at its start and
+    completes after the first.  The pair, launched many times in a row behind a kernel that writes their queries, gives
+    what the two give when each waits for the one before."""
+    o = ops()
+    dtype, page, window = torch.bfloat16, 16, None
+    rng = np.random.default_rng(nh + hd)
+    singles = [700, 33, 1, 520]                                   # decode rows: a request's last position + 1
+    portions = [(300, 140), (0, 90)]                              # (start position, tokens)
+    lens = singles + [s + n for s, n in portions]
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, lens, page, nkv, hd, dtype)
+    n1, T = len(singles), len(singles) + sum(n for _, n in portions)
+    q_host = torch.from_numpy(rng.standard_normal((T, nh * hd)).astype(np.float32)).to(dtype)
+    positions = torch.tensor([L - 1 for L in singles], dtype=torch.int32, device=DEV)
+    items = torch.arange(n1, dtype=torch.int32, device=DEV)
+    row_start = torch.from_numpy(np.concatenate([[n1], n1 + np.cumsum([n for _, n in portions])]).astype(np.int32)).to(DEV)
+    start_pos = torch.tensor([s for s, _ in portions], dtype=torch.int32, device=DEV)
+    table_d, kc_d, vc_d = torch.from_numpy(table).to(DEV), kc.to(DEV), vc.to(DEV)
+    scale = 1 / math.sqrt(hd)
+    chunk, n_splits = 64, -(-table.shape[1] * page // 64)
+    part_acc = torch.empty(n1 * nh * n_splits * hd, device=DEV)
+    part_ml = torch.empty(n1 * nh * n_splits * 2, device=DEV)
+    status = o.new_status(DEV)
+    src = q_host.to(DEV)
+    q = torch.empty_like(src)
+
+    def pair(side_by_side, out):
+        q.copy_(src)                                              # the kernel before the pair writes what both read
+        took = o.attention_prefill(q, kc_d, vc_d, row_start, start_pos, len(portions), table_d[n1:], page, n_pages, window,
+                                   scale, out, nh, nkv, hd, status, kernel=kernel, dependents_after_wait=side_by_side)
+        assert took == (2 if side_by_side else True)
+        assert o.paged_attention_split(q[:n1], kc_d, vc_d, positions, items, table_d, page, n_pages, window, scale, out[:n1],
+                                       part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, fresh=1,
+                                       overlap_prev=side_by_side)
+
+    want = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    pair(False, want)
+    torch.cuda.synchronize()
+    for _ in range(20):
+        got = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        pair(True, got)
+        o.linear(got, torch.eye(nh * hd, dtype=dtype, device=DEV)[:8].contiguous(),
+                 torch.empty(T, 8, dtype=dtype, device=DEV))      # a kernel behind the pair that reads all its rows
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    o.read_status(status)
+    ref = attention_reference(q_host[0].double().numpy(), ks[0].double().numpy(), vs[0].double().numpy(), singles[0] - 1, nh, nkv,
+                              hd, scale, window)
+    assert np.abs(want[0].float().cpu().double().numpy() - ref).max() <= 1.5e-2 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05", "tcgen05_one_tile"])
 def test_attention_prefill_far_key_and_refusals(kernel):
     o = ops()
