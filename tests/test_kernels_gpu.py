@@ -638,6 +638,40 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, page, window, kernel):
             t += 1
 
 
+@pytest.mark.parametrize("nh,nkv", [(6, 2), (8, 2), (5, 1)])
+@pytest.mark.parametrize("start,n", [(3180, 488), (2017, 130), (1, 260)])
+def test_attention_prefill_portion_far_into_its_request(nh, nkv, start, n):
+    """A portion that starts thousands of keys in: the two query tiles of a CTA walk dozens of key steps in turn, and
+    where the second tile's last position lies in a further block of 128 keys than the first's it has a step more.
+    Launched repeatedly (the tiles' hand-over is a matter of timing), every launch must give the same rows, and those
+    the reference's."""
+    o = ops()
+    hd, page, dtype = 64, 16, torch.bfloat16
+    rng = np.random.default_rng(start + nh)
+    table, kc, vc, ks, vs, n_pages = make_paged(rng, [start + n], page, nkv, hd, dtype)
+    q = torch.from_numpy(rng.standard_normal((n, nh * hd)).astype(np.float32)).to(dtype)
+    status = o.new_status(DEV)
+    scale = 1 / math.sqrt(hd)
+    args = (q.to(DEV), kc.to(DEV), vc.to(DEV), torch.tensor([0, n], dtype=torch.int32, device=DEV),
+            torch.tensor([start], dtype=torch.int32, device=DEV), 1, torch.from_numpy(table).to(DEV), page, n_pages, None, scale)
+    first = None
+    for rep in range(30):
+        out = torch.full((n, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        assert o.attention_prefill(*args, out, nh, nkv, hd, status, kernel="tcgen05")
+        torch.cuda.synchronize()
+        o.read_status(status)
+        if first is None:
+            first = out
+        else:
+            assert torch.equal(out, first), rep
+    got = first.float().cpu().double().numpy()
+    kd, vd = ks[0].double().numpy(), vs[0].double().numpy()
+    for i in list(range(0, n, 37)) + [n - 1]:
+        ref = attention_reference(q[i].double().numpy(), kd, vd, start + i, nh, nkv, hd, scale, None)
+        err = np.abs(got[i] - ref).max()
+        assert err <= 1.5e-2 * max(1.0, np.abs(ref).max()), (i, err)
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (6, 2, 64), (4, 2, 128)])
 @pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_one_tile"])
 def test_portion_attention_and_decode_row_attention_side_by_side(nh, nkv, hd, kernel):
