@@ -522,7 +522,7 @@ def test_kernels_refuse_sizes_they_do_not_take():
                                           p(z(16 * 4096)), p(z(2 * 4096)), 1, 1, 1, 16, 32, 4096, p(st), stream) == -2
     qb, kvb = z(1, 64, dt=torch.bfloat16), z(2, 16, 64, dt=torch.bfloat16)
     assert k.imparo_attention_decode_mma(p(qb), p(kvb), p(kvb), p(zi(1)), p(zi(1)), p(tab), 4096, 16, 2, 0, 1.0,
-                                         p(z(1, 64, dt=torch.bfloat16)), p(z(64 * 4096)), p(z(2 * 4096)), 1, 1, 1, 64, 64, 4096, 0,
+                                         p(z(1, 64, dt=torch.bfloat16)), p(z(64 * 4096)), p(z(2 * 4096)), 1, 1, 1, 64, 64, 4096, 0, 0,
                                          p(st), stream) == -2
     torch.cuda.synchronize()
     o.read_status(st)
