@@ -67,8 +67,8 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
     return make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
                       *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
 }
-// shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers, then the exchange
-// buffer of the SwiGLU epilogue.  Tiles are 1024-byte aligned (128-byte swizzle).  With a producer
+// shared memory: [stages] x (A tile 16 KB | B tile NT*128 B), then barriers; the exchange buffer of the
+// SwiGLU epilogue lies over the ring's first stage.  Tiles are 1024-byte aligned (128-byte swizzle).  With a producer
 // (PROD != PROD_NONE) the ring carries W tiles only and the token operand of all the CTA's k-blocks
 // follows the ring.
 template <int PROD> struct ThreadsOf { static constexpr int value = (PROD == PROD_COMBINE) ? 320 : THREADS; };
@@ -89,7 +89,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ C
     uint64_t* b_ready = acc_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_ready + 1);
     int* flags = reinterpret_cast<int*>(tmem_slot + 1);            // [0]: this CTA folds the splits
-    float* exch = reinterpret_cast<float*>(aux + 256);             // SwiGLU: 2 x [128][17], a 16-token chunk each
+    // SwiGLU: 2 x [128][17], a 16-token chunk each.  The epilogue runs when every product has read its stage and
+    // no load is in flight, so the exchange buffer lies over the ring's first stage and costs no shared memory of
+    // its own: what it would have taken is a deeper ring, or room for the next kernel's CTA beside this one.
+    float* exch = reinterpret_cast<float*>(smem);
+    static_assert(EPI != SWIGLU_BF16 || STAGES * STAGE_BYTES >= 2 * 128 * 17 * 4, "the exchange buffer lies over the ring");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x;                 // which 128 rows of W (SwiGLU: which 64 features)
@@ -467,7 +471,7 @@ static thread_local bool g_configure_only = false;
 
 template <int NT, int STAGES, int EPI, int PROD = PROD_NONE>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Params& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (PROD != PROD_NONE ? 0 : NT * BK * 2)) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
+    constexpr size_t fixed = 1024 + (size_t)STAGES * (BM * BK * 2 + (PROD != PROD_NONE ? 0 : NT * BK * 2)) + 256;
     static_assert(fixed <= 227 * 1024, "stage ring exceeds shared memory");
     const size_t smem = fixed + (PROD != PROD_NONE ? (size_t)p.kb_cap * NT * BK * 2 : 0);
     if (smem > 227 * 1024) return -25;          // the resident input does not fit: the caller makes the tensor with its own kernel
@@ -503,7 +507,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMa
 // How many clusters of `cluster` CTAs of this kernel the device holds at once (0 on error).
 template <int NT, int STAGES, int EPI>
 static int max_clusters(int cluster) {
-    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256 + (EPI == SWIGLU_BF16 ? 2 * 128 * 17 * 4 : 0);
+    constexpr size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + NT * BK * 2) + 256;
     auto kern = gemm_kernel<NT, STAGES, EPI, PROD_NONE>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
@@ -522,13 +526,29 @@ static int max_clusters(int cluster) {
 // Ring depth.  Measured in the decode step (batch 8): 11 stages 1.050 ms, 5 stages 1.038 ms,
 // 3 stages 1.076 ms.  A ring of 5 leaves room for a second CTA per SM, and with programmatic
 // dependent launch that second CTA is the NEXT product's: it fills its ring with weights while
-// this one is still streaming, which is worth more than a deeper ring of one's own.
+// this one is still streaming, which is worth more than a deeper ring of one's own.  (Again later, at 0.77 ms
+// per step: 4 stages 0.788 ms, 5 stages 0.764, 6 stages 0.767.)
 constexpr int deep_stages_for(int nt) { return nt <= 32 ? 5 : nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
 constexpr int stages_for(int nt) { return nt <= 64 ? 4 : nt == 128 ? 5 : 4; }
+// The SwiGLU product (gate+up, the step's largest stream, K whole in every CTA) takes one stage more than would
+// fit with an exchange buffer of its own; the buffer lies over the ring instead.  Batch 8: 5 stages 0.769-0.773 ms per
+// step, 6 stages 0.763-0.765, 7 stages 0.781-0.784 (the next product's CTA no longer fits beside it).  Batch 64:
+// 4 stages 1.272-1.284 ms, 5 stages 1.236-1.242, 6 stages 1.233-1.236.
+constexpr int swiglu_stages_for(int nt) { return nt <= 64 ? 6 : nt == 128 ? 5 : 4; }
 
 template <int EPI>
 static int launch_nt(int nt, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Params& p, dim3 grid, cudaStream_t stream) {
     const bool deep = (long long)grid.x * grid.y * grid.z <= 148;
+    if (EPI == SWIGLU_BF16) {
+        switch (nt) {
+            case 16: return launch<16, swiglu_stages_for(16), EPI>(mw, mx, mo, p, grid, stream);
+            case 32: return launch<32, swiglu_stages_for(32), EPI>(mw, mx, mo, p, grid, stream);
+            case 64: return launch<64, swiglu_stages_for(64), EPI>(mw, mx, mo, p, grid, stream);
+            case 128: return launch<128, swiglu_stages_for(128), EPI>(mw, mx, mo, p, grid, stream);
+            case 256: return launch<256, swiglu_stages_for(256), EPI>(mw, mx, mo, p, grid, stream);
+        }
+        return -22;
+    }
     switch (nt) {
         case 16: return deep ? launch<16, deep_stages_for(16), EPI>(mw, mx, mo, p, grid, stream) : launch<16, stages_for(16), EPI>(mw, mx, mo, p, grid, stream);
         case 32: return deep ? launch<32, deep_stages_for(32), EPI>(mw, mx, mo, p, grid, stream) : launch<32, stages_for(32), EPI>(mw, mx, mo, p, grid, stream);
