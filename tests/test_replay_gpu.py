@@ -39,6 +39,79 @@ def test_family(name, dtype, family):
         assert traces.max_live_tokens(steps) < total
 
 
+SWITCHED = [{"decode_from_qkv": False}, {"fuse_producers": False}, {"unfolded": False}, {"defer_adds": False},
+            {"gemm": "library"}, {"prefill_gemm": "library"}, {"prefill_linear": True}, {"attn_prefill": "mma"},
+            {"attn_prefill": "tcgen05_one_tile"}, {"attn_side_by_side": False}, {"pad_rows": False}, {"capture_first": False},
+            {"use_graphs": False}]
+
+
+@pytest.mark.parametrize("name", ["B", "F"])
+@pytest.mark.parametrize("switched", SWITCHED, ids=lambda d: "-".join(f"{k}={v}" for k, v in d.items()))
+def test_every_switch_leaves_a_path_that_gives_the_same_logits(name, switched):
+    """The engine's switches choose between kernels and between ways of launching them; whichever way one is set,
+    a mixed trace in bfloat16 gives the plain implementation's logits."""
+    from imparo_b200.engine import Engine
+    reqs = make_requests(name, LENGTHS[name])
+    steps = traces.mixed(reqs, seed=5)
+    page = PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, 64)
+    top = {k: v for k, v in switched.items() if k in ("pad_rows", "capture_first", "use_graphs")}
+    eng = Engine(model_dir(name), dtype="bfloat16", ctx=max_tokens, parallel=4, page_size=page,
+                 num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens),
+                 switches={k: v for k, v in switched.items() if k not in top}, **top)
+    for k, v in switched.items():
+        assert getattr(eng.engine_config if k in top else eng.engine_config.switches, k) == v
+    check_trace(eng, steps, name, reqs, "bfloat16")
+
+
+_WIDE = {}
+
+
+def _wide_run(switched):
+    """Two layers at LFM2-1.2B width: a prompt of 1,100 tokens, a second request's portion of 270 beside the first's
+    decode row, then both decoding; every wanted row's logits."""
+    import torch
+    from imparo_b200.engine import Engine, StepItem
+    cfg = {"architectures": ["Lfm2ForCausalLM"], "vocab_size": 8192, "hidden_size": 2048, "num_hidden_layers": 2,
+           "layer_types": ["conv", "full_attention"], "num_attention_heads": 32, "num_key_value_heads": 8,
+           "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256, "conv_L_cache": 3,
+           "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_embedding": True}
+    top = {k: v for k, v in switched.items() if k in ("pad_rows", "capture_first", "use_graphs")}
+    eng = Engine(config=cfg, seed=11, dtype="bfloat16", ctx=2048, parallel=3, page_size=16, max_step_tokens=2048,
+                 random_init={"norm_jitter": 0.1, "matrix_std": 0.02},
+                 switches={k: v for k, v in switched.items() if k not in top}, **top)
+    rng = np.random.default_rng(23)
+    a, b = rng.integers(0, 8192, 1100 + 8).tolist(), rng.integers(0, 8192, 270 + 8).tolist()
+    eng.add_request(1)
+    eng.add_request(2)
+    rows = [eng.step([StepItem(1, a[:1100], [0, 500, 1099])])]
+    rows.append(eng.step([StepItem(1, [a[1100]], [0]), StepItem(2, b[:270], [0, 269])]))
+    for i in range(1, 8):
+        rows.append(eng.step([StepItem(1, [a[1100 + i]], [0]), StepItem(2, [b[269 + i]], [0])]))
+    eng.check_device_status()
+    eng.end_request(1); eng.end_request(2)
+    eng.cache.check()
+    out = np.concatenate([r.cpu().numpy() for r in rows])
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
+@pytest.mark.parametrize("switched", SWITCHED, ids=lambda d: "-".join(f"{k}={v}" for k, v in d.items()))
+def test_every_switch_at_full_width(switched):
+    """The same at the width the tensor-core kernels are made for (the tiny models take few of these paths): each
+    switch's other setting against the defaults, in bfloat16."""
+    if "default" not in _WIDE:
+        _WIDE["default"] = _wide_run({})
+    ref = _WIDE["default"]
+    got = _wide_run(switched)
+    assert np.isfinite(ref).all() and np.isfinite(got).all()
+    scale = float(np.abs(ref).max())
+    assert scale > 0.1 and np.abs(ref[0] - ref[-1]).max() > 0.2 * scale
+    err = float(np.abs(got - ref).max())
+    assert err <= 2.5e-2 * scale, (switched, err, scale)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cutting_does_not_change_logits_beyond_rounding(dtype):
     """The same positions through four ways of cutting: 32-bit results agree to ~1e-6."""
