@@ -123,6 +123,7 @@ class CacheManager:
                 off += slots * padded
             self.state_segments = torch.tensor(segs if segs else [(0, 0)], dtype=torch.int64, device=device)
             self.n_state_segments = len(segs)
+            self.state_max_per_slot = max((per for _, per in segs), default=0)     # sizes the clearing kernel's grid
 
     def __del__(self):
         try:

@@ -249,7 +249,7 @@ class StepFunction:
         if batch.fresh_slots is not None and getattr(cache, "n_state_segments", 0):
             # a fresh request's state starts at zero: one kernel over the flat state arena, first in the step's chain
             ops.zero_state_slots(cache.state_arena, cache.state_segments, cache.n_state_segments, batch.fresh_slots,
-                                 cache.arena_slots, self.rt.status)
+                                 cache.arena_slots, self.rt.status, max_per_slot=getattr(cache, "state_max_per_slot", None))
         x, picked = self.model.forward(batch, self._views, wanted=(batch.want_rows, batch.n_want))
         if not batch.n_want:
             return None

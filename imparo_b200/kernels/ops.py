@@ -863,14 +863,18 @@ def gated_conv(bcx, w, bias, state, item_row_start, item_of_token, item_slot, y,
 
 
 def zero_state_slots(arena: torch.Tensor, segments: torch.Tensor, n_segments: int, slots: torch.Tensor, n_slots_total: int,
-                     status: torch.Tensor) -> None:
+                     status: torch.Tensor, max_per_slot: Optional[int] = None) -> None:
     """Zero, in every state tensor of the arena, the slots named in `slots` (int32 on the device; entries below 0
-    are skipped).  segments: int64 [n_segments, 2] on the device: (offset in the arena, floats per slot)."""
+    are skipped).  segments: int64 [n_segments, 2] on the device: (offset in the arena, floats per slot).
+    max_per_slot: the largest of those sizes, which the host knows (it sizes the grid: 1,024 floats per block; without
+    it the launch takes the most blocks per tensor and slot, 64, and a step of 32 requests waits 20 us for 20,000
+    blocks of which a handful have work)."""
     _cuda(arena, segments, slots, status)
     _need(arena.dtype == torch.float32 and segments.dtype == torch.int64 and slots.dtype == torch.int32, "zero_state_slots: dtypes")
     if n_segments == 0 or slots.numel() == 0:
         return
-    _check(_lib.kernels().imparo_zero_state_slots(_ptr(arena), _ptr(segments), int(n_segments), int(arena.numel()), _ptr(slots),
+    _check(_lib.kernels().imparo_zero_state_slots(_ptr(arena), _ptr(segments), int(n_segments),
+                                                  int(arena.numel() if max_per_slot is None else max_per_slot), _ptr(slots),
                                                   slots.numel(), int(n_slots_total), _ptr(status), _stream()), "zero_state_slots")
 
 
