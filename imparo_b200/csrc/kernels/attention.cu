@@ -354,11 +354,15 @@ qk_norm_rope_token_warp_kernel(const __nv_bfloat16* __restrict__ qkv, const int*
                                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                                __nv_bfloat16* __restrict__ v_cache,
                                const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                               int n_tok, int nh, int nkv, int* status) {
+                               int n_tok, int nh, int nkv, int share, int* status) {
     constexpr int LPH = HD / 8, HPL = 32 / LPH, CHUNK = 8, NF = HD / 64;      // lanes per head, heads per load, loads in flight, frequencies per lane
     pdl_trigger();
     const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    // share: warps that divide a token's heads between them.  A portion of a few hundred tokens is fewer warps than the
+    // SMs have schedulers, each walking its token's heads in rounds of dependent loads: 6.5 us for 512 tokens of 40
+    // heads; shared out, every warp has one round.
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int t = w / share, mine = w - t * share;
     if (t >= n_tok) return;
     const int total = nh + 2 * nkv;
     const int sub = lane % LPH, hsel = lane / LPH;           // which 8 dims of the head, which head of the load
@@ -403,8 +407,10 @@ qk_norm_rope_token_warp_kernel(const __nv_bfloat16* __restrict__ qkv, const int*
         report(status, IMPARO_ST_PAGE_RANGE, 2, t, page);     // the token's keys and values are skipped below, its queries written
     const __nv_bfloat16* src = qkv + (size_t)t * total * HD + 8 * sub;
     const bool upper = sub >= LPH / 2;
-    const int n_loads = (total + HPL - 1) / HPL;
-    for (int g0 = 0; g0 < n_loads; g0 += CHUNK) {
+    const int all_loads = (total + HPL - 1) / HPL;
+    const int per_warp = (all_loads + share - 1) / share;
+    const int n_loads = min(all_loads, (mine + 1) * per_warp);
+    for (int g0 = mine * per_warp; g0 < n_loads; g0 += CHUNK) {
         uint4 in[CHUNK];
 #pragma unroll
         for (int u = 0; u < CHUNK; ++u) {
@@ -586,9 +592,15 @@ extern "C" int imparo_qk_norm_rope_store(const void* qkv, int dtype, const int* 
 #define IMPARO_QKV(V_) launch(qk_norm_rope_rows_vec_kernel<V_>, dim3(n_tok), dim3(256), 0, stream, (const __nv_bfloat16*)qkv, positions, \
             item_of_token, q_w, k_w, inv_freq, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, \
             max_blocks, page_size, n_pages, nh, nkv, status)
-#define IMPARO_QKW(HD_) launch(qk_norm_rope_token_warp_kernel<HD_>, dim3((n_tok + 3) / 4), dim3(128), 0, stream, (const __nv_bfloat16*)qkv, \
+        // warps per token: enough to give the device about 2,048 warps, at most 8 (and no more than the token has loads)
+        int share = n_tok >= 2048 ? 1 : n_tok >= 1024 ? 2 : n_tok >= 512 ? 4 : 8;
+        {
+            const int loads = (nh + 2 * nkv + (hd == 64 ? 4 : 2) - 1) / (hd == 64 ? 4 : 2);
+            while (share > 1 && share > loads) share >>= 1;
+        }
+#define IMPARO_QKW(HD_) launch(qk_norm_rope_token_warp_kernel<HD_>, dim3((unsigned)(((long long)n_tok * share + 3) / 4)), dim3(128), 0, stream, (const __nv_bfloat16*)qkv, \
             positions, item_of_token, q_w, k_w, inv_freq, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, \
-            max_blocks, page_size, n_pages, n_tok, nh, nkv, status)
+            max_blocks, page_size, n_pages, n_tok, nh, nkv, share, status)
         const bool w_ok = (((uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0;                  // the norm weights are read 16 bytes at a time
         if (hd == 64 && w_ok) IMPARO_QKW(64); else if (hd == 128 && w_ok) IMPARO_QKW(128);
         else if (hd == 64) IMPARO_QKV(2); else if (hd == 128) IMPARO_QKV(4); else IMPARO_QKV(8);

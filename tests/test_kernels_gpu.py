@@ -1041,13 +1041,15 @@ def test_decode_attention_from_the_qkv_partials(nh, nkv, hd, n_rot, page, window
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(5, 2, 64), (3, 1, 128), (32, 8, 64)])
-@pytest.mark.parametrize("normed,rotated", [(False, True), (True, False), (False, False)])
-def test_qk_kernel_of_prompt_portions_without_norm_or_rotation(nh, nkv, hd, normed, rotated):
+@pytest.mark.parametrize("normed,rotated,T", [(False, True, 300), (True, False, 300), (False, False, 300),
+                                              (True, True, 600), (True, True, 1100), (True, True, 2050)])
+def test_qk_kernel_of_prompt_portions_without_norm_or_rotation(nh, nkv, hd, normed, rotated, T):
     """The warp-per-token kernel (bfloat16, 256 tokens or more, heads of 64 / 128) with null norm weights (no per-head
-    norm on that side) and with no rotation: what is left is a copy of the values into q and the pages."""
+    norm on that side) and with no rotation: what is left is a copy of the values into q and the pages.  And with both,
+    at the token counts where a token's heads are shared among 8, 4 and 2 warps or belong to one."""
     o = ops()
     rng = np.random.default_rng(nh + hd)
-    page, T, eps = 16, 300, 1e-5
+    page, eps = 16, 1e-5
     n_pages = T // page + 2
     positions = np.arange(T, dtype=np.int32)
     items = np.zeros(T, dtype=np.int32)
@@ -1078,7 +1080,7 @@ def test_qk_kernel_of_prompt_portions_without_norm_or_rotation(nh, nkv, hd, norm
             out[:, half:] = rows[:, :half] * np.sin(ang) + rows[:, half:] * np.cos(ang)
             rows = out
         return rows.reshape(-1)
-    for t in (0, 1, 15, 16, 255, 299):
+    for t in (0, 1, 15, 16, 255, 299, T // 2 + 1, T - 1):
         qr = ref(x[t, :nh * hd].reshape(nh, hd), qw, t)
         kr = ref(x[t, nh * hd:(nh + nkv) * hd].reshape(nkv, hd), kw, t)
         assert np.abs(q_out[t].float().cpu().numpy() - qr).max() <= 1e-2 * np.abs(qr).max()
