@@ -756,6 +756,31 @@ def test_attention_prefill_far_key_and_refusals(kernel):
     assert not o.attention_prefill(zf, zf, zf, None, None, 1, None, 4, 1, None, 1.0, zf, 1, 1, 64, None)
 
 
+@pytest.mark.parametrize("sized", [True, False])
+def test_zero_state_slots_clears_the_named_slots_only(sized):
+    """State tensors of very different sizes in one arena (5, 3,072 and 70,000 floats per slot: less than a block's
+    share, a few blocks, more than the grid's 64 blocks cover in one pass), a padded list of fresh slots; with the
+    largest per-slot size given (the engine's call) and without."""
+    o = ops()
+    slots_total, pers = 6, [5, 3072, 70000]
+    segs, off = [], 0
+    for per in pers:
+        segs.append((off, per))
+        off += slots_total * ((per + 3) // 4 * 4)
+    arena = torch.ones(off, device=DEV)
+    fresh = torch.tensor([1, -1, 4, -1], dtype=torch.int32, device=DEV)
+    st = o.new_status(DEV)
+    o.zero_state_slots(arena, torch.tensor(segs, dtype=torch.int64, device=DEV), len(segs), fresh, slots_total, st,
+                       max_per_slot=max(pers) if sized else None)
+    torch.cuda.synchronize()
+    o.read_status(st)
+    host = arena.cpu().numpy()
+    for (start, per) in segs:
+        for slot in range(slots_total):
+            got = host[start + slot * per:start + (slot + 1) * per]
+            assert (got == (0.0 if slot in (1, 4) else 1.0)).all(), (per, slot)
+
+
 @pytest.mark.parametrize("n,n_prev", [(1, 1), (37, 8), (700, 64)])
 def test_take_sampled_tokens(n, n_prev):
     """token_ids[i] = prev[src[i]] where src[i] >= 0; other rows keep what the host wrote."""
